@@ -1,0 +1,79 @@
+// Instantiations and launcher of the exact dQ / dTheta / dW backward kernel, plus the small
+// helper kernels of the backward (partial reduction, D = rowsum(dO*O)).
+#include "bwd_exact.cuh"
+#include "launch_util.cuh"
+
+namespace fmta {
+
+// Sum per-slot partials in slot order: out[i] = sum_s part[s * n + i].
+__global__ void reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int n_slots, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float t = 0.f;
+  for (int s = 0; s < n_slots; ++s) t += part[(size_t)s * n + i];
+  out[i] = t;
+}
+
+// D[row] = sum_d dO[row,d] * O[row,d]; one warp per row.  O may be fp32 or bf16.
+template <bool O_BF16>
+__global__ void rowdot_kernel(const bf16* __restrict__ dO, const void* __restrict__ O, float* __restrict__ Dv, size_t rows, int d) {
+  const size_t row = (size_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float t = 0.f;
+  for (int c = lane * 2; c < d; c += 64) {
+    const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(dO + row * d + c);
+    float o0, o1;
+    if (O_BF16) {
+      const __nv_bfloat162 o = *reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const bf16*>(O) + row * d + c);
+      o0 = __low2float(o); o1 = __high2float(o);
+    } else {
+      const float2 o = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(O) + row * d + c);
+      o0 = o.x; o1 = o.y;
+    }
+    t = fmaf(__low2float(g), o0, t);
+    t = fmaf(__high2float(g), o1, t);
+  }
+  t = warp_sum(t);
+  if (lane == 0) Dv[row] = t;
+}
+
+template <int D, int CQ, int CK>
+static cudaError_t launch_bwd_dq_t(const TrainParams& p, cudaStream_t stream) {
+  const int nQB = (p.N + 63) / 64;
+  dim3 grid(nQB, p.H, p.B), block(256);
+  const bool mix = (p.Wmix != nullptr) && p.G > 1;
+  if (mix) {
+    if constexpr (CQ == 3) {
+      return cudaErrorInvalidValue;
+    } else {
+      using Cfg = BwdExactCfg<D, CQ, CK, true>;
+      return launch_kernel<TrainParams>(bwd_dq_kernel<D, CQ, CK, true>, grid, block, Cfg::kSmemBytes, stream, p.G, p);
+    }
+  }
+  using Cfg = BwdExactCfg<D, CQ, CK, false>;
+  return launch_kernel<TrainParams>(bwd_dq_kernel<D, CQ, CK, false>, grid, block, Cfg::kSmemBytes, stream, 1, p);
+}
+
+cudaError_t launch_bwd_dq(const TrainParams& p, cudaStream_t stream) {
+  const bool mix = (p.Wmix != nullptr) && p.G > 1;
+  int cq = p.cq, ck = p.ck;
+  const bool has_theta = p.theta != nullptr;
+  if (mix && cq == 3 && ck == 5) { cq = -1; }
+  FMTA_DISPATCH_D(p.d, FMTA_DISPATCH_CONV(cq, ck, has_theta, return launch_bwd_dq_t<D_, CQ_, CK_>(p, stream);););
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_reduce_partials(const float* part, float* out, int n_slots, int n, cudaStream_t stream) {
+  reduce_partials_kernel<<<(n + 127) / 128, 128, 0, stream>>>(part, out, n_slots, n);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rowdot(const void* dO, const void* O, int o_bf16, float* Dv, size_t rows, int d, cudaStream_t stream) {
+  const unsigned blocks = (unsigned)((rows + 7) / 8);
+  if (o_bf16) rowdot_kernel<true><<<blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(dO), O, Dv, rows, d);
+  else rowdot_kernel<false><<<blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(dO), O, Dv, rows, d);
+  return cudaGetLastError();
+}
+
+}  // namespace fmta

@@ -1,0 +1,179 @@
+// C-ABI entry points of libfmta_b200.so: argument validation, parameter blocks, launches.
+// Declarations and the reference interfaces they stand in for are in include/fmta_b200.h.
+#include <cuda_runtime.h>
+
+#include "../../include/fmta_b200.h"
+#include "fmta_params.h"
+#include "launch_util.cuh"
+
+using namespace fmta;
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_cuda(cudaError_t e) {
+  if (e == cudaSuccess) return FMTA_OK;
+  g_last_cuda_error = (int)e;
+  (void)cudaGetLastError();  // clear the sticky launch-configuration error, if any
+  return FMTA_ERR_CUDA;
+}
+
+int check_train_dims(int B, int H, int N, int d, int cq, int ck, int G, bool has_theta, bool has_w) {
+  if (B < 1 || H < 1 || N < 1 || B > 65535 || H > 65535) return FMTA_ERR_SHAPE;
+  if (d != 32 && d != 64 && d != 128) return FMTA_ERR_UNSUPPORTED;
+  if (has_theta) {
+    if (cq < 1 || ck < 1) return FMTA_ERR_SHAPE;
+    if (cq > 16 || ck > 17 || (ck % 2) == 0) return FMTA_ERR_UNSUPPORTED;
+  }
+  if (has_w) {
+    if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return FMTA_ERR_UNSUPPORTED;
+    if (H % G != 0) return FMTA_ERR_SHAPE;
+  }
+  return FMTA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fmta_version(void) { return 100; }
+
+const char* fmta_strerror(int status) {
+  switch (status) {
+    case FMTA_OK: return "ok";
+    case FMTA_ERR_NULL: return "a required pointer is NULL";
+    case FMTA_ERR_SHAPE: return "a dimension is out of range or inconsistent";
+    case FMTA_ERR_UNSUPPORTED: return "unsupported head dim, filter shape (c_q<=16, odd c_k<=17) or group size";
+    case FMTA_ERR_ALIGN: return "a tensor pointer is not 16-byte aligned";
+    case FMTA_ERR_WORKSPACE: return "workspace missing or too small (see fmta_workspace_bytes)";
+    case FMTA_ERR_CUDA: return "the CUDA runtime rejected a launch (see fmta_last_cuda_error)";
+    default: return "unknown status";
+  }
+}
+
+int fmta_last_cuda_error(void) { return g_last_cuda_error; }
+
+size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, int G) {
+  (void)d;
+  if (op == FMTA_OP_BWD_DQ) {
+    const size_t slots = (size_t)B * ((N + 63) / 64);
+    size_t n = slots * H * (size_t)(cq * ck);
+    if (G > 1) n += slots * (size_t)(H / G) * G * G;
+    return n * sizeof(float);
+  }
+  if (op == FMTA_OP_FWD_TC) {
+    // un-normalised partial O (fp32) + partial M, L + the stacked key operand (c_q bf16 copies of K)
+    const size_t rows = (size_t)B * H * N;
+    return rows * d * 4 + rows * 8 + rows * (size_t)cq * d * 2 + 4096;
+  }
+  return 0;
+}
+
+int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, const float* wmix,
+             void* O, float* M, float* L, float* LSE, int B, int H, int N, int d, int cq, int ck,
+             int G, float scale, int causal, int o_dtype, int path, void* workspace,
+             size_t workspace_bytes, void* stream) {
+  (void)path; (void)workspace; (void)workspace_bytes;
+  if (!Q || !K || !V || !O) return FMTA_ERR_NULL;
+  if (int s = check_train_dims(B, H, N, d, cq, ck, G, theta != nullptr, wmix != nullptr)) return s;
+  if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return FMTA_ERR_ALIGN;
+  if (o_dtype != FMTA_DTYPE_F32 && o_dtype != FMTA_DTYPE_BF16) return FMTA_ERR_UNSUPPORTED;
+  TrainParams p = {};
+  p.Q = (const __nv_bfloat16*)Q; p.K = (const __nv_bfloat16*)K; p.V = (const __nv_bfloat16*)V;
+  p.theta = theta; p.Wmix = (wmix && G > 1) ? wmix : nullptr;
+  p.O = O; p.M = M; p.L = L; p.LSEout = LSE;
+  p.B = B; p.H = H; p.N = N; p.d = d;
+  p.cq = theta ? cq : 1; p.ck = theta ? ck : 1; p.G = (wmix && G > 1) ? G : 1;
+  p.scale = scale; p.causal = causal; p.o_bf16 = (o_dtype == FMTA_DTYPE_BF16);
+  p.kmode = kAllTiles;
+  // a 1x1 mixing "group" is a per-head scalar; fold it away by treating it as no mix only
+  // when W is absent -- with G == 1 and W given the scalar still applies:
+  if (wmix && G == 1) return FMTA_ERR_UNSUPPORTED;
+  return check_cuda(launch_fwd_exact(p, (cudaStream_t)stream));
+}
+
+int fmta_bwd_prep_D(const void* dO, const void* O, int o_dtype, float* D, size_t rows, int d,
+                    void* stream) {
+  if (!dO || !O || !D) return FMTA_ERR_NULL;
+  if (rows == 0 || d < 2 || (d % 2) != 0) return FMTA_ERR_SHAPE;
+  if (o_dtype != FMTA_DTYPE_F32 && o_dtype != FMTA_DTYPE_BF16) return FMTA_ERR_UNSUPPORTED;
+  return check_cuda(launch_rowdot(dO, O, o_dtype == FMTA_DTYPE_BF16, D, rows, d, (cudaStream_t)stream));
+}
+
+static int fill_bwd(TrainParams& p, const void* Q, const void* K, const void* V, const void* dO,
+                    const float* D, const float* LSE, const float* theta, const float* wmix, int B,
+                    int H, int N, int d, int cq, int ck, int G, float scale, int causal) {
+  if (!Q || !K || !V || !dO || !D || !LSE) return FMTA_ERR_NULL;
+  if (int s = check_train_dims(B, H, N, d, cq, ck, G, theta != nullptr, wmix != nullptr)) return s;
+  if (wmix && G == 1) return FMTA_ERR_UNSUPPORTED;
+  if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(dO)) return FMTA_ERR_ALIGN;
+  p.Q = (const __nv_bfloat16*)Q; p.K = (const __nv_bfloat16*)K; p.V = (const __nv_bfloat16*)V;
+  p.dO = (const __nv_bfloat16*)dO; p.Dvec = D; p.LSE = LSE;
+  p.theta = theta; p.Wmix = wmix;
+  p.B = B; p.H = H; p.N = N; p.d = d;
+  p.cq = theta ? cq : 1; p.ck = theta ? ck : 1; p.G = wmix ? G : 1;
+  p.scale = scale; p.causal = causal; p.kmode = kAllTiles;
+  return FMTA_OK;
+}
+
+int fmta_bwd_dq_dw(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+                   const float* LSE, const float* theta, const float* wmix, float* dQ,
+                   float* dTheta, float* dW, int B, int H, int N, int d, int cq, int ck, int G,
+                   float scale, int causal, void* workspace, size_t workspace_bytes, void* stream) {
+  TrainParams p = {};
+  if (int s = fill_bwd(p, Q, K, V, dO, D, LSE, theta, wmix, B, H, N, d, cq, ck, G, scale, causal)) return s;
+  if (!dQ || !aligned16(dQ)) return dQ ? FMTA_ERR_ALIGN : FMTA_ERR_NULL;
+  if ((theta && !dTheta) || (wmix && !dW)) return FMTA_ERR_NULL;
+  const size_t need = fmta_workspace_bytes(FMTA_OP_BWD_DQ, B, H, N, d, p.cq, p.ck, p.G);
+  const bool want_part = (theta != nullptr) || (wmix != nullptr);
+  if (want_part && (!workspace || workspace_bytes < need)) return FMTA_ERR_WORKSPACE;
+  const int slots = B * ((N + 63) / 64);
+  const size_t n_theta = (size_t)H * p.cq * p.ck;
+  p.dQ = dQ;
+  p.n_slots = slots;
+  p.dTheta_part = theta ? reinterpret_cast<float*>(workspace) : nullptr;
+  p.dW_part = wmix ? reinterpret_cast<float*>(workspace) + (theta ? (size_t)slots * n_theta : 0) : nullptr;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (int s = check_cuda(launch_bwd_dq(p, st))) return s;
+  if (theta)
+    if (int s = check_cuda(launch_reduce_partials(p.dTheta_part, dTheta, slots, (int)n_theta, st))) return s;
+  if (wmix)
+    if (int s = check_cuda(launch_reduce_partials(p.dW_part, dW, slots, H * G, st))) return s;
+  return FMTA_OK;
+}
+
+int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+                  const float* LSE, const float* theta, const float* wmix, float* dK, float* dV,
+                  int B, int H, int N, int d, int cq, int ck, int G, float scale, int causal,
+                  void* stream) {
+  TrainParams p = {};
+  if (int s = fill_bwd(p, Q, K, V, dO, D, LSE, theta, wmix, B, H, N, d, cq, ck, G, scale, causal)) return s;
+  if (!dK || !dV) return FMTA_ERR_NULL;
+  if (!aligned16(dK) || !aligned16(dV)) return FMTA_ERR_ALIGN;
+  p.dK = dK; p.dV = dV;
+  return check_cuda(launch_bwd_dkdv(p, (cudaStream_t)stream));
+}
+
+int fmta_decode(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
+                float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
+                int ck, int k_splits, float scale, void* stream) {
+  if (!Q || !K || !V || !theta || !O_splits || !M_splits || !L_splits) return FMTA_ERR_NULL;
+  if (B < 1 || H < 1 || Nk < 1 || B > 65535 || H > 65535) return FMTA_ERR_SHAPE;
+  if (q_len < 1 || q_len > 16) return FMTA_ERR_SHAPE;          // flash_conv_attention_inference.py:66-67
+  if (k_splits < 1 || k_splits > Nk) return FMTA_ERR_SHAPE;     // fwd_inference_wrapper.cu:65-66
+  if (d != 32 && d != 64 && d != 128) return FMTA_ERR_UNSUPPORTED;
+  if (cq < 1 || ck < 1) return FMTA_ERR_SHAPE;
+  if (cq > 16 || ck > 17 || (ck % 2) == 0) return FMTA_ERR_UNSUPPORTED;
+  if (!aligned16(Q) || !aligned16(K) || !aligned16(V)) return FMTA_ERR_ALIGN;
+  DecodeParams p = {};
+  p.Q = (const __nv_bfloat16*)Q; p.K = (const __nv_bfloat16*)K; p.V = (const __nv_bfloat16*)V;
+  p.theta = theta; p.O_splits = O_splits; p.M_splits = M_splits; p.L_splits = L_splits;
+  p.B = B; p.H = H; p.q_len = q_len; p.Nk = Nk; p.d = d; p.cq = cq; p.ck = ck; p.k_splits = k_splits;
+  p.scale = scale;
+  return check_cuda(launch_decode(p, (cudaStream_t)stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,63 @@
+// Host-side launch helpers shared by the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "fmta_params.h"
+
+namespace fmta {
+
+// Launch `kern` with dynamic shared memory and, when cluster_y > 1, a thread-block cluster of
+// (1, cluster_y, 1) CTAs (the heads of one mixing group).  No TMA multicast is involved; the
+// cluster only provides distributed shared memory and cluster barriers.
+template <typename P>
+inline cudaError_t launch_kernel(void (*kern)(const P), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, int cluster_y, const P& params) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (cluster_y > 1) {
+    if (cluster_y > 8) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (e != cudaSuccess) return e;
+    }
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = cluster_y;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, params);
+}
+
+// Compile-time specialisations of the filter shape: (6,11) and (3,5) are unrolled, a NULL filter skips
+// the conv (template value (1,1)), anything else takes the run-time path (CQ = CK = 0).
+#define FMTA_DISPATCH_CONV(cq, ck, has_theta, ...)                           \
+  do {                                                                        \
+    if (!(has_theta)) { constexpr int CQ_ = 1, CK_ = 1; __VA_ARGS__ }                               \
+    else if ((cq) == 6 && (ck) == 11) { constexpr int CQ_ = 6, CK_ = 11; __VA_ARGS__ }          \
+    else if ((cq) == 3 && (ck) == 5) { constexpr int CQ_ = 3, CK_ = 5; __VA_ARGS__ }            \
+    else { constexpr int CQ_ = 0, CK_ = 0; __VA_ARGS__ }                                        \
+  } while (0)
+
+#define FMTA_DISPATCH_D(d, ...)                                   \
+  do {                                                            \
+    if ((d) == 32) { constexpr int D_ = 32; __VA_ARGS__ }          \
+    else if ((d) == 64) { constexpr int D_ = 64; __VA_ARGS__ }     \
+    else if ((d) == 128) { constexpr int D_ = 128; __VA_ARGS__ }   \
+    else return cudaErrorInvalidValue;                            \
+  } while (0)
+
+cudaError_t launch_fwd_exact(const TrainParams& p, cudaStream_t stream);
+cudaError_t launch_bwd_dq(const TrainParams& p, cudaStream_t stream);
+cudaError_t launch_bwd_dkdv(const TrainParams& p, cudaStream_t stream);
+cudaError_t launch_reduce_partials(const float* part, float* out, int n_slots, int n, cudaStream_t stream);
+cudaError_t launch_rowdot(const void* dO, const void* O, int o_bf16, float* Dv, size_t rows, int d, cudaStream_t stream);
+cudaError_t launch_decode(const DecodeParams& p, cudaStream_t stream);
+
+}  // namespace fmta

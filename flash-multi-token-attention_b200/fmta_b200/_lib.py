@@ -1,0 +1,81 @@
+"""ctypes binding of libfmta_b200.so (the C ABI declared in include/fmta_b200.h).
+
+There is no CPU or PyTorch fallback: if the library is missing this module raises at
+import, and every op requires CUDA tensors.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfmta_b200.so")
+
+FMTA_DTYPE_F32 = 0
+FMTA_DTYPE_BF16 = 1
+FMTA_OP_BWD_DQ = 1
+FMTA_OP_FWD_TC = 2
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "fmta_b200: %s is missing. Build it with `python flash-multi-token-attention_b200/build.py` "
+        "(needs nvcc); there is no fallback path." % LIB_PATH)
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _fp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+
+lib.fmta_version.restype = _i
+lib.fmta_strerror.restype = ctypes.c_char_p
+lib.fmta_strerror.argtypes = [_i]
+lib.fmta_last_cuda_error.restype = _i
+lib.fmta_workspace_bytes.restype = _sz
+lib.fmta_workspace_bytes.argtypes = [_i] * 8
+lib.fmta_fwd.restype = _i
+lib.fmta_fwd.argtypes = [_vp, _vp, _vp, _fp, _fp, _vp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
+                         _vp, _sz, _vp]
+lib.fmta_bwd_prep_D.restype = _i
+lib.fmta_bwd_prep_D.argtypes = [_vp, _vp, _i, _fp, _sz, _i, _vp]
+lib.fmta_bwd_dq_dw.restype = _i
+lib.fmta_bwd_dq_dw.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i,
+                               _f, _i, _vp, _sz, _vp]
+lib.fmta_bwd_dkdv.restype = _i
+lib.fmta_bwd_dkdv.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _f, _i,
+                              _vp]
+lib.fmta_decode.restype = _i
+lib.fmta_decode.argtypes = [_vp, _vp, _vp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
+
+EXPORTS = ["fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
+           "fmta_bwd_prep_D", "fmta_bwd_dq_dw", "fmta_bwd_dkdv", "fmta_decode"]
+
+
+def check(status, what):
+    """Raise RuntimeError (what TORCH_CHECK raises in the reference wrappers) on a non-zero status."""
+    if status != 0:
+        msg = lib.fmta_strerror(status).decode()
+        extra = ""
+        if status == -6:
+            extra = " (cudaError %d)" % lib.fmta_last_cuda_error()
+        raise RuntimeError("%s: %s%s" % (what, msg, extra))
+
+
+def ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_ptr():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def require_cuda_bf16(t, name):
+    """CHECK_INPUT + dtype check of the reference wrappers (fwd_wrapper.cu:25-33)."""
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    if t.dtype != torch.bfloat16:
+        raise RuntimeError("%s must be bfloat16" % name)
+
+
+def as_f32(t):
+    return t if (t.dtype == torch.float32 and t.is_contiguous()) else t.to(torch.float32).contiguous()

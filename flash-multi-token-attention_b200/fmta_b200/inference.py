@@ -1,0 +1,46 @@
+"""Decode API, mirroring ``conv_attn/flash_conv_attention_inference.py``:
+``forward_inference`` (the pybind function of fwd_inference_bindings.cpp:20-23) and
+``fwd_conv_attn_inference`` (the Python wrapper at :33-93)."""
+import torch
+
+from ._lib import lib, check, ptr, stream_ptr, require_cuda_bf16, as_f32
+
+
+def forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal, num_k_blocks=None):
+    """(O_splits [B,H,k_splits,d], M_splits, L_splits [B,H,k_splits]) fp32 with the merged,
+    normalised result in split 0 (fwd_inference.cu:359-368).  ``causal`` is accepted and has no
+    effect, exactly as in the reference kernel (fwd_inference.cu:36 is never read);
+    ``num_k_blocks`` is accepted for signature compatibility and ignored."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
+        require_cuda_bf16(t, n)
+    B, H, q_len, d = Q.shape
+    if q_len > 16 or q_len < 1:
+        raise RuntimeError("Q sequence length must be between 1 and 16 for inference")
+    if K.shape[0] != B or K.shape[1] != H or K.shape[3] != d or V.shape != K.shape:
+        raise RuntimeError("K/V must be [batch, heads, seq_len, d_head] matching Q")
+    Nk = K.shape[2]
+    cq, ck = int(conv_kernel.shape[1]), int(conv_kernel.shape[2])
+    if pad_q != cq - 1 or pad_k != (ck - 1) // 2:
+        raise RuntimeError("pad_q/pad_k must be (kx-1, (ky-1)//2)")
+    if k_splits <= 0:
+        raise RuntimeError("k_splits must be positive")
+    if k_splits > Nk:
+        raise RuntimeError("k_splits cannot be larger than seq_len_k")
+    theta = as_f32(conv_kernel)
+    O = torch.empty((B, H, k_splits, d), dtype=torch.float32, device=Q.device)
+    M = torch.empty((B, H, k_splits), dtype=torch.float32, device=Q.device)
+    L = torch.empty_like(M)
+    st = lib.fmta_decode(ptr(Q), ptr(K), ptr(V), ptr(theta), ptr(O), ptr(M), ptr(L), B, H, q_len, Nk, d, cq, ck,
+                         int(k_splits), float(scale), stream_ptr())
+    check(st, "fmta_decode")
+    return O, M, L
+
+
+def fwd_conv_attn_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal):
+    """(O [B,H,1,d], M [B,H,1], L [B,H,1]) for the last query row
+    (flash_conv_attention_inference.py:33-93).  The reference front-pads Q to 16 rows with
+    zeros; zero rows contribute nothing, so Q is passed as is."""
+    if Q.shape[2] > 16:
+        raise ValueError(f"Q sequence length must be <= 16 for inference, got {Q.shape[2]}")
+    O, M, L = forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal)
+    return O[:, :, 0:1, :], M[:, :, 0:1], L[:, :, 0:1]

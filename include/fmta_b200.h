@@ -1,0 +1,126 @@
+/*
+ * fmta_b200 - C ABI of the B200-native fused multi-token (conv) attention hot path.
+ *
+ * One shared library (libfmta_b200.so), plain pointers and sizes, no torch types.  Each entry
+ * point is what a binding of the reference package would call in place of one of its pybind11
+ * functions; the reference interface it replaces is cited beside it (paths are relative to the
+ * reference checkout).
+ *
+ * Conventions
+ *   - every tensor pointer is DEVICE memory, contiguous, row-major in the stated shape;
+ *     Q/K/V/dO are bf16 (the reference contract, fwd_wrapper.cu:30-33), theta / W / LSE / D
+ *     are fp32 (the reference rounds them to bf16, conv_attention_cuda.py:77,115,144; this
+ *     library does not);
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing
+ *     synchronises the device (the reference launches on the legacy default stream and
+ *     device-synchronises in decode, fwd_inference.cu:425);
+ *   - return value 0 = enqueued; negative = rejected on the host, nothing was launched
+ *     (see fmta_strerror).  Launch errors reported by the CUDA runtime map to FMTA_ERR_CUDA;
+ *   - the callee allocates nothing unless stated; workspaces are caller-owned and sized by
+ *     fmta_workspace_bytes;
+ *   - supported head dims: 32, 64, 128.  Filter shapes: any c_q in [1,16], odd c_k in [1,17]
+ *     (c_k must be odd: the reference's own PyTorch path fails for even c_k);
+ *   - head mixing: G consecutive heads form a group mixed by a G x G matrix
+ *     (W layout [H/G, G, G], row = output head); G in {1,2,4,8,16}, H % G == 0.
+ */
+#ifndef FMTA_B200_H_
+#define FMTA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FMTA_OK 0
+#define FMTA_ERR_NULL (-1)        /* a required pointer is NULL */
+#define FMTA_ERR_SHAPE (-2)       /* a dimension is out of range or inconsistent */
+#define FMTA_ERR_UNSUPPORTED (-3) /* head dim / filter shape / group size not supported */
+#define FMTA_ERR_ALIGN (-4)       /* a pointer is not 16-byte aligned */
+#define FMTA_ERR_WORKSPACE (-5)   /* workspace missing or too small */
+#define FMTA_ERR_CUDA (-6)        /* the CUDA runtime rejected a launch (see fmta_last_cuda_error) */
+
+#define FMTA_DTYPE_F32 0
+#define FMTA_DTYPE_BF16 1
+
+#define FMTA_OP_BWD_DQ 1 /* for fmta_workspace_bytes */
+#define FMTA_OP_FWD_TC 2
+
+/* Library version (major*10000 + minor*100 + patch). */
+int fmta_version(void);
+
+/* Text for a status code returned by any entry point. */
+const char* fmta_strerror(int status);
+
+/* cudaError_t value of the last launch failure seen by this thread (0 if none). */
+int fmta_last_cuda_error(void);
+
+/*
+ * Forward.  Replaces `forward(Q,K,V,conv_kernel,scale,pad_q,pad_k,causal) -> (O,M,L)`
+ * (conv_attn/bindings.cpp:46-48, kernels/fwd_wrapper.cu:15-100) and, with `wmix`,
+ * `head_conv_attention_forward(q,k,v,w,scale,causal) -> (o,l,m)` (head_conv_attn/fwd_kernel.py:282).
+ *   Q,K,V  bf16 [B,H,N,d]      theta fp32 [H,cq,ck] or NULL (no key-query conv)
+ *   wmix   fp32 [H/G,G,G] or NULL     O [B,H,N,d] fp32 or bf16 (o_dtype)
+ *   M,L    fp32 [B,H,N] row max / row sum of exp(C-M), either may be NULL
+ *   LSE    fp32 [B,H,N] = M + log L, may be NULL
+ * path: 0 = exact tile kernel everywhere; 1 = stacked-GEMM tensor-core kernel off the causal
+ * band plus exact tiles on it (needs workspace, see FMTA_OP_FWD_TC); -1 = library default.
+ */
+int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, const float* wmix,
+             void* O, float* M, float* L, float* LSE, int B, int H, int N, int d, int cq, int ck,
+             int G, float scale, int causal, int o_dtype, int path, void* workspace,
+             size_t workspace_bytes, void* stream);
+
+/*
+ * D[b,h,i] = sum_d dO[b,h,i,:] * O[b,h,i,:], kept in fp32.  Replaces the torch expression at
+ * conv_attention_cuda.py:144 (which rounds D to bf16).  rows = B*H*N.
+ */
+int fmta_bwd_prep_D(const void* dO, const void* O, int o_dtype, float* D, size_t rows, int d,
+                    void* stream);
+
+/*
+ * dQ and the filter / mixing gradients.  Replaces `dq_backward(Q,K,V,dO,D,L,conv_kernel,...) ->
+ * (dQ, dconv_kernel)` (conv_attn/bindings.cpp:50-52, kernels/dq_bwd_wrapper.cu:11-93; its `L`
+ * argument is LSE) and `head_conv_attention_bwd_dq_dw` (head_conv_attn/bwd_dq_dw.py:373).
+ *   dQ fp32 [B,H,N,d]   dTheta fp32 [H,cq,ck] (NULL when theta is NULL)
+ *   dW fp32 [H/G,G,G] (NULL when wmix is NULL)
+ * dTheta and dW are summed over the batch in a fixed order (per-CTA partials in `workspace`,
+ * then one reduction), so repeated calls give bit-identical results.
+ */
+int fmta_bwd_dq_dw(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+                   const float* LSE, const float* theta, const float* wmix, float* dQ,
+                   float* dTheta, float* dW, int B, int H, int N, int d, int cq, int ck, int G,
+                   float scale, int causal, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * dK and dV.  Replaces `dkdv_backward(...) -> (dK, dV)` (conv_attn/bindings.cpp:54-56,
+ * kernels/dkdv_wrapper.cu:12-89) and `head_conv_attention_bwd_dkdv` (head_conv_attn/bwd_dk_dv.py:407).
+ */
+int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+                  const float* LSE, const float* theta, const float* wmix, float* dK, float* dV,
+                  int B, int H, int N, int d, int cq, int ck, int G, float scale, int causal,
+                  void* stream);
+
+/*
+ * Decode: last query row over a KV cache with split-K.  Replaces
+ * `forward_inference(Q,K,V,conv_kernel,k_splits,scale,pad_q,pad_k,causal,num_k_blocks) ->
+ * (O_splits,M_splits,L_splits)` (conv_attn/fwd_inference_bindings.cpp:20-23,
+ * kernels/fwd_inference_wrapper.cu:13-120).  As there, scores are rectangular (q_len recent
+ * query rows x Nk keys), no causal mask is applied, and the merged, normalised result is left in
+ * split 0; the other splits hold un-normalised partials.
+ *   Q bf16 [B,H,q_len,d] (1 <= q_len <= 16; no padding to 16 rows is needed)
+ *   K,V bf16 [B,H,Nk,d]   theta fp32 [H,cq,ck]
+ *   O_splits fp32 [B,H,k_splits,d]   M_splits, L_splits fp32 [B,H,k_splits]
+ */
+int fmta_decode(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
+                float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
+                int ck, int k_splits, float scale, void* stream);
+
+/* Bytes of caller-owned workspace an op needs for the given problem (0 if none). */
+size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, int G);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FMTA_B200_H_ */

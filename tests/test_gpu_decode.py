@@ -1,0 +1,75 @@
+"""GPU parity of the decode kernel (C ABI) against the reference-generated fixtures and the
+streaming oracle."""
+import math
+
+import pytest
+import torch
+
+from helpers import TOL_BF16, load_golden, maxabs
+from oracle import conv_attn_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(Q, K, V, theta, scale, k_splits):
+    import fmta_b200 as F
+    cq, ck = theta.shape[1:]
+    Qb, Kb, Vb = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V))
+    O, M, L = F.fwd_conv_attn_inference(Qb, Kb, Vb, theta.cuda(), k_splits, scale, cq - 1, (ck - 1) // 2, False)
+    torch.cuda.synchronize()
+    return O, M, L
+
+
+@pytest.mark.parametrize("name,k_splits", [("decode_ref_script_5x5", 4), ("decode_ref_script_5x5", 1),
+                                           ("decode_6x11_qlen6", 3), ("decode_6x11_qlen6", 1),
+                                           ("decode_3x3_qlen2", 2), ("decode_3x3_qlen2", 7)])
+def test_golden(name, k_splits):
+    z = load_golden(name)
+    O, M, L = _run(z["Q"], z["K"], z["V"], z["theta"], float(z["scale"]), k_splits)
+    assert O.shape == z["O"].shape and M.shape == z["M"].shape
+    assert maxabs(O, z["O"]) <= TOL_BF16
+    assert maxabs(M, z["M"]) <= TOL_BF16
+    assert maxabs(M + torch.log(L), z["M"] + torch.log(z["L"])) <= TOL_BF16
+
+
+@pytest.mark.parametrize("B,H,q_len,Nk,d,cq,ck,k_splits", [
+    (2, 2, 6, 1000, 128, 6, 11, 4),
+    (1, 3, 16, 513, 64, 6, 11, 5),     # 16 query rows but only 6 taps see them
+    (1, 2, 12, 777, 64, 11, 11, 2),    # more than 8 live rows -> 16-row fragments
+    (1, 1, 1, 65, 32, 3, 3, 1),        # a single query row
+    (2, 1, 6, 17, 128, 6, 11, 1),      # cache shorter than a warp's step
+    (1, 2, 6, 4096, 128, 6, 11, 16),
+])
+def test_oracle_shapes(B, H, q_len, Nk, d, cq, ck, k_splits):
+    Q, K, V, _, theta = orc.make_inputs(B, H, 0, d, cq, ck, seed=Nk, dtype=torch.bfloat16, Nk=Nk, q_len=q_len)
+    scale = 1.0 / math.sqrt(d)
+    Or, Mr, Lr = orc.decode_last_row_streaming(Q, K, V, theta, scale, chunk=512)
+    O, M, L = _run(Q, K, V, theta, scale, k_splits)
+    assert maxabs(O, Or) <= TOL_BF16
+    assert maxabs(M, Mr) <= TOL_BF16
+    assert maxabs(M + torch.log(L), Mr + torch.log(Lr)) <= TOL_BF16
+
+
+def test_split_invariance_and_split0_convention():
+    import fmta_b200 as F
+    Q, K, V, _, theta = orc.make_inputs(1, 2, 0, 64, 6, 11, seed=1, dtype=torch.bfloat16, Nk=2000, q_len=6)
+    outs = [_run(Q, K, V, theta, 0.125, s) for s in (1, 2, 8, 31)]
+    for O, M, L in outs[1:]:
+        assert maxabs(O, outs[0][0]) <= 1e-4
+        assert maxabs(M, outs[0][1]) <= 1e-5
+    Qb, Kb, Vb = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V))
+    Os, Ms, Ls = F.forward_inference(Qb, Kb, Vb, theta.cuda(), 8, 0.125, 5, 5, False, 0)
+    assert Os.shape == (1, 2, 8, 64) and Ms.shape == (1, 2, 8)
+
+
+def test_rejects_bad_inputs():
+    import fmta_b200 as F
+    Q = torch.zeros(1, 1, 17, 64, device="cuda", dtype=torch.bfloat16)
+    K = torch.zeros(1, 1, 64, 64, device="cuda", dtype=torch.bfloat16)
+    th = torch.zeros(1, 3, 3, device="cuda")
+    with pytest.raises(ValueError):
+        F.fwd_conv_attn_inference(Q, K, K, th, 1, 1.0, 2, 1, False)       # q_len > 16
+    with pytest.raises(RuntimeError):
+        F.fwd_conv_attn_inference(Q[:, :, :4], K, K, th, 65, 1.0, 2, 1, False)   # k_splits > Nk
+    with pytest.raises(RuntimeError):
+        F.fwd_conv_attn_inference(Q[:, :, :4], K, K, th, 0, 1.0, 2, 1, False)
