@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the conv-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-decode]
+
+One "step" = conv-attention forward + backward (D prep, dQ/dTheta, dK/dV, partial reduction,
+and for N > 1 the all-reduce of dTheta) on the bf16 training configuration
+B=4, H=16, N=4096, d=64, theta (6,11), causal -- PER GPU (weak scaling: every rank holds its own
+batch of 4; the only collective is the 4 KB dTheta all-reduce over NCCL).  `value` is the
+whole-job FlashAttention-convention throughput 14*d*E / t (E = causal score elements); the
+conv's own FLOPs are reported separately and never added to the numerator.
+
+Also reported in the same JSON line: `e2e` (same step with host->device copies of Q,K,V,dO from
+pinned memory and the device->host read of dTheta inside the timed region), `roofline` for the
+dominant kernel, `cpu_baseline` (the CPU oracle -- a port of the reference's PyTorch path -- on
+the host cores, bounded sample), `decode` (fwd_inference over a 32768-long KV cache, HBM GB/s),
+clocks sampled during the timed region.
+
+`--impl reference` times the reference's CPU path (the oracle port, all host threads) on a
+bounded sample of the same workload and prints the same kind of line with "impl": "reference".
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "flash-multi-token-attention_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+CFG = dict(B=4, H=16, N=4096, d=64, cq=6, ck=11)                 # training configuration (per GPU)
+DEC = dict(B=32, H=32, d=128, Nk=32768, q_len=6, cq=6, ck=11, k_splits=2)   # decode configuration
+METRIC = "conv-attn fwd+bwd TFLOP/s"
+
+
+def flops_attn(B, H, N, d):
+    E = B * H * N * (N + 1) / 2
+    return 14.0 * d * E, E
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            j = json.load(f)
+        return dict(tflops=j.get("bf16_tflops"), tflops_sustained=j.get("bf16_tflops_sustained"),
+                    hbm=j.get("hbm_gbs"), source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return None
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_reference_sample(steps=1, warmup=0):
+    """The reference's CPU path (oracle port: dense scores, conv2d, softmax, autograd backward) on
+    ONE (batch, head) slice of the training configuration, all host threads."""
+    from oracle import conv_attn_oracle as orc
+    N, d, cq, ck = CFG["N"], CFG["d"], CFG["cq"], CFG["ck"]
+    Q, K, V, dO, th = orc.make_inputs(1, 1, N, d, cq, ck, seed=0, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    ts = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.conv_attn_bwd_autograd(Q, K, V, th, dO, scale, True)   # forward + backward
+        if i >= warmup:
+            ts.append(time.perf_counter() - t0)
+    t = sum(ts) / len(ts)
+    fl, _ = flops_attn(1, 1, N, d)
+    return dict(value=fl / t / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
+                sample="1 of %d (batch, head) slices of the workload, fwd+bwd, fp32, %d run(s), %.2f s each; "
+                       "slices are independent so the full job is %dx this" % (CFG["B"] * CFG["H"], len(ts), t,
+                                                                              CFG["B"] * CFG["H"]),
+                host_cpus=os.cpu_count(), seconds_per_slice=t)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    steps = max(1, min(args.steps, 5))
+    cb = cpu_reference_sample(steps=steps, warmup=1 if args.warmup > 0 else 0)
+    line = dict(metric=METRIC, value=cb["value"], unit="TFLOP/s", n_gpus=args.gpus, steps=steps,
+                warmup=1 if args.warmup > 0 else 0, ms_per_step=cb["seconds_per_slice"] * 1e3,
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                impl="reference",
+                config=dict(workload="train fwd+bwd B=4,H=16,N=4096,d=64,theta(6,11),causal; "
+                                     "each step = one (b,h) slice of it on the host cores", **CFG),
+                cpu_baseline=cb,
+                e2e=dict(value=cb["value"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true", help="tiny shapes (profiling / debugging)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch.distributed as dist
+    import fmta_b200 as F
+    from fmta_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(CFG)
+    dec = dict(DEC)
+    if args.small:
+        cfg.update(B=1, H=4, N=2048)
+        dec.update(B=2, H=8, Nk=8192)
+    B, H, N, d, cq, ck = (cfg[k] for k in ("B", "H", "N", "d", "cq", "ck"))
+    scale = 1.0 / math.sqrt(d)
+    pq, pk = cq - 1, (ck - 1) // 2
+
+    g = torch.Generator().manual_seed(1234 + rank)
+    host = [torch.randn(B, H, N, d, generator=g).to(torch.bfloat16).pin_memory() for _ in range(4)]
+    th = torch.randn(H, cq, ck, generator=torch.Generator().manual_seed(7)) * 0.02
+    th[:, cq - 1, ck // 2] += 1.0
+    th = th.to(dev)
+    q, k, v, do = (t.to(dev) for t in host)
+    dth_host = torch.empty(H, cq, ck, dtype=torch.float32).pin_memory()
+    stream = torch.cuda.current_stream()
+    kern_ev = []   # (start, end) events around the dominant kernel, per step
+
+    def step(q, k, v, do, record=False):
+        O, M, L, LSE = F.forward(q, k, v, th, scale, pq, pk, True, return_lse=True)
+        D = F.rowdot(do, O)
+        if record:
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+        dQ, dTh = F.dq_backward(q, k, v, do, D, LSE, th, scale, pq, pk, True)
+        if record:
+            e1.record(stream)
+            kern_ev.append((e0, e1))
+        dK, dV = F.dkdv_backward(q, k, v, do, D, LSE, th, scale, pq, pk, True)
+        if world > 1:
+            dist.all_reduce(dTh)
+        return O, dQ, dK, dV, dTh
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # ---- device-resident throughput ----
+    for _ in range(args.warmup):
+        step(q, k, v, do)
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms = timed(lambda: step(q, k, v, do, record=True), args.steps)
+    clocks = sampler.stop() if sampler else None
+    ms_step = ms / args.steps
+    fl, E = flops_attn(B, H, N, d)
+    value = world * fl / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: host buffers in, dTheta out ----
+    def e2e_step():
+        dq_, dk_, dv_, ddo_ = (t.to(dev, non_blocking=True) for t in host)
+        out = step(dq_, dk_, dv_, ddo_)
+        dth_host.copy_(out[4], non_blocking=True)
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    e2e = dict(value=world * fl / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", h2d_bytes_per_step=h2d,
+               d2h_bytes_per_step=dth_host.numel() * 4, ms_per_step=ms_e2e)
+
+    # ---- roofline of the dominant kernel (dQ/dTheta backward: S, dP, dQ contractions = 6*d*E) ----
+    peaks = measured_peaks()
+    kms = statistics.mean(a.elapsed_time(b) for a, b in kern_ev) if kern_ev else None
+    roof = None
+    if kms:
+        ach = 6.0 * d * E / (kms * 1e-3) / 1e12
+        roof = dict(bound="tensor", kernel="bwd_dq_kernel", achieved=ach, peak=peaks["tflops_sustained"],
+                    unit="TFLOP/s", frac=ach / peaks["tflops_sustained"], peak_source=peaks["source"] + " (sustained)",
+                    traffic=None, ms_per_launch=kms,
+                    note="conv + filter-gradient + adjoint-conv of this kernel run on the FP32 pipe "
+                         "(%.1f GFLOP per launch, not counted in `achieved`)" % (3 * 2 * cq * ck * E / 1e9))
+
+    line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                data="synthetic",
+                config=dict(workload="train fwd+bwd bf16 B=%d(per GPU),H=%d,N=%d,d=%d,theta(%d,%d),causal" % (B, H, N, d, cq, ck),
+                            global_batch=B * world, parallelism="batch x head sharding, dTheta all-reduce" if world > 1 else "single GPU",
+                            l2="inputs+outputs per step (%.0f MB) exceed the 126 MB L2" % ((4 * 2 + 4 * 4) * B * H * N * d / 1e6),
+                            flops_attn_gflop=fl / 1e9, flops_conv_gflop=8 * cq * ck * E / 1e9),
+                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=5 * args.steps)
+
+    # ---- decode (HBM-bound), rank-local, reported beside the headline ----
+    if not args.no_decode:
+        try:
+            line["decode"] = bench_decode(F, dev, dec, peaks, world, timed)
+        except torch.OutOfMemoryError as e:   # pragma: no cover
+            line["decode"] = dict(error="out of memory: %s" % str(e)[:80])
+
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_reference_sample(steps=3, warmup=1)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bench_decode(F, dev, dec, peaks, world, timed):
+    B, H, d, Nk, ql, cq, ck, ks = (dec[k] for k in ("B", "H", "d", "Nk", "q_len", "cq", "ck", "k_splits"))
+    g = torch.Generator(device=dev).manual_seed(5)
+    K = torch.randn(B, H, Nk, d, device=dev, dtype=torch.bfloat16, generator=g)
+    V = torch.randn(B, H, Nk, d, device=dev, dtype=torch.bfloat16, generator=g)
+    Q = torch.randn(B, H, ql, d, device=dev, dtype=torch.bfloat16, generator=g)
+    th = torch.randn(H, cq, ck, device=dev, generator=g) * 0.02
+    th[:, cq - 1, ck // 2] += 1.0
+    sc = 1.0 / math.sqrt(d)
+    fn = lambda: F.forward_inference(Q, K, V, th, ks, sc, cq - 1, (ck - 1) // 2, False, 0)
+    for _ in range(3):
+        fn()
+    steps = 10
+    ms = timed(fn, steps) / steps
+    by = 2 * B * H * Nk * d * 2 + B * H * ql * d * 2 + B * H * d * 4
+    gbs = by / (ms * 1e-3) / 1e9
+    return dict(metric="decode HBM GB/s", value=world * gbs, unit="GB/s", ms_per_step=ms,
+                config=dict(workload="fwd_inference bf16 B=%d(per GPU),H=%d,d=%d,Nk=%d,q_len=%d,theta(%d,%d),k_splits=%d"
+                            % (B, H, d, Nk, ql, cq, ck, ks), l2="17 GB of K/V per step >> L2"),
+                roofline=dict(bound="hbm", kernel="decode_kernel", achieved=gbs, peak=peaks["hbm"], unit="GB/s",
+                              frac=gbs / peaks["hbm"], peak_source=peaks["source"], traffic=None),
+                gpu_launches=2 * steps)
+
+
+if __name__ == "__main__":
+    main()

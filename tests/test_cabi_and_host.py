@@ -1,0 +1,141 @@
+"""CPU-side checks: the C-ABI library loads and exports every symbol declared in
+include/fmta_b200.h, host-side validation rejects bad arguments without touching a GPU, and the
+batch x head sharding logic (including a world_size-2 gloo all-reduce of the filter gradient)."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import ROOT
+
+
+def _declared_symbols():
+    txt = open(os.path.join(ROOT, "include", "fmta_b200.h")).read()
+    return sorted(set(re.findall(r"\b(fmta_[a-z_A-Z0-9]+)\s*\(", txt)))
+
+
+def test_library_exports_every_declared_symbol():
+    import fmta_b200
+    from fmta_b200 import _lib
+    names = _declared_symbols()
+    assert len(names) >= 9
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), n
+    assert set(_lib.EXPORTS) <= set(names)
+    assert _lib.lib.fmta_version() >= 100
+
+
+def test_status_strings():
+    from fmta_b200._lib import lib
+    seen = {lib.fmta_strerror(s).decode() for s in range(0, -8, -1)}
+    assert len(seen) == 8 and "ok" in seen
+
+
+def test_host_validation_needs_no_gpu():
+    """Every rejection below happens before any CUDA call."""
+    from fmta_b200._lib import lib
+    P = ctypes.c_void_p
+    good = P(0x1000)
+    def fwd(Q=good, O=good, N=16, d=64, cq=3, ck=3, theta=good, G=1, w=None, H=2):
+        return lib.fmta_fwd(Q, good, good, theta, w, O, None, None, None, 1, H, N, d, cq, ck, G, 1.0, 1, 0, 0,
+                            None, 0, None)
+    assert fwd(Q=None) == -1
+    assert fwd(N=0) == -2
+    assert fwd(d=48) == -3
+    assert fwd(ck=4) == -3
+    assert fwd(cq=17) == -3
+    assert fwd(Q=P(0x1004)) == -4
+    assert fwd(G=3, w=good, H=6) == -3
+    assert fwd(G=4, w=good, H=6) == -2
+    dec = lambda q_len=6, ks=1, Nk=64: lib.fmta_decode(good, good, good, good, good, good, good, 1, 1, q_len, Nk,
+                                                        64, 3, 3, ks, 1.0, None)
+    assert dec(q_len=17) == -2 and dec(ks=0) == -2 and dec(ks=65) == -2
+    assert lib.fmta_bwd_dq_dw(good, good, good, good, good, good, good, None, good, good, None, 1, 2, 64, 64, 3, 3,
+                              1, 1.0, 1, None, 0, None) == -5     # workspace missing
+    assert lib.fmta_workspace_bytes(1, 4, 16, 4096, 64, 6, 11, 1) == 4 * 64 * 16 * 66 * 4
+
+
+def test_ops_refuse_cpu_tensors():
+    import fmta_b200 as F
+    Q = torch.zeros(1, 2, 16, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        F.forward(Q, Q, Q, torch.zeros(2, 3, 3), 1.0, 2, 1, True)
+    with pytest.raises(RuntimeError):
+        F.fwd_conv_attn_inference(Q, Q, Q, torch.zeros(2, 3, 3), 1, 1.0, 2, 1, False)
+
+
+def test_module_state_dict_names():
+    import fmta_b200 as F
+    m = F.ConvAttentionCUDA(4, 6, 11, init_random=False)
+    assert list(m.state_dict().keys()) == ["conv_weight"]
+    assert m.conv_weight.shape == (4, 6, 11) and float(m.conv_weight[0, 5, 5]) == 1.0
+    assert float(m.conv_weight.sum()) == 4.0
+    m2 = F.ConvAttentionCUDA(2, 3, 3, init_random=False, init_first=True)
+    assert float(m2.conv_weight[1, 0, 0]) == 1.0
+    h = F.HeadConvAttention(8)
+    assert list(h.state_dict().keys()) == ["head_conv_weights"] and h.head_conv_weights.dtype == torch.float16
+
+
+def test_unit_partition_covers_everything():
+    from fmta_b200 import sharding as sh
+    for n in (1, 7, 16, 64, 1024):
+        for ws in (1, 2, 4, 8):
+            rs = [sh.unit_range(n, ws, r) for r in range(ws)]
+            assert rs[0][0] == 0 and rs[-1][1] == n
+            assert all(rs[i][1] == rs[i + 1][0] for i in range(ws - 1))
+            assert max(b - a for a, b in rs) - min(b - a for a, b in rs) <= 1
+    # head-mix groups stay whole; plan kinds
+    assert sh.shard_plan(2, 32, 4, 8, 3)["mode"] == "head"
+    assert sh.shard_plan(2, 32, 4, 8, 3)["h_lo"] == 12
+    assert sh.shard_plan(8, 12, 4, 8, 0)["mode"] == "batch"
+    p = sh.shard_plan(3, 12, 4, 2, 1)
+    assert p["mode"] == "unit"
+    pieces = sh.unit_slices(sh.shard_plan(3, 12, 4, 2, 0)) + sh.unit_slices(p)
+    covered = sorted((b, h) for b, h0, h1 in pieces for h in range(h0, h1))
+    assert covered == [(b, h) for b in range(3) for h in range(12)]
+    assert all(h0 % 4 == 0 and h1 % 4 == 0 for _, h0, h1 in pieces)
+
+
+_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[2])
+from fmta_b200 import sharding as sh
+from oracle import conv_attn_oracle as orc
+dist.init_process_group("gloo", rank=int(os.environ["RANK"]), world_size=int(os.environ["WORLD_SIZE"]))
+rank, ws = dist.get_rank(), dist.get_world_size()
+B, H, N, d, cq, ck = 2, 4, 24, 16, 3, 5
+Q, K, V, dO, th = orc.make_inputs(B, H, N, d, cq, ck, seed=7)
+full = orc.conv_attn_bwd_autograd(Q, K, V, th, dO, None, True)
+for mode_B, mode_H in ((B, H), (B, 3)):       # head split, then (H=3 -> not divisible) batch split
+    Hh = mode_H
+    plan = sh.shard_plan(B, Hh, 1, ws, rank)
+    sl = lambda t: sh.local_slice(t[:, :Hh], plan)
+    th_l = th[plan["h_lo"]:plan["h_hi"]]
+    g = orc.conv_attn_bwd_autograd(sl(Q), sl(K), sl(V), th_l, sl(dO), None, True)
+    dth = sh.allreduce_param_grad(g[3], plan)
+    ref = orc.conv_attn_bwd_autograd(Q[:, :Hh], K[:, :Hh], V[:, :Hh], th[:Hh], dO[:, :Hh], None, True)
+    assert dth.shape == ref[3].shape, (dth.shape, ref[3].shape, plan)
+    assert float((dth - ref[3]).abs().max()) < 1e-4, plan
+    assert float((g[0] - ref[0][plan["b_lo"]:plan["b_hi"], plan["h_lo"]:plan["h_hi"]]).abs().max()) < 1e-5
+dist.destroy_process_group()
+print("OK", rank)
+'''
+
+
+def test_sharded_backward_matches_unsharded_gloo_world2(tmp_path):
+    """Two CPU ranks: each runs the (oracle) backward on its batch x head slice, the filter
+    gradient is all-reduced; the result must equal the unsharded one."""
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    pkg = os.path.join(ROOT, "flash-multi-token-attention_b200")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29533", WORLD_SIZE="2", OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, str(script), pkg, ROOT], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+    assert all("OK" in o for o in outs)
