@@ -50,6 +50,7 @@ const char* fmta_strerror(int status) {
     case FMTA_ERR_ALIGN: return "a tensor pointer is not 16-byte aligned";
     case FMTA_ERR_WORKSPACE: return "workspace missing or too small (see fmta_workspace_bytes)";
     case FMTA_ERR_CUDA: return "the CUDA runtime rejected a launch (see fmta_last_cuda_error)";
+    case FMTA_ERR_SCRATCH_LIMIT: return "problem too large for the built-in 4 MiB scratch of fmta_bwd_dq_dw_static; use fmta_bwd_dq_dw with a workspace";
     default: return "unknown status";
   }
 }

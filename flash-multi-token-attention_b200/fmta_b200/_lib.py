@@ -39,6 +39,9 @@ lib.fmta_bwd_prep_D.argtypes = [_vp, _vp, _i, _fp, _sz, _i, _vp]
 lib.fmta_bwd_dq_dw.restype = _i
 lib.fmta_bwd_dq_dw.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i,
                                _f, _i, _vp, _sz, _vp]
+lib.fmta_bwd_dq_dw_static.restype = _i
+lib.fmta_bwd_dq_dw_static.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i,
+                                      _i, _f, _i, _vp]
 lib.fmta_bwd_dkdv.restype = _i
 lib.fmta_bwd_dkdv.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _f, _i,
                               _vp]
@@ -46,7 +49,7 @@ lib.fmta_decode.restype = _i
 lib.fmta_decode.argtypes = [_vp, _vp, _vp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
 
 EXPORTS = ["fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
-           "fmta_bwd_prep_D", "fmta_bwd_dq_dw", "fmta_bwd_dkdv", "fmta_decode"]
+           "fmta_bwd_prep_D", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode"]
 
 
 def check(status, what):

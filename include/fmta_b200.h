@@ -40,6 +40,10 @@ extern "C" {
 #define FMTA_ERR_ALIGN (-4)       /* a pointer is not 16-byte aligned */
 #define FMTA_ERR_WORKSPACE (-5)   /* workspace missing or too small */
 #define FMTA_ERR_CUDA (-6)        /* the CUDA runtime rejected a launch (see fmta_last_cuda_error) */
+#define FMTA_ERR_SCRATCH_LIMIT (-7) /* problem needs more than FMTA_STATIC_SCRATCH_BYTES of built-in scratch */
+
+/* Size of the library's built-in scratch array used by fmta_bwd_dq_dw_static (4 MiB per GPU). */
+#define FMTA_STATIC_SCRATCH_BYTES ((size_t)4 << 20)
 
 #define FMTA_DTYPE_F32 0
 #define FMTA_DTYPE_BF16 1
@@ -116,6 +120,31 @@ int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, c
 int fmta_decode(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
                 float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
                 int ck, int k_splits, float scale, void* stream);
+
+/*
+ * Allocation-free variant of fmta_bwd_dq_dw (no counterpart in the reference, whose wrappers
+ * always allocate with torch).  Same arguments without the workspace: the per-CTA partial sums
+ * of dTheta / dW go to a 4 MiB array that lives inside the library's device image.  Meant for
+ * callers that cannot allocate device memory at the call site -- a serving loop whose memory
+ * pool is frozen, a host framework that owns the whole GPU, a foreign-language binding with no
+ * allocator to hand -- and so cannot provide the workspace of fmta_bwd_dq_dw.  The function
+ * itself calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - limit: fmta_workspace_bytes(FMTA_OP_BWD_DQ, ...) must not exceed
+ *     FMTA_STATIC_SCRATCH_BYTES, i.e. B * ceil(N/64) * (H*cq*ck + H*G) * 4 <= 4 MiB (the bf16
+ *     training shape B=4,H=16,N=4096,(6,11) needs 1.03 MiB); larger problems return
+ *     FMTA_ERR_SCRATCH_LIMIT and launch nothing;
+ *   - the first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress with that device current); make that first call outside any
+ *     stream capture;
+ *   - all calls on a device share the one array.  It keeps the previous call's contents, which
+ *     is harmless because every slot is rewritten before it is read, but two calls whose kernels
+ *     overlap on the GPU (different streams, or different host threads) race on it: serialise
+ *     them.  The array occupies 4 MiB on every GPU that loads the library, until the process ends.
+ */
+int fmta_bwd_dq_dw_static(const void* Q, const void* K, const void* V, const void* dO,
+                          const float* D, const float* LSE, const float* theta, const float* wmix,
+                          float* dQ, float* dTheta, float* dW, int B, int H, int N, int d, int cq,
+                          int ck, int G, float scale, int causal, void* stream);
 
 /* Bytes of caller-owned workspace an op needs for the given problem (0 if none). */
 size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, int G);
