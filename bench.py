@@ -172,7 +172,7 @@ def main():
     dec = dict(DEC)
     if args.small:
         cfg.update(B=1, H=4, N=2048)
-        dec.update(B=2, H=8, Nk=8192)
+        dec.update(B=4, H=32, Nk=16384)   # 0.5 GB of K/V: larger than L2, small enough to profile
     B, H, N, d, cq, ck = (cfg[k] for k in ("B", "H", "N", "d", "cq", "ck"))
     scale = 1.0 / math.sqrt(d)
     pq, pk = cq - 1, (ck - 1) // 2
