@@ -66,9 +66,8 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
     return n * sizeof(float);
   }
   if (op == FMTA_OP_FWD_TC) {
-    // un-normalised partial O (fp32) + partial M, L + the stacked key operand (c_q bf16 copies of K)
-    const size_t rows = (size_t)B * H * N;
-    return rows * d * 4 + rows * 8 + rows * (size_t)cq * d * 2 + 4096;
+    // the stacked key operand (c_q bf16 copies of K) + un-normalised partial O (fp32), M, L
+    return fwd_tc_workspace_bytes(B, H, N, d, cq);
   }
   return 0;
 }
@@ -77,7 +76,6 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
              void* O, float* M, float* L, float* LSE, int B, int H, int N, int d, int cq, int ck,
              int G, float scale, int causal, int o_dtype, int path, void* workspace,
              size_t workspace_bytes, void* stream) {
-  (void)path; (void)workspace; (void)workspace_bytes;
   if (!Q || !K || !V || !O) return FMTA_ERR_NULL;
   if (int s = check_train_dims(B, H, N, d, cq, ck, G, theta != nullptr, wmix != nullptr)) return s;
   if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return FMTA_ERR_ALIGN;
@@ -93,6 +91,22 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
   // a 1x1 mixing "group" is a per-head scalar; fold it away by treating it as no mix only
   // when W is absent -- with G == 1 and W given the scalar still applies:
   if (wmix && G == 1) return FMTA_ERR_UNSUPPORTED;
+  if (path != 0 && path != 1 && path != -1) return FMTA_ERR_SHAPE;
+  bool use_tc = (path != 0) && fwd_tc_supported(p);
+  if (path == 1 && !use_tc) return FMTA_ERR_UNSUPPORTED;
+  if (use_tc) {
+    const size_t need = fwd_tc_workspace_bytes(B, H, N, d, p.cq);
+    if (!workspace || workspace_bytes < need) {
+      if (path == 1) return FMTA_ERR_WORKSPACE;
+      use_tc = false;   // library default without a workspace: exact kernel everywhere
+    }
+  }
+  if (use_tc) {
+    // stacked tensor-core kernel off the causal band, then the exact kernel on the band tiles,
+    // continuing the online softmax from the un-normalised partial
+    if (int s = check_cuda(launch_fwd_tc(p, workspace, &p.Opart, &p.Mpart, &p.Lpart, (cudaStream_t)stream))) return s;
+    p.kmode = kBandTiles;
+  }
   return check_cuda(launch_fwd_exact(p, (cudaStream_t)stream));
 }
 

@@ -96,8 +96,11 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
   if (causal) {
     kb_end = min(nKB - 1, (i0 + BR - 1) / BC);
     if (p.kmode == kBandTiles) {
-      const int t = i0 - pq - pk - BC + 1;
-      kb_begin = (t < 0) ? 0 : (t / BC + 1);
+      // key blocks below this were done by the stacked tensor-core kernel, which works on
+      // 128-row query blocks and 64-key blocks that lie entirely off the causal band
+      const int i0t = (i0 / 128) * 128;
+      const int t = i0t - pq - pk + 1;
+      kb_begin = (t > 0) ? (t / 64) : 0;
     }
   } else if (p.kmode == kBandTiles) {
     kb_begin = nKB;  // no causal band: nothing to do here
