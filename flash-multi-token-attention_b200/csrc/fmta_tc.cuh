@@ -133,6 +133,20 @@ FMTA_DEVINL void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)accumulate)
       : "memory");
 }
+// Same with the descriptors given as (constant high word, low word): the low word holds the
+// start address, so stepping through an operand is a 32-bit add.  ACC selects accumulate (1) or
+// overwrite (0) at compile time.
+template <int ACC>
+FMTA_DEVINL void mma_ss2(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC)
+      : "memory");
+}
 // Arrive on an mbarrier once all MMAs issued so far by this thread have completed.
 FMTA_DEVINL void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

@@ -92,15 +92,15 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
   }
 
   // key-block range
+  const bool band_only = (p.kmode == kBandTiles);
   int kb_begin = 0, kb_end = nKB - 1;
   if (causal) {
     kb_end = min(nKB - 1, (i0 + BR - 1) / BC);
     if (p.kmode == kBandTiles) {
-      // key blocks below this were done by the stacked tensor-core kernel, which works on
-      // 128-row query blocks and 64-key blocks that lie entirely off the causal band
-      const int i0t = (i0 / 128) * 128;
-      const int t = i0t - pq - pk + 1;
-      kb_begin = (t > 0) ? (t / 64) : 0;
+      // entries with query - key >= pad_q + pad_k were done by the stacked tensor-core kernel;
+      // the band entries of this row block lie in key blocks >= (i0 - band + 1) / 64
+      const int t = i0 - (pq + pk) + 1;
+      kb_begin = (t > 0) ? (t / BC) : 0;
     }
   } else if (p.kmode == kBandTiles) {
     kb_begin = nKB;  // no causal band: nothing to do here
@@ -214,8 +214,8 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
       const int c = 2 * lane;
       float2 v = *reinterpret_cast<const float2*>(cbuf + r * C_LD + c);
       const int qi = i0 + r, kj = j0 + c;
-      if (kj >= N || (causal && kj > qi)) v.x = -INFINITY;
-      if (kj + 1 >= N || (causal && kj + 1 > qi)) v.y = -INFINITY;
+      if (kj >= N || (causal && kj > qi) || (band_only && qi - kj >= pq + pk)) v.x = -INFINITY;
+      if (kj + 1 >= N || (causal && kj + 1 > qi) || (band_only && qi - (kj + 1) >= pq + pk)) v.y = -INFINITY;
       const float mx = warp_max(fmaxf(v.x, v.y));
       const float m_old = sM[r];
       const float m_new = fmaxf(m_old, mx);

@@ -6,10 +6,12 @@
 // so those tiles are FlashAttention with c_q accumulating MMAs per score tile and no work on the
 // FP32 pipe.  This file holds
 //   ktilde_kernel : the memory-bound pre-pass that writes the c_q bf16 operands Kt_a;
-//   fwd_tc_kernel : the warp-specialised main kernel (1 TMA warp, 1 MMA warp, 4 softmax warps);
+//   fwd_tc_kernel : the warp-specialised main kernel (1 TMA warp, 1 MMA warp, 2 softmax warpgroups);
 //   launch_fwd_tc : tensor maps + launches.
-// The kernel leaves an UN-normalised partial (O, m, l) per query row; the exact tile kernel then
-// walks the remaining (band) key blocks starting from that state and writes the final O, M, L.
+// Ownership is per score entry: the stacked kernel takes every entry with query - key >= pad_q +
+// pad_k (masking the rest of a diagonal tile), the exact tile kernel takes the band entries.  The
+// kernel leaves an UN-normalised partial (O, m, l) per query row; the exact kernel continues the
+// online softmax from that state over the band and writes the final O, M, L.
 //
 // Row-shifted A operands without copies: Q is staged in the no-swizzle K-major core-matrix
 // layout [d/8][rows][8 elements]; the M-direction stride of that layout is 16 bytes, so the
@@ -40,7 +42,7 @@ __global__ void __launch_bounds__(256) ktilde_kernel(const bf16* __restrict__ K,
   constexpr int RPB = 256 / CPR;      // rows per block
   __shared__ float sTh[16 * 20];
   const int bh = blockIdx.y, h = bh % H;
-  for (int i = threadIdx.x; i < cq * ck; i += 256) sTh[(i / ck) * 20 + (i % ck)] = theta[(size_t)h * cq * ck + i] * scale;
+  for (int i = threadIdx.x; i < cq * ck; i += 256) sTh[(i / ck) * 20 + (i % ck)] = theta[(size_t)h * cq * ck + i] * scale;   // scale already carries log2(e)
   __syncthreads();
   const int j = blockIdx.x * RPB + threadIdx.x / CPR, c = threadIdx.x % CPR;
   if (j >= N) return;
@@ -84,78 +86,92 @@ __global__ void __launch_bounds__(256) ktilde_kernel(const bf16* __restrict__ K,
 // ------------------------------------------------------------------------------------------
 struct TcParams {
   float* Opart;   // [B,H,N,D] un-normalised
-  float* Mpart;   // [B,H,N]
+  float* Mpart;   // [B,H,N]  running max, natural-log units
   float* Lpart;
   int* status;    // device word: set non-zero when a bounded wait expired
   int H, N, cq, ck, causal;
 };
 
+// One CTA owns 256 query rows as two 128-row tiles (two softmax warpgroups, one TMEM lane each
+// per row); every Kt / V tile staged in shared memory feeds the MMAs of both row tiles.
 template <int D, int BC>
 struct TcCfg {
-  static constexpr int BM = 128;               // query rows per CTA (= TMEM lanes)
+  static constexpr int BM = 128;               // rows per tile (= TMEM lanes)
+  static constexpr int NT = 2;                 // row tiles per CTA
   static constexpr int HALO = 16;              // rows staged above the block (pad_q <= 15)
-  static constexpr int QR = BM + HALO;
+  static constexpr int QR = NT * BM + HALO;    // 272 rows of Q in shared memory
   static constexpr int TILE_BYTES = BC * D * 2;
-  static constexpr int NSLOT = (D == 64) ? 12 : 7;
+  static constexpr int NSLOT = (D == 64) ? 11 : 5;
   static constexpr int oQ = 0;
   static constexpr int oP = oQ + QR * D * 2;
-  static constexpr int P_BYTES = BM * BC * 2;
-  static constexpr int oRing = ((oP + 2 * P_BYTES + 1023) / 1024) * 1024;
+  static constexpr int P_BYTES = BM * BC * 2;  // one P tile; [NT][2 buffers]
+  static constexpr int oRing = ((oP + NT * 2 * P_BYTES + 1023) / 1024) * 1024;
   static constexpr int oBar = oRing + NSLOT * TILE_BYTES;
   static constexpr int kSmemBytes = oBar + 512 + 1024;   // + alignment slack
-  static constexpr int kTmemCols = 256;        // S0 [0,BC) S1 [BC,2BC) O [2BC, 2BC+D)
-  static_assert(2 * BC + D <= kTmemCols, "TMEM budget");
+  static constexpr int kTmemCols = 512;        // S[t][buf] at (2t+buf)*64, O[t] at 256 + t*D
+  static constexpr int kThreads = (NT * 4 + 2) * 32;
+  static_assert(4 * BC + NT * D <= kTmemCols, "TMEM budget");
   static_assert(BC == 64, "softmax code assumes 64 keys per block");
 };
 
+constexpr float kRescaleTau = 8.f;   // log2 units: P may reach 2^8 before O is rescaled
+
 template <int D, int BC>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(TcCfg<D, BC>::kThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKt,
               const __grid_constant__ CUtensorMap tmV, const TcParams p) {
   using Cfg = TcCfg<D, BC>;
-  constexpr int BM = Cfg::BM, HALO = Cfg::HALO, QR = Cfg::QR, NSLOT = Cfg::NSLOT;
+  constexpr int BM = Cfg::BM, HALO = Cfg::HALO, QR = Cfg::QR, NSLOT = Cfg::NSLOT, NT = Cfg::NT;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = smem + Cfg::oQ;
   unsigned char* sP = smem + Cfg::oP;
   unsigned char* sRing = smem + Cfg::oRing;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::oBar);
-  uint64_t* full = bars;                 // [NSLOT]
-  uint64_t* empty = bars + NSLOT;        // [NSLOT]
+  uint64_t* full = bars;                 // [NSLOT]  TMA -> MMA
+  uint64_t* empty = bars + NSLOT;        // [NSLOT]  MMA -> TMA
   uint64_t* q_full = bars + 2 * NSLOT;
-  uint64_t* s_full = q_full + 1;         // [2]
-  uint64_t* p_full = s_full + 2;         // [2]
-  uint64_t* o_full = p_full + 2;
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* s_full = q_full + 1;         // [2]      S buffers of both tiles ready
+  uint64_t* p_full = s_full + 2;         // [NT][2]  P tile written (128 arrivals)
+  uint64_t* p_empty = p_full + 4;        // [NT][2]  PV that read the P tile has completed
+  uint64_t* o_full = p_empty + 4;        // [NT]     PV(t, kb) completed
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(o_full + 2);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   volatile int* s_issued = s_abort + 1;
   volatile int* s_consumed = s_abort + 2;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
-  const int nQB = (N + BM - 1) / BM;
+  const int band = pq + pk;              // entries with query - key < band belong to the exact kernel
+  const int nQB = (N + NT * BM - 1) / (NT * BM);
   const int qb = nQB - 1 - (int)blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int bh = b * p.H + h;
-  const int i0 = qb * BM;
-  int nkb;
-  if (p.causal) {
-    const int t = i0 - pq - pk + 1;
-    nkb = t > 0 ? t / BC : 0;
-  } else {
-    nkb = (N + BC - 1) / BC;
+  const int i0 = qb * NT * BM;
+  const int nKB = (N + BC - 1) / BC;
+  int nkb_t[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    const int r0 = i0 + t * BM;
+    if (r0 >= N) nkb_t[t] = 0;
+    else if (p.causal) {
+      // key blocks that hold at least one key j <= (last row) - band
+      const int last = min(N - 1, r0 + BM - 1) - band;
+      nkb_t[t] = last >= 0 ? min(nKB, last / BC + 1) : 0;
+    } else nkb_t[t] = nKB;
   }
+  const int nkb = max(nkb_t[0], nkb_t[1]);
 
   if (tid == 0) {
     for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
     tc::mbar_init(q_full, 1);
     tc::mbar_init(&s_full[0], 1); tc::mbar_init(&s_full[1], 1);
-    tc::mbar_init(&p_full[0], BM); tc::mbar_init(&p_full[1], BM);
-    tc::mbar_init(o_full, 1);
+    for (int i = 0; i < 4; ++i) { tc::mbar_init(&p_full[i], BM); tc::mbar_init(&p_empty[i], 1); }
+    tc::mbar_init(&o_full[0], 1); tc::mbar_init(&o_full[1], 1);
     *s_abort = 0; *s_issued = 0; *s_consumed = 0;
     tc::mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == NT * 4 + 1) {
     tc::tmem_alloc(s_tmem, Cfg::kTmemCols);
     tc::tmem_relinquish();
   }
@@ -163,16 +179,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t tS[2] = {tmem, tmem + BC};
-  const uint32_t tO = tmem + 2 * BC;
 
-  if (warp == 4) {
+  if (warp == NT * 4) {
     // ===================== TMA producer =====================
     if (lane == 0 && nkb > 0) {
       tc::tma_prefetch_desc(&tmQ); tc::tma_prefetch_desc(&tmKt); tc::tma_prefetch_desc(&tmV);
       tc::mbar_expect_tx(q_full, QR * D * 2);
-      for (int kc = 0; kc < D / 8; ++kc)   // one 16-byte-wide column slab per load -> [kc][row][8]
+      for (int kc = 0; kc < D / 8; ++kc) {   // 16-byte-wide column slabs -> [kc][row][8]; 2 boxes of 136 rows
         tc::tma_load_3d(sQ + kc * (QR * 16), &tmQ, q_full, kc * 8, i0 - HALO, bh);
+        tc::tma_load_3d(sQ + kc * (QR * 16) + (QR / 2) * 16, &tmQ, q_full, kc * 8, i0 - HALO + QR / 2, bh);
+      }
       int id = 0;
       bool ok = true;
       auto put = [&](bool isV, int kb, int a) {
@@ -195,12 +211,20 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (ok) put(true, kb, 0);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == NT * 4 + 1) {
     // ===================== MMA issuer =====================
     if (lane == 0 && nkb > 0) {
       constexpr uint32_t idescS = tc::make_idesc(BM, BC, 0, 0);
       constexpr uint32_t idescPV = tc::make_idesc(BM, D, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aRing = smem_u32(sRing);
+      // descriptors split into a constant high word and a low word that carries the start address
+      const uint64_t dQ0 = tc::make_sdesc(smem_u32(sQ) + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);
+      const uint64_t dK0 = tc::make_sdesc(smem_u32(sRing), 16, 1024, tc::kLayoutSW128);
+      const uint64_t dP0 = tc::make_sdesc(smem_u32(sP), BM * 16, 128, tc::kLayoutNone);
+      const uint64_t dV0 = tc::make_sdesc(smem_u32(sRing), BC * 128, 1024, tc::kLayoutSW128);
+      const uint32_t aS_hi = (uint32_t)(dQ0 >> 32), bS_hi = (uint32_t)(dK0 >> 32), bS_lo = (uint32_t)dK0;
+      const uint32_t aS_lo[NT] = {(uint32_t)dQ0, (uint32_t)dQ0 + (uint32_t)BM};
+      const uint32_t aP_hi = (uint32_t)(dP0 >> 32), aP_lo = (uint32_t)dP0;
+      const uint32_t bV_hi = (uint32_t)(dV0 >> 32), bV_lo = (uint32_t)dV0;
       int id = 0;
       bool ok = tc::mbar_wait(q_full, 0, s_abort);
       auto issue_S = [&](int kb) {
@@ -208,13 +232,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
           if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
           tc::tc_fence_after();
-          const uint32_t aB = aRing + slot * Cfg::TILE_BYTES;
-          const uint32_t aA = aQ + (HALO - pq + a) * 16;
+          const uint32_t b_lo = bS_lo + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint64_t ad = tc::make_sdesc(aA + (2 * k) * (QR * 16), QR * 16, 128, tc::kLayoutNone);
-            const uint64_t bd = tc::make_sdesc(aB + (k / 4) * (BC * 128) + (k % 4) * 32, 16, 1024, tc::kLayoutSW128);
-            tc::mma_ss(tS[kb & 1], ad, bd, idescS, (a | k) != 0);
+          for (int t = 0; t < NT; ++t) {
+            if (kb < nkb_t[t]) {
+              const uint32_t a_lo = aS_lo[t] + (uint32_t)a;            // one row down = +16 bytes
+              const uint32_t dS = tmem + (2 * t + (kb & 1)) * BC;
+              if (a == 0) tc::mma_ss2<0>(dS, a_lo, aS_hi, b_lo, bS_hi, idescS);
+              else tc::mma_ss2<1>(dS, a_lo, aS_hi, b_lo, bS_hi, idescS);
+#pragma unroll
+              for (int k = 1; k < D / 16; ++k)
+                tc::mma_ss2<1>(dS, a_lo + (uint32_t)(2 * k * QR), aS_hi,
+                               b_lo + (uint32_t)((k / 4) * (BC * 128 / 16) + (k % 4) * 2), bS_hi, idescS);
+            }
           }
           tc::mma_commit(&empty[slot]);
           ++id;
@@ -225,18 +255,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       auto issue_PV = [&](int kb) {
         const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
         if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
-        if (!tc::mbar_wait(&p_full[kb & 1], (kb >> 1) & 1, s_abort)) { ok = false; return; }
-        tc::tc_fence_after();
-        const uint32_t aB = aRing + slot * Cfg::TILE_BYTES;
-        const uint32_t aA = aP + (kb & 1) * Cfg::P_BYTES;
+        const uint32_t b_lo = bV_lo + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
 #pragma unroll
-        for (int k = 0; k < BC / 16; ++k) {
-          const uint64_t ad = tc::make_sdesc(aA + (2 * k) * (BM * 16), BM * 16, 128, tc::kLayoutNone);
-          const uint64_t bd = tc::make_sdesc(aB + k * 2048, BC * 128, 1024, tc::kLayoutSW128);
-          tc::mma_ss(tO, ad, bd, idescPV, (kb | k) != 0);
+        for (int t = 0; t < NT; ++t) {
+          if (kb < nkb_t[t] && ok) {
+            if (!tc::mbar_wait(&p_full[2 * t + (kb & 1)], (kb >> 1) & 1, s_abort)) { ok = false; break; }
+            tc::tc_fence_after();
+            const uint32_t a_lo = aP_lo + (uint32_t)((2 * t + (kb & 1)) * (Cfg::P_BYTES >> 4));
+            const uint32_t dO = tmem + 4 * BC + t * D;
+            if (kb == 0) tc::mma_ss2<0>(dO, a_lo, aP_hi, b_lo, bV_hi, idescPV);
+            else tc::mma_ss2<1>(dO, a_lo, aP_hi, b_lo, bV_hi, idescPV);
+#pragma unroll
+            for (int k = 1; k < BC / 16; ++k)
+              tc::mma_ss2<1>(dO, a_lo + (uint32_t)(2 * k * BM), aP_hi, b_lo + (uint32_t)(k * (2048 / 16)), bV_hi, idescPV);
+            tc::mma_commit(&p_empty[2 * t + (kb & 1)]);
+            tc::mma_commit(&o_full[t]);
+          }
         }
-        tc::mma_commit(&empty[slot]);
-        tc::mma_commit(o_full);
+        if (ok) tc::mma_commit(&empty[slot]);
         ++id;
         *s_consumed = id;
       };
@@ -247,46 +283,68 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
     }
   } else {
-    // ===================== softmax warps: one query row per thread =====================
-    const int m = tid;                                  // row within the block = TMEM lane
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f;
+    // ===================== softmax warpgroups: one query row per thread =====================
+    const int t = warp >> 2;                            // row tile of this warpgroup
+    const int m = tid & (BM - 1);                       // row within the tile = TMEM lane
+    const int gi = i0 + t * BM + m;                     // query index
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tO = tmem + 4 * BC + t * D;
+    const int my_nkb = nkb_t[t];
+    float m_run = -INFINITY, l_run = 0.f;               // log2 units (Kt carries scale * log2(e))
+    float m_true = -INFINITY;                           // true row max (m_run lags it by up to tau)
     bool ok = true;
-    for (int kb = 0; kb < nkb && ok; ++kb) {
+    for (int kb = 0; kb < my_nkb && ok; ++kb) {
       ok = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[kb & 1], (kb >> 1) & 1, s_abort));
-      if (!ok) break;   // warp-uniform: the TMEM loads below are warp-collective
+      if (!ok) break;   // warp-uniform: the TMEM accesses below are warp-collective
       tc::tc_fence_after();
+      const uint32_t tS = tmem + (2 * t + (kb & 1)) * BC;
       float s[BC];
       {
         float t0[32], t1[32];
-        tc::tmem_ld32(tS[kb & 1] + lane_base, t0);
-        tc::tmem_ld32(tS[kb & 1] + lane_base + 32, t1);
+        tc::tmem_ld32(tS + lane_base, t0);
+        tc::tmem_ld32(tS + lane_base + 32, t1);
 #pragma unroll
         for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
       }
-      if (!p.causal) {
+      const int j0 = kb * BC;
+      // mask: keys past N, and (causal) entries on or above the band, which the exact kernel owns
+      const int jlim = p.causal ? min(N - 1, gi - band) : N - 1;   // last key this row may see here
+      if (j0 + BC - 1 > jlim) {
 #pragma unroll
-        for (int i = 0; i < BC; ++i) if (kb * BC + i >= N) s[i] = -INFINITY;
+        for (int i = 0; i < BC; ++i) if (j0 + i > jlim) s[i] = -INFINITY;
       }
-      float mx = s[0];
+      float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]), mx2 = fmaxf(s[4], s[5]), mx3 = fmaxf(s[6], s[7]);
 #pragma unroll
-      for (int i = 1; i < BC; ++i) mx = fmaxf(mx, s[i]);
-      const float m_new = fmaxf(m_run, mx);             // finite: every block holds a valid key
-      const float mb = m_new * kLog2e;
-      float sum = 0.f;
+      for (int i = 8; i < BC; i += 8) {
+        mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1])); mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
+        mx2 = fmaxf(mx2, fmaxf(s[i + 4], s[i + 5])); mx3 = fmaxf(mx3, fmaxf(s[i + 6], s[i + 7]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      m_true = fmaxf(m_true, mx);
+      // lazy rescale: keep the reference max until a block exceeds it by more than tau
+      float alpha = 1.f;
+      bool need = false;
+      if (m_run == -INFINITY) {
+        m_run = mx;                                     // O and l are still zero: nothing to rescale
+      } else if (mx > m_run + kRescaleTau) {
+        alpha = exp2f(m_run - mx);
+        m_run = mx;
+        need = true;
+      }
+      const float mref = (m_run == -INFINITY) ? 0.f : m_run;
+      float sum0 = 0.f, sum1 = 0.f;
       uint32_t pk32[BC / 2];
 #pragma unroll
-      for (int i = 0; i < BC; i += 2) {
-        const float p0 = exp2f(fmaf(s[i], kLog2e, -mb)), p1 = exp2f(fmaf(s[i + 1], kLog2e, -mb));
-        sum += p0 + p1;
-        pk32[i / 2] = pack_bf16(p0, p1);
+      for (int i = 0; i < BC; i += 4) {
+        const float p0 = exp2f(s[i] - mref), p1 = exp2f(s[i + 1] - mref);
+        const float p2 = exp2f(s[i + 2] - mref), p3 = exp2f(s[i + 3] - mref);
+        sum0 += p0 + p1; sum1 += p2 + p3;
+        pk32[i / 2] = pack_bf16(p0, p1); pk32[i / 2 + 1] = pack_bf16(p2, p3);
       }
-      const float alpha = exp2f((m_run - m_new) * kLog2e);   // 0 on the first block
-      l_run = l_run * alpha + sum;
-      m_run = m_new;
-      if (kb > 0) {
-        // O *= alpha (needs PV(kb-1) complete; that also frees P buffer kb&1 used by PV(kb-2))
-        ok = __all_sync(0xffffffffu, tc::mbar_wait(o_full, (kb - 1) & 1, s_abort));
+      l_run = l_run * alpha + (sum0 + sum1);
+      if (__any_sync(0xffffffffu, need)) {
+        // O *= alpha; PV(kb-1) must have completed (kb >= 1 here: need is false on the first block)
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (kb - 1) & 1, s_abort));
         if (!ok) break;
         tc::tc_fence_after();
 #pragma unroll
@@ -299,19 +357,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         tc::tmem_wait_st();
       }
-      unsigned char* pb = sP + (kb & 1) * Cfg::P_BYTES + m * 16;
+      if (kb >= 2) {   // the PV that read this P buffer two blocks ago must be done
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(&p_empty[2 * t + (kb & 1)], ((kb >> 1) - 1) & 1, s_abort));
+        if (!ok) break;
+      }
+      unsigned char* pb = sP + (2 * t + (kb & 1)) * Cfg::P_BYTES + m * 16;
 #pragma unroll
       for (int kc = 0; kc < BC / 8; ++kc)
         *reinterpret_cast<uint4*>(pb + kc * (BM * 16)) = make_uint4(pk32[4 * kc], pk32[4 * kc + 1], pk32[4 * kc + 2], pk32[4 * kc + 3]);
       tc::fence_proxy_async_smem();
       tc::tc_fence_before();
-      tc::mbar_arrive(&p_full[kb & 1]);
+      tc::mbar_arrive(&p_full[2 * t + (kb & 1)]);
     }
     // ---- epilogue: un-normalised partial row ----
-    const int gi = i0 + m;
-    if (nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(o_full, (nkb - 1) & 1, s_abort));
+    if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (my_nkb - 1) & 1, s_abort));
     tc::tc_fence_after();
-    const bool have = (nkb > 0) && ok;                  // warp-uniform
+    const bool have = (my_nkb > 0) && ok;               // warp-uniform
+    // re-reference the partial to the true row max (what the reference reports as M)
+    const float fix = (m_true == -INFINITY) ? 0.f : exp2f(m_run - m_true);
     float* orow = p.Opart + ((size_t)bh * N + (gi < N ? gi : 0)) * D;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
@@ -324,12 +387,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       if (gi < N) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(orow + c * 32 + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(orow + c * 32 + i) = make_float4(o[i] * fix, o[i + 1] * fix, o[i + 2] * fix, o[i + 3] * fix);
       }
     }
     if (gi < N) {
-      p.Mpart[(size_t)bh * N + gi] = have ? m_run : -INFINITY;
-      p.Lpart[(size_t)bh * N + gi] = have ? l_run : 0.f;
+      const bool any = have && (m_run != -INFINITY);
+      p.Mpart[(size_t)bh * N + gi] = any ? m_true * 0.6931471805599453f : -INFINITY;
+      p.Lpart[(size_t)bh * N + gi] = any ? l_run * fix : 0.f;
     }
   }
   __syncwarp();
@@ -339,13 +403,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   if (*s_abort) {
     if (tid == 0) atomicExch(p.status, 1);
-    if (tid == 128) {   // drain copies that were issued but never consumed, with a bounded wait
+    if (tid == NT * 4 * 32) {   // drain copies that were issued but never consumed, with a bounded wait
       volatile int never = 0;
       for (int id = *s_consumed; id < *s_issued; ++id) tc::mbar_wait(&full[id % NSLOT], (id / NSLOT) & 1, &never);
     }
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == NT * 4 + 1) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, Cfg::kTmemCols);
   }
@@ -393,12 +457,12 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
   {
     constexpr int RPB = 256 / (D / 8);
     dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH);
-    ktilde_kernel<D><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale);
+    ktilde_kernel<D><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale * kLog2e);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   alignas(64) CUtensorMap tmQ, tmKt, tmV;
-  if (!make_map(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR, false)) return cudaErrorInvalidValue;
+  if (!make_map(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR / 2, false)) return cudaErrorInvalidValue;
   if (!make_map(&tmKt, Kt, D, p.N, BH * p.cq, 64, BC, true)) return cudaErrorInvalidValue;
   if (!make_map(&tmV, p.V, D, p.N, BH, 64, BC, true)) return cudaErrorInvalidValue;
   TcParams tp;
@@ -407,8 +471,8 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
   auto kern = fwd_tc_kernel<D, BC>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.N + Cfg::BM - 1) / Cfg::BM, p.H, p.B);
-  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, tp);
+  dim3 grid((p.N + Cfg::NT * Cfg::BM - 1) / (Cfg::NT * Cfg::BM), p.H, p.B);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, tp);
   return cudaGetLastError();
 }
 
