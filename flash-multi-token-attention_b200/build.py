@@ -41,7 +41,7 @@ def _newest_header():
 
 
 def _compile(src, obj, verbose):
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-c", src, "-o", obj]
+    cmd = [_nvcc()] + NVCC_FLAGS + os.environ.get("FMTA_NVCC_EXTRA", "").split() + ["-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     log = r.stdout + r.stderr
     with open(obj + ".log", "w") as f:

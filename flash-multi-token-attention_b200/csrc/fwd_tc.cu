@@ -32,6 +32,13 @@
 
 namespace fmta {
 
+#ifdef FMTA_TC_TRACE
+__device__ long long g_trace[16384];
+#define TRACE(slot) do { if (trace_on) g_trace[(slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot) do {} while (0)
+#endif
+
 // ------------------------------------------------------------------------------------------
 // Kt[bh, a, j, :] = scale * sum_b theta[h, a, b] * K[bh, j + b - pad_k, :]   (bf16, zero beyond ends)
 template <int D>
@@ -86,55 +93,63 @@ __global__ void __launch_bounds__(256) ktilde_kernel(const bf16* __restrict__ K,
 // ------------------------------------------------------------------------------------------
 struct TcParams {
   float* Opart;   // [B,H,N,D] un-normalised
-  float* Mpart;   // [B,H,N]  running max, natural-log units
+  float* Mpart;   // [B,H,N]  row max, natural-log units
   float* Lpart;
   int* status;    // device word: set non-zero when a bounded wait expired
   int H, N, cq, ck, causal;
 };
 
-// One CTA owns 256 query rows as two 128-row tiles (two softmax warpgroups, one TMEM lane each
-// per row); every Kt / V tile staged in shared memory feeds the MMAs of both row tiles.
-template <int D, int BC>
+// One CTA owns NT row tiles of 128 query rows (one softmax warpgroup and one TMEM lane per row);
+// key blocks are 128 wide so that every score MMA is 128 x 128 x 16 -- the 64-wide variant was
+// bound by shared-memory operand fetch (4 KB of A per 2 KB of B).  Every Kt / V tile staged in
+// shared memory feeds the MMAs of all row tiles.  Tensor memory per row tile: S (128 columns,
+// fp32), P (64 columns, bf16 pairs) and O (D columns, fp32); S is released to the next block's
+// MMAs as soon as the softmax threads have loaded it into registers.
+template <int D>
 struct TcCfg {
   static constexpr int BM = 128;               // rows per tile (= TMEM lanes)
-  static constexpr int NT = 2;                 // row tiles per CTA
+  static constexpr int BC = 128;               // keys per block
+  static constexpr int NT = (D == 64) ? 2 : 1; // row tiles per CTA (TMEM: NT * (128 + 64 + D) <= 512)
   static constexpr int HALO = 16;              // rows staged above the block (pad_q <= 15)
-  static constexpr int QR = NT * BM + HALO;    // 272 rows of Q in shared memory
-  static constexpr int TILE_BYTES = BC * D * 2;
-  static constexpr int NSLOT = (D == 64) ? 11 : 5;
+  static constexpr int QR = NT * BM + HALO;    // rows of Q in shared memory
+  static constexpr int QBOX = QR / 2;          // Q is fetched as two boxes per 16-byte column slab
+  static constexpr int SLABS = D / 64;         // 64-element (128-byte) column slabs per row
+  static constexpr int TILE_BYTES = BC * 128;  // one ring tile: 128 keys x 64 elements, 128B-swizzled
+  static constexpr int NSLOT = 11;
   static constexpr int oQ = 0;
-  static constexpr int oP = oQ + QR * D * 2;
-  static constexpr int P_BYTES = BM * BC * 2;  // one P tile; [NT][2 buffers]
-  static constexpr int oRing = ((oP + NT * 2 * P_BYTES + 1023) / 1024) * 1024;
+  static constexpr int oRing = ((oQ + QR * D * 2 + 1023) / 1024) * 1024;
   static constexpr int oBar = oRing + NSLOT * TILE_BYTES;
   static constexpr int kSmemBytes = oBar + 512 + 1024;   // + alignment slack
-  static constexpr int kTmemCols = 512;        // S[t][buf] at (2t+buf)*64, O[t] at 256 + t*D
-  static constexpr int kThreads = (NT * 4 + 2) * 32;
-  static_assert(4 * BC + NT * D <= kTmemCols, "TMEM budget");
-  static_assert(BC == 64, "softmax code assumes 64 keys per block");
+  static constexpr int kTmemCols = 512;
+  static constexpr int colS = 0;               // S[t] at colS + t*128
+  static constexpr int colP = NT * 128;        // P[t] at colP + t*64
+  static constexpr int colO = NT * 192;        // O[t] at colO + t*D
+  static constexpr int kThreads = (NT * 4 + 1 + NT) * 32;   // softmax warpgroups, TMA warp, one MMA warp per row tile
+  static_assert(NT * (192 + D) <= kTmemCols, "TMEM budget");
+  static_assert(QR <= 512 && QBOX <= 256, "TMA box limit");
 };
 
 constexpr float kRescaleTau = 8.f;   // log2 units: P may reach 2^8 before O is rescaled
 
-template <int D, int BC>
-__global__ void __launch_bounds__(TcCfg<D, BC>::kThreads, 1)
+template <int D>
+__global__ void __launch_bounds__(TcCfg<D>::kThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKt,
               const __grid_constant__ CUtensorMap tmV, const TcParams p) {
-  using Cfg = TcCfg<D, BC>;
-  constexpr int BM = Cfg::BM, HALO = Cfg::HALO, QR = Cfg::QR, NSLOT = Cfg::NSLOT, NT = Cfg::NT;
+  using Cfg = TcCfg<D>;
+  constexpr int BM = Cfg::BM, BC = Cfg::BC, HALO = Cfg::HALO, QR = Cfg::QR, NSLOT = Cfg::NSLOT, NT = Cfg::NT;
+  constexpr int SLABS = Cfg::SLABS;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = smem + Cfg::oQ;
-  unsigned char* sP = smem + Cfg::oP;
   unsigned char* sRing = smem + Cfg::oRing;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::oBar);
   uint64_t* full = bars;                 // [NSLOT]  TMA -> MMA
   uint64_t* empty = bars + NSLOT;        // [NSLOT]  MMA -> TMA
   uint64_t* q_full = bars + 2 * NSLOT;
-  uint64_t* s_full = q_full + 1;         // [2]      S buffers of both tiles ready
-  uint64_t* p_full = s_full + 2;         // [NT][2]  P tile written (128 arrivals)
-  uint64_t* p_empty = p_full + 4;        // [NT][2]  PV that read the P tile has completed
-  uint64_t* o_full = p_empty + 4;        // [NT]     PV(t, kb) completed
+  uint64_t* s_full = q_full + 1;         // [NT]  S[t] ready (one commit per key block)
+  uint64_t* s_free = s_full + 2;         // [NT]  S[t] loaded into registers (128 arrivals)
+  uint64_t* p_full = s_free + 2;         // [NT]  P[t] written to tensor memory (128 arrivals)
+  uint64_t* o_full = p_full + 2;         // [NT]  PV(t, kb) completed
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(o_full + 2);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   volatile int* s_issued = s_abort + 1;
@@ -149,7 +164,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int bh = b * p.H + h;
   const int i0 = qb * NT * BM;
   const int nKB = (N + BC - 1) / BC;
-  int nkb_t[NT];
+  int nkb_t[2] = {0, 0};
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
     const int r0 = i0 + t * BM;
@@ -161,17 +176,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     } else nkb_t[t] = nKB;
   }
   const int nkb = max(nkb_t[0], nkb_t[1]);
+#ifdef FMTA_TC_TRACE
+  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+#endif
 
   if (tid == 0) {
-    for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
+    for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], NT); }   // every MMA warp releases a slot
     tc::mbar_init(q_full, 1);
-    tc::mbar_init(&s_full[0], 1); tc::mbar_init(&s_full[1], 1);
-    for (int i = 0; i < 4; ++i) { tc::mbar_init(&p_full[i], BM); tc::mbar_init(&p_empty[i], 1); }
-    tc::mbar_init(&o_full[0], 1); tc::mbar_init(&o_full[1], 1);
+    for (int i = 0; i < 2; ++i) { tc::mbar_init(&s_full[i], 1); tc::mbar_init(&s_free[i], BM); tc::mbar_init(&p_full[i], BM); tc::mbar_init(&o_full[i], 1); }
     *s_abort = 0; *s_issued = 0; *s_consumed = 0;
     tc::mbar_fence_init();
   }
-  if (warp == NT * 4 + 1) {
+  if (warp == NT * 4 + 1) {   // the first MMA warp owns the tensor-memory allocation
     tc::tmem_alloc(s_tmem, Cfg::kTmemCols);
     tc::tmem_relinquish();
   }
@@ -185,102 +201,108 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (lane == 0 && nkb > 0) {
       tc::tma_prefetch_desc(&tmQ); tc::tma_prefetch_desc(&tmKt); tc::tma_prefetch_desc(&tmV);
       tc::mbar_expect_tx(q_full, QR * D * 2);
-      for (int kc = 0; kc < D / 8; ++kc) {   // 16-byte-wide column slabs -> [kc][row][8]; 2 boxes of 136 rows
+      for (int kc = 0; kc < D / 8; ++kc) {   // 16-byte-wide column slabs -> [kc][row][8 elements]
         tc::tma_load_3d(sQ + kc * (QR * 16), &tmQ, q_full, kc * 8, i0 - HALO, bh);
-        tc::tma_load_3d(sQ + kc * (QR * 16) + (QR / 2) * 16, &tmQ, q_full, kc * 8, i0 - HALO + QR / 2, bh);
+        tc::tma_load_3d(sQ + kc * (QR * 16) + Cfg::QBOX * 16, &tmQ, q_full, kc * 8, i0 - HALO + Cfg::QBOX, bh);
       }
       int id = 0;
       bool ok = true;
-      auto put = [&](bool isV, int kb, int a) {
+      auto put = [&](const CUtensorMap* map, int x, int y, int z) {
         const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
         if (!tc::mbar_wait(&empty[slot], ph ^ 1, s_abort)) { ok = false; return; }
         tc::mbar_expect_tx(&full[slot], Cfg::TILE_BYTES);
-        unsigned char* dst = sRing + slot * Cfg::TILE_BYTES;
-#pragma unroll
-        for (int s = 0; s < D / 64; ++s) {
-          if (isV) tc::tma_load_3d(dst + s * (BC * 128), &tmV, &full[slot], s * 64, kb * BC, bh);
-          else tc::tma_load_3d(dst + s * (BC * 128), &tmKt, &full[slot], s * 64, kb * BC, bh * cq + a);
-        }
+        tc::tma_load_3d(sRing + slot * Cfg::TILE_BYTES, map, &full[slot], x, y, z);
         ++id;
         *s_issued = id;
       };
       // same order as the MMA warp consumes: S(0); then S(kb+1), V(kb)
-      for (int a = 0; a < cq && ok; ++a) put(false, 0, a);
+      for (int a = 0; a < cq && ok; ++a)
+        for (int sl = 0; sl < SLABS && ok; ++sl) put(&tmKt, sl * 64, 0, bh * cq + a);
       for (int kb = 0; kb < nkb && ok; ++kb) {
-        if (kb + 1 < nkb) for (int a = 0; a < cq && ok; ++a) put(false, kb + 1, a);
-        if (ok) put(true, kb, 0);
+        if (kb + 1 < nkb)
+          for (int a = 0; a < cq && ok; ++a)
+            for (int sl = 0; sl < SLABS && ok; ++sl) put(&tmKt, sl * 64, (kb + 1) * BC, bh * cq + a);
+        for (int sl = 0; sl < SLABS && ok; ++sl) put(&tmV, sl * 64, kb * BC, bh);
       }
     }
-  } else if (warp == NT * 4 + 1) {
-    // ===================== MMA issuer =====================
+  } else if (warp > NT * 4) {
+    // ===================== MMA issuers: one warp (one elected thread) per row tile =====================
+    // Both walk the same tile stream; a ring slot is released when every issuer has committed
+    // its MMAs on it.  Two issuers keep the tensor pipe fed while one of them sits in a barrier
+    // wait or a commit.
+    const int t = warp - (NT * 4 + 1);
     if (lane == 0 && nkb > 0) {
       constexpr uint32_t idescS = tc::make_idesc(BM, BC, 0, 0);
-      constexpr uint32_t idescPV = tc::make_idesc(BM, D, 0, 1);
+      constexpr uint32_t idescPV = tc::make_idesc(BM, 64, 0, 1);
       // descriptors split into a constant high word and a low word that carries the start address
-      const uint64_t dQ0 = tc::make_sdesc(smem_u32(sQ) + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);
+      const uint64_t dQ0 = tc::make_sdesc(smem_u32(sQ) + (t * BM + HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);
       const uint64_t dK0 = tc::make_sdesc(smem_u32(sRing), 16, 1024, tc::kLayoutSW128);
-      const uint64_t dP0 = tc::make_sdesc(smem_u32(sP), BM * 16, 128, tc::kLayoutNone);
-      const uint64_t dV0 = tc::make_sdesc(smem_u32(sRing), BC * 128, 1024, tc::kLayoutSW128);
-      const uint32_t aS_hi = (uint32_t)(dQ0 >> 32), bS_hi = (uint32_t)(dK0 >> 32), bS_lo = (uint32_t)dK0;
-      const uint32_t aS_lo[NT] = {(uint32_t)dQ0, (uint32_t)dQ0 + (uint32_t)BM};
-      const uint32_t aP_hi = (uint32_t)(dP0 >> 32), aP_lo = (uint32_t)dP0;
-      const uint32_t bV_hi = (uint32_t)(dV0 >> 32), bV_lo = (uint32_t)dV0;
+      const uint32_t aS_hi = (uint32_t)(dQ0 >> 32), aS_lo = (uint32_t)dQ0;
+      const uint32_t b_hi = (uint32_t)(dK0 >> 32), b_lo0 = (uint32_t)dK0;
+      const uint32_t dS = tmem + Cfg::colS + t * 128;
+      const uint32_t aP = tmem + Cfg::colP + t * 64;            // bf16 pairs: 8 columns per 16 keys
+      const int my_nkb = nkb_t[t];
       int id = 0;
       bool ok = tc::mbar_wait(q_full, 0, s_abort);
       auto issue_S = [&](int kb) {
+        const bool active = kb < my_nkb;
+        // S[t] is single-buffered: wait until the softmax threads have taken block kb-1 out of it
+        if (active && kb > 0) {
+          ok = tc::mbar_wait(&s_free[t], (kb - 1) & 1, s_abort);
+          tc::tc_fence_after();
+        }
         for (int a = 0; a < cq && ok; ++a) {
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) {
+            const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
+            if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
+            if (active) {
+              tc::tc_fence_after();
+              const uint32_t b_lo = b_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
+              const uint32_t a_lo = aS_lo + (uint32_t)(a + sl * 8 * QR);   // row shift = +16 B per row
+              if (a == 0 && sl == 0) tc::mma_ss2<0>(dS, a_lo, aS_hi, b_lo, b_hi, idescS);
+              else tc::mma_ss2<1>(dS, a_lo, aS_hi, b_lo, b_hi, idescS);
+#pragma unroll
+              for (int k = 1; k < 4; ++k)
+                tc::mma_ss2<1>(dS, a_lo + (uint32_t)(2 * k * QR), aS_hi, b_lo + (uint32_t)(k * 2), b_hi, idescS);
+            }
+            tc::mma_commit(&empty[slot]);
+            ++id;
+          }
+        }
+        if (ok && active) tc::mma_commit(&s_full[t]);
+      };
+      auto issue_PV = [&](int kb) {
+        const bool active = kb < my_nkb;
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) {
           const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
           if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
-          tc::tc_fence_after();
-          const uint32_t b_lo = bS_lo + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
+          if (active) {
+            if (sl == 0 && !tc::mbar_wait(&p_full[t], kb & 1, s_abort)) { ok = false; return; }
+            tc::tc_fence_after();
+            const uint32_t b_lo = b_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
+            const uint32_t dO = tmem + Cfg::colO + t * D + sl * 64;
+            if (kb == 0) tc::mma_ts2<0>(dO, aP, b_lo, b_hi, idescPV);
+            else tc::mma_ts2<1>(dO, aP, b_lo, b_hi, idescPV);
 #pragma unroll
-          for (int t = 0; t < NT; ++t) {
-            if (kb < nkb_t[t]) {
-              const uint32_t a_lo = aS_lo[t] + (uint32_t)a;            // one row down = +16 bytes
-              const uint32_t dS = tmem + (2 * t + (kb & 1)) * BC;
-              if (a == 0) tc::mma_ss2<0>(dS, a_lo, aS_hi, b_lo, bS_hi, idescS);
-              else tc::mma_ss2<1>(dS, a_lo, aS_hi, b_lo, bS_hi, idescS);
-#pragma unroll
-              for (int k = 1; k < D / 16; ++k)
-                tc::mma_ss2<1>(dS, a_lo + (uint32_t)(2 * k * QR), aS_hi,
-                               b_lo + (uint32_t)((k / 4) * (BC * 128 / 16) + (k % 4) * 2), bS_hi, idescS);
-            }
+            for (int k = 1; k < BC / 16; ++k)
+              tc::mma_ts2<1>(dO, aP + 8 * k, b_lo + (uint32_t)(k * (2048 / 16)), b_hi, idescPV);
+            if (sl == SLABS - 1) tc::mma_commit(&o_full[t]);
           }
           tc::mma_commit(&empty[slot]);
           ++id;
-          *s_consumed = id;
         }
-        if (ok) tc::mma_commit(&s_full[kb & 1]);
-      };
-      auto issue_PV = [&](int kb) {
-        const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
-        if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
-        const uint32_t b_lo = bV_lo + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          if (kb < nkb_t[t] && ok) {
-            if (!tc::mbar_wait(&p_full[2 * t + (kb & 1)], (kb >> 1) & 1, s_abort)) { ok = false; break; }
-            tc::tc_fence_after();
-            const uint32_t a_lo = aP_lo + (uint32_t)((2 * t + (kb & 1)) * (Cfg::P_BYTES >> 4));
-            const uint32_t dO = tmem + 4 * BC + t * D;
-            if (kb == 0) tc::mma_ss2<0>(dO, a_lo, aP_hi, b_lo, bV_hi, idescPV);
-            else tc::mma_ss2<1>(dO, a_lo, aP_hi, b_lo, bV_hi, idescPV);
-#pragma unroll
-            for (int k = 1; k < BC / 16; ++k)
-              tc::mma_ss2<1>(dO, a_lo + (uint32_t)(2 * k * BM), aP_hi, b_lo + (uint32_t)(k * (2048 / 16)), bV_hi, idescPV);
-            tc::mma_commit(&p_empty[2 * t + (kb & 1)]);
-            tc::mma_commit(&o_full[t]);
-          }
-        }
-        if (ok) tc::mma_commit(&empty[slot]);
-        ++id;
-        *s_consumed = id;
       };
       if (ok) issue_S(0);
       for (int kb = 0; kb < nkb && ok; ++kb) {
+        if (t == 0) TRACE(8192 + kb * 4 + 0);
         if (kb + 1 < nkb) issue_S(kb + 1);
+        if (t == 0) TRACE(8192 + kb * 4 + 1);
         if (ok) issue_PV(kb);
+        if (t == 0) TRACE(8192 + kb * 4 + 2);
       }
+      if (t == 0) *s_consumed = id;
     }
   } else {
     // ===================== softmax warpgroups: one query row per thread =====================
@@ -288,24 +310,31 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int m = tid & (BM - 1);                       // row within the tile = TMEM lane
     const int gi = i0 + t * BM + m;                     // query index
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tO = tmem + 4 * BC + t * D;
+    const uint32_t tS = tmem + Cfg::colS + t * 128 + lane_base;
+    const uint32_t tP = tmem + Cfg::colP + t * 64 + lane_base;
+    const uint32_t tO = tmem + Cfg::colO + t * D + lane_base;
     const int my_nkb = nkb_t[t];
     float m_run = -INFINITY, l_run = 0.f;               // log2 units (Kt carries scale * log2(e))
     float m_true = -INFINITY;                           // true row max (m_run lags it by up to tau)
     bool ok = true;
     for (int kb = 0; kb < my_nkb && ok; ++kb) {
-      ok = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[kb & 1], (kb >> 1) & 1, s_abort));
+      if (tid == 0) TRACE(kb * 8 + 0);
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[t], kb & 1, s_abort));
       if (!ok) break;   // warp-uniform: the TMEM accesses below are warp-collective
       tc::tc_fence_after();
-      const uint32_t tS = tmem + (2 * t + (kb & 1)) * BC;
       float s[BC];
       {
-        float t0[32], t1[32];
-        tc::tmem_ld32(tS + lane_base, t0);
-        tc::tmem_ld32(tS + lane_base + 32, t1);
+        float t0[32], t1[32], t2[32], t3[32];
+        tc::tmem_ld32_nowait(tS, t0); tc::tmem_ld32_nowait(tS + 32, t1);
+        tc::tmem_ld32_nowait(tS + 64, t2); tc::tmem_ld32_nowait(tS + 96, t3);
+        tc::tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
+        for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; s[64 + i] = t2[i]; s[96 + i] = t3[i]; }
       }
+      // S[t] is in registers: let the MMA warp overwrite it with the next key block
+      tc::tc_fence_before();
+      tc::mbar_arrive(&s_free[t]);
+      if (tid == 0) TRACE(kb * 8 + 1);
       const int j0 = kb * BC;
       // mask: keys past N, and (causal) entries on or above the band, which the exact kernel owns
       const int jlim = p.causal ? min(N - 1, gi - band) : N - 1;   // last key this row may see here
@@ -342,32 +371,36 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         pk32[i / 2] = pack_bf16(p0, p1); pk32[i / 2 + 1] = pack_bf16(p2, p3);
       }
       l_run = l_run * alpha + (sum0 + sum1);
-      if (__any_sync(0xffffffffu, need)) {
-        // O *= alpha; PV(kb-1) must have completed (kb >= 1 here: need is false on the first block)
+      if (tid == 0) TRACE(kb * 8 + 2);
+      if (kb > 0) {
+        // PV(kb-1) complete: P[t] may be overwritten and O touched.  Waited for on every block
+        // (not only when O is rescaled) so that the parity wait never aliases an older phase.
         ok = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (kb - 1) & 1, s_abort));
         if (!ok) break;
         tc::tc_fence_after();
+      }
+      if (tid == 0) TRACE(kb * 8 + 3);
+      if (__any_sync(0xffffffffu, need)) {   // O *= alpha (need is false on the first block)
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           float o[32];
-          tc::tmem_ld32(tO + lane_base + c * 32, o);
+          tc::tmem_ld32(tO + c * 32, o);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= alpha;
-          tc::tmem_st32(tO + lane_base + c * 32, o);
+          tc::tmem_st32(tO + c * 32, o);
         }
-        tc::tmem_wait_st();
       }
-      if (kb >= 2) {   // the PV that read this P buffer two blocks ago must be done
-        ok = __all_sync(0xffffffffu, tc::mbar_wait(&p_empty[2 * t + (kb & 1)], ((kb >> 1) - 1) & 1, s_abort));
-        if (!ok) break;
-      }
-      unsigned char* pb = sP + (2 * t + (kb & 1)) * Cfg::P_BYTES + m * 16;
+      {
+        uint32_t lo[32], hi[32];
 #pragma unroll
-      for (int kc = 0; kc < BC / 8; ++kc)
-        *reinterpret_cast<uint4*>(pb + kc * (BM * 16)) = make_uint4(pk32[4 * kc], pk32[4 * kc + 1], pk32[4 * kc + 2], pk32[4 * kc + 3]);
-      tc::fence_proxy_async_smem();
+        for (int i = 0; i < 32; ++i) { lo[i] = pk32[i]; hi[i] = pk32[32 + i]; }
+        tc::tmem_st32u(tP, lo);
+        tc::tmem_st32u(tP + 32, hi);
+      }
+      tc::tmem_wait_st();
       tc::tc_fence_before();
-      tc::mbar_arrive(&p_full[2 * t + (kb & 1)]);
+      tc::mbar_arrive(&p_full[t]);
+      if (tid == 0) TRACE(kb * 8 + 5);
     }
     // ---- epilogue: un-normalised partial row ----
     if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (my_nkb - 1) & 1, s_abort));
@@ -380,7 +413,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int c = 0; c < D / 32; ++c) {
       float o[32];
       if (have) {
-        tc::tmem_ld32(tO + lane_base + c * 32, o);      // warp-collective: every lane takes part
+        tc::tmem_ld32(tO + c * 32, o);                  // warp-collective: every lane takes part
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = 0.f;
@@ -451,8 +484,7 @@ bool make_map(CUtensorMap* map, const void* base, int D, int rows, size_t outer,
 template <int D>
 cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpart, float* Lpart, int* status,
                         cudaStream_t stream) {
-  constexpr int BC = 64;
-  using Cfg = TcCfg<D, BC>;
+  using Cfg = TcCfg<D>;
   const size_t BH = (size_t)p.B * p.H;
   {
     constexpr int RPB = 256 / (D / 8);
@@ -462,13 +494,13 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
     if (e != cudaSuccess) return e;
   }
   alignas(64) CUtensorMap tmQ, tmKt, tmV;
-  if (!make_map(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR / 2, false)) return cudaErrorInvalidValue;
-  if (!make_map(&tmKt, Kt, D, p.N, BH * p.cq, 64, BC, true)) return cudaErrorInvalidValue;
-  if (!make_map(&tmV, p.V, D, p.N, BH, 64, BC, true)) return cudaErrorInvalidValue;
+  if (!make_map(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QBOX, false)) return cudaErrorInvalidValue;
+  if (!make_map(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
+  if (!make_map(&tmV, p.V, D, p.N, BH, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
   TcParams tp;
   tp.Opart = Opart; tp.Mpart = Mpart; tp.Lpart = Lpart; tp.status = status;
   tp.H = p.H; tp.N = p.N; tp.cq = p.cq; tp.ck = p.ck; tp.causal = p.causal;
-  auto kern = fwd_tc_kernel<D, BC>;
+  auto kern = fwd_tc_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((p.N + Cfg::NT * Cfg::BM - 1) / (Cfg::NT * Cfg::BM), p.H, p.B);
@@ -508,5 +540,11 @@ cudaError_t launch_fwd_tc(const TrainParams& p, void* workspace, const float** O
   *Opart = Op; *Mpart = Mp; *Lpart = Lp;
   return e;
 }
+
+#ifdef FMTA_TC_TRACE
+extern "C" int fmta_debug_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n);
+}
+#endif
 
 }  // namespace fmta
