@@ -193,11 +193,10 @@ def main():
         if record:
             e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
             e0.record(stream)
-        dQ, dTh = F.dq_backward(q, k, v, do, D, LSE, th, scale, pq, pk, True)
+        dQ, dK, dV, dTh = F.backward(q, k, v, do, D, LSE, th, scale, pq, pk, True)
         if record:
             e1.record(stream)
             kern_ev.append((e0, e1))
-        dK, dV = F.dkdv_backward(q, k, v, do, D, LSE, th, scale, pq, pk, True)
         if world > 1:
             dist.all_reduce(dTh)
         return O, dQ, dK, dV, dTh

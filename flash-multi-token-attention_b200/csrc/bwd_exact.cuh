@@ -121,6 +121,8 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
   const int N = p.N;
   const bool causal = p.causal != 0;
   const int pq = cq - 1, pk = (ck - 1) / 2;
+  // band mode: entries with query - key >= pad_q + pad_k belong to the stacked tensor-core kernels
+  const bool band_only = (p.kmode == kBandTiles);
 
   // ---- 1. S on the large region ----
   {
@@ -165,7 +167,7 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int kj = j0 - HC + s * 16 + i;
-        const bool ok = (qi < N) && (kj >= 0) && (kj < N) && !(causal && kj > qi);
+        const bool ok = (qi < N) && (kj >= 0) && (kj < N) && !(causal && kj > qi) && !(band_only && qi - kj >= pq + pk);
         acc[i] = ok ? exp2f((acc[i] - lse) * kLog2e) : 0.f;
       }
     }
@@ -196,7 +198,7 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int kj = j0 - HC + s * 16 + i;
-        const bool ok = (qi < N) && (kj >= 0) && (kj < N) && !(causal && kj > qi);
+        const bool ok = (qi < N) && (kj >= 0) && (kj < N) && !(causal && kj > qi) && !(band_only && qi - kj >= pq + pk);
         acc[i] = ok ? exp2f((acc[i] - lse) * kLog2e) : 0.f;
       }
       float4* o = reinterpret_cast<float4*>(sm.sE + r * E_LD + s * 16);
@@ -414,11 +416,21 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
   cp_async_commit();
 
   const int kb_end = causal ? min(nKB - 1, (i0 + BR - 1) / BC) : nKB - 1;
+  int kb_begin = 0;
+  if (p.kmode == kBandTiles) {
+    // key blocks whose dC region (keys [j0-HC, j0+BC+HC)) can hold a band entry of rows >= i0
+    if (causal) {
+      const int t = i0 - (cq - 1 + (ck - 1) / 2) - (BC + HC - 1);
+      kb_begin = (t < 0) ? 0 : (t / BC + 1);
+    } else {
+      kb_begin = nKB;   // no band without a causal mask
+    }
+  }
   constexpr int ONT = D / 16;
   float accQ[ONT][4] = {};
   const int mt = warp & 3, nh = warp >> 2;
 
-  for (int kb = 0; kb <= kb_end; ++kb) {
+  for (int kb = kb_begin; kb <= kb_end; ++kb) {
     const int j0 = kb * BC;
     load_rows_async<D, Cfg::NT>(sm.sK, QK_LD, Kg, j0 - 2 * HC, Cfg::SR, N, tid);
     load_rows_async<D, Cfg::NT>(sm.sV, QK_LD, Vg, j0 - HC, Cfg::ER, N, tid);
@@ -438,8 +450,18 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
 #pragma unroll
     for (int j = 0; j < ONT; ++j) {
       const int col = nh * (D / 2) + j * 8 + (lane & 3) * 2;
-      if (i0 + r0 < N) *reinterpret_cast<float2*>(p.dQ + (bh * N + i0 + r0) * D + col) = make_float2(accQ[j][0] * p.scale, accQ[j][1] * p.scale);
-      if (i0 + r1 < N) *reinterpret_cast<float2*>(p.dQ + (bh * N + i0 + r1) * D + col) = make_float2(accQ[j][2] * p.scale, accQ[j][3] * p.scale);
+      if (i0 + r0 < N) {
+        float2* o = reinterpret_cast<float2*>(p.dQ + (bh * N + i0 + r0) * D + col);
+        float2 v = make_float2(accQ[j][0] * p.scale, accQ[j][1] * p.scale);
+        if (p.accumulate) { const float2 u = *o; v.x += u.x; v.y += u.y; }
+        *o = v;
+      }
+      if (i0 + r1 < N) {
+        float2* o = reinterpret_cast<float2*>(p.dQ + (bh * N + i0 + r1) * D + col);
+        float2 v = make_float2(accQ[j][2] * p.scale, accQ[j][3] * p.scale);
+        if (p.accumulate) { const float2 u = *o; v.x += u.x; v.y += u.y; }
+        *o = v;
+      }
     }
   }
   // per-CTA partials of dTheta and dW (fixed summation order over warps)
@@ -495,11 +517,17 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
   cp_async_commit();
 
   const int qb_begin = causal ? (j0 / BR) : 0;
+  int qb_end = nQB - 1;
+  if (p.kmode == kBandTiles) {
+    // query blocks whose dC region (rows [i0, i0+BR+H1), keys [j0-HC, j0+BC+HC)) can hold a band entry
+    if (causal) qb_end = min(nQB - 1, (j0 + BC + HC - 1 + (cq - 1 + (ck - 1) / 2) - 1) / BR);
+    else qb_end = -1;
+  }
   constexpr int ONT = D / 16;
   float accK[ONT][4] = {}, accV[ONT][4] = {};
   const int mt = warp & 3, nh = warp >> 2;
 
-  for (int qb = qb_begin; qb < nQB; ++qb) {
+  for (int qb = qb_begin; qb <= qb_end; ++qb) {
     const int i0 = qb * BR;
     bwd_load_rowstats<D, CQ, CK, MIX>(sm, p, bh, i0, tid);
     load_rows_async<D, Cfg::NT>(sm.sQ, QK_LD, Qg, i0 - H1, Cfg::SR, N, tid);
@@ -519,13 +547,20 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
 #pragma unroll
   for (int j = 0; j < ONT; ++j) {
     const int col = nh * (D / 2) + j * 8 + (lane & 3) * 2;
-    if (j0 + r0 < N) {
-      *reinterpret_cast<float2*>(p.dK + (bh * N + j0 + r0) * D + col) = make_float2(accK[j][0] * p.scale, accK[j][1] * p.scale);
-      *reinterpret_cast<float2*>(p.dV + (bh * N + j0 + r0) * D + col) = make_float2(accV[j][0], accV[j][1]);
-    }
-    if (j0 + r1 < N) {
-      *reinterpret_cast<float2*>(p.dK + (bh * N + j0 + r1) * D + col) = make_float2(accK[j][2] * p.scale, accK[j][3] * p.scale);
-      *reinterpret_cast<float2*>(p.dV + (bh * N + j0 + r1) * D + col) = make_float2(accV[j][2], accV[j][3]);
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = hh ? r1 : r0;
+      if (j0 + r < N) {
+        float2* ok_ = reinterpret_cast<float2*>(p.dK + (bh * N + j0 + r) * D + col);
+        float2* ov_ = reinterpret_cast<float2*>(p.dV + (bh * N + j0 + r) * D + col);
+        float2 vk = make_float2(accK[j][2 * hh] * p.scale, accK[j][2 * hh + 1] * p.scale);
+        float2 vv = make_float2(accV[j][2 * hh], accV[j][2 * hh + 1]);
+        if (p.accumulate) {
+          const float2 uk = *ok_, uv = *ov_;
+          vk.x += uk.x; vk.y += uk.y; vv.x += uv.x; vv.y += uv.y;
+        }
+        *ok_ = vk; *ov_ = vv;
+      }
     }
   }
 }

@@ -1,0 +1,744 @@
+// Stacked-GEMM conv-attention backward on tcgen05 / TMEM / TMA (entries off the causal band).
+//
+// With Kt_a[j] = scale * log2(e) * sum_b theta[a,b] k_{j+b-pad_k} (the forward's pre-pass) and
+// Q^(a)[i] = q_{i-(pad_q-a)}, every entry with query - key >= pad_q + pad_k satisfies
+//     C = sum_a Q^(a) Kt_a^T,   P = exp2(C - LSE*log2e),   dP = dO V^T,   dC = P * (dP - D)
+//     dQ[i'] = ln2 * sum_a sum_j dC[i' + pad_q - a, j] Kt_a[j]
+//     dKt_a  = dC^T Q^(a)  (gradient w.r.t. Kt_a / (scale*log2e) ... i.e. before the pre-pass scaling)     dV = P^T dO
+// and dK / dTheta follow from dKt_a by the adjoint of the pre-pass (dk_post_kernel).
+// The band entries are handled by the exact kernels (bwd_exact.cuh, kmode = kBandTiles), which
+// accumulate into the same outputs.
+//
+//   bwd_dq_tc_kernel   : CTA = NT query-row tiles, loops key blocks.  A tile computes dC for
+//                        128 rows but owns only the first 112 of them as dQ rows: dQ row i'
+//                        needs dC rows i'..i'+pad_q, so consecutive tiles overlap by 16 rows
+//                        (recomputed, like the halo of the exact kernels) and no dQ row is
+//                        ever shared between CTAs.  The row shift of dC is free: dC is staged
+//                        in shared memory in the no-swizzle K-major core-matrix layout whose
+//                        M stride is 16 bytes, exactly as Q is in the forward.
+//   bwd_dkdv_tc_kernel : CTA = 128 keys (= TMEM lanes), loops 64-row query blocks; transposed
+//                        scores S^T = Kt_a Q^(a)T so that P^T and dC^T land with keys on the
+//                        lanes and feed the dV / dKt MMAs straight from tensor memory.
+// Every mbarrier wait is bounded; no TMA multicast, no cluster, cta_group::1 only.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "fmta_params.h"
+#include "fmta_tc.cuh"
+#include "launch_util.cuh"
+
+namespace fmta {
+
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct BwdTcParams {
+  const float* LSE;   // [B,H,N] natural log
+  const float* Dvec;  // [B,H,N]
+  float* dQ;          // [B,H,N,D]   (dq kernel: overwritten)
+  float* dV;          // [B,H,N,D]   (dkdv kernel: overwritten)
+  float* dKt;         // [B,H,cq,N,D] (dkdv kernel: overwritten)
+  int* status;
+  int H, N, cq, ck, causal;
+};
+
+// ==========================================================================================
+// dQ
+// ==========================================================================================
+template <int D>
+struct DqCfg {
+  static_assert(D == 64, "the dQ tensor-core kernel is instantiated for d = 64");
+  static constexpr int BM = 128;               // dC rows per tile (= TMEM lanes)
+  static constexpr int OWN = 112;              // dQ rows a tile owns
+  static constexpr int BC = 64;                // keys per block
+  static constexpr int NT = 2;                 // row tiles per CTA
+  static constexpr int HALO = 16;
+  static constexpr int QR = HALO + OWN * (NT - 1) + BM;   // 256 rows of Q
+  static constexpr int DR = BM + 16;           // rows of a dC buffer (16 zero rows below)
+  static constexpr int TILE_BYTES = BC * 128;  // Kt / V ring tile: 64 keys x 64 elements
+  static constexpr int NSLOT = 14;             // two key blocks of (cq <= 6) Kt tiles + V
+  static constexpr int oQ = 0;                                  // [D/8][QR][16 B]
+  static constexpr int odO = oQ + QR * D * 2;                   // NT x [128 rows][128 B], 128B swizzle
+  static constexpr int odC = odO + NT * BM * 128;               // NT x [BC/8][DR][16 B]
+  static constexpr int oRing = ((odC + NT * (BC / 8) * DR * 16 + 1023) / 1024) * 1024;
+  static constexpr int oBar = oRing + NSLOT * TILE_BYTES;
+  static constexpr int kSmemBytes = oBar + 512 + 1024;
+  static constexpr int kTmemCols = 512;        // per tile t: S at 192t, dP at 192t+64, dQ at 192t+128
+  static constexpr int kThreads = (NT * 4 + 1 + NT) * 32;
+};
+
+template <int D>
+__global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
+bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                 const __grid_constant__ CUtensorMap tmKt, const __grid_constant__ CUtensorMap tmV,
+                 const BwdTcParams p) {
+  using Cfg = DqCfg<D>;
+  constexpr int BM = Cfg::BM, OWN = Cfg::OWN, BC = Cfg::BC, NT = Cfg::NT, HALO = Cfg::HALO, QR = Cfg::QR;
+  constexpr int DR = Cfg::DR, NSLOT = Cfg::NSLOT;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sQ = smem + Cfg::oQ;
+  unsigned char* sdO = smem + Cfg::odO;
+  unsigned char* sdC = smem + Cfg::odC;
+  unsigned char* sRing = smem + Cfg::oRing;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::oBar);
+  uint64_t* full = bars;                 // [NSLOT]
+  uint64_t* empty = bars + NSLOT;        // [NSLOT]  count NT
+  uint64_t* q_full = bars + 2 * NSLOT;   // Q and dO staged
+  uint64_t* sdp_full = q_full + 1;       // [NT] S and dP of the block complete
+  uint64_t* s_free = sdp_full + 2;       // [NT] S and dP taken into registers (128 arrivals)
+  uint64_t* dc_full = s_free + 2;        // [NT] dC tile written to shared memory (128 arrivals)
+  uint64_t* dq_done = dc_full + 2;       // [NT] dQ MMAs of the block complete (dC buffer reusable)
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(dq_done + 2);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
+  const int band = pq + pk;
+  const int rows_per_cta = OWN * NT;
+  const int nQB = (N + rows_per_cta - 1) / rows_per_cta;
+  const int qb = nQB - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int bh = b * p.H + h;
+  const int R0 = qb * rows_per_cta;
+  const int nKB = (N + BC - 1) / BC;
+  int nkb_t[2] = {0, 0};
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    const int r0 = R0 + t * OWN;
+    if (r0 >= N) nkb_t[t] = 0;
+    else if (p.causal) {
+      const int last = min(N - 1, r0 + BM - 1) - band;
+      nkb_t[t] = last >= 0 ? min(nKB, last / BC + 1) : 0;
+    } else nkb_t[t] = nKB;
+  }
+  const int nkb = max(nkb_t[0], nkb_t[1]);
+
+  if (tid == 0) {
+    for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], NT); }
+    tc::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&sdp_full[i], 1); tc::mbar_init(&s_free[i], BM); tc::mbar_init(&dc_full[i], BM);
+      tc::mbar_init(&dq_done[i], 1);
+    }
+    *s_abort = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == NT * 4 + 1) {
+    tc::tmem_alloc(s_tmem, Cfg::kTmemCols);
+    tc::tmem_relinquish();
+  }
+  // zero the dC buffers once: the 16 pad rows below each tile are read by the shifted views
+  for (int i = tid; i < NT * (BC / 8) * DR * 4; i += Cfg::kThreads) reinterpret_cast<uint32_t*>(sdC)[i] = 0u;
+  tc::fence_proxy_async_smem();
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+
+  if (warp == NT * 4) {
+    // ===================== TMA producer =====================
+    if (lane == 0 && nkb > 0) {
+      tc::tma_prefetch_desc(&tmQ); tc::tma_prefetch_desc(&tmdO); tc::tma_prefetch_desc(&tmKt); tc::tma_prefetch_desc(&tmV);
+      tc::mbar_expect_tx(q_full, QR * D * 2 + NT * BM * 128);
+      for (int kc = 0; kc < D / 8; ++kc) {
+        tc::tma_load_3d(sQ + kc * (QR * 16), &tmQ, q_full, kc * 8, R0 - HALO, bh);
+        tc::tma_load_3d(sQ + kc * (QR * 16) + (QR / 2) * 16, &tmQ, q_full, kc * 8, R0 - HALO + QR / 2, bh);
+      }
+      for (int t = 0; t < NT; ++t) tc::tma_load_3d(sdO + t * (BM * 128), &tmdO, q_full, 0, R0 + t * OWN, bh);
+      int id = 0;
+      bool ok = true;
+      auto put = [&](const CUtensorMap* map, int y, int z) {
+        const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
+        if (!tc::mbar_wait(&empty[slot], ph ^ 1, s_abort)) { ok = false; return; }
+        tc::mbar_expect_tx(&full[slot], Cfg::TILE_BYTES);
+        tc::tma_load_3d(sRing + slot * Cfg::TILE_BYTES, map, &full[slot], 0, y, z);
+        ++id;
+      };
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        for (int a = 0; a < cq && ok; ++a) put(&tmKt, kb * BC, bh * cq + a);
+        if (ok) put(&tmV, kb * BC, bh);
+      }
+    }
+  } else if (warp > NT * 4) {
+    // ===================== MMA issuers: one per row tile =====================
+    const int t = warp - (NT * 4 + 1);
+    if (lane == 0 && nkb > 0) {
+      constexpr uint32_t idescS = tc::make_idesc(BM, BC, 0, 0);    // S, dP: 128 x 64, both K-major
+      constexpr uint32_t idescQ = tc::make_idesc(BM, D, 0, 1);     // dQ: 128 x D, B (Kt) MN-major
+      const uint64_t dQa = tc::make_sdesc(smem_u32(sQ) + (HALO + t * OWN - pq) * 16, QR * 16, 128, tc::kLayoutNone);
+      const uint64_t dOa = tc::make_sdesc(smem_u32(sdO) + t * (BM * 128), 16, 1024, tc::kLayoutSW128);
+      const uint64_t dCa = tc::make_sdesc(smem_u32(sdC) + t * ((BC / 8) * DR * 16), DR * 16, 128, tc::kLayoutNone);
+      const uint64_t dKb = tc::make_sdesc(smem_u32(sRing), 16, 1024, tc::kLayoutSW128);
+      const uint32_t q_hi = (uint32_t)(dQa >> 32), q_lo = (uint32_t)dQa;
+      const uint32_t o_hi = (uint32_t)(dOa >> 32), o_lo = (uint32_t)dOa;
+      const uint32_t c_hi = (uint32_t)(dCa >> 32), c_lo = (uint32_t)dCa;
+      const uint32_t k_hi = (uint32_t)(dKb >> 32), k_lo0 = (uint32_t)dKb;
+      const uint32_t tS = tmem + t * 192, tP = tS + 64, tQ = tS + 128;
+      const int my_nkb = nkb_t[t];
+      const int per = cq + 1;                                // ring tiles per key block
+      bool ok = tc::mbar_wait(q_full, 0, s_abort);
+      auto issue_SdP = [&](int kb) {
+        const bool active = kb < my_nkb;
+        if (active && kb > 0) {
+          ok = tc::mbar_wait(&s_free[t], (kb - 1) & 1, s_abort);
+          tc::tc_fence_after();
+        }
+        for (int a = 0; a < cq && ok; ++a) {
+          const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
+          if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
+          if (active) {
+            tc::tc_fence_after();
+            const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
+            const uint32_t a_lo = q_lo + (uint32_t)a;
+            if (a == 0) tc::mma_ss2<0>(tS, a_lo, q_hi, b_lo, k_hi, idescS);
+            else tc::mma_ss2<1>(tS, a_lo, q_hi, b_lo, k_hi, idescS);
+#pragma unroll
+            for (int k = 1; k < D / 16; ++k)
+              tc::mma_ss2<1>(tS, a_lo + (uint32_t)(2 * k * QR), q_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
+          }
+          // the Kt tile stays in shared memory: it is the B operand of dQ(kb) as well
+        }
+        if (!ok) return;
+        {
+          const int id = kb * per + cq, slot = id % NSLOT, ph = (id / NSLOT) & 1;
+          if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
+          if (active) {
+            tc::tc_fence_after();
+            const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
+            tc::mma_ss2<0>(tP, o_lo, o_hi, b_lo, k_hi, idescS);
+#pragma unroll
+            for (int k = 1; k < D / 16; ++k)
+              tc::mma_ss2<1>(tP, o_lo + (uint32_t)(2 * k), o_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
+          }
+          tc::mma_commit(&empty[slot]);
+          if (active) tc::mma_commit(&sdp_full[t]);
+        }
+      };
+      auto issue_dQ = [&](int kb) {
+        const bool active = kb < my_nkb;
+        if (active) {
+          ok = tc::mbar_wait(&dc_full[t], kb & 1, s_abort);
+          tc::tc_fence_after();
+        }
+        for (int a = 0; a < cq && ok; ++a) {
+          const int id = kb * per + a, slot = id % NSLOT;
+          if (active) {
+            const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
+            const uint32_t a_lo = c_lo + (uint32_t)(pq - a);       // dC rows i' + pad_q - a
+            if (kb == 0 && a == 0) tc::mma_ss2<0>(tQ, a_lo, c_hi, b_lo, k_hi, idescQ);
+            else tc::mma_ss2<1>(tQ, a_lo, c_hi, b_lo, k_hi, idescQ);
+#pragma unroll
+            for (int k = 1; k < BC / 16; ++k)
+              tc::mma_ss2<1>(tQ, a_lo + (uint32_t)(2 * k * DR), c_hi, b_lo + (uint32_t)(k * (2048 / 16)), k_hi, idescQ);
+          }
+          tc::mma_commit(&empty[slot]);
+        }
+        if (ok && active) tc::mma_commit(&dq_done[t]);
+      };
+      if (ok) issue_SdP(0);
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        if (kb + 1 < nkb) issue_SdP(kb + 1);
+        if (ok) issue_dQ(kb);
+      }
+    }
+  } else {
+    // ===================== element-wise warpgroups: one dC row per thread =====================
+    const int t = warp >> 2;
+    const int m = tid & (BM - 1);
+    const int gi = R0 + t * OWN + m;                    // query index of this dC row
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + t * 192 + lane_base, tP = tS + 64, tQ = tS + 128;
+    const int my_nkb = nkb_t[t];
+    const bool row_ok = gi < N;
+    const float lse2 = row_ok ? p.LSE[(size_t)bh * N + gi] * kLog2e : 0.f;
+    const float dvec = row_ok ? p.Dvec[(size_t)bh * N + gi] : 0.f;
+    unsigned char* cbuf = sdC + t * ((BC / 8) * DR * 16) + m * 16;
+    bool ok = true;
+    for (int kb = 0; kb < my_nkb && ok; ++kb) {
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(&sdp_full[t], kb & 1, s_abort));
+      if (!ok) break;
+      tc::tc_fence_after();
+      float s[BC], dp[BC];
+      {
+        float t0[32], t1[32], t2[32], t3[32];
+        tc::tmem_ld32_nowait(tS, t0); tc::tmem_ld32_nowait(tS + 32, t1);
+        tc::tmem_ld32_nowait(tP, t2); tc::tmem_ld32_nowait(tP + 32, t3);
+        tc::tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; dp[i] = t2[i]; dp[32 + i] = t3[i]; }
+      }
+      tc::tc_fence_before();
+      tc::mbar_arrive(&s_free[t]);
+      const int j0 = kb * BC;
+      const int jlim = row_ok ? (p.causal ? min(N - 1, gi - band) : N - 1) : -1;   // last key owned here
+      uint32_t pk32[BC / 2];
+#pragma unroll
+      for (int i = 0; i < BC; i += 2) {
+        float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
+        float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
+        if (j0 + i > jlim) c0 = 0.f;
+        if (j0 + i + 1 > jlim) c1 = 0.f;
+        pk32[i / 2] = pack_bf16(c0, c1);
+      }
+      if (kb > 0) {   // dQ(kb-1) has finished reading the dC buffer
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (kb - 1) & 1, s_abort));
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int kc = 0; kc < BC / 8; ++kc)
+        *reinterpret_cast<uint4*>(cbuf + kc * (DR * 16)) = make_uint4(pk32[4 * kc], pk32[4 * kc + 1], pk32[4 * kc + 2], pk32[4 * kc + 3]);
+      tc::fence_proxy_async_smem();
+      tc::mbar_arrive(&dc_full[t]);
+    }
+    // ---- epilogue: the 112 owned dQ rows of this tile ----
+    if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (my_nkb - 1) & 1, s_abort));
+    tc::tc_fence_after();
+    const bool have = (my_nkb > 0) && ok;
+    const bool store = row_ok && (m < OWN);
+    float* orow = p.dQ + ((size_t)bh * N + (row_ok ? gi : 0)) * D;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      float o[32];
+      if (have) {
+        tc::tmem_ld32(tQ + c * 32, o);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0.f;
+      }
+      if (store) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(orow + c * 32 + i) = make_float4(o[i] * kLn2, o[i + 1] * kLn2, o[i + 2] * kLn2, o[i + 3] * kLn2);
+      }
+    }
+  }
+  __syncwarp();
+
+  tc::tc_fence_before();
+  __syncthreads();
+  if (*s_abort && tid == 0) atomicExch(p.status, 1);
+  if (warp == NT * 4 + 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem, Cfg::kTmemCols);
+  }
+}
+
+// ==========================================================================================
+// dK-tilde / dV
+// ==========================================================================================
+template <int D>
+struct DkvCfg {
+  static_assert(D == 64, "the dK/dV tensor-core kernel is instantiated for d = 64");
+  static constexpr int BK = 128;               // keys per CTA (= TMEM lanes)
+  static constexpr int BR = 64;                // query rows per block
+  static constexpr int HALO = 16;
+  static constexpr int QR = BR + HALO;         // 80 rows of Q per stage
+  static constexpr int MAXCQ = 6;              // dV + 6 dKt accumulators of 64 columns + 64 scratch = 512
+  static constexpr int NSTG = 3;
+  static constexpr int KT_BYTES = BK * 128;    // one resident Kt / V tile
+  static constexpr int oKt = 0;                                   // MAXCQ x [128 keys][128 B], 128B swizzle
+  static constexpr int oV = oKt + MAXCQ * KT_BYTES;
+  static constexpr int oStage = oV + KT_BYTES;
+  static constexpr int sgdO = 0;                                  // [64 rows][128 B], 128B swizzle
+  static constexpr int sgQ = BR * 128;                            // [D/8][QR][16 B]
+  static constexpr int sgLD = sgQ + QR * D * 2;                   // LSE*log2e [64], D [64]
+  static constexpr int STAGE_BYTES = ((sgLD + 2 * BR * 4 + 1023) / 1024) * 1024;
+  static constexpr int oBar = oStage + NSTG * STAGE_BYTES;
+  static constexpr int kSmemBytes = oBar + 512 + 1024;
+  static constexpr int kTmemCols = 512;        // dV at 0, dKt_a at 64*(1+a), scratch X at 448
+  static constexpr int colX = 448;
+  static constexpr int kEwWarps = 8;
+  static constexpr int kThreads = (kEwWarps + 2) * 32;
+};
+
+template <int D>
+__global__ void __launch_bounds__(DkvCfg<D>::kThreads, 1)
+bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmKt, const __grid_constant__ CUtensorMap tmV,
+                   const BwdTcParams p) {
+  using Cfg = DkvCfg<D>;
+  constexpr int BK = Cfg::BK, BR = Cfg::BR, HALO = Cfg::HALO, QR = Cfg::QR, NSTG = Cfg::NSTG;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sKt = smem + Cfg::oKt;
+  unsigned char* sV = smem + Cfg::oV;
+  unsigned char* sStage = smem + Cfg::oStage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::oBar);
+  uint64_t* full = bars;                 // [NSTG]
+  uint64_t* empty = bars + NSTG;         // [NSTG]
+  uint64_t* kv_full = bars + 2 * NSTG;
+  uint64_t* st_full = kv_full + 1;       // S^T in X
+  uint64_t* x_free = st_full + 1;        // S^T taken into registers (256 arrivals)
+  uint64_t* dpt_full = x_free + 1;       // dP^T in X
+  uint64_t* pdc_full = dpt_full + 1;     // P^T and dC^T (bf16) written to X (256 arrivals)
+  uint64_t* all_done = pdc_full + 1;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(all_done + 1);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
+  const int band = pq + pk;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int bh = b * p.H + h;
+  const int j0 = blockIdx.x * BK;        // early key tiles see the most query blocks: longest first
+  const int nQB = (N + BR - 1) / BR;
+  const int qb_begin = p.causal ? min(nQB, (j0 + band) / BR) : 0;
+  const int nblk = nQB - qb_begin;
+
+  if (tid == 0) {
+    for (int i = 0; i < NSTG; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
+    tc::mbar_init(kv_full, 1);
+    tc::mbar_init(st_full, 1); tc::mbar_init(x_free, Cfg::kEwWarps * 32);
+    tc::mbar_init(dpt_full, 1); tc::mbar_init(pdc_full, Cfg::kEwWarps * 32);
+    tc::mbar_init(all_done, 1);
+    *s_abort = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == Cfg::kEwWarps + 1) {
+    tc::tmem_alloc(s_tmem, Cfg::kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  const uint32_t tX = tmem + Cfg::colX;
+
+  if (warp == Cfg::kEwWarps) {
+    // ===================== producer warp (TMA + row statistics) =====================
+    if (nblk > 0) {
+      if (lane == 0) {
+        tc::tma_prefetch_desc(&tmQ); tc::tma_prefetch_desc(&tmdO); tc::tma_prefetch_desc(&tmKt); tc::tma_prefetch_desc(&tmV);
+        tc::mbar_expect_tx(kv_full, (cq + 1) * Cfg::KT_BYTES);
+        for (int a = 0; a < cq; ++a) tc::tma_load_3d(sKt + a * Cfg::KT_BYTES, &tmKt, kv_full, 0, j0, bh * cq + a);
+        tc::tma_load_3d(sV, &tmV, kv_full, 0, j0, bh);
+      }
+      bool ok = true;
+      for (int it = 0; it < nblk && ok; ++it) {
+        const int st = it % NSTG, ph = (it / NSTG) & 1;
+        const int i0 = (qb_begin + it) * BR;
+        unsigned char* sg = sStage + st * Cfg::STAGE_BYTES;
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(&empty[st], ph ^ 1, s_abort));
+        if (!ok) break;
+        // LSE * log2(e) and D of the 64 rows: two rows per lane, plain loads and stores
+        float* ld = reinterpret_cast<float*>(sg + Cfg::sgLD);
+#pragma unroll
+        for (int r = lane; r < BR; r += 32) {
+          const int gi = i0 + r;
+          ld[r] = gi < N ? p.LSE[(size_t)bh * N + gi] * kLog2e : 0.f;
+          ld[BR + r] = gi < N ? p.Dvec[(size_t)bh * N + gi] : 0.f;
+        }
+        __syncwarp();
+        if (lane == 0) {
+          tc::mbar_expect_tx(&full[st], BR * 128 + QR * D * 2);
+          tc::tma_load_3d(sg + Cfg::sgdO, &tmdO, &full[st], 0, i0, bh);
+          for (int kc = 0; kc < D / 8; ++kc)
+            tc::tma_load_3d(sg + Cfg::sgQ + kc * (QR * 16), &tmQ, &full[st], kc * 8, i0 - HALO, bh);
+        }
+      }
+    }
+  } else if (warp == Cfg::kEwWarps + 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idescT = tc::make_idesc(BK, BR, 0, 0);    // S^T, dP^T: 128 x 64, K-major operands
+      constexpr uint32_t idescA = tc::make_idesc(BK, D, 0, 1);     // dV, dKt: 128 x D, B MN-major
+      const uint64_t dKtA = tc::make_sdesc(smem_u32(sKt), 16, 1024, tc::kLayoutSW128);
+      const uint32_t kt_hi = (uint32_t)(dKtA >> 32), kt_lo = (uint32_t)dKtA;
+      const uint32_t v_lo = kt_lo + (uint32_t)((Cfg::oV - Cfg::oKt) >> 4);
+      bool ok = tc::mbar_wait(kv_full, 0, s_abort);
+      for (int it = 0; it < nblk && ok; ++it) {
+        const int st = it % NSTG, ph = (it / NSTG) & 1;
+        const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
+        // B operands of this stage
+        const uint64_t dQk = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);   // K-major, N = rows
+        const uint64_t dQm = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, 128, QR * 16, tc::kLayoutNone);   // MN-major, K = rows
+        const uint64_t dOk = tc::make_sdesc(sg + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
+        const uint32_t qk_hi = (uint32_t)(dQk >> 32), qk_lo = (uint32_t)dQk;
+        const uint32_t qm_hi = (uint32_t)(dQm >> 32), qm_lo = (uint32_t)dQm;
+        const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
+        if (!tc::mbar_wait(&full[st], ph, s_abort)) { ok = false; break; }
+        tc::tc_fence_after();
+        // S^T = sum_a Kt_a Q^(a)T   (X is free: the MMAs that read it were issued earlier)
+        for (int a = 0; a < cq; ++a) {
+          const uint32_t a_lo = kt_lo + (uint32_t)(a * (Cfg::KT_BYTES >> 4));
+          const uint32_t b_lo = qk_lo + (uint32_t)a;
+          if (a == 0) tc::mma_ss2<0>(tX, a_lo, kt_hi, b_lo, qk_hi, idescT);
+          else tc::mma_ss2<1>(tX, a_lo, kt_hi, b_lo, qk_hi, idescT);
+#pragma unroll
+          for (int k = 1; k < D / 16; ++k)
+            tc::mma_ss2<1>(tX, a_lo + (uint32_t)(2 * k), kt_hi, b_lo + (uint32_t)(2 * k * QR), qk_hi, idescT);
+        }
+        tc::mma_commit(st_full);
+        if (!tc::mbar_wait(x_free, it & 1, s_abort)) { ok = false; break; }
+        tc::tc_fence_after();
+        // dP^T = V dO^T
+        tc::mma_ss2<0>(tX, v_lo, kt_hi, o_lo, o_hi, idescT);
+#pragma unroll
+        for (int k = 1; k < D / 16; ++k)
+          tc::mma_ss2<1>(tX, v_lo + (uint32_t)(2 * k), kt_hi, o_lo + (uint32_t)(2 * k), o_hi, idescT);
+        tc::mma_commit(dpt_full);
+        if (!tc::mbar_wait(pdc_full, it & 1, s_abort)) { ok = false; break; }
+        tc::tc_fence_after();
+        // dV += P^T dO ;  dKt_a += dC^T Q^(a)   (A from tensor memory: 8 columns per 16 rows)
+#pragma unroll
+        for (int k = 0; k < BR / 16; ++k) {
+          if (it == 0 && k == 0) tc::mma_ts2<0>(tmem, tX, o_lo, o_hi, idescA);
+          else tc::mma_ts2<1>(tmem, tX + 8 * k, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
+        }
+        for (int a = 0; a < cq; ++a) {
+          const uint32_t dacc = tmem + 64 * (1 + a);
+          const uint32_t b_lo = qm_lo + (uint32_t)a;
+#pragma unroll
+          for (int k = 0; k < BR / 16; ++k) {
+            if (it == 0 && k == 0) tc::mma_ts2<0>(dacc, tX + 32, b_lo, qm_hi, idescA);
+            else tc::mma_ts2<1>(dacc, tX + 32 + 8 * k, b_lo + (uint32_t)(k * 16), qm_hi, idescA);
+          }
+        }
+        tc::mma_commit(&empty[st]);
+      }
+      if (ok) tc::mma_commit(all_done);
+    }
+  } else {
+    // ===================== element-wise warps: key = lane, 32 query rows per thread =====================
+    const int qtr = warp & 3, hh = warp >> 2;
+    const int key = j0 + qtr * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
+    const uint32_t tXl = tX + lane_base;
+    bool ok = true;
+    if (nblk > 0) ok = __all_sync(0xffffffffu, tc::mbar_wait(kv_full, 0, s_abort));   // (orders nothing; keeps phases simple)
+    for (int it = 0; it < nblk && ok; ++it) {
+      const int st = it % NSTG, ph = (it / NSTG) & 1;
+      const int i0 = (qb_begin + it) * BR;
+      const float* ld = reinterpret_cast<const float*>(sStage + st * Cfg::STAGE_BYTES + Cfg::sgLD);
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(&full[st], ph, s_abort));
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(st_full, it & 1, s_abort));
+      if (!ok) break;
+      tc::tc_fence_after();
+      float s[32];
+      tc::tmem_ld32(tXl + 32 * hh, s);
+      tc::tc_fence_before();
+      tc::mbar_arrive(x_free);
+      // P^T[key, i] = exp2(S^T - LSE_i), kept only where this kernel owns the entry
+      float pv[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int gi = i0 + 32 * hh + c;
+        const bool own = (key < N) && (gi < N) && (!p.causal || key <= gi - band);
+        pv[c] = own ? exp2f(s[c] - ld[32 * hh + c]) : 0.f;
+      }
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, it & 1, s_abort));
+      if (!ok) break;
+      tc::tc_fence_after();
+      tc::tmem_ld32(tXl + 32 * hh, s);                  // dP^T
+      uint32_t pp[16], cc[16];
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
+        const float d0 = pv[c] * (s[c] - ld[BR + 32 * hh + c]);
+        const float d1 = pv[c + 1] * (s[c + 1] - ld[BR + 32 * hh + c + 1]);
+        pp[c / 2] = pack_bf16(pv[c], pv[c + 1]);
+        cc[c / 2] = pack_bf16(d0, d1);
+      }
+      // both column halves of these lanes must have read dP^T before X is overwritten
+      tc::tc_fence_before();
+      tc::named_bar_sync(1 + qtr, 64);
+      tc::tc_fence_after();
+      tc::tmem_st16u(tXl + 16 * hh, pp);                // P^T : X columns [0,32)
+      tc::tmem_st16u(tXl + 32 + 16 * hh, cc);           // dC^T: X columns [32,64)
+      tc::tmem_wait_st();
+      tc::tc_fence_before();
+      tc::mbar_arrive(pdc_full);
+    }
+    // ---- epilogue: dV and dKt_a rows of this key ----
+    if (nblk > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(all_done, 0, s_abort));
+    tc::tc_fence_after();
+    const bool have = (nblk > 0) && ok;
+    const bool store = key < N;
+    const size_t krow = (size_t)(store ? key : 0);
+    for (int ch = 7 * hh; ch < 7 * hh + 7; ++ch) {      // 14 chunks of 32 columns over the two halves
+      const int acc = ch >> 1, half = ch & 1;
+      if (acc > cq) break;
+      float o[32];
+      if (have) {
+        tc::tmem_ld32(tmem + lane_base + ch * 32, o);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0.f;
+      }
+      if (store) {
+        float* dst;
+        float f;
+        if (acc == 0) { dst = p.dV + ((size_t)bh * N + krow) * D + half * 32; f = 1.f; }
+        else { dst = p.dKt + (((size_t)bh * cq + (acc - 1)) * N + krow) * D + half * 32; f = 1.f; }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i] * f, o[i + 1] * f, o[i + 2] * f, o[i + 3] * f);
+      }
+    }
+  }
+  __syncwarp();
+
+  tc::tc_fence_before();
+  __syncthreads();
+  if (*s_abort && tid == 0) atomicExch(p.status, 1);
+  if (warp == Cfg::kEwWarps + 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Adjoint of the Kt pre-pass:   dK[j] = sum_{a,b} scale*theta[a,b] * dKt_a[j - b + pad_k]
+//                      dTheta[a,b]   += scale * sum_j <dKt_a[j], k_{j+b-pad_k}>
+// One CTA per (32 keys, batch*head); dTheta leaves as one partial per CTA.
+template <int D>
+__global__ void __launch_bounds__(256) dk_post_kernel(const float* __restrict__ dKt, const bf16* __restrict__ K,
+                                                      const float* __restrict__ theta, float* __restrict__ dK,
+                                                      float* __restrict__ dTheta_part, int H, int N, int cq, int ck,
+                                                      float scale, int n_jblocks) {
+  constexpr int CPR = D / 8, RPB = 256 / CPR;
+  __shared__ float sTh[6 * 20];
+  __shared__ float sRed[8][6 * 17];
+  const int bh = blockIdx.y, h = bh % H, b = bh / H;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < cq * ck; i += 256) sTh[(i / ck) * 20 + (i % ck)] = theta[(size_t)h * cq * ck + i] * scale;
+  __syncthreads();
+  const int j = blockIdx.x * RPB + tid / CPR, c = tid % CPR;
+  const int pk = (ck - 1) / 2;
+  const bool valid = j < N;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int a = 0; a < cq; ++a) {
+    const float* base = dKt + (((size_t)bh * cq + a) * N) * D + c * 8;
+    float own[8];   // dKt_a[j] chunk, for the dTheta term
+#pragma unroll
+    for (int e = 0; e < 8; ++e) own[e] = 0.f;
+    if (valid) {
+      const float4 u0 = *reinterpret_cast<const float4*>(base + (size_t)j * D), u1 = *reinterpret_cast<const float4*>(base + (size_t)j * D + 4);
+      own[0] = u0.x; own[1] = u0.y; own[2] = u0.z; own[3] = u0.w; own[4] = u1.x; own[5] = u1.y; own[6] = u1.z; own[7] = u1.w;
+    }
+    for (int bb = 0; bb < ck; ++bb) {
+      // dK: source row j - bb + pk
+      const int js = j - bb + pk;
+      if (valid && js >= 0 && js < N) {
+        const float w = sTh[a * 20 + bb];
+        const float4 u0 = *reinterpret_cast<const float4*>(base + (size_t)js * D), u1 = *reinterpret_cast<const float4*>(base + (size_t)js * D + 4);
+        acc[0] = fmaf(w, u0.x, acc[0]); acc[1] = fmaf(w, u0.y, acc[1]); acc[2] = fmaf(w, u0.z, acc[2]); acc[3] = fmaf(w, u0.w, acc[3]);
+        acc[4] = fmaf(w, u1.x, acc[4]); acc[5] = fmaf(w, u1.y, acc[5]); acc[6] = fmaf(w, u1.z, acc[6]); acc[7] = fmaf(w, u1.w, acc[7]);
+      }
+      // dTheta[a,bb]: <dKt_a[j], k_{j+bb-pk}>
+      float t = 0.f;
+      const int jk = j + bb - pk;
+      if (valid && jk >= 0 && jk < N) {
+        const uint4 kv = *reinterpret_cast<const uint4*>(K + ((size_t)bh * N + jk) * D + c * 8);
+        const uint32_t w32[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          t = fmaf(own[2 * e], __uint_as_float(w32[e] << 16), t);
+          t = fmaf(own[2 * e + 1], __uint_as_float(w32[e] & 0xffff0000u), t);
+        }
+      }
+      t = warp_sum(t);
+      if (lane == 0) sRed[warp][a * 17 + bb] = t;
+    }
+  }
+  if (valid) {
+    float* o = dK + ((size_t)bh * N + j) * D + c * 8;
+    *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+  __syncthreads();
+  const int slot = b * n_jblocks + blockIdx.x;
+  for (int i = tid; i < cq * ck; i += 256) {
+    const int a = i / ck, bb = i % ck;
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sRed[w][a * 17 + bb];
+    dTheta_part[((size_t)slot * H + h) * (cq * ck) + i] = t * scale;
+  }
+}
+
+// ==========================================================================================
+// host side
+// ==========================================================================================
+bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128);
+bool tensor_maps_available();
+cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream);
+
+bool bwd_tc_supported(const TrainParams& p) {
+  return p.theta != nullptr && p.Wmix == nullptr && p.d == 64 && p.cq >= 1 && p.cq <= 6 && tensor_maps_available();
+}
+
+size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq) {
+  const size_t rows = (size_t)B * H * N;
+  auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+  // Kt (bf16) + dKt (fp32) + status
+  return up(rows * cq * d * 2) + up(rows * cq * d * 4) + 2048;
+}
+
+cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t stream) {
+  constexpr int D = 64;
+  using Cfg = DqCfg<D>;
+  const size_t rows = (size_t)p.B * p.H * p.N, BH = (size_t)p.B * p.H;
+  auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+  unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
+  __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
+  w += up(rows * p.cq * D * 4);
+  int* status = reinterpret_cast<int*>(w);
+  cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return e;
+  e = launch_ktilde(p, Kt, stream);
+  if (e != cudaSuccess) return e;
+  alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV;
+  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR / 2, false)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmdO, p.dO, D, p.N, BH, 64, Cfg::BM, true)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmV, p.V, D, p.N, BH, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
+  BwdTcParams bp = {};
+  bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dQ = p.dQ; bp.status = status;
+  bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
+  auto kern = bwd_dq_tc_kernel<D>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int rows_per_cta = Cfg::OWN * Cfg::NT;
+  dim3 grid((p.N + rows_per_cta - 1) / rows_per_cta, p.H, p.B);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
+  return cudaGetLastError();
+}
+
+
+cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream) {
+  constexpr int D = 64;
+  using Cfg = DkvCfg<D>;
+  const size_t rows = (size_t)p.B * p.H * p.N, BH = (size_t)p.B * p.H;
+  auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+  unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
+  __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
+  float* dKt = reinterpret_cast<float*>(w); w += up(rows * p.cq * D * 4);
+  int* status = reinterpret_cast<int*>(w);
+  alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV;
+  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR, false)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmdO, p.dO, D, p.N, BH, 64, Cfg::BR, true)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmV, p.V, D, p.N, BH, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
+  BwdTcParams bp = {};
+  bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dV = p.dV; bp.dKt = dKt; bp.status = status;
+  bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
+  auto kern = bwd_dkdv_tc_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  dim3 grid((p.N + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  constexpr int RPB = 256 / (D / 8);
+  const int njb = (p.N + RPB - 1) / RPB;
+  dim3 g2(njb, (unsigned)BH);
+  dk_post_kernel<D><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.ck, p.scale, njb);
+  return cudaGetLastError();
+}
+
+// slots of dTheta partials written by dk_post_kernel
+int bwd_tc_theta_slots(int B, int N) { return B * ((N + 31) / 32); }
+
+}  // namespace fmta

@@ -11,6 +11,7 @@ using namespace fmta;
 namespace {
 
 thread_local int g_last_cuda_error = 0;
+int g_path = -1;   // process-wide default: -1 auto, 0 exact kernels only, 1 tensor-core kernels + exact band
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -57,6 +58,12 @@ const char* fmta_strerror(int status) {
 
 int fmta_last_cuda_error(void) { return g_last_cuda_error; }
 
+int fmta_set_path(int path) {
+  const int old = g_path;
+  if (path >= -1 && path <= 2) g_path = path;
+  return old;
+}
+
 size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, int G) {
   (void)d;
   if (op == FMTA_OP_BWD_DQ) {
@@ -64,6 +71,13 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
     size_t n = slots * H * (size_t)(cq * ck);
     if (G > 1) n += slots * (size_t)(H / G) * G * G;
     return n * sizeof(float);
+  }
+  if (op == FMTA_OP_BWD_TC) {
+    // dTheta partials of the exact band kernel and of the tensor-core post-pass (one contiguous
+    // slot array, rounded up), followed by the tensor-core backward's buffers
+    const size_t slots = (size_t)B * ((N + 63) / 64) + (size_t)bwd_tc_theta_slots(B, N);
+    const size_t part = (slots * H * (size_t)(cq * ck) * sizeof(float) + 1023) / 1024 * 1024;
+    return part + bwd_tc_workspace_bytes(B, H, N, d, cq);
   }
   if (op == FMTA_OP_FWD_TC) {
     // the stacked key operand (c_q bf16 copies of K) + un-normalised partial O (fp32), M, L
@@ -170,6 +184,59 @@ int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, c
   if (!aligned16(dK) || !aligned16(dV)) return FMTA_ERR_ALIGN;
   p.dK = dK; p.dV = dV;
   return check_cuda(launch_bwd_dkdv(p, (cudaStream_t)stream));
+}
+
+int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+             const float* LSE, const float* theta, const float* wmix, float* dQ, float* dK, float* dV,
+             float* dTheta, float* dW, int B, int H, int N, int d, int cq, int ck, int G, float scale,
+             int causal, int path, void* workspace, size_t workspace_bytes, void* stream) {
+  TrainParams p = {};
+  if (int s = fill_bwd(p, Q, K, V, dO, D, LSE, theta, wmix, B, H, N, d, cq, ck, G, scale, causal)) return s;
+  if (!dQ || !dK || !dV) return FMTA_ERR_NULL;
+  if (!aligned16(dQ) || !aligned16(dK) || !aligned16(dV)) return FMTA_ERR_ALIGN;
+  if ((theta && !dTheta) || (wmix && !dW)) return FMTA_ERR_NULL;
+  if (path != 0 && path != 1 && path != -1) return FMTA_ERR_SHAPE;
+  if (path == -1) path = g_path;
+  cudaStream_t st = (cudaStream_t)stream;
+  bool use_tc = (path != 0) && bwd_tc_supported(p);
+  if (path == 1 && !use_tc) return FMTA_ERR_UNSUPPORTED;
+  const size_t need_tc = fmta_workspace_bytes(FMTA_OP_BWD_TC, B, H, N, d, p.cq, p.ck, p.G);
+  if (use_tc && (!workspace || workspace_bytes < need_tc)) {
+    if (path == 1) return FMTA_ERR_WORKSPACE;
+    use_tc = false;
+  }
+  p.dQ = dQ; p.dK = dK; p.dV = dV;
+  const int slots_ex = B * ((N + 63) / 64);
+  const size_t n_theta = (size_t)H * p.cq * p.ck;
+  if (!use_tc) {
+    const size_t need = fmta_workspace_bytes(FMTA_OP_BWD_DQ, B, H, N, d, p.cq, p.ck, p.G);
+    const bool want_part = (theta != nullptr) || (wmix != nullptr);
+    if (want_part && (!workspace || workspace_bytes < need)) return FMTA_ERR_WORKSPACE;
+    p.n_slots = slots_ex;
+    p.dTheta_part = theta ? reinterpret_cast<float*>(workspace) : nullptr;
+    p.dW_part = wmix ? reinterpret_cast<float*>(workspace) + (theta ? (size_t)slots_ex * n_theta : 0) : nullptr;
+    if (int s = check_cuda(launch_bwd_dq(p, st))) return s;
+    if (int s = check_cuda(launch_bwd_dkdv(p, st))) return s;
+    if (theta)
+      if (int s = check_cuda(launch_reduce_partials(p.dTheta_part, dTheta, slots_ex, (int)n_theta, st))) return s;
+    if (wmix)
+      if (int s = check_cuda(launch_reduce_partials(p.dW_part, dW, slots_ex, H * G, st))) return s;
+    return FMTA_OK;
+  }
+  // tensor-core kernels for the entries off the causal band, exact kernels (accumulating) on it
+  const int slots_tc = bwd_tc_theta_slots(B, N);
+  float* part = reinterpret_cast<float*>(workspace);
+  const size_t part_bytes = ((size_t)(slots_ex + slots_tc) * n_theta * sizeof(float) + 1023) / 1024 * 1024;
+  void* tcw = reinterpret_cast<unsigned char*>(workspace) + part_bytes;
+  if (int s = check_cuda(launch_bwd_dq_tc(p, tcw, st))) return s;
+  if (int s = check_cuda(launch_bwd_dkdv_tc(p, tcw, part + (size_t)slots_ex * n_theta, st))) return s;
+  p.kmode = kBandTiles;
+  p.accumulate = 1;
+  p.n_slots = slots_ex;
+  p.dTheta_part = part;
+  if (int s = check_cuda(launch_bwd_dq(p, st))) return s;
+  if (int s = check_cuda(launch_bwd_dkdv(p, st))) return s;
+  return check_cuda(launch_reduce_partials(part, dTheta, slots_ex + slots_tc, (int)n_theta, st));
 }
 
 int fmta_decode(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,

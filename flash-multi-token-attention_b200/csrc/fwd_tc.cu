@@ -469,7 +469,11 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // bf16 tensor viewed as [outer][rows][D] (D contiguous); box = {box_x, box_rows, 1}
-bool make_map(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128) {
+}  // namespace
+
+bool tensor_maps_available() { return get_encode_fn() != nullptr; }
+
+bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)outer};
@@ -481,22 +485,36 @@ bool make_map(CUtensorMap* map, const void* base, int D, int rows, size_t outer,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Pre-pass: Kt = scale * log2(e) * (theta applied along the key axis of K), c_q bf16 copies.
+cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream) {
+  const size_t BH = (size_t)p.B * p.H;
+  if (p.d == 64) {
+    constexpr int RPB = 256 / (64 / 8);
+    dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH);
+    ktilde_kernel<64><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale * kLog2e);
+  } else {
+    constexpr int RPB = 256 / (128 / 8);
+    dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH);
+    ktilde_kernel<128><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale * kLog2e);
+  }
+  return cudaGetLastError();
+}
+
+namespace {
+
 template <int D>
 cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpart, float* Lpart, int* status,
                         cudaStream_t stream) {
   using Cfg = TcCfg<D>;
   const size_t BH = (size_t)p.B * p.H;
   {
-    constexpr int RPB = 256 / (D / 8);
-    dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH);
-    ktilde_kernel<D><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale * kLog2e);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_ktilde(p, Kt, stream);
     if (e != cudaSuccess) return e;
   }
   alignas(64) CUtensorMap tmQ, tmKt, tmV;
-  if (!make_map(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QBOX, false)) return cudaErrorInvalidValue;
-  if (!make_map(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
-  if (!make_map(&tmV, p.V, D, p.N, BH, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QBOX, false)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmV, p.V, D, p.N, BH, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
   TcParams tp;
   tp.Opart = Opart; tp.Mpart = Mpart; tp.Lpart = Lpart; tp.status = status;
   tp.H = p.H; tp.N = p.N; tp.cq = p.cq; tp.ck = p.ck; tp.causal = p.causal;

@@ -61,6 +61,11 @@ cudaError_t launch_rowdot(const void* dO, const void* O, int o_bf16, float* Dv, 
 cudaError_t launch_decode(const DecodeParams& p, cudaStream_t stream);
 bool fwd_tc_supported(const TrainParams& p);
 size_t fwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
+bool bwd_tc_supported(const TrainParams& p);
+size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
+cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t stream);
+cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream);
+int bwd_tc_theta_slots(int B, int N);
 cudaError_t launch_fwd_tc(const TrainParams& p, void* workspace, const float** Opart, const float** Mpart,
                           const float** Lpart, cudaStream_t stream);
 

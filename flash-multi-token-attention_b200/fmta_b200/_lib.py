@@ -15,6 +15,7 @@ FMTA_DTYPE_F32 = 0
 FMTA_DTYPE_BF16 = 1
 FMTA_OP_BWD_DQ = 1
 FMTA_OP_FWD_TC = 2
+FMTA_OP_BWD_TC = 3
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -42,6 +43,11 @@ lib.fmta_bwd_dq_dw.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp,
 lib.fmta_bwd_dq_dw_static.restype = _i
 lib.fmta_bwd_dq_dw_static.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i,
                                       _i, _f, _i, _vp]
+lib.fmta_bwd.restype = _i
+lib.fmta_bwd.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _f,
+                         _i, _i, _vp, _sz, _vp]
+lib.fmta_set_path.restype = _i
+lib.fmta_set_path.argtypes = [_i]
 lib.fmta_bwd_dkdv.restype = _i
 lib.fmta_bwd_dkdv.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _f, _i,
                               _vp]
@@ -49,7 +55,7 @@ lib.fmta_decode.restype = _i
 lib.fmta_decode.argtypes = [_vp, _vp, _vp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
 
 EXPORTS = ["fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
-           "fmta_bwd_prep_D", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode"]
+           "fmta_bwd_prep_D", "fmta_bwd", "fmta_set_path", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode"]
 
 
 def check(status, what):

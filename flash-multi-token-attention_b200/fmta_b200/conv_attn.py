@@ -100,6 +100,28 @@ def dkdv_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
     return dK, dV
 
 
+def backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, path=-1):
+    """(dQ, dK, dV, dconv_kernel), all fp32, in one call (`fmta_bwd`): what the reference obtains
+    from `dq_backward` + `dkdv_backward` (conv_attention_cuda.py:147-152).  ``path`` as in the C ABI:
+    0 exact kernels, 1 tensor-core kernels + exact band, -1 library default."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (dO, "dO")):
+        require_cuda_bf16(t, n)
+    B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
+    theta, Dv, LSE = as_f32(conv_kernel), as_f32(D), as_f32(L)
+    dQ = torch.empty((B, H, N, d), dtype=torch.float32, device=Q.device)
+    dK = torch.empty_like(dQ)
+    dV = torch.empty_like(dQ)
+    dTheta = torch.empty((H, cq, ck), dtype=torch.float32, device=Q.device)
+    op = _lib.FMTA_OP_BWD_DQ if path == 0 else _lib.FMTA_OP_BWD_TC
+    ws_bytes = lib.fmta_workspace_bytes(op, B, H, N, d, cq, ck, 1)
+    ws = _workspace(ws_bytes, Q.device)
+    st = lib.fmta_bwd(ptr(Q), ptr(K), ptr(V), ptr(dO), ptr(Dv), ptr(LSE), ptr(theta), None, ptr(dQ), ptr(dK), ptr(dV),
+                      ptr(dTheta), None, B, H, N, d, cq, ck, 1, float(scale), int(bool(causal)), int(path), ptr(ws),
+                      ws_bytes, stream_ptr())
+    check(st, "fmta_bwd")
+    return dQ, dK, dV, dTheta
+
+
 class FlashConvAttentionCUDAFunction(torch.autograd.Function):
     """autograd.Function with the argument list of conv_attention_cuda.py:96-163."""
 
@@ -117,8 +139,7 @@ class FlashConvAttentionCUDAFunction(torch.autograd.Function):
         Q, K, V, conv_kernel, LSE, O = ctx.saved_tensors
         dOb = dO.to(torch.bfloat16).contiguous()
         D = rowdot(dOb, O)
-        dQ, dTheta = dq_backward(Q, K, V, dOb, D, LSE, conv_kernel, ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal)
-        dK, dV = dkdv_backward(Q, K, V, dOb, D, LSE, conv_kernel, ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal)
+        dQ, dK, dV, dTheta = backward(Q, K, V, dOb, D, LSE, conv_kernel, ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal)
         tq, tk, tv = ctx.in_dtypes
         return dQ.to(tq), dK.to(tk), dV.to(tv), dTheta.to(conv_kernel.dtype), None, None, None, None
 

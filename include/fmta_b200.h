@@ -50,12 +50,20 @@ extern "C" {
 
 #define FMTA_OP_BWD_DQ 1 /* for fmta_workspace_bytes */
 #define FMTA_OP_FWD_TC 2
+#define FMTA_OP_BWD_TC 3
 
 /* Library version (major*10000 + minor*100 + patch). */
 int fmta_version(void);
 
 /* Text for a status code returned by any entry point. */
 const char* fmta_strerror(int status);
+
+/*
+ * Process-wide kernel selection for the entry points that have no `path` argument:
+ * -1 = library default, 0 = exact tile kernels only, 1 = tensor-core kernels off the causal band
+ * plus exact kernels on it.  Returns the previous value.
+ */
+int fmta_set_path(int path);
 
 /* cudaError_t value of the last launch failure seen by this thread (0 if none). */
 int fmta_last_cuda_error(void);
@@ -105,6 +113,20 @@ int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, c
                   const float* LSE, const float* theta, const float* wmix, float* dK, float* dV,
                   int B, int H, int N, int d, int cq, int ck, int G, float scale, int causal,
                   void* stream);
+
+/*
+ * Whole backward in one call: dQ, dK, dV, dTheta (and dW).  Replaces the pair of calls made by
+ * `FlashConvAttentionCUDAFunction.backward` (conv_attn/conv_attention_cuda.py:147-152).
+ * path: 0 = exact tile kernels; 1 = stacked-GEMM tensor-core kernels for the entries off the
+ * causal band + exact kernels (accumulating) on the band -- needs d = 64, c_q <= 6, no head
+ * mixing, and a workspace of fmta_workspace_bytes(FMTA_OP_BWD_TC, ...); -1 = the process-wide
+ * default (fmta_set_path), which picks 1 whenever it is available and the workspace suffices.
+ * With path 0 the workspace need is that of FMTA_OP_BWD_DQ.
+ */
+int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+             const float* LSE, const float* theta, const float* wmix, float* dQ, float* dK, float* dV,
+             float* dTheta, float* dW, int B, int H, int N, int d, int cq, int ck, int G, float scale,
+             int causal, int path, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Decode: last query row over a KV cache with split-K.  Replaces
