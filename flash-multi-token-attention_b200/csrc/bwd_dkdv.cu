@@ -22,6 +22,7 @@ static cudaError_t launch_bwd_dkdv_t(const TrainParams& p, cudaStream_t stream) 
 }
 
 cudaError_t launch_bwd_dkdv(const TrainParams& p, cudaStream_t stream) {
+  ScopedKernelTimer timer_(kKernBwdDkdvExact, stream);
   const bool mix = (p.Wmix != nullptr) && p.G > 1;
   int cq = p.cq, ck = p.ck;
   const bool has_theta = p.theta != nullptr;

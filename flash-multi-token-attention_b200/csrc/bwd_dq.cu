@@ -56,6 +56,7 @@ static cudaError_t launch_bwd_dq_t(const TrainParams& p, cudaStream_t stream) {
 }
 
 cudaError_t launch_bwd_dq(const TrainParams& p, cudaStream_t stream) {
+  ScopedKernelTimer timer_(kKernBwdDqExact, stream);
   const bool mix = (p.Wmix != nullptr) && p.G > 1;
   int cq = p.cq, ck = p.ck;
   const bool has_theta = p.theta != nullptr;

@@ -702,7 +702,8 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t
   if (e != cudaSuccess) return e;
   const int rows_per_cta = Cfg::OWN * Cfg::NT;
   dim3 grid((p.N + rows_per_cta - 1) / rows_per_cta, p.H, p.B);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
+  { ScopedKernelTimer timer_(kKernBwdDqTc, stream);
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp); }
   return cudaGetLastError();
 }
 
@@ -728,7 +729,8 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((p.N + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
+  { ScopedKernelTimer timer_(kKernBwdDkdvTc, stream);
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp); }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   constexpr int RPB = 256 / (D / 8);

@@ -38,6 +38,8 @@ int check_train_dims(int B, int H, int N, int d, int cq, int ck, int G, bool has
 
 }  // namespace
 
+namespace fmta { ProfileHook g_profile_hook = {0, nullptr, nullptr}; }
+
 extern "C" {
 
 int fmta_version(void) { return 100; }
@@ -57,6 +59,15 @@ const char* fmta_strerror(int status) {
 }
 
 int fmta_last_cuda_error(void) { return g_last_cuda_error; }
+
+int fmta_profile_kernel(int kernel_id, void* start_event, void* stop_event) {
+  if (kernel_id < 0 || kernel_id > 7) return FMTA_ERR_SHAPE;
+  if (kernel_id != 0 && (!start_event || !stop_event)) return FMTA_ERR_NULL;
+  g_profile_hook.id = kernel_id;
+  g_profile_hook.start = (cudaEvent_t)start_event;
+  g_profile_hook.stop = (cudaEvent_t)stop_event;
+  return FMTA_OK;
+}
 
 int fmta_set_path(int path) {
   const int old = g_path;

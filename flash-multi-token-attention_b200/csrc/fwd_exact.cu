@@ -22,6 +22,7 @@ static cudaError_t launch_fwd_exact_t(const TrainParams& p, cudaStream_t stream)
 }
 
 cudaError_t launch_fwd_exact(const TrainParams& p, cudaStream_t stream) {
+  ScopedKernelTimer timer_(kKernFwdExact, stream);
   const bool mix = (p.Wmix != nullptr) && p.G > 1;
   int cq = p.cq, ck = p.ck;
   const bool has_theta = p.theta != nullptr;

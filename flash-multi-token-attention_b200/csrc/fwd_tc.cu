@@ -522,7 +522,8 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((p.N + Cfg::NT * Cfg::BM - 1) / (Cfg::NT * Cfg::BM), p.H, p.B);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, tp);
+  { ScopedKernelTimer timer_(kKernFwdTc, stream);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, tp); }
   return cudaGetLastError();
 }
 

@@ -53,6 +53,18 @@ inline cudaError_t launch_kernel(void (*kern)(const P), dim3 grid, dim3 block, s
     else return cudaErrorInvalidValue;                            \
   } while (0)
 
+// Optional timing hook: when armed for a kernel id, the launcher of that kernel records the two
+// events around the launch on the launch stream (see fmta_profile_kernel in the C ABI).
+enum KernelId : int { kKernNone = 0, kKernFwdTc = 1, kKernFwdExact = 2, kKernBwdDqTc = 3, kKernBwdDkdvTc = 4,
+                      kKernBwdDqExact = 5, kKernBwdDkdvExact = 6, kKernDecode = 7 };
+struct ProfileHook { int id; cudaEvent_t start, stop; };
+extern ProfileHook g_profile_hook;
+struct ScopedKernelTimer {
+  bool on; cudaStream_t st;
+  ScopedKernelTimer(int id, cudaStream_t s) : on(g_profile_hook.id == id), st(s) { if (on) cudaEventRecord(g_profile_hook.start, st); }
+  ~ScopedKernelTimer() { if (on) cudaEventRecord(g_profile_hook.stop, st); }
+};
+
 cudaError_t launch_fwd_exact(const TrainParams& p, cudaStream_t stream);
 cudaError_t launch_bwd_dq(const TrainParams& p, cudaStream_t stream);
 cudaError_t launch_bwd_dkdv(const TrainParams& p, cudaStream_t stream);

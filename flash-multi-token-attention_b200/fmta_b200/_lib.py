@@ -46,6 +46,8 @@ lib.fmta_bwd_dq_dw_static.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _f
 lib.fmta_bwd.restype = _i
 lib.fmta_bwd.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _f,
                          _i, _i, _vp, _sz, _vp]
+lib.fmta_profile_kernel.restype = _i
+lib.fmta_profile_kernel.argtypes = [_i, _vp, _vp]
 lib.fmta_set_path.restype = _i
 lib.fmta_set_path.argtypes = [_i]
 lib.fmta_bwd_dkdv.restype = _i
@@ -55,7 +57,7 @@ lib.fmta_decode.restype = _i
 lib.fmta_decode.argtypes = [_vp, _vp, _vp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
 
 EXPORTS = ["fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
-           "fmta_bwd_prep_D", "fmta_bwd", "fmta_set_path", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode"]
+           "fmta_bwd_prep_D", "fmta_bwd", "fmta_set_path", "fmta_profile_kernel", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode"]
 
 
 def check(status, what):

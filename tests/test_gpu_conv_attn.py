@@ -128,3 +128,36 @@ def test_rejects_bad_inputs():
         F.forward(Q48, Q48, Q48, th, 1.0, 2, 1, True)              # unsupported head dim
     with pytest.raises(RuntimeError):
         F.forward(Q, Q, Q, th, 1.0, 1, 1, True)                    # pads inconsistent with the filter
+
+
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("B,H,N,d,cq,ck,causal", [
+    (1, 2, 520, 64, 6, 11, True),     # several 224-row dQ tiles and 128-key dK tiles, ragged N
+    (2, 1, 300, 64, 3, 5, False),     # no causal band: everything on the tensor-core kernels
+    (1, 1, 100, 64, 6, 11, True),     # shorter than one tile
+])
+def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
+    """fmta_bwd with the exact kernels (path 0) and with the stacked-GEMM tensor-core kernels plus
+    exact band (path 1) against the oracle; forward run on both paths as well."""
+    import fmta_b200 as F
+    Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=17 + N, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
+    th = theta.cuda()
+    O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, causal, return_lse=True, path=path)
+    Dv = F.rowdot(do, O)
+    dQ, dK, dV, dTh = F.backward(q, k, v, do, Dv, LSE, th, scale, cq - 1, (ck - 1) // 2, causal, path=path)
+    torch.cuda.synchronize()
+    Or, Mr, Lr = orc.conv_attn_fwd(Q, K, V, theta, scale, causal)
+    rq, rk, rv, rt = orc.conv_attn_bwd_autograd(Q, K, V, theta, dO, scale, causal)
+    _check(dict(O=O, M=M, L=L, LSE=LSE, dQ=dQ, dK=dK, dV=dV, dTheta=dTh),
+           dict(O=Or, M=Mr, L=Lr, dQ=rq, dK=rk, dV=rv, dTheta=rt), dtheta_rel=5e-3)
+
+
+def test_tensor_core_path_rejected_when_unsupported():
+    import fmta_b200 as F
+    Q = torch.zeros(1, 1, 64, 128, device="cuda", dtype=torch.bfloat16)
+    th = torch.zeros(1, 6, 11, device="cuda")
+    LSE = torch.zeros(1, 1, 64, device="cuda")
+    with pytest.raises(RuntimeError):   # the tensor-core backward exists for d = 64 only
+        F.backward(Q, Q, Q, Q, LSE, LSE, th, 1.0, 5, 5, True, path=1)
