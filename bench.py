@@ -146,7 +146,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true")
@@ -229,11 +229,14 @@ def main():
         return ms
 
     # ---- device-resident throughput ----
-    for _ in range(args.warmup):
-        step(q, k, v, do)
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
+    t_w = time.perf_counter()
+    for _ in range(args.warmup):
+        step(q, k, v, do)
+    while time.perf_counter() - t_w < 0.3:      # keep the GPU under load until nvidia-smi has sampled it
+        step(q, k, v, do)
     ms = timed(lambda: step(q, k, v, do, record=True), args.steps)
     clocks = sampler.stop() if sampler else None
     ms_step = ms / args.steps
