@@ -22,7 +22,7 @@ constexpr int kDecRing = 64;   // keys kept per warp for the conv window
 
 FMTA_DEVINL uint4 ldg_nc_v4(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
@@ -37,7 +37,7 @@ __host__ __device__ inline int decode_keys_per_split(int Nk, int k_splits) {
 }
 
 template <int D, bool R16>
-__global__ void __launch_bounds__(kDecWarps * 32) decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeParams p) {
   constexpr int KS = D / 16;       // k-steps of the MMA
   constexpr int CH = D / 32;       // 32-element chunks per row (one 16-byte load per lane each)
   constexpr int LPR = D / 8;       // lanes covering one V row with 16-byte loads
