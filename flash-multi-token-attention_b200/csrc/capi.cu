@@ -86,7 +86,9 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
   if (op == FMTA_OP_BWD_TC) {
     // dTheta partials of the exact band kernel and of the tensor-core post-pass (one contiguous
     // slot array, rounded up), followed by the tensor-core backward's buffers
-    const size_t slots = (size_t)B * ((N + 63) / 64) + (size_t)bwd_tc_theta_slots(B, N);
+    int off, ownq, ownk;
+    band_geometry(cq, ck, &off, &ownq, &ownk);
+    const size_t slots = (size_t)B * ((N + ownq - 1) / ownq) + (size_t)bwd_tc_theta_slots(B, N);
     const size_t part = (slots * H * (size_t)(cq * ck) * sizeof(float) + 1023) / 1024 * 1024;
     return part + bwd_tc_workspace_bytes(B, H, N, d, cq);
   }
@@ -131,6 +133,7 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
     // continuing the online softmax from the un-normalised partial
     if (int s = check_cuda(launch_fwd_tc(p, workspace, &p.Opart, &p.Mpart, &p.Lpart, (cudaStream_t)stream))) return s;
     p.kmode = kBandTiles;
+    band_geometry(p.cq, p.ck, &p.band_off, &p.band_ownq, &p.band_ownk);
   }
   return check_cuda(launch_fwd_exact(p, (cudaStream_t)stream));
 }
@@ -217,7 +220,7 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
     use_tc = false;
   }
   p.dQ = dQ; p.dK = dK; p.dV = dV;
-  const int slots_ex = B * ((N + 63) / 64);
+  int slots_ex = B * ((N + 63) / 64);
   const size_t n_theta = (size_t)H * p.cq * p.ck;
   if (!use_tc) {
     const size_t need = fmta_workspace_bytes(FMTA_OP_BWD_DQ, B, H, N, d, p.cq, p.ck, p.G);
@@ -235,6 +238,8 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
     return FMTA_OK;
   }
   // tensor-core kernels for the entries off the causal band, exact kernels (accumulating) on it
+  band_geometry(p.cq, p.ck, &p.band_off, &p.band_ownq, &p.band_ownk);
+  slots_ex = B * ((N + p.band_ownq - 1) / p.band_ownq);   // one dTheta partial per band CTA
   const int slots_tc = bwd_tc_theta_slots(B, N);
   float* part = reinterpret_cast<float*>(workspace);
   const size_t part_bytes = ((size_t)(slots_ex + slots_tc) * n_theta * sizeof(float) + 1023) / 1024 * 1024;

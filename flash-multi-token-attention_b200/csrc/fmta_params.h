@@ -40,7 +40,24 @@ struct TrainParams {
   int kmode;
   int accumulate;            // backward: add into dQ/dK/dV instead of overwriting
   int n_slots;
+  // band mode (kmode == kBandTiles): one 64x64 tile per CTA, placed so that it holds every band entry
+  // of the rows (keys) the CTA owns: key tile starts band_off before the first owned row
+  int band_off;              // 16 or 32
+  int band_ownq;             // query rows owned per CTA (forward, dQ kernel)
+  int band_ownk;             // keys owned per CTA (dK/dV kernel)
 };
+
+// Geometry of the band tiles for a filter shape (see TrainParams::band_*).
+inline void band_geometry(int cq, int ck, int* off, int* ownq, int* ownk) {
+  const int pq = cq - 1, pk = (ck - 1) / 2, band = pq + pk;
+  *off = (band + pk <= 17) ? 16 : 32;
+  int oq = 64 - *off;
+  if (72 - *off - pq < oq) oq = 72 - *off - pq;
+  *ownq = oq;
+  int ok = 65 - band - pq;
+  if (ok > 48) ok = 48;
+  *ownk = ok;
+}
 
 struct DecodeParams {
   const __nv_bfloat16* Q;    // [B,H,q_len,d]

@@ -68,10 +68,12 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = p.N, H = p.H;
-  const int nQB = (N + BR - 1) / BR, nKB = (N + BC - 1) / BC;
+  const bool band_only = (p.kmode == kBandTiles);
+  const int own_rows = band_only ? p.band_ownq : BR;      // rows this CTA stores
+  const int nQB = (N + own_rows - 1) / own_rows, nKB = (N + BC - 1) / BC;
   const int qb = nQB - 1 - (int)blockIdx.x;  // long (late) query blocks first
   const int h = blockIdx.y, b = blockIdx.z;
-  const int i0 = qb * BR;
+  const int i0 = qb * own_rows;
   const int cq = (CQ > 0) ? CQ : p.cq, ck = (CQ > 0) ? CK : p.ck;
   const int pq = cq - 1, pk = (ck - 1) / 2;
   const bool causal = p.causal != 0;
@@ -91,19 +93,15 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
     if (tid < G * G) sW[tid] = p.Wmix[(size_t)(h / G) * G * G + tid];
   }
 
-  // key-block range
-  const bool band_only = (p.kmode == kBandTiles);
+  // key-block range.  Band mode: the entries with query - key >= pad_q + pad_k were done by the
+  // stacked tensor-core kernel; the band entries of the own_rows rows owned here all lie in the
+  // single 64-key tile that starts band_off keys before the first owned row.
   int kb_begin = 0, kb_end = nKB - 1;
-  if (causal) {
+  if (band_only) {
+    kb_begin = 0;
+    kb_end = causal ? 0 : -1;      // no causal band: nothing to do here but finalise
+  } else if (causal) {
     kb_end = min(nKB - 1, (i0 + BR - 1) / BC);
-    if (p.kmode == kBandTiles) {
-      // entries with query - key >= pad_q + pad_k were done by the stacked tensor-core kernel;
-      // the band entries of this row block lie in key blocks >= (i0 - band + 1) / 64
-      const int t = i0 - (pq + pk) + 1;
-      kb_begin = (t > 0) ? (t / BC) : 0;
-    }
-  } else if (p.kmode == kBandTiles) {
-    kb_begin = nKB;  // no causal band: nothing to do here
   }
 
   // running softmax state and output accumulators
@@ -135,7 +133,7 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
   cp_async_commit();
 
   for (int kb = kb_begin; kb <= kb_end; ++kb) {
-    const int j0 = kb * BC;
+    const int j0 = band_only ? (i0 - p.band_off) : kb * BC;
     load_rows_async<D, Cfg::NT>(sK, QK_LD, Kg, j0 - HC, SC, N, tid);
     load_rows_async<D, Cfg::NT>(sV, QK_LD, Vg, j0, BC, N, tid);
     cp_async_commit();
@@ -214,8 +212,8 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
       const int c = 2 * lane;
       float2 v = *reinterpret_cast<const float2*>(cbuf + r * C_LD + c);
       const int qi = i0 + r, kj = j0 + c;
-      if (kj >= N || (causal && kj > qi) || (band_only && qi - kj >= pq + pk)) v.x = -INFINITY;
-      if (kj + 1 >= N || (causal && kj + 1 > qi) || (band_only && qi - (kj + 1) >= pq + pk)) v.y = -INFINITY;
+      if (kj < 0 || kj >= N || (causal && kj > qi) || (band_only && qi - kj >= pq + pk)) v.x = -INFINITY;
+      if (kj + 1 < 0 || kj + 1 >= N || (causal && kj + 1 > qi) || (band_only && qi - (kj + 1) >= pq + pk)) v.y = -INFINITY;
       const float mx = warp_max(fmaxf(v.x, v.y));
       const float m_old = sM[r];
       const float m_new = fmaxf(m_old, mx);
@@ -256,15 +254,15 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
       const float o00 = accO[j][0] * inv0, o01 = accO[j][1] * inv0, o10 = accO[j][2] * inv1, o11 = accO[j][3] * inv1;
       if (p.o_bf16) {
         bf16* O = reinterpret_cast<bf16*>(p.O);
-        if (i0 + fr0 < N) *reinterpret_cast<uint32_t*>(O + (bh * N + i0 + fr0) * D + col) = pack_bf16(o00, o01);
-        if (i0 + fr1 < N) *reinterpret_cast<uint32_t*>(O + (bh * N + i0 + fr1) * D + col) = pack_bf16(o10, o11);
+        if (i0 + fr0 < N && fr0 < own_rows) *reinterpret_cast<uint32_t*>(O + (bh * N + i0 + fr0) * D + col) = pack_bf16(o00, o01);
+        if (i0 + fr1 < N && fr1 < own_rows) *reinterpret_cast<uint32_t*>(O + (bh * N + i0 + fr1) * D + col) = pack_bf16(o10, o11);
       } else {
         float* O = reinterpret_cast<float*>(p.O);
-        if (i0 + fr0 < N) *reinterpret_cast<float2*>(O + (bh * N + i0 + fr0) * D + col) = make_float2(o00, o01);
-        if (i0 + fr1 < N) *reinterpret_cast<float2*>(O + (bh * N + i0 + fr1) * D + col) = make_float2(o10, o11);
+        if (i0 + fr0 < N && fr0 < own_rows) *reinterpret_cast<float2*>(O + (bh * N + i0 + fr0) * D + col) = make_float2(o00, o01);
+        if (i0 + fr1 < N && fr1 < own_rows) *reinterpret_cast<float2*>(O + (bh * N + i0 + fr1) * D + col) = make_float2(o10, o11);
       }
     }
-    if (tid < BR && i0 + tid < N) {
+    if (tid < own_rows && i0 + tid < N) {
       const float m = sM[tid], l = sL[tid];
       if (p.M) p.M[bh * N + i0 + tid] = m;
       if (p.L) p.L[bh * N + i0 + tid] = l;
