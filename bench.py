@@ -152,6 +152,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="tiny shapes (profiling / debugging)")
+    ap.add_argument("--train-shape", default=None, help="B,H,N,d of the training step (profiling captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -174,6 +175,9 @@ def main():
     if args.small:
         cfg.update(B=1, H=4, N=2048)
         dec.update(B=4, H=32, Nk=16384)   # 0.5 GB of K/V: larger than L2, small enough to profile
+    if args.train_shape:
+        tb, th_, tn, td = (int(x) for x in args.train_shape.split(","))
+        cfg.update(B=tb, H=th_, N=tn, d=td)
     B, H, N, d, cq, ck = (cfg[k] for k in ("B", "H", "N", "d", "cq", "ck"))
     scale = 1.0 / math.sqrt(d)
     pq, pk = cq - 1, (ck - 1) // 2
