@@ -45,49 +45,37 @@ template <int D>
 __global__ void __launch_bounds__(256) ktilde_kernel(const bf16* __restrict__ K, const float* __restrict__ theta,
                                                      bf16* __restrict__ Kt, int H, int N, int cq, int ck,
                                                      float scale) {
+  // one thread = one 16-byte chunk of one output row of ONE tap (blockIdx.z): light threads, many of them
   constexpr int CPR = D / 8;          // 16-byte chunks per row
   constexpr int RPB = 256 / CPR;      // rows per block
-  __shared__ float sTh[16 * 20];
-  const int bh = blockIdx.y, h = bh % H;
-  for (int i = threadIdx.x; i < cq * ck; i += 256) sTh[(i / ck) * 20 + (i % ck)] = theta[(size_t)h * cq * ck + i] * scale;   // scale already carries log2(e)
+  __shared__ float sTh[20];
+  const int bh = blockIdx.y, h = bh % H, a = blockIdx.z;
+  if (threadIdx.x < ck) sTh[threadIdx.x] = theta[((size_t)h * cq + a) * ck + threadIdx.x] * scale;   // scale carries log2(e)
   __syncthreads();
   const int j = blockIdx.x * RPB + threadIdx.x / CPR, c = threadIdx.x % CPR;
   if (j >= N) return;
   const int pk = (ck - 1) / 2;
-  const bf16* Kb = K + (size_t)bh * N * D;
-  for (int a0 = 0; a0 < cq; a0 += 8) {
-    float acc[8][8];
+  const bf16* Kb = K + (size_t)bh * N * D + c * 8;
+  float acc[8];
 #pragma unroll
-    for (int a = 0; a < 8; ++a)
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll 4
+  for (int b = 0; b < ck; ++b) {
+    const int jj = j + b - pk;
+    if (jj < 0 || jj >= N) continue;
+    const uint4 kv = *reinterpret_cast<const uint4*>(Kb + (size_t)jj * D);
+    const float w = sTh[b];
+    const uint32_t w32[4] = {kv.x, kv.y, kv.z, kv.w};
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[a][e] = 0.f;
-    for (int b = 0; b < ck; ++b) {
-      const int jj = j + b - pk;
-      if (jj < 0 || jj >= N) continue;
-      const uint4 kv = *reinterpret_cast<const uint4*>(Kb + (size_t)jj * D + c * 8);
-      const uint32_t w32[4] = {kv.x, kv.y, kv.z, kv.w};
-      float kf[8];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) { kf[2 * e] = __uint_as_float(w32[e] << 16); kf[2 * e + 1] = __uint_as_float(w32[e] & 0xffff0000u); }
-#pragma unroll
-      for (int a = 0; a < 8; ++a) {
-        if (a0 + a < cq) {
-          const float w = sTh[(a0 + a) * 20 + b];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[a][e] = fmaf(w, kf[e], acc[a][e]);
-        }
-      }
-    }
-#pragma unroll
-    for (int a = 0; a < 8; ++a) {
-      if (a0 + a < cq) {
-        uint4 o;
-        o.x = pack_bf16(acc[a][0], acc[a][1]); o.y = pack_bf16(acc[a][2], acc[a][3]);
-        o.z = pack_bf16(acc[a][4], acc[a][5]); o.w = pack_bf16(acc[a][6], acc[a][7]);
-        *reinterpret_cast<uint4*>(Kt + (((size_t)bh * cq + a0 + a) * N + j) * D + c * 8) = o;
-      }
+    for (int e = 0; e < 4; ++e) {
+      acc[2 * e] = fmaf(w, __uint_as_float(w32[e] << 16), acc[2 * e]);
+      acc[2 * e + 1] = fmaf(w, __uint_as_float(w32[e] & 0xffff0000u), acc[2 * e + 1]);
     }
   }
+  uint4 o;
+  o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+  o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(Kt + (((size_t)bh * cq + a) * N + j) * D + c * 8) = o;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -490,11 +478,11 @@ cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t 
   const size_t BH = (size_t)p.B * p.H;
   if (p.d == 64) {
     constexpr int RPB = 256 / (64 / 8);
-    dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH);
+    dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH, p.cq);
     ktilde_kernel<64><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale * kLog2e);
   } else {
     constexpr int RPB = 256 / (128 / 8);
-    dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH);
+    dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH, p.cq);
     ktilde_kernel<128><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale * kLog2e);
   }
   return cudaGetLastError();
