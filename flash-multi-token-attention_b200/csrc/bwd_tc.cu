@@ -17,8 +17,8 @@
 //                        in shared memory in the no-swizzle K-major core-matrix layout whose
 //                        M stride is 16 bytes, exactly as Q is in the forward.
 //   bwd_dkdv_tc_kernel : CTA = 128 keys (= TMEM lanes), loops 64-row query blocks; transposed
-//                        scores S^T = Kt_a Q^(a)T so that P^T and dC^T land with keys on the
-//                        lanes and feed the dV / dKt MMAs straight from tensor memory.
+//                        scores S^T = Kt_a Q^(a)T so that P^T and dC^T are produced with keys on the
+//                        lanes (rows of the dV / dKt accumulators).
 // Every mbarrier wait is bounded; no TMA multicast, no cluster, cta_group::1 only.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -30,6 +30,13 @@
 namespace fmta {
 
 constexpr float kLn2 = 0.6931471805599453f;
+
+#ifdef FMTA_TC_TRACE
+__device__ long long g_trace_bwd[16384];
+#define TRACEB(slot) do { if (trace_on) g_trace_bwd[(slot)] = clock64(); } while (0)
+#else
+#define TRACEB(slot) do {} while (0)
+#endif
 
 struct BwdTcParams {
   const float* LSE;   // [B,H,N] natural log
@@ -343,7 +350,9 @@ struct DkvCfg {
   static constexpr int sgQ = BR * 128;                            // [D/8][QR][16 B]
   static constexpr int sgLD = sgQ + QR * D * 2;                   // LSE*log2e [64], D [64]
   static constexpr int STAGE_BYTES = ((sgLD + 2 * BR * 4 + 1023) / 1024) * 1024;
-  static constexpr int oBar = oStage + NSTG * STAGE_BYTES;
+  static constexpr int oPT = oStage + NSTG * STAGE_BYTES;         // P^T : [BR/8][128 keys][16 B] (K-major A operand)
+  static constexpr int oDCT = oPT + (BR / 8) * BK * 16;           // dC^T: same layout
+  static constexpr int oBar = oDCT + (BR / 8) * BK * 16;
   static constexpr int kSmemBytes = oBar + 512 + 1024;
   static constexpr int kTmemCols = 512;        // dV at 0, dKt_a at 64*(1+a), scratch X at 448
   static constexpr int colX = 448;
@@ -368,10 +377,12 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* empty = bars + NSTG;         // [NSTG]
   uint64_t* kv_full = bars + 2 * NSTG;
   uint64_t* st_full = kv_full + 1;       // S^T in X
-  uint64_t* x_free = st_full + 1;        // S^T taken into registers (256 arrivals)
+  uint64_t* x_free = st_full + 1;        // S^T taken into registers (256 arrivals): X free for dP^T
   uint64_t* dpt_full = x_free + 1;       // dP^T in X
-  uint64_t* pdc_full = dpt_full + 1;     // P^T and dC^T (bf16) written to X (256 arrivals)
-  uint64_t* all_done = pdc_full + 1;
+  uint64_t* x_free2 = dpt_full + 1;      // dP^T taken into registers (256 arrivals): X free for the next S^T
+  uint64_t* pdc_full = x_free2 + 1;      // P^T and dC^T (bf16) written to shared memory (256 arrivals)
+  uint64_t* pdc_free = pdc_full + 1;     // the dV / dKt MMAs that read them have completed
+  uint64_t* all_done = pdc_free + 1;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(all_done + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
@@ -389,7 +400,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < NSTG; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
     tc::mbar_init(kv_full, 1);
     tc::mbar_init(st_full, 1); tc::mbar_init(x_free, Cfg::kEwWarps * 32);
-    tc::mbar_init(dpt_full, 1); tc::mbar_init(pdc_full, Cfg::kEwWarps * 32);
+    tc::mbar_init(dpt_full, 1); tc::mbar_init(x_free2, Cfg::kEwWarps * 32);
+    tc::mbar_init(pdc_full, Cfg::kEwWarps * 32); tc::mbar_init(pdc_free, 1);
     tc::mbar_init(all_done, 1);
     *s_abort = 0;
     tc::mbar_fence_init();
@@ -403,6 +415,9 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc::tc_fence_after();
   const uint32_t tmem = *s_tmem;
   const uint32_t tX = tmem + Cfg::colX;
+#ifdef FMTA_TC_TRACE
+  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+#endif
 
   if (warp == Cfg::kEwWarps) {
     // ===================== producer warp (TMA + row statistics) =====================
@@ -445,20 +460,51 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint64_t dKtA = tc::make_sdesc(smem_u32(sKt), 16, 1024, tc::kLayoutSW128);
       const uint32_t kt_hi = (uint32_t)(dKtA >> 32), kt_lo = (uint32_t)dKtA;
       const uint32_t v_lo = kt_lo + (uint32_t)((Cfg::oV - Cfg::oKt) >> 4);
+      const uint64_t dPTa = tc::make_sdesc(smem_u32(smem + Cfg::oPT), BK * 16, 128, tc::kLayoutNone);
+      const uint64_t dDCa = tc::make_sdesc(smem_u32(smem + Cfg::oDCT), BK * 16, 128, tc::kLayoutNone);
+      const uint32_t pt_hi = (uint32_t)(dPTa >> 32), pt_lo = (uint32_t)dPTa, dc_lo = (uint32_t)dDCa;
       bool ok = tc::mbar_wait(kv_full, 0, s_abort);
+      // dV += P^T dO ; dKt_a += dC^T Q^(a) for block `it` (A operands from shared memory)
+      auto issue_acc = [&](int it) {
+        const int st = it % NSTG;
+        const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
+        const uint64_t dQm = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, 128, QR * 16, tc::kLayoutNone);   // MN-major, K = rows
+        const uint64_t dOk = tc::make_sdesc(sg + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
+        const uint32_t qm_hi = (uint32_t)(dQm >> 32), qm_lo = (uint32_t)dQm;
+        const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
+        if (!tc::mbar_wait(pdc_full, it & 1, s_abort)) { ok = false; return; }
+        tc::tc_fence_after();
+        TRACEB(it * 8 + 6 + 8);
+#pragma unroll
+        for (int k = 0; k < BR / 16; ++k) {
+          if (it == 0 && k == 0) tc::mma_ss2<0>(tmem, pt_lo, pt_hi, o_lo, o_hi, idescA);
+          else tc::mma_ss2<1>(tmem, pt_lo + (uint32_t)(2 * k * BK), pt_hi, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
+        }
+        for (int a = 0; a < cq; ++a) {
+          const uint32_t dacc = tmem + 64 * (1 + a);
+          const uint32_t b_lo = qm_lo + (uint32_t)a;
+#pragma unroll
+          for (int k = 0; k < BR / 16; ++k) {
+            if (it == 0 && k == 0) tc::mma_ss2<0>(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA);
+            else tc::mma_ss2<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idescA);
+          }
+        }
+        tc::mma_commit(&empty[st]);
+        tc::mma_commit(pdc_free);
+      };
       for (int it = 0; it < nblk && ok; ++it) {
         const int st = it % NSTG, ph = (it / NSTG) & 1;
         const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
-        // B operands of this stage
         const uint64_t dQk = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);   // K-major, N = rows
-        const uint64_t dQm = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, 128, QR * 16, tc::kLayoutNone);   // MN-major, K = rows
         const uint64_t dOk = tc::make_sdesc(sg + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
         const uint32_t qk_hi = (uint32_t)(dQk >> 32), qk_lo = (uint32_t)dQk;
-        const uint32_t qm_hi = (uint32_t)(dQm >> 32), qm_lo = (uint32_t)dQm;
         const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
+        TRACEB(it * 8 + 0);
         if (!tc::mbar_wait(&full[st], ph, s_abort)) { ok = false; break; }
+        if (it > 0 && !tc::mbar_wait(x_free2, (it - 1) & 1, s_abort)) { ok = false; break; }   // X free again
         tc::tc_fence_after();
-        // S^T = sum_a Kt_a Q^(a)T   (X is free: the MMAs that read it were issued earlier)
+        TRACEB(it * 8 + 1);
+        // S^T = sum_a Kt_a Q^(a)T
         for (int a = 0; a < cq; ++a) {
           const uint32_t a_lo = kt_lo + (uint32_t)(a * (Cfg::KT_BYTES >> 4));
           const uint32_t b_lo = qk_lo + (uint32_t)a;
@@ -469,33 +515,22 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc::mma_ss2<1>(tX, a_lo + (uint32_t)(2 * k), kt_hi, b_lo + (uint32_t)(2 * k * QR), qk_hi, idescT);
         }
         tc::mma_commit(st_full);
+        TRACEB(it * 8 + 2);
+        // while the element-wise warps work on block `it`, feed the accumulators with block it-1
+        if (it > 0) { issue_acc(it - 1); if (!ok) break; }
+        TRACEB(it * 8 + 3);
         if (!tc::mbar_wait(x_free, it & 1, s_abort)) { ok = false; break; }
         tc::tc_fence_after();
+        TRACEB(it * 8 + 4);
         // dP^T = V dO^T
         tc::mma_ss2<0>(tX, v_lo, kt_hi, o_lo, o_hi, idescT);
 #pragma unroll
         for (int k = 1; k < D / 16; ++k)
           tc::mma_ss2<1>(tX, v_lo + (uint32_t)(2 * k), kt_hi, o_lo + (uint32_t)(2 * k), o_hi, idescT);
         tc::mma_commit(dpt_full);
-        if (!tc::mbar_wait(pdc_full, it & 1, s_abort)) { ok = false; break; }
-        tc::tc_fence_after();
-        // dV += P^T dO ;  dKt_a += dC^T Q^(a)   (A from tensor memory: 8 columns per 16 rows)
-#pragma unroll
-        for (int k = 0; k < BR / 16; ++k) {
-          if (it == 0 && k == 0) tc::mma_ts2<0>(tmem, tX, o_lo, o_hi, idescA);
-          else tc::mma_ts2<1>(tmem, tX + 8 * k, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
-        }
-        for (int a = 0; a < cq; ++a) {
-          const uint32_t dacc = tmem + 64 * (1 + a);
-          const uint32_t b_lo = qm_lo + (uint32_t)a;
-#pragma unroll
-          for (int k = 0; k < BR / 16; ++k) {
-            if (it == 0 && k == 0) tc::mma_ts2<0>(dacc, tX + 32, b_lo, qm_hi, idescA);
-            else tc::mma_ts2<1>(dacc, tX + 32 + 8 * k, b_lo + (uint32_t)(k * 16), qm_hi, idescA);
-          }
-        }
-        tc::mma_commit(&empty[st]);
+        TRACEB(it * 8 + 5);
       }
+      if (ok) issue_acc(nblk - 1);
       if (ok) tc::mma_commit(all_done);
     }
   } else {
@@ -531,6 +566,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!ok) break;
       tc::tc_fence_after();
       tc::tmem_ld32(tXl + 32 * hh, s);                  // dP^T
+      tc::tc_fence_before();
+      tc::mbar_arrive(x_free2);                         // X may take the next block's S^T
       uint32_t pp[16], cc[16];
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
@@ -539,14 +576,20 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         pp[c / 2] = pack_bf16(pv[c], pv[c + 1]);
         cc[c / 2] = pack_bf16(d0, d1);
       }
-      // both column halves of these lanes must have read dP^T before X is overwritten
-      tc::tc_fence_before();
-      tc::named_bar_sync(1 + qtr, 64);
-      tc::tc_fence_after();
-      tc::tmem_st16u(tXl + 16 * hh, pp);                // P^T : X columns [0,32)
-      tc::tmem_st16u(tXl + 32 + 16 * hh, cc);           // dC^T: X columns [32,64)
-      tc::tmem_wait_st();
-      tc::tc_fence_before();
+      if (it > 0) {   // the MMAs of block it-1 have finished reading the P^T / dC^T buffers
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(pdc_free, (it - 1) & 1, s_abort));
+        if (!ok) break;
+      }
+      {
+        unsigned char* pt = smem + Cfg::oPT + (qtr * 32 + lane) * 16;
+        unsigned char* dc = smem + Cfg::oDCT + (qtr * 32 + lane) * 16;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {               // 8 rows (16 bytes) per K-chunk
+          *reinterpret_cast<uint4*>(pt + (4 * hh + q4) * (BK * 16)) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]);
+          *reinterpret_cast<uint4*>(dc + (4 * hh + q4) * (BK * 16)) = make_uint4(cc[4 * q4], cc[4 * q4 + 1], cc[4 * q4 + 2], cc[4 * q4 + 3]);
+        }
+      }
+      tc::fence_proxy_async_smem();
       tc::mbar_arrive(pdc_full);
     }
     // ---- epilogue: dV and dKt_a rows of this key ----
@@ -742,5 +785,11 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
 
 // slots of dTheta partials written by dk_post_kernel
 int bwd_tc_theta_slots(int B, int N) { return B * ((N + 31) / 32); }
+
+#ifdef FMTA_TC_TRACE
+extern "C" int fmta_debug_trace_bwd(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace_bwd, sizeof(long long) * n);
+}
+#endif
 
 }  // namespace fmta
