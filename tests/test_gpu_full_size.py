@@ -1,0 +1,99 @@
+"""Parity at the sequence lengths of the benchmark configurations (the oracle is O(N^2), so it
+is run on a slice: a few heads of the training shape, row blocks of the long one, one (batch, head)
+pair of the decode cache) plus size-independent properties on the full training shape."""
+import math
+
+import pytest
+import torch
+
+from helpers import TOL_BF16, maxabs
+from oracle import conv_attn_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def test_training_shape_slice_N4096():
+    """B=1, H=2 slice of the bf16 training configuration (N=4096, d=64, theta (6,11)): forward and
+    fused backward on the default (tensor-core + band) path against the dense oracle."""
+    import fmta_b200 as F
+    B, H, N, d, cq, ck = 1, 2, 4096, 64, 6, 11
+    Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=4096, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
+    th = theta.cuda()
+    O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True)
+    Dv = F.rowdot(do, O)
+    dQ, dK, dV, dTh = F.backward(q, k, v, do, Dv, LSE, th, scale, cq - 1, (ck - 1) // 2, True)
+    torch.cuda.synchronize()
+    Or, Mr, Lr = orc.conv_attn_fwd(Q, K, V, theta, scale, True)
+    rq, rk, rv, rt = orc.conv_attn_bwd_autograd(Q, K, V, theta, dO, scale, True)
+    assert maxabs(O, Or) <= TOL_BF16
+    assert maxabs(M, Mr) <= TOL_BF16
+    assert maxabs(LSE, Mr + torch.log(Lr)) <= TOL_BF16
+    assert maxabs(dQ, rq) <= TOL_BF16
+    assert maxabs(dK, rk) <= TOL_BF16
+    assert maxabs(dV, rv) <= TOL_BF16
+    assert maxabs(dTh, rt) <= max(TOL_BF16, 5e-3 * float(rt.abs().max()))
+
+
+def test_long_sequence_row_blocks_N16384_d128():
+    """d=128 sweep shape at N=16384: forward checked on row blocks with the O(rows x N) oracle."""
+    import fmta_b200 as F
+    B, H, N, d, cq, ck = 1, 1, 16384, 128, 6, 11
+    Q, K, V, _, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=16384, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    q, k, v = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V))
+    O, M, L = F.forward(q, k, v, theta.cuda(), scale, cq - 1, (ck - 1) // 2, True)
+    torch.cuda.synchronize()
+    for i0, i1 in ((0, 40), (8000, 8040), (12281, 12300), (16320, 16384)):
+        Or, Mr, Lr = orc.conv_attn_fwd_rowblock(Q, K, V, theta, i0, i1, scale, True)
+        assert maxabs(O[:, :, i0:i1], Or) <= TOL_BF16
+        assert maxabs(M[:, :, i0:i1], Mr) <= TOL_BF16
+        assert maxabs((M + torch.log(L))[:, :, i0:i1], Mr + torch.log(Lr)) <= TOL_BF16
+
+
+def test_full_training_shape_properties():
+    """Whole bf16 training configuration (B=4,H=16,N=4096,d=64): properties that need no oracle.
+    O is linear in V; rows of P sum to one (O == 1 for V == 1); dV is linear in dO."""
+    import fmta_b200 as F
+    B, H, N, d, cq, ck = 4, 16, 4096, 64, 6, 11
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q, k, v1, v2, do = (torch.randn(B, H, N, d, device="cuda", generator=g).to(torch.bfloat16) for _ in range(5))
+    th = torch.randn(H, cq, ck, device="cuda", generator=g) * 0.02
+    th[:, cq - 1, ck // 2] += 1.0
+    scale = 1.0 / math.sqrt(d)
+    f = lambda v: F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True)
+    O1, M1, L1, LSE = f(v1)
+    O2 = f(v2)[0]
+    O12 = f((v1.float() + v2.float()).to(torch.bfloat16))[0]
+    # v1+v2 is rounded to bf16 once more: allow that rounding (2^-8 relative on |v| <~ 6)
+    assert float((O12 - (O1 + O2)).abs().max()) <= 4e-2
+    ones = torch.ones_like(v1)
+    Oone = f(ones)[0]
+    assert float((Oone - 1.0).abs().max()) <= 1e-2
+    assert torch.isfinite(M1).all() and torch.isfinite(L1).all() and float(L1.min()) >= 1.0 - 1e-3
+    D1 = F.rowdot(do, O1)
+    g1 = F.backward(q, k, v1, do, D1, LSE, th, scale, cq - 1, (ck - 1) // 2, True)
+    for t in g1:
+        assert torch.isfinite(t).all()
+    # the gradient w.r.t. V does not depend on D and is linear in dO
+    do2 = (do.float() * 0.5).to(torch.bfloat16)
+    g2 = F.backward(q, k, v1, do2, F.rowdot(do2, O1), LSE, th, scale, cq - 1, (ck - 1) // 2, True)
+    assert float((g2[2] - 0.5 * g1[2]).abs().max()) <= 1e-2
+    assert float((g2[0] - 0.5 * g1[0]).abs().max()) <= 1e-2      # dQ, dK, dTheta are linear in dO too
+    assert float((g2[3] - 0.5 * g1[3]).abs().max()) <= 5e-3 * float(g1[3].abs().max())
+
+
+def test_decode_full_cache_length():
+    """One (batch, head) pair of the decode configuration: Nk=32768, d=128, q_len=6, theta (6,11)."""
+    import fmta_b200 as F
+    B, H, Nk, d, cq, ck, q_len = 1, 2, 32768, 128, 6, 11, 6
+    Q, K, V, _, theta = orc.make_inputs(B, H, 0, d, cq, ck, seed=32768, dtype=torch.bfloat16, Nk=Nk, q_len=q_len)
+    scale = 1.0 / math.sqrt(d)
+    Or, Mr, Lr = orc.decode_last_row_streaming(Q, K, V, theta, scale, chunk=4096)
+    qb, kb, vb = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V))
+    for ks in (1, 4):
+        O, M, L = F.fwd_conv_attn_inference(qb, kb, vb, theta.cuda(), ks, scale, cq - 1, (ck - 1) // 2, False)
+        assert maxabs(O, Or) <= TOL_BF16
+        assert maxabs(M, Mr) <= TOL_BF16
+        assert maxabs(M + torch.log(L), Mr + torch.log(Lr)) <= TOL_BF16
