@@ -357,7 +357,7 @@ struct DkvCfg {
   static constexpr int kTmemCols = 512;        // dV at 0, dKt_a at 64*(1+a), scratch X at 448
   static constexpr int colX = 448;
   static constexpr int kEwWarps = 8;
-  static constexpr int kThreads = (kEwWarps + 2) * 32;
+  static constexpr int kThreads = (kEwWarps + 4) * 32;   // + producer, issuer S, issuers A0 and A1
 };
 
 template <int D>
@@ -397,12 +397,12 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int nblk = nQB - qb_begin;
 
   if (tid == 0) {
-    for (int i = 0; i < NSTG; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
+    for (int i = 0; i < NSTG; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 3); }   // three issuers release a stage
     tc::mbar_init(kv_full, 1);
     tc::mbar_init(st_full, 1); tc::mbar_init(x_free, Cfg::kEwWarps * 32);
     tc::mbar_init(dpt_full, 1); tc::mbar_init(x_free2, Cfg::kEwWarps * 32);
-    tc::mbar_init(pdc_full, Cfg::kEwWarps * 32); tc::mbar_init(pdc_free, 1);
-    tc::mbar_init(all_done, 1);
+    tc::mbar_init(pdc_full, Cfg::kEwWarps * 32); tc::mbar_init(pdc_free, 2);
+    tc::mbar_init(all_done, 2);
     *s_abort = 0;
     tc::mbar_fence_init();
   }
@@ -453,45 +453,15 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else if (warp == Cfg::kEwWarps + 1) {
-    // ===================== MMA issuer =====================
+    // ===================== MMA issuer S: S^T and dP^T of block `it` into the scratch columns X ==========
+    // One thread issues an MMA every 50-100 clocks whatever its size, so the three MMA streams of a
+    // block (S^T/dP^T, dV + first half of the dKt taps, second half of the taps) have a warp each.
     if (lane == 0 && nblk > 0) {
-      constexpr uint32_t idescT = tc::make_idesc(BK, BR, 0, 0);    // S^T, dP^T: 128 x 64, K-major operands
-      constexpr uint32_t idescA = tc::make_idesc(BK, D, 0, 1);     // dV, dKt: 128 x D, B MN-major
+      constexpr uint32_t idescT = tc::make_idesc(BK, BR, 0, 0);    // 128 x 64, K-major operands
       const uint64_t dKtA = tc::make_sdesc(smem_u32(sKt), 16, 1024, tc::kLayoutSW128);
       const uint32_t kt_hi = (uint32_t)(dKtA >> 32), kt_lo = (uint32_t)dKtA;
       const uint32_t v_lo = kt_lo + (uint32_t)((Cfg::oV - Cfg::oKt) >> 4);
-      const uint64_t dPTa = tc::make_sdesc(smem_u32(smem + Cfg::oPT), BK * 16, 128, tc::kLayoutNone);
-      const uint64_t dDCa = tc::make_sdesc(smem_u32(smem + Cfg::oDCT), BK * 16, 128, tc::kLayoutNone);
-      const uint32_t pt_hi = (uint32_t)(dPTa >> 32), pt_lo = (uint32_t)dPTa, dc_lo = (uint32_t)dDCa;
       bool ok = tc::mbar_wait(kv_full, 0, s_abort);
-      // dV += P^T dO ; dKt_a += dC^T Q^(a) for block `it` (A operands from shared memory)
-      auto issue_acc = [&](int it) {
-        const int st = it % NSTG;
-        const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
-        const uint64_t dQm = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, 128, QR * 16, tc::kLayoutNone);   // MN-major, K = rows
-        const uint64_t dOk = tc::make_sdesc(sg + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
-        const uint32_t qm_hi = (uint32_t)(dQm >> 32), qm_lo = (uint32_t)dQm;
-        const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
-        if (!tc::mbar_wait(pdc_full, it & 1, s_abort)) { ok = false; return; }
-        tc::tc_fence_after();
-        TRACEB(it * 8 + 6 + 8);
-#pragma unroll
-        for (int k = 0; k < BR / 16; ++k) {
-          if (it == 0 && k == 0) tc::mma_ss2<0>(tmem, pt_lo, pt_hi, o_lo, o_hi, idescA);
-          else tc::mma_ss2<1>(tmem, pt_lo + (uint32_t)(2 * k * BK), pt_hi, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
-        }
-        for (int a = 0; a < cq; ++a) {
-          const uint32_t dacc = tmem + 64 * (1 + a);
-          const uint32_t b_lo = qm_lo + (uint32_t)a;
-#pragma unroll
-          for (int k = 0; k < BR / 16; ++k) {
-            if (it == 0 && k == 0) tc::mma_ss2<0>(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA);
-            else tc::mma_ss2<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idescA);
-          }
-        }
-        tc::mma_commit(&empty[st]);
-        tc::mma_commit(pdc_free);
-      };
       for (int it = 0; it < nblk && ok; ++it) {
         const int st = it % NSTG, ph = (it / NSTG) & 1;
         const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
@@ -508,17 +478,13 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int a = 0; a < cq; ++a) {
           const uint32_t a_lo = kt_lo + (uint32_t)(a * (Cfg::KT_BYTES >> 4));
           const uint32_t b_lo = qk_lo + (uint32_t)a;
-          if (a == 0) tc::mma_ss2<0>(tX, a_lo, kt_hi, b_lo, qk_hi, idescT);
-          else tc::mma_ss2<1>(tX, a_lo, kt_hi, b_lo, qk_hi, idescT);
+          tc::mma_ss2p(tX, a_lo, kt_hi, b_lo, qk_hi, idescT, a != 0);
 #pragma unroll
           for (int k = 1; k < D / 16; ++k)
             tc::mma_ss2<1>(tX, a_lo + (uint32_t)(2 * k), kt_hi, b_lo + (uint32_t)(2 * k * QR), qk_hi, idescT);
         }
         tc::mma_commit(st_full);
         TRACEB(it * 8 + 2);
-        // while the element-wise warps work on block `it`, feed the accumulators with block it-1
-        if (it > 0) { issue_acc(it - 1); if (!ok) break; }
-        TRACEB(it * 8 + 3);
         if (!tc::mbar_wait(x_free, it & 1, s_abort)) { ok = false; break; }
         tc::tc_fence_after();
         TRACEB(it * 8 + 4);
@@ -528,9 +494,49 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int k = 1; k < D / 16; ++k)
           tc::mma_ss2<1>(tX, v_lo + (uint32_t)(2 * k), kt_hi, o_lo + (uint32_t)(2 * k), o_hi, idescT);
         tc::mma_commit(dpt_full);
+        tc::mma_commit(&empty[st]);
         TRACEB(it * 8 + 5);
       }
-      if (ok) issue_acc(nblk - 1);
+    }
+  } else if (warp >= Cfg::kEwWarps + 2) {
+    // ===================== MMA issuers A0 / A1: dV += P^T dO ; dKt_a += dC^T Q^(a) =====================
+    const int ai = warp - (Cfg::kEwWarps + 2);
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idescA = tc::make_idesc(BK, D, 0, 1);     // 128 x D, B MN-major
+      const int a_half = cq / 2;
+      const int a_begin = ai == 0 ? 0 : a_half, a_end = ai == 0 ? a_half : cq;
+      const uint64_t dPTa = tc::make_sdesc(smem_u32(smem + Cfg::oPT), BK * 16, 128, tc::kLayoutNone);
+      const uint64_t dDCa = tc::make_sdesc(smem_u32(smem + Cfg::oDCT), BK * 16, 128, tc::kLayoutNone);
+      const uint32_t pt_hi = (uint32_t)(dPTa >> 32), pt_lo = (uint32_t)dPTa, dc_lo = (uint32_t)dDCa;
+      bool ok = true;
+      for (int it = 0; it < nblk && ok; ++it) {
+        const int st = it % NSTG, ph = (it / NSTG) & 1;
+        const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
+        const uint64_t dQm = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, 128, QR * 16, tc::kLayoutNone);   // MN-major, K = rows
+        const uint64_t dOk = tc::make_sdesc(sg + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
+        const uint32_t qm_hi = (uint32_t)(dQm >> 32), qm_lo = (uint32_t)dQm;
+        const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
+        const uint32_t acc_on = it != 0;
+        if (!tc::mbar_wait(&full[st], ph, s_abort)) { ok = false; break; }
+        if (!tc::mbar_wait(pdc_full, it & 1, s_abort)) { ok = false; break; }
+        tc::tc_fence_after();
+        if (ai == 0) {
+          tc::mma_ss2p(tmem, pt_lo, pt_hi, o_lo, o_hi, idescA, acc_on);
+#pragma unroll
+          for (int k = 1; k < BR / 16; ++k)
+            tc::mma_ss2<1>(tmem, pt_lo + (uint32_t)(2 * k * BK), pt_hi, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
+        }
+        for (int a = a_begin; a < a_end; ++a) {
+          const uint32_t dacc = tmem + 64 * (1 + a);
+          const uint32_t b_lo = qm_lo + (uint32_t)a;
+          tc::mma_ss2p(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA, acc_on);
+#pragma unroll
+          for (int k = 1; k < BR / 16; ++k)
+            tc::mma_ss2<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idescA);
+        }
+        tc::mma_commit(&empty[st]);
+        tc::mma_commit(pdc_free);
+      }
       if (ok) tc::mma_commit(all_done);
     }
   } else {

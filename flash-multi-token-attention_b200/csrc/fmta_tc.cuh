@@ -161,6 +161,18 @@ FMTA_DEVINL void mma_ss2(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t
       ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC)
       : "memory");
 }
+// Same with the accumulate flag in a register (no branch around the first MMA of a chain).
+FMTA_DEVINL void mma_ss2p(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // A operand in tensor memory (128 lanes = rows, each 32-bit column = 2 consecutive K elements),
 // B in shared memory.
 template <int ACC>
