@@ -237,21 +237,29 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
       if (int s = check_cuda(launch_reduce_partials(p.dW_part, dW, slots_ex, H * G, st))) return s;
     return FMTA_OK;
   }
-  // tensor-core kernels for the entries off the causal band, exact kernels (accumulating) on it
+  // tensor-core kernels for the entries off the causal band, then the band kernel adds its part
+  const bool lean_band = bwd_band_supported(p);
   band_geometry(p.cq, p.ck, &p.band_off, &p.band_ownq, &p.band_ownk);
-  slots_ex = B * ((N + p.band_ownq - 1) / p.band_ownq);   // one dTheta partial per band CTA
+  slots_ex = lean_band ? bwd_band_theta_slots(B, N, p.cq, p.ck)
+                       : B * ((N + p.band_ownq - 1) / p.band_ownq);   // one dTheta partial per band CTA
   const int slots_tc = bwd_tc_theta_slots(B, N);
   float* part = reinterpret_cast<float*>(workspace);
   const size_t part_bytes = ((size_t)(slots_ex + slots_tc) * n_theta * sizeof(float) + 1023) / 1024 * 1024;
   void* tcw = reinterpret_cast<unsigned char*>(workspace) + part_bytes;
   if (int s = check_cuda(launch_bwd_dq_tc(p, tcw, st))) return s;
   if (int s = check_cuda(launch_bwd_dkdv_tc(p, tcw, part + (size_t)slots_ex * n_theta, st))) return s;
-  p.kmode = kBandTiles;
-  p.accumulate = 1;
   p.n_slots = slots_ex;
   p.dTheta_part = part;
-  if (int s = check_cuda(launch_bwd_dq(p, st))) return s;
-  if (int s = check_cuda(launch_bwd_dkdv(p, st))) return s;
+  if (lean_band && causal) {
+    if (int s = check_cuda(launch_bwd_band(p, st))) return s;
+  } else if (lean_band) {
+    if (int s = check_cuda(cudaMemsetAsync(part, 0, (size_t)slots_ex * n_theta * sizeof(float), st))) return s;
+  } else {
+    p.kmode = kBandTiles;
+    p.accumulate = 1;
+    if (int s = check_cuda(launch_bwd_dq(p, st))) return s;
+    if (int s = check_cuda(launch_bwd_dkdv(p, st))) return s;
+  }
   return check_cuda(launch_reduce_partials(part, dTheta, slots_ex + slots_tc, (int)n_theta, st));
 }
 
