@@ -57,6 +57,14 @@ inline int bwd_band_positions(int cq, int ck) {
   return r < bandcfg::RC ? r : bandcfg::RC;
 }
 
+#ifdef FMTA_TC_TRACE
+__device__ long long g_trace_band[16];
+#define TRACEK(slot) do { if (blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_trace_band[(slot)] = clock64(); } while (0)
+#else
+#define TRACEK(slot) do {} while (0)
+#endif
+
+template <int CQ, int CK>   // filter shape at compile time, or (0, 0): read from the parameters
 __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainParams p) {
   using namespace bandcfg;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -74,7 +82,7 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   float* sRed = reinterpret_cast<float*>(smem + oRed);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int N = p.N, H = p.H, cq = p.cq, ck = p.ck;
+  const int N = p.N, H = p.H, cq = (CQ > 0) ? CQ : p.cq, ck = (CQ > 0) ? CK : p.ck;
   const int pq = cq - 1, pk = (ck - 1) / 2, band = pq + pk, W = band + pk;
   const int R = min(RC, RC - (W - 1 + pq));
   const int h = blockIdx.y, b = blockIdx.z;
@@ -85,6 +93,7 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   const bf16* Vg = p.V + bh * (size_t)N * D;
   const bf16* dOg = p.dO + bh * (size_t)N * D;
 
+  TRACEK(0);
   load_rows_async<D, NT>(sQ, LD, Qg, t0 - 16, RS, N, tid);
   load_rows_async<D, NT>(sK, LD, Kg, t0 - 48, RK, N, tid);
   load_rows_async<D, NT>(sV, LD, Vg, t0 - 16, RS, N, tid);
@@ -99,6 +108,7 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   }
   cp_async_wait<0>();
   __syncthreads();
+  TRACEK(1);
 
   // ---- Sb and dPb on 16 x 16 tiles along the diagonal ----
   {
@@ -139,60 +149,111 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
     }
   }
   __syncthreads();
+  TRACEK(2);
 
   // ---- the padded dC rows take over the V buffer ----
   for (int i = tid; i < RC * DC_LD; i += NT) sdC[i] = 0.f;
   __syncthreads();
+  TRACEK(3);
 
-  // ---- conv, P and dC: one (row, diagonal) pair at a time ----
-  for (int o = tid; o < RC * band; o += NT) {
-    const int x = o / band, dd = o - x * band;
-    const int gi = t0 + x;
-    float c = 0.f;
-    for (int a = 0; a < cq; ++a) {
-      const float* row = sSb + (x + 16 - pq + a) * SB_LD + band + dd + a - pq + pk;
-      const float* th = sTheta + a * kThetaLdBand;
-      for (int bb = 0; bb < ck; ++bb) c = fmaf(th[bb], row[-bb], c);
+  // ---- conv, P and dC: (row, diagonal) pairs, KC per thread side by side for ILP ----
+  if (band > 0) {
+    constexpr int KC = (CQ > 0) ? (RC * (CQ - 1 + (CK - 1) / 2) + NT - 1) / NT : (RC * MAXBAND + NT - 1) / NT;
+    const int nout = RC * band;
+    float c[KC];
+    const float* rp[KC];
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+      const int o = min(tid + k * NT, nout - 1);
+      const int x = o / band, dd = o - x * band;
+      rp[k] = sSb + (x + 16 - pq) * SB_LD + band + dd - pq + pk;
+      c[k] = 0.f;
     }
-    const bool live = (gi < N) && (gi - dd >= 0);
-    const float pr = live ? exp2f(c * kLog2e - sLse[x]) : 0.f;
-    const float dp = sP[x * P_LD + dd];
-    sP[x * P_LD + dd] = pr;
-    sdC[x * DC_LD + pk + dd] = pr * (dp - sDv[x]);
+#pragma unroll
+    for (int a = 0; a < cq; ++a) {
+      const float* th = sTheta + a * kThetaLdBand;
+#pragma unroll
+      for (int bb = 0; bb < ck; ++bb) {
+        const float w = th[bb];
+#pragma unroll
+        for (int k = 0; k < KC; ++k) c[k] = fmaf(w, rp[k][a * (SB_LD + 1) - bb], c[k]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+      const int o = tid + k * NT;
+      if (o < nout) {
+        const int x = o / band, dd = o - x * band;
+        const int gi = t0 + x;
+        const bool live = (gi < N) && (gi - dd >= 0);
+        const float pr = live ? exp2f(c[k] * kLog2e - sLse[x]) : 0.f;
+        const float dp = sP[x * P_LD + dd];
+        sP[x * P_LD + dd] = pr;
+        sdC[x * DC_LD + pk + dd] = pr * (dp - sDv[x]);
+      }
+    }
   }
   __syncthreads();
+  TRACEK(4);
 
-  // ---- dTheta: one thread per tap, row groups in parallel ----
+  // ---- dTheta: one thread per tap, row groups in parallel; the columns past the band are zero ----
   {
     const int ntaps = cq * ck;
     const int ngroups = NT / ntaps;
     const int g = tid / ntaps, tap = tid - g * ntaps;
-    float t = 0.f;
+    float t0s = 0.f, t1s = 0.f;
     if (g < ngroups) {
       const int a = tap / ck, bb = tap - a * ck;
-      for (int x = g; x < R; x += ngroups) {
-        const float* rs = sSb + (x + 16 - pq + a) * SB_LD + band + a - pq + pk - bb;
-        const float* rc = sdC + x * DC_LD + pk;
-        for (int dd = 0; dd < band; ++dd) t = fmaf(rc[dd], rs[dd], t);
+      const float* rs = sSb + (16 - pq + a) * SB_LD + band + a - pq + pk - bb;
+      const float* rc = sdC + pk;
+      constexpr int NB = (CQ > 0) ? (CQ - 1 + (CK - 1) / 2) : MAXBAND;
+      int x = g;
+      for (; x + ngroups < R; x += 2 * ngroups) {
+        const float* rs0 = rs + x * SB_LD; const float* rc0 = rc + x * DC_LD;
+        const float* rs1 = rs0 + ngroups * SB_LD; const float* rc1 = rc0 + ngroups * DC_LD;
+#pragma unroll
+        for (int dd = 0; dd < NB; ++dd) { t0s = fmaf(rc0[dd], rs0[dd], t0s); t1s = fmaf(rc1[dd], rs1[dd], t1s); }
+      }
+      if (x < R) {
+        const float* rs0 = rs + x * SB_LD; const float* rc0 = rc + x * DC_LD;
+#pragma unroll
+        for (int dd = 0; dd < NB; ++dd) t0s = fmaf(rc0[dd], rs0[dd], t0s);
       }
     }
-    sRed[tid] = t;
+    sRed[tid] = t0s + t1s;
   }
+  TRACEK(5);
   // ---- adjoint conv: dSb[i', e] for the rows that feed the owned positions ----
-  {
-    const int nrows = R + W - 1;
-    for (int o = tid; o < nrows * W; o += NT) {
+  if (W > 0) {
+    constexpr int KA = (CQ > 0) ? ((RC - (CQ - 1)) * (CQ - 1 + CK - 1) + NT - 1) / NT : (RC * MAXW + NT - 1) / NT;
+    const int nout = (R + W - 1) * W;
+    float sacc[KA];
+    const float* rp[KA];
+#pragma unroll
+    for (int k = 0; k < KA; ++k) {
+      const int o = min(tid + k * NT, nout - 1);
       const int xr = o / W, e = o - xr * W;
-      float s = 0.f;
-      for (int a = 0; a < cq; ++a) {
-        const float* row = sdC + (xr + pq - a) * DC_LD + e - a + pq;   // column pk + (e - a + pq - pk + b)
-        const float* th = sTheta + a * kThetaLdBand;
-        for (int bb = 0; bb < ck; ++bb) s = fmaf(th[bb], row[bb], s);
+      rp[k] = sdC + (xr + pq) * DC_LD + e + pq;   // tap (a, b) reads column pk + (e - a + pq - pk + b) of row xr + pq - a
+      sacc[k] = 0.f;
+    }
+#pragma unroll
+    for (int a = 0; a < cq; ++a) {
+      const float* th = sTheta + a * kThetaLdBand;
+#pragma unroll
+      for (int bb = 0; bb < ck; ++bb) {
+        const float w = th[bb];
+#pragma unroll
+        for (int k = 0; k < KA; ++k) sacc[k] = fmaf(w, rp[k][bb - a * (DC_LD + 1)], sacc[k]);
       }
-      sdS[xr * DS_LD + e] = s * p.scale;
+    }
+#pragma unroll
+    for (int k = 0; k < KA; ++k) {
+      const int o = tid + k * NT;
+      if (o < nout) sdS[(o / W) * DS_LD + (o % W)] = sacc[k] * p.scale;
     }
   }
   __syncthreads();
+  TRACEK(6);
   {
     const int ntaps = cq * ck;
     if (tid < ntaps) {
@@ -203,35 +264,52 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
       p.dTheta_part[((size_t)slot * H + h) * ntaps + tid] = t;
     }
   }
+  TRACEK(7);
 
-  // ---- dQ, dK, dV of the owned positions: one warp per position, two head dims per lane ----
-  for (int xr = warp; xr < R; xr += NT / 32) {
-    const int t = t0 + xr;
-    if (t >= N) break;
-    float* gq = p.dQ + (bh * N + t) * D + 2 * lane;
-    float* gk = p.dK + (bh * N + t) * D + 2 * lane;
-    float* gv = p.dV + (bh * N + t) * D + 2 * lane;
-    float2 aq = *reinterpret_cast<const float2*>(gq);
-    float2 ak = *reinterpret_cast<const float2*>(gk);
-    float2 av = *reinterpret_cast<const float2*>(gv);
+  // ---- dQ, dK, dV of the owned positions: one warp per position (two at a time), two head dims per lane ----
+  for (int xr0 = warp; xr0 < R; xr0 += 2 * (NT / 32)) {
+    const int xr1 = xr0 + NT / 32;
+    const int ta = t0 + xr0, tb = t0 + xr1;
+    if (ta >= N) break;
+    const bool two = (xr1 < R) && (tb < N);
+    const int xb = two ? xr1 : xr0;                       // second position (a repeat of the first when absent)
+    float* ga = p.dQ + (bh * N + ta) * D + 2 * lane;
+    float* gb = p.dQ + (bh * N + t0 + xb) * D + 2 * lane;
+    const ptrdiff_t kofs = p.dK - p.dQ, vofs = p.dV - p.dQ;  // element offsets between the three outputs
+    float2 aq0 = *reinterpret_cast<const float2*>(ga), ak0 = *reinterpret_cast<const float2*>(ga + kofs), av0 = *reinterpret_cast<const float2*>(ga + vofs);
+    float2 aq1 = *reinterpret_cast<const float2*>(gb), ak1 = *reinterpret_cast<const float2*>(gb + kofs), av1 = *reinterpret_cast<const float2*>(gb + vofs);
+#pragma unroll 3
     for (int e = 0; e < W; ++e) {
-      const float s1 = sdS[xr * DS_LD + e];
-      const __nv_bfloat162 kk = *reinterpret_cast<const __nv_bfloat162*>(sK + (xr + 48 - e) * LD + 2 * lane);
-      aq.x = fmaf(s1, __low2float(kk), aq.x); aq.y = fmaf(s1, __high2float(kk), aq.y);
-      const float s2 = sdS[(xr + e) * DS_LD + e];
-      const __nv_bfloat162 qq = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xr + 16 + e) * LD + 2 * lane);
-      ak.x = fmaf(s2, __low2float(qq), ak.x); ak.y = fmaf(s2, __high2float(qq), ak.y);
+      const float s10 = sdS[xr0 * DS_LD + e], s11 = sdS[xb * DS_LD + e];
+      const float s20 = sdS[(xr0 + e) * DS_LD + e], s21 = sdS[(xb + e) * DS_LD + e];
+      const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xr0 + 48 - e) * LD + 2 * lane);
+      const __nv_bfloat162 k1 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xb + 48 - e) * LD + 2 * lane);
+      const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xr0 + 16 + e) * LD + 2 * lane);
+      const __nv_bfloat162 q1 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xb + 16 + e) * LD + 2 * lane);
+      aq0.x = fmaf(s10, __low2float(k0), aq0.x); aq0.y = fmaf(s10, __high2float(k0), aq0.y);
+      aq1.x = fmaf(s11, __low2float(k1), aq1.x); aq1.y = fmaf(s11, __high2float(k1), aq1.y);
+      ak0.x = fmaf(s20, __low2float(q0), ak0.x); ak0.y = fmaf(s20, __high2float(q0), ak0.y);
+      ak1.x = fmaf(s21, __low2float(q1), ak1.x); ak1.y = fmaf(s21, __high2float(q1), ak1.y);
     }
+#pragma unroll 2
     for (int dd = 0; dd < band; ++dd) {
-      const float pr = sP[(xr + dd) * P_LD + dd];
-      const __nv_bfloat162 oo = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xr + dd) * LD + 2 * lane);
-      av.x = fmaf(pr, __low2float(oo), av.x); av.y = fmaf(pr, __high2float(oo), av.y);
+      const float p0 = sP[(xr0 + dd) * P_LD + dd], p1 = sP[(xb + dd) * P_LD + dd];
+      const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xr0 + dd) * LD + 2 * lane);
+      const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xb + dd) * LD + 2 * lane);
+      av0.x = fmaf(p0, __low2float(o0), av0.x); av0.y = fmaf(p0, __high2float(o0), av0.y);
+      av1.x = fmaf(p1, __low2float(o1), av1.x); av1.y = fmaf(p1, __high2float(o1), av1.y);
     }
-    *reinterpret_cast<float2*>(gq) = aq;
-    *reinterpret_cast<float2*>(gk) = ak;
-    *reinterpret_cast<float2*>(gv) = av;
+    *reinterpret_cast<float2*>(ga) = aq0; *reinterpret_cast<float2*>(ga + kofs) = ak0; *reinterpret_cast<float2*>(ga + vofs) = av0;
+    if (two) { *reinterpret_cast<float2*>(gb) = aq1; *reinterpret_cast<float2*>(gb + kofs) = ak1; *reinterpret_cast<float2*>(gb + vofs) = av1; }
   }
+  TRACEK(8);
 }
+
+#ifdef FMTA_TC_TRACE
+extern "C" int fmta_debug_trace_band(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace_band, sizeof(long long) * n);
+}
+#endif
 
 bool bwd_band_supported(const TrainParams& p) {
   const int pq = p.cq - 1, pk = (p.ck - 1) / 2;
@@ -249,7 +327,9 @@ cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream) {
   const int R = bwd_band_positions(p.cq, p.ck);
   dim3 grid((p.N + R - 1) / R, p.H, p.B);
   ScopedKernelTimer timer_(kKernBwdBand, stream);
-  return launch_kernel<TrainParams>(bwd_band_kernel, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
+  if (p.cq == 6 && p.ck == 11)
+    return launch_kernel<TrainParams>(bwd_band_kernel<6, 11>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
+  return launch_kernel<TrainParams>(bwd_band_kernel<0, 0>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
 }
 
 }  // namespace fmta

@@ -61,7 +61,7 @@ const char* fmta_strerror(int status) {
 int fmta_last_cuda_error(void) { return g_last_cuda_error; }
 
 int fmta_profile_kernel(int kernel_id, void* start_event, void* stop_event) {
-  if (kernel_id < 0 || kernel_id > 7) return FMTA_ERR_SHAPE;
+  if (kernel_id < 0 || kernel_id > 8) return FMTA_ERR_SHAPE;
   if (kernel_id != 0 && (!start_event || !stop_event)) return FMTA_ERR_NULL;
   g_profile_hook.id = kernel_id;
   g_profile_hook.start = (cudaEvent_t)start_event;
