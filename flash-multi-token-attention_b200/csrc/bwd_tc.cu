@@ -70,7 +70,7 @@ struct DqCfg {
   static constexpr int oBar = oRing + NSLOT * TILE_BYTES;
   static constexpr int kSmemBytes = oBar + 512 + 1024;
   static constexpr int kTmemCols = 512;        // per tile t: S at 192t, dP at 192t+64, dQ at 192t+128
-  static constexpr int kThreads = (NT * 4 + 1 + NT) * 32;
+  static constexpr int kThreads = (NT * 4 + 1 + 2 * NT) * 32;   // element-wise warps, TMA warp, two MMA issuer warps per tile
 };
 
 template <int D>
@@ -89,7 +89,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   unsigned char* sRing = smem + Cfg::oRing;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::oBar);
   uint64_t* full = bars;                 // [NSLOT]
-  uint64_t* empty = bars + NSLOT;        // [NSLOT]  count NT
+  uint64_t* empty = bars + NSLOT;        // [NSLOT]  count 2 NT
   uint64_t* q_full = bars + 2 * NSLOT;   // Q and dO staged
   uint64_t* sdp_full = q_full + 1;       // [NT] S and dP of the block complete
   uint64_t* s_free = sdp_full + 2;       // [NT] S and dP taken into registers (128 arrivals)
@@ -121,7 +121,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int nkb = max(nkb_t[0], nkb_t[1]);
 
   if (tid == 0) {
-    for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], NT); }
+    for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 2 * NT); }   // every issuer releases every tile
     tc::mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&sdp_full[i], 1); tc::mbar_init(&s_free[i], BM); tc::mbar_init(&dc_full[i], BM);
@@ -167,8 +167,12 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp > NT * 4) {
-    // ===================== MMA issuers: one per row tile =====================
-    const int t = warp - (NT * 4 + 1);
+    // ===================== MMA issuers: two per row tile =====================
+    // One thread issues an MMA every 50-100 clocks whatever its size, so S/dP and dQ of a tile
+    // are issued by different warps (warps NT*4+1+t: S and dP; warps NT*4+1+NT+t: dQ).
+    const int wi = warp - (NT * 4 + 1);
+    const int t = wi % NT;
+    const bool is_dq = wi >= NT;
     if (lane == 0 && nkb > 0) {
       constexpr uint32_t idescS = tc::make_idesc(BM, BC, 0, 0);    // S, dP: 128 x 64, both K-major
       constexpr uint32_t idescQ = tc::make_idesc(BM, D, 0, 1);     // dQ: 128 x D, B (Kt) MN-major
@@ -184,31 +188,30 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int my_nkb = nkb_t[t];
       const int per = cq + 1;                                // ring tiles per key block
       bool ok = tc::mbar_wait(q_full, 0, s_abort);
-      auto issue_SdP = [&](int kb) {
-        const bool active = kb < my_nkb;
-        if (active && kb > 0) {
-          ok = tc::mbar_wait(&s_free[t], (kb - 1) & 1, s_abort);
-          tc::tc_fence_after();
-        }
-        for (int a = 0; a < cq && ok; ++a) {
-          const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
-          if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
-          if (active) {
+      if (!is_dq) {
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          const bool active = kb < my_nkb;
+          if (active && kb > 0) {
+            ok = tc::mbar_wait(&s_free[t], (kb - 1) & 1, s_abort);
             tc::tc_fence_after();
-            const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
-            const uint32_t a_lo = q_lo + (uint32_t)a;
-            if (a == 0) tc::mma_ss2<0>(tS, a_lo, q_hi, b_lo, k_hi, idescS);
-            else tc::mma_ss2<1>(tS, a_lo, q_hi, b_lo, k_hi, idescS);
-#pragma unroll
-            for (int k = 1; k < D / 16; ++k)
-              tc::mma_ss2<1>(tS, a_lo + (uint32_t)(2 * k * QR), q_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
           }
-          // the Kt tile stays in shared memory: it is the B operand of dQ(kb) as well
-        }
-        if (!ok) return;
-        {
+          for (int a = 0; a < cq && ok; ++a) {
+            const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
+            if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
+            if (active) {
+              tc::tc_fence_after();
+              const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
+              const uint32_t a_lo = q_lo + (uint32_t)a;
+              tc::mma_ss2p(tS, a_lo, q_hi, b_lo, k_hi, idescS, a != 0);
+#pragma unroll
+              for (int k = 1; k < D / 16; ++k)
+                tc::mma_ss2<1>(tS, a_lo + (uint32_t)(2 * k * QR), q_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
+            }
+            tc::mma_commit(&empty[slot]);      // (the dQ issuers hold the Kt tile until dQ(kb) is done)
+          }
+          if (!ok) break;
           const int id = kb * per + cq, slot = id % NSLOT, ph = (id / NSLOT) & 1;
-          if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
+          if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
           if (active) {
             tc::tc_fence_after();
             const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
@@ -220,32 +223,35 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc::mma_commit(&empty[slot]);
           if (active) tc::mma_commit(&sdp_full[t]);
         }
-      };
-      auto issue_dQ = [&](int kb) {
-        const bool active = kb < my_nkb;
-        if (active) {
-          ok = tc::mbar_wait(&dc_full[t], kb & 1, s_abort);
-          tc::tc_fence_after();
-        }
-        for (int a = 0; a < cq && ok; ++a) {
-          const int id = kb * per + a, slot = id % NSLOT;
+      } else {
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          const bool active = kb < my_nkb;
           if (active) {
-            const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
-            const uint32_t a_lo = c_lo + (uint32_t)(pq - a);       // dC rows i' + pad_q - a
-            if (kb == 0 && a == 0) tc::mma_ss2<0>(tQ, a_lo, c_hi, b_lo, k_hi, idescQ);
-            else tc::mma_ss2<1>(tQ, a_lo, c_hi, b_lo, k_hi, idescQ);
-#pragma unroll
-            for (int k = 1; k < BC / 16; ++k)
-              tc::mma_ss2<1>(tQ, a_lo + (uint32_t)(2 * k * DR), c_hi, b_lo + (uint32_t)(k * (2048 / 16)), k_hi, idescQ);
+            ok = tc::mbar_wait(&dc_full[t], kb & 1, s_abort);
+            tc::tc_fence_after();
           }
-          tc::mma_commit(&empty[slot]);
+          for (int a = 0; a < cq && ok; ++a) {
+            const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
+            if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
+            if (active) {
+              tc::tc_fence_after();
+              const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
+              const uint32_t a_lo = c_lo + (uint32_t)(pq - a);       // dC rows i' + pad_q - a
+              tc::mma_ss2p(tQ, a_lo, c_hi, b_lo, k_hi, idescQ, (kb != 0) || (a != 0));
+#pragma unroll
+              for (int k = 1; k < BC / 16; ++k)
+                tc::mma_ss2<1>(tQ, a_lo + (uint32_t)(2 * k * DR), c_hi, b_lo + (uint32_t)(k * (2048 / 16)), k_hi, idescQ);
+            }
+            tc::mma_commit(&empty[slot]);
+          }
+          if (!ok) break;
+          {   // the V tile of the block is not read here: release it right away
+            const int id = kb * per + cq, slot = id % NSLOT, ph = (id / NSLOT) & 1;
+            if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
+            tc::mbar_arrive(&empty[slot]);
+          }
+          if (active) tc::mma_commit(&dq_done[t]);
         }
-        if (ok && active) tc::mma_commit(&dq_done[t]);
-      };
-      if (ok) issue_SdP(0);
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        if (kb + 1 < nkb) issue_SdP(kb + 1);
-        if (ok) issue_dQ(kb);
       }
     }
   } else {
