@@ -34,8 +34,11 @@ constexpr float kLn2 = 0.6931471805599453f;
 #ifdef FMTA_TC_TRACE
 __device__ long long g_trace_bwd[16384];
 #define TRACEB(slot) do { if (trace_on) g_trace_bwd[(slot)] = clock64(); } while (0)
+__device__ long long g_cta_times[3 * 8192];
+#define TRACEQ(slot) do { if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) g_trace_bwd[8192 + (slot)] = clock64(); } while (0)
 #else
 #define TRACEB(slot) do {} while (0)
+#define TRACEQ(slot) do {} while (0)
 #endif
 
 struct BwdTcParams {
@@ -99,6 +102,10 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef FMTA_TC_TRACE
+  long long cta_t0 = 0;
+  if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t0));
+#endif
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
   const int band = pq + pk;
   const int rows_per_cta = OWN * NT;
@@ -191,10 +198,12 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!is_dq) {
         for (int kb = 0; kb < nkb && ok; ++kb) {
           const bool active = kb < my_nkb;
+          if (t == 0) TRACEQ(kb * 8 + 0);
           if (active && kb > 0) {
             ok = tc::mbar_wait(&s_free[t], (kb - 1) & 1, s_abort);
             tc::tc_fence_after();
           }
+          if (t == 0) TRACEQ(kb * 8 + 1);
           for (int a = 0; a < cq && ok; ++a) {
             const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
             if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
@@ -222,14 +231,17 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
           tc::mma_commit(&empty[slot]);
           if (active) tc::mma_commit(&sdp_full[t]);
+          if (t == 0) TRACEQ(kb * 8 + 2);
         }
       } else {
         for (int kb = 0; kb < nkb && ok; ++kb) {
           const bool active = kb < my_nkb;
+          if (t == 0) TRACEQ(kb * 8 + 3);
           if (active) {
             ok = tc::mbar_wait(&dc_full[t], kb & 1, s_abort);
             tc::tc_fence_after();
           }
+          if (t == 0) TRACEQ(kb * 8 + 4);
           for (int a = 0; a < cq && ok; ++a) {
             const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
             if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
@@ -251,6 +263,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tc::mbar_arrive(&empty[slot]);
           }
           if (active) tc::mma_commit(&dq_done[t]);
+          if (t == 0) TRACEQ(kb * 8 + 5);
         }
       }
     }
@@ -268,9 +281,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     unsigned char* cbuf = sdC + t * ((BC / 8) * DR * 16) + m * 16;
     bool ok = true;
     for (int kb = 0; kb < my_nkb && ok; ++kb) {
+      if (tid == 0) TRACEQ(1024 + kb * 8 + 0);
       ok = __all_sync(0xffffffffu, tc::mbar_wait(&sdp_full[t], kb & 1, s_abort));
       if (!ok) break;
       tc::tc_fence_after();
+      if (tid == 0) TRACEQ(1024 + kb * 8 + 1);
       float s[BC], dp[BC];
       {
         float t0[32], t1[32], t2[32], t3[32];
@@ -282,6 +297,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       tc::tc_fence_before();
       tc::mbar_arrive(&s_free[t]);
+      if (tid == 0) TRACEQ(1024 + kb * 8 + 2);
       const int j0 = kb * BC;
       const int jlim = row_ok ? (p.causal ? min(N - 1, gi - band) : N - 1) : -1;   // last key owned here
       uint32_t pk32[BC / 2];
@@ -293,15 +309,18 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (j0 + i + 1 > jlim) c1 = 0.f;
         pk32[i / 2] = pack_bf16(c0, c1);
       }
+      if (tid == 0) TRACEQ(1024 + kb * 8 + 3);
       if (kb > 0) {   // dQ(kb-1) has finished reading the dC buffer
         ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (kb - 1) & 1, s_abort));
         if (!ok) break;
       }
+      if (tid == 0) TRACEQ(1024 + kb * 8 + 4);
 #pragma unroll
       for (int kc = 0; kc < BC / 8; ++kc)
         *reinterpret_cast<uint4*>(cbuf + kc * (DR * 16)) = make_uint4(pk32[4 * kc], pk32[4 * kc + 1], pk32[4 * kc + 2], pk32[4 * kc + 3]);
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(&dc_full[t]);
+      if (tid == 0) TRACEQ(1024 + kb * 8 + 5);
     }
     // ---- epilogue: the 112 owned dQ rows of this tile ----
     if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (my_nkb - 1) & 1, s_abort));
@@ -329,6 +348,15 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   tc::tc_fence_before();
   __syncthreads();
+#ifdef FMTA_TC_TRACE
+  if (tid == 0) {
+    long long cta_t1; unsigned smid;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t1));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    const int cid = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (cid < 8192) { g_cta_times[3 * cid] = cta_t0; g_cta_times[3 * cid + 1] = cta_t1; g_cta_times[3 * cid + 2] = smid; }
+  }
+#endif
   if (*s_abort && tid == 0) atomicExch(p.status, 1);
   if (warp == NT * 4 + 1) {
     tc::tc_fence_after();
@@ -799,6 +827,9 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
 int bwd_tc_theta_slots(int B, int N) { return B * ((N + 31) / 32); }
 
 #ifdef FMTA_TC_TRACE
+extern "C" int fmta_debug_cta_times(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_cta_times, sizeof(long long) * n);
+}
 extern "C" int fmta_debug_trace_bwd(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_trace_bwd, sizeof(long long) * n);
 }

@@ -78,6 +78,56 @@ __global__ void __launch_bounds__(256) ktilde_kernel(const bf16* __restrict__ K,
   *reinterpret_cast<uint4*>(Kt + (((size_t)bh * cq + a) * N + j) * D + c * 8) = o;
 }
 
+// Same pre-pass with the filter width known at compile time: one thread owns one 16-byte column
+// chunk of RR consecutive rows and produces all c_q taps from a register window of RR + CK - 1
+// key rows, so every key row is loaded once per RR outputs instead of once per output and tap.
+template <int D, int CK, int RR>
+__global__ void __launch_bounds__(256) ktilde_window_kernel(const bf16* __restrict__ K, const float* __restrict__ theta,
+                                                            bf16* __restrict__ Kt, int H, int N, int cq, float scale) {
+  constexpr int CPR = D / 8, RUNS = 256 / CPR, PK = (CK - 1) / 2, WIN = RR + CK - 1;
+  __shared__ float sTh[16 * CK];
+  const int bh = blockIdx.y, h = bh % H;
+  for (int i = threadIdx.x; i < cq * CK; i += 256) sTh[i] = theta[(size_t)h * cq * CK + i] * scale;
+  __syncthreads();
+  const int j0 = (blockIdx.x * RUNS + threadIdx.x / CPR) * RR, c = threadIdx.x % CPR;
+  if (j0 >= N) return;
+  const bf16* Kb = K + (size_t)bh * N * D + c * 8;
+  uint4 win[WIN];
+#pragma unroll
+  for (int r = 0; r < WIN; ++r) {
+    const int jj = j0 + r - PK;
+    win[r] = (jj >= 0 && jj < N) ? *reinterpret_cast<const uint4*>(Kb + (size_t)jj * D) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (int a = 0; a < cq; ++a) {
+    float w[CK];
+#pragma unroll
+    for (int b = 0; b < CK; ++b) w[b] = sTh[a * CK + b];
+    bf16* out = Kt + (((size_t)bh * cq + a) * N + j0) * D + c * 8;
+#pragma unroll
+    for (int r = 0; r < RR; ++r) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (int b = 0; b < CK; ++b) {
+        const uint4 kv = win[r + b];
+        const uint32_t w32[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] = fmaf(w[b], __uint_as_float(w32[e] << 16), acc[2 * e]);
+          acc[2 * e + 1] = fmaf(w[b], __uint_as_float(w32[e] & 0xffff0000u), acc[2 * e + 1]);
+        }
+      }
+      if (j0 + r < N) {
+        uint4 o;
+        o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(out + (size_t)r * D) = o;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 struct TcParams {
   float* Opart;   // [B,H,N,D] un-normalised
@@ -476,14 +526,28 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, s
 // Pre-pass: Kt = scale * log2(e) * (theta applied along the key axis of K), c_q bf16 copies.
 cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream) {
   const size_t BH = (size_t)p.B * p.H;
+  const float sc = p.scale * kLog2e;
+  if (p.ck == 11 && p.cq <= 16) {
+    constexpr int RR = 8;
+    if (p.d == 64) {
+      constexpr int RUNS = 256 / (64 / 8);
+      dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);
+      ktilde_window_kernel<64, 11, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
+    } else {
+      constexpr int RUNS = 256 / (128 / 8);
+      dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);
+      ktilde_window_kernel<128, 11, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
+    }
+    return cudaGetLastError();
+  }
   if (p.d == 64) {
     constexpr int RPB = 256 / (64 / 8);
     dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH, p.cq);
-    ktilde_kernel<64><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale * kLog2e);
+    ktilde_kernel<64><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, sc);
   } else {
     constexpr int RPB = 256 / (128 / 8);
     dim3 grid((p.N + RPB - 1) / RPB, (unsigned)BH, p.cq);
-    ktilde_kernel<128><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, p.scale * kLog2e);
+    ktilde_kernel<128><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, p.ck, sc);
   }
   return cudaGetLastError();
 }
