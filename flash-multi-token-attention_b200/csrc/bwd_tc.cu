@@ -741,12 +741,105 @@ __global__ void __launch_bounds__(256) dk_post_kernel(const float* __restrict__ 
   }
 }
 
+// Same adjoint with the filter width known at compile time.  A CTA owns 64 keys; the dKt_a rows
+// it needs (64 + CK - 1, fp32) are staged in shared memory with cp.async, double-buffered over
+// the filter rows a, so the loads of tap a+1 overlap the arithmetic of tap a.  One thread owns a
+// 4-float column chunk of RR consecutive keys and keeps its RR + CK - 1 rows of dKt_a and of K
+// (bf16, read once from global memory) in registers; the dTheta terms are summed per thread over its rows and leave the warp through
+// one reduction per filter row.
+template <int D, int CK, int RR>
+__global__ void __launch_bounds__(256) dk_post_window_kernel(const float* __restrict__ dKt, const bf16* __restrict__ K,
+                                                             const float* __restrict__ theta, float* __restrict__ dK,
+                                                             float* __restrict__ dTheta_part, int H, int N, int cq,
+                                                             float scale, int n_jblocks) {
+  constexpr int CPR = D / 4, RUNS = 256 / CPR, PK = (CK - 1) / 2, WIN = RR + CK - 1;
+  constexpr int ROWS = RUNS * RR, TR = ROWS + CK - 1;     // keys per CTA, rows staged
+  __shared__ __align__(16) float sT[2][TR * D];
+  __shared__ float sTh[6 * CK];
+  __shared__ float sRed[8][6 * CK];
+  const int bh = blockIdx.y, h = bh % H, b = bh / H;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int J0 = blockIdx.x * ROWS;
+  auto stage = [&](int a, int buf) {
+    const float* src = dKt + (((size_t)bh * cq + a) * N) * D;
+    for (int i = tid; i < TR * (D / 4); i += 256) {
+      const int r = i / (D / 4), ch = i % (D / 4);
+      const int jj = J0 - PK + r;
+      const bool ok = jj >= 0 && jj < N;
+      cp_async16(&sT[buf][r * D + ch * 4], src + (size_t)(ok ? jj : 0) * D + ch * 4, ok);
+    }
+  };
+  stage(0, 0);
+  cp_async_commit();
+  for (int i = tid; i < cq * CK; i += 256) sTh[i] = theta[(size_t)h * cq * CK + i] * scale;
+  const int run = tid / CPR, c = tid % CPR;
+  const int r0 = run * RR;                                 // first row of this thread inside the tile (before the halo shift)
+  uint2 kw[WIN];                                           // the key rows of this thread's window, read once
+#pragma unroll
+  for (int i = 0; i < WIN; ++i) {
+    const int jj = J0 - PK + r0 + i;
+    kw[i] = (jj >= 0 && jj < N) ? *reinterpret_cast<const uint2*>(K + ((size_t)bh * N + jj) * D + c * 4) : make_uint2(0u, 0u);
+  }
+  float dk[RR][4];
+#pragma unroll
+  for (int r = 0; r < RR; ++r) { dk[r][0] = dk[r][1] = dk[r][2] = dk[r][3] = 0.f; }
+  for (int a = 0; a < cq; ++a) {
+    if (a + 1 < cq) stage(a + 1, (a + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const float* tile = sT[a & 1];
+    float4 dw[WIN];
+#pragma unroll
+    for (int i = 0; i < WIN; ++i) dw[i] = *reinterpret_cast<const float4*>(&tile[(r0 + i) * D + c * 4]);
+    float t[CK];
+#pragma unroll
+    for (int bb = 0; bb < CK; ++bb) {
+      const float w = sTh[a * CK + bb];
+      float tb = 0.f;
+#pragma unroll
+      for (int r = 0; r < RR; ++r) {
+        const float4 u = dw[r - bb + 2 * PK];            // dKt_a[j - bb + pad_k]
+        dk[r][0] = fmaf(w, u.x, dk[r][0]); dk[r][1] = fmaf(w, u.y, dk[r][1]);
+        dk[r][2] = fmaf(w, u.z, dk[r][2]); dk[r][3] = fmaf(w, u.w, dk[r][3]);
+        const float4 own = dw[r + PK];                   // dKt_a[j]
+        const uint2 kk = kw[r + bb];                     // k_{j + bb - pad_k}
+        tb = fmaf(own.x, __uint_as_float(kk.x << 16), tb);
+        tb = fmaf(own.y, __uint_as_float(kk.x & 0xffff0000u), tb);
+        tb = fmaf(own.z, __uint_as_float(kk.y << 16), tb);
+        tb = fmaf(own.w, __uint_as_float(kk.y & 0xffff0000u), tb);
+      }
+      t[bb] = tb;
+    }
+#pragma unroll
+    for (int bb = 0; bb < CK; ++bb) {
+      const float v = warp_sum(t[bb]);
+      if (lane == 0) sRed[warp][a * CK + bb] = v;
+    }
+    __syncthreads();                                       // the buffer of tap a is staged again for tap a+2
+  }
+  const int j0 = J0 + r0;
+#pragma unroll
+  for (int r = 0; r < RR; ++r)
+    if (j0 + r < N) *reinterpret_cast<float4*>(dK + ((size_t)bh * N + j0 + r) * D + c * 4) = make_float4(dk[r][0], dk[r][1], dk[r][2], dk[r][3]);
+  const int slot = b * n_jblocks + blockIdx.x;
+  for (int i = tid; i < cq * CK; i += 256) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sRed[w][i];
+    dTheta_part[((size_t)slot * H + h) * (cq * CK) + i] = t * scale;
+  }
+}
+
 // ==========================================================================================
 // host side
 // ==========================================================================================
 bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128);
 bool tensor_maps_available();
 cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream);
+
+// keys per CTA of the dKt adjoint kernel chosen for a filter width
+static int dk_post_rows_per_cta(int ck) { return ck == 11 ? 64 : 32; }
 
 bool bwd_tc_supported(const TrainParams& p) {
   return p.theta != nullptr && p.Wmix == nullptr && p.d == 64 && p.cq >= 1 && p.cq <= 6 && tensor_maps_available();
@@ -816,15 +909,22 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp); }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  constexpr int RPB = 256 / (D / 8);
-  const int njb = (p.N + RPB - 1) / RPB;
+  const int rpb = dk_post_rows_per_cta(p.ck);
+  const int njb = (p.N + rpb - 1) / rpb;
   dim3 g2(njb, (unsigned)BH);
-  dk_post_kernel<D><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.ck, p.scale, njb);
+  ScopedKernelTimer timer2_(kKernDkPost, stream);
+  if (p.ck == 11)
+    dk_post_window_kernel<D, 11, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
+  else
+    dk_post_kernel<D><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.ck, p.scale, njb);
   return cudaGetLastError();
 }
 
-// slots of dTheta partials written by dk_post_kernel
-int bwd_tc_theta_slots(int B, int N) { return B * ((N + 31) / 32); }
+// slots of dTheta partials written by the dKt adjoint kernel: one per CTA
+int bwd_tc_theta_slots(int B, int N, int ck) {
+  const int rpb = dk_post_rows_per_cta(ck);
+  return B * ((N + rpb - 1) / rpb);
+}
 
 #ifdef FMTA_TC_TRACE
 extern "C" int fmta_debug_cta_times(long long* host, int n) {

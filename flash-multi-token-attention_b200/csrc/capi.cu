@@ -61,7 +61,7 @@ const char* fmta_strerror(int status) {
 int fmta_last_cuda_error(void) { return g_last_cuda_error; }
 
 int fmta_profile_kernel(int kernel_id, void* start_event, void* stop_event) {
-  if (kernel_id < 0 || kernel_id > 8) return FMTA_ERR_SHAPE;
+  if (kernel_id < 0 || kernel_id > 10) return FMTA_ERR_SHAPE;
   if (kernel_id != 0 && (!start_event || !stop_event)) return FMTA_ERR_NULL;
   g_profile_hook.id = kernel_id;
   g_profile_hook.start = (cudaEvent_t)start_event;
@@ -88,7 +88,7 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
     // slot array, rounded up), followed by the tensor-core backward's buffers
     int off, ownq, ownk;
     band_geometry(cq, ck, &off, &ownq, &ownk);
-    const size_t slots = (size_t)B * ((N + ownq - 1) / ownq) + (size_t)bwd_tc_theta_slots(B, N);
+    const size_t slots = (size_t)B * ((N + ownq - 1) / ownq) + (size_t)bwd_tc_theta_slots(B, N, ck);
     const size_t part = (slots * H * (size_t)(cq * ck) * sizeof(float) + 1023) / 1024 * 1024;
     return part + bwd_tc_workspace_bytes(B, H, N, d, cq);
   }
@@ -242,7 +242,7 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
   band_geometry(p.cq, p.ck, &p.band_off, &p.band_ownq, &p.band_ownk);
   slots_ex = lean_band ? bwd_band_theta_slots(B, N, p.cq, p.ck)
                        : B * ((N + p.band_ownq - 1) / p.band_ownq);   // one dTheta partial per band CTA
-  const int slots_tc = bwd_tc_theta_slots(B, N);
+  const int slots_tc = bwd_tc_theta_slots(B, N, p.ck);
   float* part = reinterpret_cast<float*>(workspace);
   const size_t part_bytes = ((size_t)(slots_ex + slots_tc) * n_theta * sizeof(float) + 1023) / 1024 * 1024;
   void* tcw = reinterpret_cast<unsigned char*>(workspace) + part_bytes;

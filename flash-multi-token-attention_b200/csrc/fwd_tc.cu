@@ -525,6 +525,7 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, s
 
 // Pre-pass: Kt = scale * log2(e) * (theta applied along the key axis of K), c_q bf16 copies.
 cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream) {
+  ScopedKernelTimer timer_(kKernKtilde, stream);
   const size_t BH = (size_t)p.B * p.H;
   const float sc = p.scale * kLog2e;
   if (p.ck == 11 && p.cq <= 16) {

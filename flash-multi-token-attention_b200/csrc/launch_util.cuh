@@ -56,7 +56,7 @@ inline cudaError_t launch_kernel(void (*kern)(const P), dim3 grid, dim3 block, s
 // Optional timing hook: when armed for a kernel id, the launcher of that kernel records the two
 // events around the launch on the launch stream (see fmta_profile_kernel in the C ABI).
 enum KernelId : int { kKernNone = 0, kKernFwdTc = 1, kKernFwdExact = 2, kKernBwdDqTc = 3, kKernBwdDkdvTc = 4,
-                      kKernBwdDqExact = 5, kKernBwdDkdvExact = 6, kKernDecode = 7, kKernBwdBand = 8 };
+                      kKernBwdDqExact = 5, kKernBwdDkdvExact = 6, kKernDecode = 7, kKernBwdBand = 8, kKernKtilde = 9, kKernDkPost = 10 };
 struct ProfileHook { int id; cudaEvent_t start, stop; };
 extern ProfileHook g_profile_hook;
 struct ScopedKernelTimer {
@@ -77,7 +77,7 @@ bool bwd_tc_supported(const TrainParams& p);
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
 cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t stream);
 cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream);
-int bwd_tc_theta_slots(int B, int N);
+int bwd_tc_theta_slots(int B, int N, int ck);
 bool bwd_band_supported(const TrainParams& p);
 int bwd_band_theta_slots(int B, int N, int cq, int ck);
 cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream);

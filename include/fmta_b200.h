@@ -69,7 +69,8 @@ int fmta_set_path(int path);
  * Timing hook for benchmarks: while armed, every launch of the chosen kernel is bracketed by
  * cudaEventRecord(start) / cudaEventRecord(stop) on the launch stream, so a caller can time one
  * kernel inside a multi-kernel entry point.  kernel_id: 1 fwd tensor-core, 2 fwd exact, 3 dQ
- * tensor-core, 4 dK/dV tensor-core, 5 dQ exact, 6 dK/dV exact, 7 decode, 8 backward band;
+ * tensor-core, 4 dK/dV tensor-core, 5 dQ exact, 6 dK/dV exact, 7 decode, 8 backward band,
+ * 9 stacked-key pre-pass (last launch of the call), 10 its adjoint;
  * 0 disarms.  The events
  * are cudaEvent_t handles owned by the caller.  Not thread-safe; meant for single-threaded benches.
  */
