@@ -301,13 +301,22 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int j0 = kb * BC;
       const int jlim = row_ok ? (p.causal ? min(N - 1, gi - band) : N - 1) : -1;   // last key owned here
       uint32_t pk32[BC / 2];
+      if (__all_sync(0xffffffffu, j0 + BC - 1 <= jlim)) {      // whole block owned by every row of the warp: no masking
 #pragma unroll
-      for (int i = 0; i < BC; i += 2) {
-        float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
-        float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
-        if (j0 + i > jlim) c0 = 0.f;
-        if (j0 + i + 1 > jlim) c1 = 0.f;
-        pk32[i / 2] = pack_bf16(c0, c1);
+        for (int i = 0; i < BC; i += 2) {
+          const float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
+          const float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
+          pk32[i / 2] = pack_bf16(c0, c1);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BC; i += 2) {
+          float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
+          float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
+          if (j0 + i > jlim) c0 = 0.f;
+          if (j0 + i + 1 > jlim) c1 = 0.f;
+          pk32[i / 2] = pack_bf16(c0, c1);
+        }
       }
       if (tid == 0) TRACEQ(1024 + kb * 8 + 3);
       if (kb > 0) {   // dQ(kb-1) has finished reading the dC buffer
@@ -596,11 +605,16 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc::mbar_arrive(x_free);
       // P^T[key, i] = exp2(S^T - LSE_i), kept only where this kernel owns the entry
       float pv[32];
+      if ((j0 + BK <= N) && (i0 + BR <= N) && (!p.causal || j0 + BK - 1 + band <= i0)) {   // block owned entirely
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const int gi = i0 + 32 * hh + c;
-        const bool own = (key < N) && (gi < N) && (!p.causal || key <= gi - band);
-        pv[c] = own ? exp2f(s[c] - ld[32 * hh + c]) : 0.f;
+        for (int c = 0; c < 32; ++c) pv[c] = exp2f(s[c] - ld[32 * hh + c]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int gi = i0 + 32 * hh + c;
+          const bool own = (key < N) && (gi < N) && (!p.causal || key <= gi - band);
+          pv[c] = own ? exp2f(s[c] - ld[32 * hh + c]) : 0.f;
+        }
       }
       ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, it & 1, s_abort));
       if (!ok) break;
