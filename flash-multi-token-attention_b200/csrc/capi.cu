@@ -129,9 +129,10 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
     }
   }
   if (use_tc) {
-    // stacked tensor-core kernel off the causal band, then the exact kernel on the band tiles,
-    // continuing the online softmax from the un-normalised partial
+    // stacked tensor-core kernel off the causal band, then the band kernel, which continues the
+    // online softmax from the un-normalised partial and writes the final O, M, L
     if (int s = check_cuda(launch_fwd_tc(p, workspace, &p.Opart, &p.Mpart, &p.Lpart, (cudaStream_t)stream))) return s;
+    if (fwd_band_supported(p)) return check_cuda(launch_fwd_band(p, (cudaStream_t)stream));
     p.kmode = kBandTiles;
     band_geometry(p.cq, p.ck, &p.band_off, &p.band_ownq, &p.band_ownk);
   }
