@@ -34,10 +34,12 @@ constexpr float kLn2 = 0.6931471805599453f;
 #ifdef FMTA_TC_TRACE
 __device__ long long g_trace_bwd[16384];
 #define TRACEB(slot) do { if (trace_on) g_trace_bwd[(slot)] = clock64(); } while (0)
+#define TRACEE(slot) do { if (trace_on && tid == 0) g_trace_bwd[4096 + (slot)] = clock64(); } while (0)
 __device__ long long g_cta_times[3 * 8192];
 #define TRACEQ(slot) do { if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) g_trace_bwd[8192 + (slot)] = clock64(); } while (0)
 #else
 #define TRACEB(slot) do {} while (0)
+#define TRACEE(slot) do {} while (0)
 #define TRACEQ(slot) do {} while (0)
 #endif
 
@@ -420,10 +422,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* empty = bars + NSTG;         // [NSTG]
   uint64_t* kv_full = bars + 2 * NSTG;
   uint64_t* st_full = kv_full + 1;       // S^T in X
-  uint64_t* x_free = st_full + 1;        // S^T taken into registers (256 arrivals): X free for dP^T
-  uint64_t* dpt_full = x_free + 1;       // dP^T in X
-  uint64_t* x_free2 = dpt_full + 1;      // dP^T taken into registers (256 arrivals): X free for the next S^T
-  uint64_t* pdc_full = x_free2 + 1;      // P^T and dC^T (bf16) written to shared memory (256 arrivals)
+  uint64_t* xs_free = st_full + 1;       // S^T taken into registers (256 arrivals): X free for the next dP^T
+  uint64_t* dpt_full = xs_free + 1;      // dP^T in X
+  uint64_t* xd_free = dpt_full + 1;      // dP^T taken into registers (256 arrivals): X free for S^T
+  uint64_t* pdc_full = xd_free + 1;      // P^T and dC^T (bf16) written to shared memory (256 arrivals)
   uint64_t* pdc_free = pdc_full + 1;     // the dV / dKt MMAs that read them have completed
   uint64_t* all_done = pdc_free + 1;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(all_done + 1);
@@ -442,8 +444,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (tid == 0) {
     for (int i = 0; i < NSTG; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 3); }   // three issuers release a stage
     tc::mbar_init(kv_full, 1);
-    tc::mbar_init(st_full, 1); tc::mbar_init(x_free, Cfg::kEwWarps * 32);
-    tc::mbar_init(dpt_full, 1); tc::mbar_init(x_free2, Cfg::kEwWarps * 32);
+    tc::mbar_init(st_full, 1); tc::mbar_init(xs_free, Cfg::kEwWarps * 32);
+    tc::mbar_init(dpt_full, 1); tc::mbar_init(xd_free, Cfg::kEwWarps * 32);
     tc::mbar_init(pdc_full, Cfg::kEwWarps * 32); tc::mbar_init(pdc_free, 2);
     tc::mbar_init(all_done, 2);
     *s_abort = 0;
@@ -505,16 +507,28 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t kt_hi = (uint32_t)(dKtA >> 32), kt_lo = (uint32_t)dKtA;
       const uint32_t v_lo = kt_lo + (uint32_t)((Cfg::oV - Cfg::oKt) >> 4);
       bool ok = tc::mbar_wait(kv_full, 0, s_abort);
-      for (int it = 0; it < nblk && ok; ++it) {
+      // X holds dP^T(it) first (taken by the element-wise warps one block ahead), then S^T(it):
+      //   dP^T(0) | S^T(0) dP^T(1) | S^T(1) dP^T(2) | ...
+      auto issue_dPT = [&](int it) {
         const int st = it % NSTG, ph = (it / NSTG) & 1;
+        const uint64_t dOk = tc::make_sdesc(smem_u32(sStage + st * Cfg::STAGE_BYTES) + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
+        const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
+        if (!tc::mbar_wait(&full[st], ph, s_abort)) { ok = false; return; }
+        tc::tc_fence_after();
+        tc::mma_ss2<0>(tX, v_lo, kt_hi, o_lo, o_hi, idescT);               // dP^T = V dO^T
+#pragma unroll
+        for (int k = 1; k < D / 16; ++k)
+          tc::mma_ss2<1>(tX, v_lo + (uint32_t)(2 * k), kt_hi, o_lo + (uint32_t)(2 * k), o_hi, idescT);
+        tc::mma_commit(dpt_full);
+      };
+      if (ok) issue_dPT(0);
+      for (int it = 0; it < nblk && ok; ++it) {
+        const int st = it % NSTG;
         const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
         const uint64_t dQk = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);   // K-major, N = rows
-        const uint64_t dOk = tc::make_sdesc(sg + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
         const uint32_t qk_hi = (uint32_t)(dQk >> 32), qk_lo = (uint32_t)dQk;
-        const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
         TRACEB(it * 8 + 0);
-        if (!tc::mbar_wait(&full[st], ph, s_abort)) { ok = false; break; }
-        if (it > 0 && !tc::mbar_wait(x_free2, (it - 1) & 1, s_abort)) { ok = false; break; }   // X free again
+        if (!tc::mbar_wait(xd_free, it & 1, s_abort)) { ok = false; break; }   // dP^T(it) has left X
         tc::tc_fence_after();
         TRACEB(it * 8 + 1);
         // S^T = sum_a Kt_a Q^(a)T
@@ -527,17 +541,12 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc::mma_ss2<1>(tX, a_lo + (uint32_t)(2 * k), kt_hi, b_lo + (uint32_t)(2 * k * QR), qk_hi, idescT);
         }
         tc::mma_commit(st_full);
+        tc::mma_commit(&empty[st]);        // this issuer's reads of the stage (dO for dP^T, Q for S^T) are done then
         TRACEB(it * 8 + 2);
-        if (!tc::mbar_wait(x_free, it & 1, s_abort)) { ok = false; break; }
+        if (!tc::mbar_wait(xs_free, it & 1, s_abort)) { ok = false; break; }   // S^T(it) has left X
         tc::tc_fence_after();
         TRACEB(it * 8 + 4);
-        // dP^T = V dO^T
-        tc::mma_ss2<0>(tX, v_lo, kt_hi, o_lo, o_hi, idescT);
-#pragma unroll
-        for (int k = 1; k < D / 16; ++k)
-          tc::mma_ss2<1>(tX, v_lo + (uint32_t)(2 * k), kt_hi, o_lo + (uint32_t)(2 * k), o_hi, idescT);
-        tc::mma_commit(dpt_full);
-        tc::mma_commit(&empty[st]);
+        if (it + 1 < nblk) issue_dPT(it + 1);
         TRACEB(it * 8 + 5);
       }
     }
@@ -589,51 +598,73 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     const uint32_t tXl = tX + lane_base;
     bool ok = true;
-    if (nblk > 0) ok = __all_sync(0xffffffffu, tc::mbar_wait(kv_full, 0, s_abort));   // (orders nothing; keeps phases simple)
+    float dpc[32];                                      // dP^T of the block about to be processed
+    if (nblk > 0) {
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, 0, s_abort));
+      if (ok) {
+        tc::tc_fence_after();
+        tc::tmem_ld32(tXl + 32 * hh, dpc);
+        tc::tc_fence_before();
+        tc::mbar_arrive(xd_free);
+      }
+    }
     for (int it = 0; it < nblk && ok; ++it) {
       const int st = it % NSTG, ph = (it / NSTG) & 1;
       const int i0 = (qb_begin + it) * BR;
       const float* ld = reinterpret_cast<const float*>(sStage + st * Cfg::STAGE_BYTES + Cfg::sgLD);
       ok = __all_sync(0xffffffffu, tc::mbar_wait(&full[st], ph, s_abort));
       if (!ok) break;
+      TRACEE(it * 8 + 0);
       ok = __all_sync(0xffffffffu, tc::mbar_wait(st_full, it & 1, s_abort));
       if (!ok) break;
       tc::tc_fence_after();
+      TRACEE(it * 8 + 1);
       float s[32];
       tc::tmem_ld32(tXl + 32 * hh, s);
       tc::tc_fence_before();
-      tc::mbar_arrive(x_free);
-      // P^T[key, i] = exp2(S^T - LSE_i), kept only where this kernel owns the entry
-      float pv[32];
+      tc::mbar_arrive(xs_free);
+      // take the next block's dP^T out of X right away, so that its S^T can start while this
+      // block's arithmetic runs
+      float dpn[32];
+      TRACEE(it * 8 + 2);
+      if (it + 1 < nblk) {
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, (it + 1) & 1, s_abort));
+        if (!ok) break;
+        tc::tc_fence_after();
+        tc::tmem_ld32(tXl + 32 * hh, dpn);
+        tc::tc_fence_before();
+        tc::mbar_arrive(xd_free);
+      }
+      TRACEE(it * 8 + 3);
+      // P^T[key, i] = exp2(S^T - LSE_i), kept only where this kernel owns the entry; dC^T = P^T (dP^T - D_i)
+      uint32_t pp[16], cc[16];
       if ((j0 + BK <= N) && (i0 + BR <= N) && (!p.causal || j0 + BK - 1 + band <= i0)) {   // block owned entirely
 #pragma unroll
-        for (int c = 0; c < 32; ++c) pv[c] = exp2f(s[c] - ld[32 * hh + c]);
+        for (int c = 0; c < 32; c += 2) {
+          const float p0 = exp2f(s[c] - ld[32 * hh + c]), p1 = exp2f(s[c + 1] - ld[32 * hh + c + 1]);
+          pp[c / 2] = pack_bf16(p0, p1);
+          cc[c / 2] = pack_bf16(p0 * (dpc[c] - ld[BR + 32 * hh + c]), p1 * (dpc[c + 1] - ld[BR + 32 * hh + c + 1]));
+        }
       } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < 32; c += 2) {
           const int gi = i0 + 32 * hh + c;
-          const bool own = (key < N) && (gi < N) && (!p.causal || key <= gi - band);
-          pv[c] = own ? exp2f(s[c] - ld[32 * hh + c]) : 0.f;
+          const bool own0 = (key < N) && (gi < N) && (!p.causal || key <= gi - band);
+          const bool own1 = (key < N) && (gi + 1 < N) && (!p.causal || key <= gi + 1 - band);
+          const float p0 = own0 ? exp2f(s[c] - ld[32 * hh + c]) : 0.f;
+          const float p1 = own1 ? exp2f(s[c + 1] - ld[32 * hh + c + 1]) : 0.f;
+          pp[c / 2] = pack_bf16(p0, p1);
+          cc[c / 2] = pack_bf16(p0 * (dpc[c] - ld[BR + 32 * hh + c]), p1 * (dpc[c + 1] - ld[BR + 32 * hh + c + 1]));
         }
       }
-      ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, it & 1, s_abort));
-      if (!ok) break;
-      tc::tc_fence_after();
-      tc::tmem_ld32(tXl + 32 * hh, s);                  // dP^T
-      tc::tc_fence_before();
-      tc::mbar_arrive(x_free2);                         // X may take the next block's S^T
-      uint32_t pp[16], cc[16];
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        const float d0 = pv[c] * (s[c] - ld[BR + 32 * hh + c]);
-        const float d1 = pv[c + 1] * (s[c + 1] - ld[BR + 32 * hh + c + 1]);
-        pp[c / 2] = pack_bf16(pv[c], pv[c + 1]);
-        cc[c / 2] = pack_bf16(d0, d1);
-      }
+      for (int c = 0; c < 32; ++c) dpc[c] = dpn[c];
+      TRACEE(it * 8 + 4);
       if (it > 0) {   // the MMAs of block it-1 have finished reading the P^T / dC^T buffers
         ok = __all_sync(0xffffffffu, tc::mbar_wait(pdc_free, (it - 1) & 1, s_abort));
         if (!ok) break;
       }
+      TRACEE(it * 8 + 5);
       {
         unsigned char* pt = smem + Cfg::oPT + (qtr * 32 + lane) * 16;
         unsigned char* dc = smem + Cfg::oDCT + (qtr * 32 + lane) * 16;
@@ -645,6 +676,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(pdc_full);
+      TRACEE(it * 8 + 6);
     }
     // ---- epilogue: dV and dKt_a rows of this key ----
     if (nblk > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(all_done, 0, s_abort));
