@@ -182,7 +182,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int wi = warp - (NT * 4 + 1);
     const int t = wi % NT;
     const bool is_dq = wi >= NT;
-    if (lane == 0 && nkb > 0) {
+    if (nkb > 0) {   // all lanes run the loop; one elected lane issues (see tc::elect_one)
       constexpr uint32_t idescS = tc::make_idesc(BM, BC, 0, 0);    // S, dP: 128 x 64, both K-major
       constexpr uint32_t idescQ = tc::make_idesc(BM, D, 0, 1);     // dQ: 128 x D, B (Kt) MN-major
       const uint64_t dQa = tc::make_sdesc(smem_u32(sQ) + (HALO + t * OWN - pq) * 16, QR * 16, 128, tc::kLayoutNone);
@@ -196,43 +196,43 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t tS = tmem + t * 192, tP = tS + 64, tQ = tS + 128;
       const int my_nkb = nkb_t[t];
       const int per = cq + 1;                                // ring tiles per key block
-      bool ok = tc::mbar_wait(q_full, 0, s_abort);
+      bool ok = tc::mbar_wait_warp(q_full, 0, s_abort);
       if (!is_dq) {
         for (int kb = 0; kb < nkb && ok; ++kb) {
           const bool active = kb < my_nkb;
           if (t == 0) TRACEQ(kb * 8 + 0);
           if (active && kb > 0) {
-            ok = tc::mbar_wait(&s_free[t], (kb - 1) & 1, s_abort);
+            ok = tc::mbar_wait_warp(&s_free[t], (kb - 1) & 1, s_abort);
             tc::tc_fence_after();
           }
           if (t == 0) TRACEQ(kb * 8 + 1);
           for (int a = 0; a < cq && ok; ++a) {
             const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
-            if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
+            if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
             if (active) {
               tc::tc_fence_after();
               const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
               const uint32_t a_lo = q_lo + (uint32_t)a;
-              tc::mma_ss2p(tS, a_lo, q_hi, b_lo, k_hi, idescS, a != 0);
+              tc::mma_ss2pe(tS, a_lo, q_hi, b_lo, k_hi, idescS, a != 0);
 #pragma unroll
               for (int k = 1; k < D / 16; ++k)
-                tc::mma_ss2<1>(tS, a_lo + (uint32_t)(2 * k * QR), q_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
+                tc::mma_ss2e<1>(tS, a_lo + (uint32_t)(2 * k * QR), q_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
             }
-            tc::mma_commit(&empty[slot]);      // (the dQ issuers hold the Kt tile until dQ(kb) is done)
+            tc::mma_commit_e(&empty[slot]);      // (the dQ issuers hold the Kt tile until dQ(kb) is done)
           }
           if (!ok) break;
           const int id = kb * per + cq, slot = id % NSLOT, ph = (id / NSLOT) & 1;
-          if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
+          if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
           if (active) {
             tc::tc_fence_after();
             const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
-            tc::mma_ss2<0>(tP, o_lo, o_hi, b_lo, k_hi, idescS);
+            tc::mma_ss2e<0>(tP, o_lo, o_hi, b_lo, k_hi, idescS);
 #pragma unroll
             for (int k = 1; k < D / 16; ++k)
-              tc::mma_ss2<1>(tP, o_lo + (uint32_t)(2 * k), o_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
+              tc::mma_ss2e<1>(tP, o_lo + (uint32_t)(2 * k), o_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
           }
-          tc::mma_commit(&empty[slot]);
-          if (active) tc::mma_commit(&sdp_full[t]);
+          tc::mma_commit_e(&empty[slot]);
+          if (active) tc::mma_commit_e(&sdp_full[t]);
           if (t == 0) TRACEQ(kb * 8 + 2);
         }
       } else {
@@ -240,31 +240,31 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const bool active = kb < my_nkb;
           if (t == 0) TRACEQ(kb * 8 + 3);
           if (active) {
-            ok = tc::mbar_wait(&dc_full[t], kb & 1, s_abort);
+            ok = tc::mbar_wait_warp(&dc_full[t], kb & 1, s_abort);
             tc::tc_fence_after();
           }
           if (t == 0) TRACEQ(kb * 8 + 4);
           for (int a = 0; a < cq && ok; ++a) {
             const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
-            if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
+            if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
             if (active) {
               tc::tc_fence_after();
               const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
               const uint32_t a_lo = c_lo + (uint32_t)(pq - a);       // dC rows i' + pad_q - a
-              tc::mma_ss2p(tQ, a_lo, c_hi, b_lo, k_hi, idescQ, (kb != 0) || (a != 0));
+              tc::mma_ss2pe(tQ, a_lo, c_hi, b_lo, k_hi, idescQ, (kb != 0) || (a != 0));
 #pragma unroll
               for (int k = 1; k < BC / 16; ++k)
-                tc::mma_ss2<1>(tQ, a_lo + (uint32_t)(2 * k * DR), c_hi, b_lo + (uint32_t)(k * (2048 / 16)), k_hi, idescQ);
+                tc::mma_ss2e<1>(tQ, a_lo + (uint32_t)(2 * k * DR), c_hi, b_lo + (uint32_t)(k * (2048 / 16)), k_hi, idescQ);
             }
-            tc::mma_commit(&empty[slot]);
+            tc::mma_commit_e(&empty[slot]);
           }
           if (!ok) break;
           {   // the V tile of the block is not read here: release it right away
             const int id = kb * per + cq, slot = id % NSLOT, ph = (id / NSLOT) & 1;
-            if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; break; }
-            tc::mbar_arrive(&empty[slot]);
+            if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
+            if (tc::elect_one()) tc::mbar_arrive(&empty[slot]);
           }
-          if (active) tc::mma_commit(&dq_done[t]);
+          if (active) tc::mma_commit_e(&dq_done[t]);
           if (t == 0) TRACEQ(kb * 8 + 5);
         }
       }
@@ -501,25 +501,25 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // ===================== MMA issuer S: S^T and dP^T of block `it` into the scratch columns X ==========
     // One thread issues an MMA every 50-100 clocks whatever its size, so the three MMA streams of a
     // block (S^T/dP^T, dV + first half of the dKt taps, second half of the taps) have a warp each.
-    if (lane == 0 && nblk > 0) {
+    if (nblk > 0) {   // all lanes run the loop; one elected lane issues (see tc::elect_one)
       constexpr uint32_t idescT = tc::make_idesc(BK, BR, 0, 0);    // 128 x 64, K-major operands
       const uint64_t dKtA = tc::make_sdesc(smem_u32(sKt), 16, 1024, tc::kLayoutSW128);
       const uint32_t kt_hi = (uint32_t)(dKtA >> 32), kt_lo = (uint32_t)dKtA;
       const uint32_t v_lo = kt_lo + (uint32_t)((Cfg::oV - Cfg::oKt) >> 4);
-      bool ok = tc::mbar_wait(kv_full, 0, s_abort);
+      bool ok = tc::mbar_wait_warp(kv_full, 0, s_abort);
       // X holds dP^T(it) first (taken by the element-wise warps one block ahead), then S^T(it):
       //   dP^T(0) | S^T(0) dP^T(1) | S^T(1) dP^T(2) | ...
       auto issue_dPT = [&](int it) {
         const int st = it % NSTG, ph = (it / NSTG) & 1;
         const uint64_t dOk = tc::make_sdesc(smem_u32(sStage + st * Cfg::STAGE_BYTES) + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
         const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
-        if (!tc::mbar_wait(&full[st], ph, s_abort)) { ok = false; return; }
+        if (!tc::mbar_wait_warp(&full[st], ph, s_abort)) { ok = false; return; }
         tc::tc_fence_after();
-        tc::mma_ss2<0>(tX, v_lo, kt_hi, o_lo, o_hi, idescT);               // dP^T = V dO^T
+        tc::mma_ss2e<0>(tX, v_lo, kt_hi, o_lo, o_hi, idescT);               // dP^T = V dO^T
 #pragma unroll
         for (int k = 1; k < D / 16; ++k)
-          tc::mma_ss2<1>(tX, v_lo + (uint32_t)(2 * k), kt_hi, o_lo + (uint32_t)(2 * k), o_hi, idescT);
-        tc::mma_commit(dpt_full);
+          tc::mma_ss2e<1>(tX, v_lo + (uint32_t)(2 * k), kt_hi, o_lo + (uint32_t)(2 * k), o_hi, idescT);
+        tc::mma_commit_e(dpt_full);
       };
       if (ok) issue_dPT(0);
       for (int it = 0; it < nblk && ok; ++it) {
@@ -528,22 +528,22 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint64_t dQk = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);   // K-major, N = rows
         const uint32_t qk_hi = (uint32_t)(dQk >> 32), qk_lo = (uint32_t)dQk;
         TRACEB(it * 8 + 0);
-        if (!tc::mbar_wait(xd_free, it & 1, s_abort)) { ok = false; break; }   // dP^T(it) has left X
+        if (!tc::mbar_wait_warp(xd_free, it & 1, s_abort)) { ok = false; break; }   // dP^T(it) has left X
         tc::tc_fence_after();
         TRACEB(it * 8 + 1);
         // S^T = sum_a Kt_a Q^(a)T
         for (int a = 0; a < cq; ++a) {
           const uint32_t a_lo = kt_lo + (uint32_t)(a * (Cfg::KT_BYTES >> 4));
           const uint32_t b_lo = qk_lo + (uint32_t)a;
-          tc::mma_ss2p(tX, a_lo, kt_hi, b_lo, qk_hi, idescT, a != 0);
+          tc::mma_ss2pe(tX, a_lo, kt_hi, b_lo, qk_hi, idescT, a != 0);
 #pragma unroll
           for (int k = 1; k < D / 16; ++k)
-            tc::mma_ss2<1>(tX, a_lo + (uint32_t)(2 * k), kt_hi, b_lo + (uint32_t)(2 * k * QR), qk_hi, idescT);
+            tc::mma_ss2e<1>(tX, a_lo + (uint32_t)(2 * k), kt_hi, b_lo + (uint32_t)(2 * k * QR), qk_hi, idescT);
         }
-        tc::mma_commit(st_full);
-        tc::mma_commit(&empty[st]);        // this issuer's reads of the stage (dO for dP^T, Q for S^T) are done then
+        tc::mma_commit_e(st_full);
+        tc::mma_commit_e(&empty[st]);        // this issuer's reads of the stage (dO for dP^T, Q for S^T) are done then
         TRACEB(it * 8 + 2);
-        if (!tc::mbar_wait(xs_free, it & 1, s_abort)) { ok = false; break; }   // S^T(it) has left X
+        if (!tc::mbar_wait_warp(xs_free, it & 1, s_abort)) { ok = false; break; }   // S^T(it) has left X
         tc::tc_fence_after();
         TRACEB(it * 8 + 4);
         if (it + 1 < nblk) issue_dPT(it + 1);
@@ -553,7 +553,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp >= Cfg::kEwWarps + 2) {
     // ===================== MMA issuers A0 / A1: dV += P^T dO ; dKt_a += dC^T Q^(a) =====================
     const int ai = warp - (Cfg::kEwWarps + 2);
-    if (lane == 0 && nblk > 0) {
+    if (nblk > 0) {   // all lanes run the loop; one elected lane issues (see tc::elect_one)
       constexpr uint32_t idescA = tc::make_idesc(BK, D, 0, 1);     // 128 x D, B MN-major
       const int a_half = cq / 2;
       const int a_begin = ai == 0 ? 0 : a_half, a_end = ai == 0 ? a_half : cq;
@@ -569,27 +569,27 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t qm_hi = (uint32_t)(dQm >> 32), qm_lo = (uint32_t)dQm;
         const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
         const uint32_t acc_on = it != 0;
-        if (!tc::mbar_wait(&full[st], ph, s_abort)) { ok = false; break; }
-        if (!tc::mbar_wait(pdc_full, it & 1, s_abort)) { ok = false; break; }
+        if (!tc::mbar_wait_warp(&full[st], ph, s_abort)) { ok = false; break; }
+        if (!tc::mbar_wait_warp(pdc_full, it & 1, s_abort)) { ok = false; break; }
         tc::tc_fence_after();
         if (ai == 0) {
-          tc::mma_ss2p(tmem, pt_lo, pt_hi, o_lo, o_hi, idescA, acc_on);
+          tc::mma_ss2pe(tmem, pt_lo, pt_hi, o_lo, o_hi, idescA, acc_on);
 #pragma unroll
           for (int k = 1; k < BR / 16; ++k)
-            tc::mma_ss2<1>(tmem, pt_lo + (uint32_t)(2 * k * BK), pt_hi, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
+            tc::mma_ss2e<1>(tmem, pt_lo + (uint32_t)(2 * k * BK), pt_hi, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
         }
         for (int a = a_begin; a < a_end; ++a) {
           const uint32_t dacc = tmem + 64 * (1 + a);
           const uint32_t b_lo = qm_lo + (uint32_t)a;
-          tc::mma_ss2p(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA, acc_on);
+          tc::mma_ss2pe(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA, acc_on);
 #pragma unroll
           for (int k = 1; k < BR / 16; ++k)
-            tc::mma_ss2<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idescA);
+            tc::mma_ss2e<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idescA);
         }
-        tc::mma_commit(&empty[st]);
-        tc::mma_commit(pdc_free);
+        tc::mma_commit_e(&empty[st]);
+        tc::mma_commit_e(pdc_free);
       }
-      if (ok) tc::mma_commit(all_done);
+      if (ok) tc::mma_commit_e(all_done);
     }
   } else {
     // ===================== element-wise warps: key = lane, 32 query rows per thread =====================

@@ -213,6 +213,30 @@ FMTA_DEVINL void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// ---- warp-uniform issue ------------------------------------------------------------------
+// An MMA issuer warp runs its loop with all 32 lanes (so that descriptor arithmetic stays in
+// uniform registers) and lets one elected lane execute each tcgen05 instruction; the elected
+// lane is the same for a given member mask, so commits track the MMAs issued before them.
+FMTA_DEVINL bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+FMTA_DEVINL bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+template <int ACC>
+FMTA_DEVINL void mma_ss2e(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+  if (elect_one()) mma_ss2<ACC>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc);
+}
+FMTA_DEVINL void mma_ss2pe(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                           uint32_t accumulate) {
+  if (elect_one()) mma_ss2p(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
+}
+FMTA_DEVINL void mma_commit_e(uint64_t* bar) {
+  if (elect_one()) mma_commit(bar);
+}
+
 // Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, M x N tile.
 //   bits [4,6) D format (1 = F32); [7,10) A format (1 = BF16); [10,13) B format (1 = BF16);
 //   bit 15 A major (0 = K, 1 = MN); bit 16 B major; [17,23) N >> 3; [24,29) M >> 4.
