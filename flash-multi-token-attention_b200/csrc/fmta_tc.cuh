@@ -233,6 +233,10 @@ FMTA_DEVINL void mma_ss2pe(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32
                            uint32_t accumulate) {
   if (elect_one()) mma_ss2p(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
 }
+template <int ACC>
+FMTA_DEVINL void mma_ts2e(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+  if (elect_one()) mma_ts2<ACC>(d_tmem, a_tmem, b_lo, b_hi, idesc);
+}
 FMTA_DEVINL void mma_commit_e(uint64_t* bar) {
   if (elect_one()) mma_commit(bar);
 }

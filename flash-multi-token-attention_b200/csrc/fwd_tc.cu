@@ -269,7 +269,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     // its MMAs on it.  Two issuers keep the tensor pipe fed while one of them sits in a barrier
     // wait or a commit.
     const int t = warp - (NT * 4 + 1);
-    if (lane == 0 && nkb > 0) {
+    if (nkb > 0) {   // all lanes run the loop; one elected lane issues (see tc::elect_one)
       constexpr uint32_t idescS = tc::make_idesc(BM, BC, 0, 0);
       constexpr uint32_t idescPV = tc::make_idesc(BM, 64, 0, 1);
       // descriptors split into a constant high word and a low word that carries the start address
@@ -281,54 +281,54 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const uint32_t aP = tmem + Cfg::colP + t * 64;            // bf16 pairs: 8 columns per 16 keys
       const int my_nkb = nkb_t[t];
       int id = 0;
-      bool ok = tc::mbar_wait(q_full, 0, s_abort);
+      bool ok = tc::mbar_wait_warp(q_full, 0, s_abort);
       auto issue_S = [&](int kb) {
         const bool active = kb < my_nkb;
         // S[t] is single-buffered: wait until the softmax threads have taken block kb-1 out of it
         if (active && kb > 0) {
-          ok = tc::mbar_wait(&s_free[t], (kb - 1) & 1, s_abort);
+          ok = tc::mbar_wait_warp(&s_free[t], (kb - 1) & 1, s_abort);
           tc::tc_fence_after();
         }
         for (int a = 0; a < cq && ok; ++a) {
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
             const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
-            if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
+            if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; return; }
             if (active) {
               tc::tc_fence_after();
               const uint32_t b_lo = b_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
               const uint32_t a_lo = aS_lo + (uint32_t)(a + sl * 8 * QR);   // row shift = +16 B per row
-              if (a == 0 && sl == 0) tc::mma_ss2<0>(dS, a_lo, aS_hi, b_lo, b_hi, idescS);
-              else tc::mma_ss2<1>(dS, a_lo, aS_hi, b_lo, b_hi, idescS);
+              if (a == 0 && sl == 0) tc::mma_ss2e<0>(dS, a_lo, aS_hi, b_lo, b_hi, idescS);
+              else tc::mma_ss2e<1>(dS, a_lo, aS_hi, b_lo, b_hi, idescS);
 #pragma unroll
               for (int k = 1; k < 4; ++k)
-                tc::mma_ss2<1>(dS, a_lo + (uint32_t)(2 * k * QR), aS_hi, b_lo + (uint32_t)(k * 2), b_hi, idescS);
+                tc::mma_ss2e<1>(dS, a_lo + (uint32_t)(2 * k * QR), aS_hi, b_lo + (uint32_t)(k * 2), b_hi, idescS);
             }
-            tc::mma_commit(&empty[slot]);
+            tc::mma_commit_e(&empty[slot]);
             ++id;
           }
         }
-        if (ok && active) tc::mma_commit(&s_full[t]);
+        if (ok && active) tc::mma_commit_e(&s_full[t]);
       };
       auto issue_PV = [&](int kb) {
         const bool active = kb < my_nkb;
 #pragma unroll
         for (int sl = 0; sl < SLABS; ++sl) {
           const int slot = id % NSLOT, ph = (id / NSLOT) & 1;
-          if (!tc::mbar_wait(&full[slot], ph, s_abort)) { ok = false; return; }
+          if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; return; }
           if (active) {
-            if (sl == 0 && !tc::mbar_wait(&p_full[t], kb & 1, s_abort)) { ok = false; return; }
+            if (sl == 0 && !tc::mbar_wait_warp(&p_full[t], kb & 1, s_abort)) { ok = false; return; }
             tc::tc_fence_after();
             const uint32_t b_lo = b_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
             const uint32_t dO = tmem + Cfg::colO + t * D + sl * 64;
-            if (kb == 0) tc::mma_ts2<0>(dO, aP, b_lo, b_hi, idescPV);
-            else tc::mma_ts2<1>(dO, aP, b_lo, b_hi, idescPV);
+            if (kb == 0) tc::mma_ts2e<0>(dO, aP, b_lo, b_hi, idescPV);
+            else tc::mma_ts2e<1>(dO, aP, b_lo, b_hi, idescPV);
 #pragma unroll
             for (int k = 1; k < BC / 16; ++k)
-              tc::mma_ts2<1>(dO, aP + 8 * k, b_lo + (uint32_t)(k * (2048 / 16)), b_hi, idescPV);
-            if (sl == SLABS - 1) tc::mma_commit(&o_full[t]);
+              tc::mma_ts2e<1>(dO, aP + 8 * k, b_lo + (uint32_t)(k * (2048 / 16)), b_hi, idescPV);
+            if (sl == SLABS - 1) tc::mma_commit_e(&o_full[t]);
           }
-          tc::mma_commit(&empty[slot]);
+          tc::mma_commit_e(&empty[slot]);
           ++id;
         }
       };
