@@ -401,7 +401,7 @@ struct DkvCfg {
   static constexpr int kSmemBytes = oBar + 512 + 1024;
   static constexpr int kTmemCols = 512;        // dV at 0, dKt_a at 64*(1+a), scratch X at 448
   static constexpr int colX = 448;
-  static constexpr int kEwWarps = 8;
+  static constexpr int kEwWarps = 16;
   static constexpr int kThreads = (kEwWarps + 4) * 32;   // + producer, issuer S, issuers A0 and A1
 };
 
@@ -592,18 +592,19 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) tc::mma_commit_e(all_done);
     }
   } else {
-    // ===================== element-wise warps: key = lane, 32 query rows per thread =====================
-    const int qtr = warp & 3, hh = warp >> 2;
+    // ===================== element-wise warps: key = lane, CW query rows per thread =====================
+    constexpr int NCG = Cfg::kEwWarps / 4, CW = BR / NCG;     // column groups (warps per lane quarter), columns each
+    const int qtr = warp & 3, cg = warp >> 2;
     const int key = j0 + qtr * 32 + lane;
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
-    const uint32_t tXl = tX + lane_base;
+    const uint32_t tXl = tX + lane_base + CW * cg;
     bool ok = true;
-    float dpc[32];                                      // dP^T of the block about to be processed
+    float dpc[CW];                                      // dP^T of the block about to be processed
     if (nblk > 0) {
       ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, 0, s_abort));
       if (ok) {
         tc::tc_fence_after();
-        tc::tmem_ld32(tXl + 32 * hh, dpc);
+        tc::tmem_ldn(tXl, dpc);
         tc::tc_fence_before();
         tc::mbar_arrive(xd_free);
       }
@@ -611,7 +612,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int it = 0; it < nblk && ok; ++it) {
       const int st = it % NSTG, ph = (it / NSTG) & 1;
       const int i0 = (qb_begin + it) * BR;
-      const float* ld = reinterpret_cast<const float*>(sStage + st * Cfg::STAGE_BYTES + Cfg::sgLD);
+      const float* ld = reinterpret_cast<const float*>(sStage + st * Cfg::STAGE_BYTES + Cfg::sgLD) + CW * cg;
       ok = __all_sync(0xffffffffu, tc::mbar_wait(&full[st], ph, s_abort));
       if (!ok) break;
       TRACEE(it * 8 + 0);
@@ -619,46 +620,46 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!ok) break;
       tc::tc_fence_after();
       TRACEE(it * 8 + 1);
-      float s[32];
-      tc::tmem_ld32(tXl + 32 * hh, s);
+      float s[CW];
+      tc::tmem_ldn(tXl, s);
       tc::tc_fence_before();
       tc::mbar_arrive(xs_free);
       // take the next block's dP^T out of X right away, so that its S^T can start while this
       // block's arithmetic runs
-      float dpn[32];
+      float dpn[CW];
       TRACEE(it * 8 + 2);
       if (it + 1 < nblk) {
         ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, (it + 1) & 1, s_abort));
         if (!ok) break;
         tc::tc_fence_after();
-        tc::tmem_ld32(tXl + 32 * hh, dpn);
+        tc::tmem_ldn(tXl, dpn);
         tc::tc_fence_before();
         tc::mbar_arrive(xd_free);
       }
       TRACEE(it * 8 + 3);
       // P^T[key, i] = exp2(S^T - LSE_i), kept only where this kernel owns the entry; dC^T = P^T (dP^T - D_i)
-      uint32_t pp[16], cc[16];
+      uint32_t pp[CW / 2], cc[CW / 2];
       if ((j0 + BK <= N) && (i0 + BR <= N) && (!p.causal || j0 + BK - 1 + band <= i0)) {   // block owned entirely
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float p0 = exp2f(s[c] - ld[32 * hh + c]), p1 = exp2f(s[c + 1] - ld[32 * hh + c + 1]);
+        for (int c = 0; c < CW; c += 2) {
+          const float p0 = exp2f(s[c] - ld[c]), p1 = exp2f(s[c + 1] - ld[c + 1]);
           pp[c / 2] = pack_bf16(p0, p1);
-          cc[c / 2] = pack_bf16(p0 * (dpc[c] - ld[BR + 32 * hh + c]), p1 * (dpc[c + 1] - ld[BR + 32 * hh + c + 1]));
+          cc[c / 2] = pack_bf16(p0 * (dpc[c] - ld[BR + c]), p1 * (dpc[c + 1] - ld[BR + c + 1]));
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const int gi = i0 + 32 * hh + c;
+        for (int c = 0; c < CW; c += 2) {
+          const int gi = i0 + CW * cg + c;
           const bool own0 = (key < N) && (gi < N) && (!p.causal || key <= gi - band);
           const bool own1 = (key < N) && (gi + 1 < N) && (!p.causal || key <= gi + 1 - band);
-          const float p0 = own0 ? exp2f(s[c] - ld[32 * hh + c]) : 0.f;
-          const float p1 = own1 ? exp2f(s[c + 1] - ld[32 * hh + c + 1]) : 0.f;
+          const float p0 = own0 ? exp2f(s[c] - ld[c]) : 0.f;
+          const float p1 = own1 ? exp2f(s[c + 1] - ld[c + 1]) : 0.f;
           pp[c / 2] = pack_bf16(p0, p1);
-          cc[c / 2] = pack_bf16(p0 * (dpc[c] - ld[BR + 32 * hh + c]), p1 * (dpc[c + 1] - ld[BR + 32 * hh + c + 1]));
+          cc[c / 2] = pack_bf16(p0 * (dpc[c] - ld[BR + c]), p1 * (dpc[c + 1] - ld[BR + c + 1]));
         }
       }
 #pragma unroll
-      for (int c = 0; c < 32; ++c) dpc[c] = dpn[c];
+      for (int c = 0; c < CW; ++c) dpc[c] = dpn[c];
       TRACEE(it * 8 + 4);
       if (it > 0) {   // the MMAs of block it-1 have finished reading the P^T / dC^T buffers
         ok = __all_sync(0xffffffffu, tc::mbar_wait(pdc_free, (it - 1) & 1, s_abort));
@@ -669,24 +670,23 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         unsigned char* pt = smem + Cfg::oPT + (qtr * 32 + lane) * 16;
         unsigned char* dc = smem + Cfg::oDCT + (qtr * 32 + lane) * 16;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {               // 8 rows (16 bytes) per K-chunk
-          *reinterpret_cast<uint4*>(pt + (4 * hh + q4) * (BK * 16)) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]);
-          *reinterpret_cast<uint4*>(dc + (4 * hh + q4) * (BK * 16)) = make_uint4(cc[4 * q4], cc[4 * q4 + 1], cc[4 * q4 + 2], cc[4 * q4 + 3]);
+        for (int q4 = 0; q4 < CW / 8; ++q4) {          // 8 rows (16 bytes) per K-chunk
+          *reinterpret_cast<uint4*>(pt + ((CW / 8) * cg + q4) * (BK * 16)) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]);
+          *reinterpret_cast<uint4*>(dc + ((CW / 8) * cg + q4) * (BK * 16)) = make_uint4(cc[4 * q4], cc[4 * q4 + 1], cc[4 * q4 + 2], cc[4 * q4 + 3]);
         }
       }
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(pdc_full);
       TRACEE(it * 8 + 6);
     }
-    // ---- epilogue: dV and dKt_a rows of this key ----
+    // ---- epilogue: dV and dKt_a rows of this key; 14 chunks of 32 columns dealt round-robin to the column groups ----
     if (nblk > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(all_done, 0, s_abort));
     tc::tc_fence_after();
     const bool have = (nblk > 0) && ok;
     const bool store = key < N;
     const size_t krow = (size_t)(store ? key : 0);
-    for (int ch = 7 * hh; ch < 7 * hh + 7; ++ch) {      // 14 chunks of 32 columns over the two halves
+    for (int ch = cg; ch < 2 * (cq + 1); ch += NCG) {
       const int acc = ch >> 1, half = ch & 1;
-      if (acc > cq) break;
       float o[32];
       if (have) {
         tc::tmem_ld32(tmem + lane_base + ch * 32, o);
@@ -696,11 +696,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       if (store) {
         float* dst;
-        float f;
-        if (acc == 0) { dst = p.dV + ((size_t)bh * N + krow) * D + half * 32; f = 1.f; }
-        else { dst = p.dKt + (((size_t)bh * cq + (acc - 1)) * N + krow) * D + half * 32; f = 1.f; }
+        if (acc == 0) dst = p.dV + ((size_t)bh * N + krow) * D + half * 32;
+        else dst = p.dKt + (((size_t)bh * cq + (acc - 1)) * N + krow) * D + half * 32;
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i] * f, o[i + 1] * f, o[i + 2] * f, o[i + 3] * f);
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
       }
     }
   }

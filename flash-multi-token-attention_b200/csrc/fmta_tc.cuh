@@ -103,6 +103,18 @@ FMTA_DEVINL void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 32 lanes x 16 columns.
+FMTA_DEVINL void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]),
+        "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+FMTA_DEVINL void tmem_ldn(uint32_t taddr, float (&v)[32]) { tmem_ld32(taddr, v); }
+FMTA_DEVINL void tmem_ldn(uint32_t taddr, float (&v)[16]) { tmem_ld16(taddr, v); }
 // Same without the trailing wait, for issuing several loads back to back (follow with tmem_wait_ld).
 FMTA_DEVINL void tmem_ld32_nowait(uint32_t taddr, float (&v)[32]) {
   asm volatile(
