@@ -36,6 +36,7 @@ constexpr int SB_LD = 37;                           // band (zero pad for e < 0)
 constexpr int DC_LD = 43;                           // pad_k + band + pad_q + 2 pad_k columns, odd
 constexpr int P_LD = 13;
 constexpr int DS_LD = 21;
+constexpr int A_LD = 40;                            // bf16 operand tiles of the output GEMMs: 32 columns + 8 (ldmatrix)
 constexpr int oQ = 0;
 constexpr int oK = oQ + RS * LD * 2;
 constexpr int oV = oK + RK * LD * 2;                // V rows; later reused for the padded dC rows
@@ -76,6 +77,11 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   float* sSb = reinterpret_cast<float*>(smem + oSb);
   float* sP = reinterpret_cast<float*>(smem + oP);
   float* sdS = reinterpret_cast<float*>(smem + odS);
+  // with W <= 17 the output phase runs on mma.sync from dense bf16 tiles: P in the dS buffer's place,
+  // dS (two arrangements) in the Sb buffer's place once dTheta no longer needs Sb
+  bf16* sAV = reinterpret_cast<bf16*>(smem + odS);
+  bf16* sAQ = reinterpret_cast<bf16*>(smem + oSb);
+  bf16* sAK = sAQ + RC * A_LD;
   float* sLse = reinterpret_cast<float*>(smem + oLD);
   float* sDv = sLse + RC;
   float* sTheta = reinterpret_cast<float*>(smem + oTheta);
@@ -85,6 +91,7 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   const int N = p.N, H = p.H, cq = (CQ > 0) ? CQ : p.cq, ck = (CQ > 0) ? CK : p.ck;
   const int pq = cq - 1, pk = (ck - 1) / 2, band = pq + pk, W = band + pk;
   const int R = min(RC, RC - (W - 1 + pq));
+  const bool mma_out = (W <= 17);
   const int h = blockIdx.y, b = blockIdx.z;
   const size_t bh = (size_t)b * H + h;
   const int t0 = blockIdx.x * R;
@@ -101,6 +108,7 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   cp_async_commit();
   for (int i = tid; i < cq * ck; i += NT) sTheta[(i / ck) * kThetaLdBand + (i % ck)] = p.theta[((size_t)h * cq) * ck + i];
   for (int i = tid; i < RS * SB_LD; i += NT) sSb[i] = 0.f;
+  if (mma_out) for (int i = tid; i < RC * A_LD / 2; i += NT) reinterpret_cast<uint32_t*>(sAV)[i] = 0u;
   if (tid < RC) {
     const int gi = t0 + tid;
     sLse[tid] = gi < N ? p.LSE[bh * N + gi] * kLog2e : 0.f;
@@ -188,8 +196,13 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
         const bool live = (gi < N) && (gi - dd >= 0);
         const float pr = live ? exp2f(c[k] * kLog2e - sLse[x]) : 0.f;
         const float dp = sP[x * P_LD + dd];
-        sP[x * P_LD + dd] = pr;
         sdC[x * DC_LD + pk + dd] = pr * (dp - sDv[x]);
+        if (mma_out) {            // P^T operand of dV: row = key position x - dd, column = x relative to that key's tile
+          const int j = x - dd;
+          if (j >= 0) sAV[j * A_LD + x - (j & ~15)] = __float2bfloat16(pr);
+        } else {
+          sP[x * P_LD + dd] = pr;
+        }
       }
     }
   }
@@ -223,6 +236,11 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
     sRed[tid] = t0s + t1s;
   }
   TRACEK(5);
+  if (mma_out) {      // Sb is dead now: its place takes the two dense arrangements of dS
+    __syncthreads();
+    for (int i = tid; i < 2 * RC * A_LD / 2; i += NT) reinterpret_cast<uint32_t*>(sAQ)[i] = 0u;
+    __syncthreads();
+  }
   // ---- adjoint conv: dSb[i', e] for the rows that feed the owned positions ----
   if (W > 0) {
     constexpr int KA = (CQ > 0) ? ((RC - (CQ - 1)) * (CQ - 1 + CK - 1) + NT - 1) / NT : (RC * MAXW + NT - 1) / NT;
@@ -249,7 +267,18 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
 #pragma unroll
     for (int k = 0; k < KA; ++k) {
       const int o = tid + k * NT;
-      if (o < nout) sdS[(o / W) * DS_LD + (o % W)] = sacc[k] * p.scale;
+      if (o < nout) {
+        const int xr = o / W, e = o - xr * W;
+        const float v = sacc[k] * p.scale;
+        if (mma_out) {
+          const bf16 vb = __float2bfloat16(v);
+          sAQ[xr * A_LD + (xr & 15) - e + 16] = vb;            // dQ: row = query position, column = key relative to (tile start - 16)
+          const int j = xr - e;
+          if (j >= 0) sAK[j * A_LD + xr - (j & ~15)] = vb;     // dK: row = key position, column = query relative to the key's tile
+        } else {
+          sdS[xr * DS_LD + e] = v;
+        }
+      }
     }
   }
   __syncthreads();
@@ -266,41 +295,71 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   }
   TRACEK(7);
 
+  if (mma_out) {
+    // ---- dQ, dK, dV on mma.sync: 16 positions x 32 head dims per job, accumulating onto the values in memory ----
+    const int ntile = (R + 15) / 16;
+    for (int job = warp; job < ntile * 6; job += NT / 32) {
+      const int m = job / 6, which = (job % 6) >> 1, ch = job & 1;      // which: 0 dQ, 1 dK, 2 dV
+      const int x0 = 16 * m + (lane >> 2), x1 = x0 + 8;
+      const bool ok0 = (x0 < R) && (t0 + x0 < N), ok1 = (x1 < R) && (t0 + x1 < N);
+      float* gout = (which == 0) ? p.dQ : (which == 1) ? p.dK : p.dV;
+      float* g0 = gout + (bh * N + t0 + x0) * D + ch * 32 + (lane & 3) * 2;
+      float* g1 = gout + (bh * N + t0 + x1) * D + ch * 32 + (lane & 3) * 2;
+      float acc[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 v0 = make_float2(0.f, 0.f), v1 = v0;
+        if (ok0) v0 = *reinterpret_cast<const float2*>(g0 + j * 8);
+        if (ok1) v1 = *reinterpret_cast<const float2*>(g1 + j * 8);
+        acc[j][0] = v0.x; acc[j][1] = v0.y; acc[j][2] = v1.x; acc[j][3] = v1.y;
+      }
+      const int kd = (m == RC / 16 - 1 && which != 0) ? 16 : 32;        // the last tile must not read past the Q / dO rows
+      const bf16* A = (which == 0) ? sAQ : (which == 1) ? sAK : sAV;
+      const bf16* Bm = (which == 0) ? sK + (16 * m + 32) * LD : (which == 1) ? sQ + (16 * m + 16) * LD : sdO + (16 * m) * LD;
+      warp_gemm<4, false, true>(acc, A + 16 * m * A_LD, A_LD, Bm + ch * 32, LD, kd, lane);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (ok0) *reinterpret_cast<float2*>(g0 + j * 8) = make_float2(acc[j][0], acc[j][1]);
+        if (ok1) *reinterpret_cast<float2*>(g1 + j * 8) = make_float2(acc[j][2], acc[j][3]);
+      }
+    }
+  } else {
   // ---- dQ, dK, dV of the owned positions: one warp per position (two at a time), two head dims per lane ----
-  for (int xr0 = warp; xr0 < R; xr0 += 2 * (NT / 32)) {
-    const int xr1 = xr0 + NT / 32;
-    const int ta = t0 + xr0, tb = t0 + xr1;
-    if (ta >= N) break;
-    const bool two = (xr1 < R) && (tb < N);
-    const int xb = two ? xr1 : xr0;                       // second position (a repeat of the first when absent)
-    float* ga = p.dQ + (bh * N + ta) * D + 2 * lane;
-    float* gb = p.dQ + (bh * N + t0 + xb) * D + 2 * lane;
-    const ptrdiff_t kofs = p.dK - p.dQ, vofs = p.dV - p.dQ;  // element offsets between the three outputs
-    float2 aq0 = *reinterpret_cast<const float2*>(ga), ak0 = *reinterpret_cast<const float2*>(ga + kofs), av0 = *reinterpret_cast<const float2*>(ga + vofs);
-    float2 aq1 = *reinterpret_cast<const float2*>(gb), ak1 = *reinterpret_cast<const float2*>(gb + kofs), av1 = *reinterpret_cast<const float2*>(gb + vofs);
+    for (int xr0 = warp; xr0 < R; xr0 += 2 * (NT / 32)) {
+      const int xr1 = xr0 + NT / 32;
+      const int ta = t0 + xr0, tb = t0 + xr1;
+      if (ta >= N) break;
+      const bool two = (xr1 < R) && (tb < N);
+      const int xb = two ? xr1 : xr0;                       // second position (a repeat of the first when absent)
+      float* ga = p.dQ + (bh * N + ta) * D + 2 * lane;
+      float* gb = p.dQ + (bh * N + t0 + xb) * D + 2 * lane;
+      const ptrdiff_t kofs = p.dK - p.dQ, vofs = p.dV - p.dQ;  // element offsets between the three outputs
+      float2 aq0 = *reinterpret_cast<const float2*>(ga), ak0 = *reinterpret_cast<const float2*>(ga + kofs), av0 = *reinterpret_cast<const float2*>(ga + vofs);
+      float2 aq1 = *reinterpret_cast<const float2*>(gb), ak1 = *reinterpret_cast<const float2*>(gb + kofs), av1 = *reinterpret_cast<const float2*>(gb + vofs);
 #pragma unroll 3
-    for (int e = 0; e < W; ++e) {
-      const float s10 = sdS[xr0 * DS_LD + e], s11 = sdS[xb * DS_LD + e];
-      const float s20 = sdS[(xr0 + e) * DS_LD + e], s21 = sdS[(xb + e) * DS_LD + e];
-      const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xr0 + 48 - e) * LD + 2 * lane);
-      const __nv_bfloat162 k1 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xb + 48 - e) * LD + 2 * lane);
-      const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xr0 + 16 + e) * LD + 2 * lane);
-      const __nv_bfloat162 q1 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xb + 16 + e) * LD + 2 * lane);
-      aq0.x = fmaf(s10, __low2float(k0), aq0.x); aq0.y = fmaf(s10, __high2float(k0), aq0.y);
-      aq1.x = fmaf(s11, __low2float(k1), aq1.x); aq1.y = fmaf(s11, __high2float(k1), aq1.y);
-      ak0.x = fmaf(s20, __low2float(q0), ak0.x); ak0.y = fmaf(s20, __high2float(q0), ak0.y);
-      ak1.x = fmaf(s21, __low2float(q1), ak1.x); ak1.y = fmaf(s21, __high2float(q1), ak1.y);
-    }
+      for (int e = 0; e < W; ++e) {
+        const float s10 = sdS[xr0 * DS_LD + e], s11 = sdS[xb * DS_LD + e];
+        const float s20 = sdS[(xr0 + e) * DS_LD + e], s21 = sdS[(xb + e) * DS_LD + e];
+        const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xr0 + 48 - e) * LD + 2 * lane);
+        const __nv_bfloat162 k1 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xb + 48 - e) * LD + 2 * lane);
+        const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xr0 + 16 + e) * LD + 2 * lane);
+        const __nv_bfloat162 q1 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xb + 16 + e) * LD + 2 * lane);
+        aq0.x = fmaf(s10, __low2float(k0), aq0.x); aq0.y = fmaf(s10, __high2float(k0), aq0.y);
+        aq1.x = fmaf(s11, __low2float(k1), aq1.x); aq1.y = fmaf(s11, __high2float(k1), aq1.y);
+        ak0.x = fmaf(s20, __low2float(q0), ak0.x); ak0.y = fmaf(s20, __high2float(q0), ak0.y);
+        ak1.x = fmaf(s21, __low2float(q1), ak1.x); ak1.y = fmaf(s21, __high2float(q1), ak1.y);
+      }
 #pragma unroll 2
-    for (int dd = 0; dd < band; ++dd) {
-      const float p0 = sP[(xr0 + dd) * P_LD + dd], p1 = sP[(xb + dd) * P_LD + dd];
-      const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xr0 + dd) * LD + 2 * lane);
-      const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xb + dd) * LD + 2 * lane);
-      av0.x = fmaf(p0, __low2float(o0), av0.x); av0.y = fmaf(p0, __high2float(o0), av0.y);
-      av1.x = fmaf(p1, __low2float(o1), av1.x); av1.y = fmaf(p1, __high2float(o1), av1.y);
+      for (int dd = 0; dd < band; ++dd) {
+        const float p0 = sP[(xr0 + dd) * P_LD + dd], p1 = sP[(xb + dd) * P_LD + dd];
+        const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xr0 + dd) * LD + 2 * lane);
+        const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xb + dd) * LD + 2 * lane);
+        av0.x = fmaf(p0, __low2float(o0), av0.x); av0.y = fmaf(p0, __high2float(o0), av0.y);
+        av1.x = fmaf(p1, __low2float(o1), av1.x); av1.y = fmaf(p1, __high2float(o1), av1.y);
+      }
+      *reinterpret_cast<float2*>(ga) = aq0; *reinterpret_cast<float2*>(ga + kofs) = ak0; *reinterpret_cast<float2*>(ga + vofs) = av0;
+      if (two) { *reinterpret_cast<float2*>(gb) = aq1; *reinterpret_cast<float2*>(gb + kofs) = ak1; *reinterpret_cast<float2*>(gb + vofs) = av1; }
     }
-    *reinterpret_cast<float2*>(ga) = aq0; *reinterpret_cast<float2*>(ga + kofs) = ak0; *reinterpret_cast<float2*>(ga + vofs) = av0;
-    if (two) { *reinterpret_cast<float2*>(gb) = aq1; *reinterpret_cast<float2*>(gb + kofs) = ak1; *reinterpret_cast<float2*>(gb + vofs) = av1; }
   }
   TRACEK(8);
 }
