@@ -164,8 +164,51 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   __syncthreads();
   TRACEK(3);
 
-  // ---- conv, P and dC: (row, diagonal) pairs, KC per thread side by side for ILP ----
-  if (band > 0) {
+  // ---- conv, P and dC ----
+  if constexpr (CQ > 0) {
+    // compile-time filter: a thread owns half of the diagonals of one row and keeps the score
+    // segment each filter row needs in registers (one shared-memory load per ~5 FMAs)
+    constexpr int PQ = CQ - 1, PK = (CK - 1) / 2, BAND = PQ + PK, HB = (BAND + 1) / 2, SEG = HB + CK - 1;
+    if (tid < 2 * RC) {
+      const int x = tid >> 1, half = tid & 1;
+      const int d0 = half * HB, cnt = half ? BAND - HB : HB;
+      float c[HB];
+#pragma unroll
+      for (int i = 0; i < HB; ++i) c[i] = 0.f;
+#pragma unroll
+      for (int a = 0; a < CQ; ++a) {
+        const float* row = sSb + (x + 16 - PQ + a) * SB_LD + BAND + d0 + a - PQ + PK - (CK - 1);
+        float seg[SEG];
+#pragma unroll
+        for (int i = 0; i < SEG; ++i) seg[i] = row[i];
+#pragma unroll
+        for (int bb = 0; bb < CK; ++bb) {
+          const float w = sTheta[a * kThetaLdBand + bb];
+#pragma unroll
+          for (int i = 0; i < HB; ++i) c[i] = fmaf(w, seg[i + (CK - 1 - bb)], c[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < HB; ++i) {
+        if (i < cnt) {
+          const int dd = d0 + i;
+          const float cval = c[i];
+      const int gi = t0 + x;
+          const bool live = (gi < N) && (gi - dd >= 0);
+          const float pr = live ? exp2f(cval * kLog2e - sLse[x]) : 0.f;
+          const float dp = sP[x * P_LD + dd];
+          sdC[x * DC_LD + pk + dd] = pr * (dp - sDv[x]);
+          if (mma_out) {            // P^T operand of dV: row = key position x - dd, column = x relative to that key's tile
+            const int j = x - dd;
+            if (j >= 0) sAV[j * A_LD + x - (j & ~15)] = __float2bfloat16(pr);
+          } else {
+            sP[x * P_LD + dd] = pr;
+          }
+        }
+      }
+    }
+  } else
+  if (band > 0) {   // run-time filter: (row, diagonal) pairs, KC per thread side by side for ILP
     constexpr int KC = (CQ > 0) ? (RC * (CQ - 1 + (CK - 1) / 2) + NT - 1) / NT : (RC * MAXBAND + NT - 1) / NT;
     const int nout = RC * band;
     float c[KC];
@@ -209,8 +252,36 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   __syncthreads();
   TRACEK(4);
 
-  // ---- dTheta: one thread per tap, row groups in parallel; the columns past the band are zero ----
-  {
+  // ---- dTheta ----
+  if constexpr (CQ > 0) {
+    // one warp per filter row a, lanes over the owned rows; the dC row and the score segment live in registers
+    constexpr int PQ = CQ - 1, PK = (CK - 1) / 2, BAND = PQ + PK, SEG = BAND + CK - 1;
+    if (warp < CQ) {
+      const int a = warp;
+      float t[CK];
+#pragma unroll
+      for (int bb = 0; bb < CK; ++bb) t[bb] = 0.f;
+      for (int x = lane; x < R; x += 32) {
+        float dc[BAND], seg[SEG];
+        const float* rc = sdC + x * DC_LD + PK;
+        const float* row = sSb + (x + 16 - PQ + a) * SB_LD + BAND + a - PQ + PK - (CK - 1);
+#pragma unroll
+        for (int i = 0; i < BAND; ++i) dc[i] = rc[i];
+#pragma unroll
+        for (int i = 0; i < SEG; ++i) seg[i] = row[i];
+#pragma unroll
+        for (int bb = 0; bb < CK; ++bb)
+#pragma unroll
+          for (int i = 0; i < BAND; ++i) t[bb] = fmaf(dc[i], seg[i + (CK - 1 - bb)], t[bb]);
+      }
+#pragma unroll
+      for (int bb = 0; bb < CK; ++bb) {
+        const float v = warp_sum(t[bb]);
+        if (lane == 0) sRed[a * CK + bb] = v;
+      }
+    }
+  } else
+  {   // run-time filter: one thread per tap, row groups in parallel; the columns past the band are zero
     const int ntaps = cq * ck;
     const int ngroups = NT / ntaps;
     const int g = tid / ntaps, tap = tid - g * ntaps;
@@ -242,7 +313,47 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
     __syncthreads();
   }
   // ---- adjoint conv: dSb[i', e] for the rows that feed the owned positions ----
-  if (W > 0) {
+  if constexpr (CQ > 0) {
+    // a thread owns half of the diagonals e of one row; the dC segment of each filter row in registers
+    constexpr int PQ = CQ - 1, PK = (CK - 1) / 2, WW = PQ + 2 * PK, HW = (WW + 1) / 2, SEG = HW + CK - 1;
+    if (tid < 2 * (R + WW - 1)) {
+      const int xr = tid >> 1, half = tid & 1;
+      const int e0 = half * HW, cnt = half ? WW - HW : HW;
+      float sa[HW];
+#pragma unroll
+      for (int i = 0; i < HW; ++i) sa[i] = 0.f;
+#pragma unroll
+      for (int a = 0; a < CQ; ++a) {
+        const float* row = sdC + (xr + PQ - a) * DC_LD + e0 - a + PQ;   // column pk + (e - a + pq - pk + b)
+        float seg[SEG];
+#pragma unroll
+        for (int i = 0; i < SEG; ++i) seg[i] = row[i];
+#pragma unroll
+        for (int bb = 0; bb < CK; ++bb) {
+          const float w = sTheta[a * kThetaLdBand + bb];
+#pragma unroll
+          for (int i = 0; i < HW; ++i) sa[i] = fmaf(w, seg[i + bb], sa[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < HW; ++i) {
+        if (i < cnt) {
+          const int e = e0 + i;
+          const float sval = sa[i];
+        const float v = sval * p.scale;
+          if (mma_out) {
+            const bf16 vb = __float2bfloat16(v);
+            sAQ[xr * A_LD + (xr & 15) - e + 16] = vb;            // dQ: row = query position, column = key relative to (tile start - 16)
+            const int j = xr - e;
+            if (j >= 0) sAK[j * A_LD + xr - (j & ~15)] = vb;     // dK: row = key position, column = query relative to the key's tile
+          } else {
+            sdS[xr * DS_LD + e] = v;
+          }
+        }
+      }
+    }
+  } else
+  if (W > 0) {   // run-time filter
     constexpr int KA = (CQ > 0) ? ((RC - (CQ - 1)) * (CQ - 1 + CK - 1) + NT - 1) / NT : (RC * MAXW + NT - 1) / NT;
     const int nout = (R + W - 1) * W;
     float sacc[KA];
@@ -286,7 +397,7 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   {
     const int ntaps = cq * ck;
     if (tid < ntaps) {
-      const int ngroups = NT / ntaps;
+      const int ngroups = (CQ > 0) ? 1 : NT / ntaps;
       float t = 0.f;
       for (int g = 0; g < ngroups; ++g) t += sRed[g * ntaps + tid];
       const int slot = b * gridDim.x + blockIdx.x;
