@@ -99,7 +99,36 @@ __global__ void __launch_bounds__(FwdBandCfg<D>::NT, 2) fwd_band_kernel(const Tr
     }
     __syncthreads();
 
-    // ---- conv: (row, diagonal) pairs, KC per thread side by side ----
+    // ---- conv ----
+    if constexpr (CQ > 0) {
+      // compile-time filter: a thread owns half of the diagonals of one row and keeps the score
+      // segment each filter row needs in registers
+      constexpr int PQ = CQ - 1, PK = (CK - 1) / 2, BAND = PQ + PK, HB = (BAND + 1) / 2, SEG = HB + CK - 1;
+      if (tid < 2 * R) {
+        const int x = tid >> 1, half = tid & 1;
+        const int d0 = half * HB, cnt = half ? BAND - HB : HB;
+        float c[HB];
+#pragma unroll
+        for (int i = 0; i < HB; ++i) c[i] = 0.f;
+#pragma unroll
+        for (int a = 0; a < CQ; ++a) {
+          const float* row = sSb + (x + 16 - PQ + a) * SB_LD + BAND + d0 + a - PQ + PK - (CK - 1);
+          float seg[SEG];
+#pragma unroll
+          for (int i = 0; i < SEG; ++i) seg[i] = row[i];
+#pragma unroll
+          for (int bb = 0; bb < CK; ++bb) {
+            const float w = sTheta[a * kThLd + bb];
+#pragma unroll
+            for (int i = 0; i < HB; ++i) c[i] = fmaf(w, seg[i + (CK - 1 - bb)], c[i]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < HB; ++i)
+          if (i < cnt) sC[x * C_LD + d0 + i] = c[i];
+      }
+    } else {
+    // run-time filter: (row, diagonal) pairs, KC per thread side by side
     constexpr int KC = (CQ > 0) ? (R * (CQ - 1 + (CK - 1) / 2) + NT - 1) / NT : (R * Cfg::MAXBAND + NT - 1) / NT;
     const int nout = R * band;
     float c[KC];
@@ -125,6 +154,7 @@ __global__ void __launch_bounds__(FwdBandCfg<D>::NT, 2) fwd_band_kernel(const Tr
     for (int k = 0; k < KC; ++k) {
       const int o = tid + k * NT;
       if (o < nout) { const int x = o / band; sC[x * C_LD + (o - x * band)] = c[k]; }
+    }
     }
     __syncthreads();
   }
