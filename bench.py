@@ -192,8 +192,9 @@ def main():
     stream = torch.cuda.current_stream()
     # the dominant kernel of the step is timed alone through the library's profiling hook
     # (cudaEventRecord around that one launch, on the launch stream)
-    KERNELS = {1: "fwd_tc_kernel", 2: "fwd_exact_kernel", 3: "bwd_dq_tc_kernel", 4: "bwd_dkdv_tc_kernel",
-               5: "bwd_dq_kernel", 6: "bwd_dkdv_kernel"}
+    KERNELS = {1: "fwd_tc_kernel", 2: "fwd_band_kernel", 3: "bwd_dq_tc_kernel", 4: "bwd_dkdv_tc_kernel",
+               5: "bwd_dq_kernel", 6: "bwd_dkdv_kernel", 8: "bwd_band_kernel", 9: "ktilde_window_kernel",
+               10: "dk_post_window_kernel"}
     DOMINANT = 4
     kern_ev = []   # (start, end) events around the dominant kernel, per step
 
@@ -248,16 +249,51 @@ def main():
     value = world * fl / (ms_step * 1e-3) / 1e12
 
     # ---- end to end: host buffers in, dTheta out ----
-    def e2e_step():
-        dq_, dk_, dv_, ddo_ = (t.to(dev, non_blocking=True) for t in host)
-        out = step(dq_, dk_, dv_, ddo_)
-        dth_host.copy_(out[4], non_blocking=True)
-    for _ in range(2):
-        e2e_step()
-    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    # Every step copies its four inputs from pinned host memory and reads dTheta back.  The copy of
+    # step i+1 runs on a second stream into the other of two device buffer sets while step i
+    # computes (the usual input prefetch); the first copy of a timed run is not overlapped.
+    copy_stream = torch.cuda.Stream(device=dev)
+    dev_bufs = [[torch.empty_like(t, device=dev) for t in host] for _ in range(2)]
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def prefetch(slot):
+        copy_stream.wait_event(consumed[slot])          # the step that last read this buffer set is done
+        with torch.cuda.stream(copy_stream):
+            for dst, src in zip(dev_bufs[slot], host):
+                dst.copy_(src, non_blocking=True)
+            copied[slot].record(copy_stream)
+
+    def e2e_run(steps):
+        for ev in consumed:
+            ev.record(stream)
+        prefetch(0)
+        for i in range(steps):
+            slot = i & 1
+            if i + 1 < steps:
+                prefetch(slot ^ 1)
+            stream.wait_event(copied[slot])
+            out = step(*dev_bufs[slot])
+            consumed[slot].record(stream)
+            dth_host.copy_(out[4], non_blocking=True)
+
+    e2e_run(2)
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    e2e_run(args.steps)
+    e1.record(stream)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    ms_e2e /= args.steps
     h2d = sum(t.numel() * t.element_size() for t in host)
     e2e = dict(value=world * fl / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", h2d_bytes_per_step=h2d,
-               d2h_bytes_per_step=dth_host.numel() * 4, ms_per_step=ms_e2e)
+               d2h_bytes_per_step=dth_host.numel() * 4, ms_per_step=ms_e2e,
+               note="inputs of step i+1 are copied on a second stream while step i computes")
 
     # ---- roofline of the dominant kernel: bwd_dkdv_tc_kernel (dK~/dV on tcgen05) ----
     # algorithmic work of that kernel per launch (FlashAttention convention): recompute S, dP,
@@ -283,7 +319,9 @@ def main():
                             global_batch=B * world, parallelism="batch x head sharding, dTheta all-reduce" if world > 1 else "single GPU",
                             l2="inputs+outputs per step (%.0f MB) exceed the 126 MB L2" % ((4 * 2 + 4 * 4) * B * H * N * d / 1e6),
                             flops_attn_gflop=fl / 1e9, flops_conv_gflop=8 * cq * ck * E / 1e9),
-                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=12 * args.steps)
+                # kernels of this library per step: forward = stacked-key pre-pass, fwd_tc, fwd_band; rowdot;
+                # backward = pre-pass, dq_tc, dkdv_tc, dKt adjoint, bwd_band, partial reduction
+                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=10 * args.steps)
 
     # ---- decode (HBM-bound), rank-local, reported beside the headline ----
     if not args.no_decode:

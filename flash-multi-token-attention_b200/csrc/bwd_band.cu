@@ -481,11 +481,6 @@ extern "C" int fmta_debug_trace_band(long long* host, int n) {
 }
 #endif
 
-bool bwd_band_supported(const TrainParams& p) {
-  const int pq = p.cq - 1, pk = (p.ck - 1) / 2;
-  return p.theta != nullptr && p.Wmix == nullptr && p.d == bandcfg::D && pq <= bandcfg::MAXPQ && pk <= bandcfg::MAXPK;
-}
-
 int bwd_band_theta_slots(int B, int N, int cq, int ck) {
   const int R = bwd_band_positions(cq, ck);
   return B * ((N + R - 1) / R);

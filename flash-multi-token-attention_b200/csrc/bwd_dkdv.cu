@@ -6,7 +6,7 @@ namespace fmta {
 
 template <int D, int CQ, int CK>
 static cudaError_t launch_bwd_dkdv_t(const TrainParams& p, cudaStream_t stream) {
-  const int own = (p.kmode == kBandTiles) ? p.band_ownk : 64;
+  const int own = 64;
   const int nKB = (p.N + own - 1) / own;
   dim3 grid(nKB, p.H, p.B), block(256);
   const bool mix = (p.Wmix != nullptr) && p.G > 1;

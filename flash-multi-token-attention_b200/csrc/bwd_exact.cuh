@@ -112,7 +112,7 @@ struct BwdSmem {
 // Leaves bf16 P (owned tile) in sPb and bf16 dS (owned tile) in sDS, visible CTA-wide.
 template <int D, int CQ, int CK, bool MIX, bool WANT_DTHETA>
 FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& p, int i0, int j0,
-                          int cq, int ck, int G, int grank, int tid, int own_rows) {
+                          int cq, int ck, int G, int grank, int tid) {
   using Cfg = BwdExactCfg<D, CQ, CK, MIX>;
   constexpr int BR = Cfg::BR, H1 = Cfg::H1, HC = Cfg::HC, ER = Cfg::ER, EC = Cfg::EC;
   constexpr int SR = Cfg::SR, SC = Cfg::SC, S_LD = Cfg::S_LD, E_LD = Cfg::E_LD, QK_LD = Cfg::QK_LD;
@@ -122,7 +122,6 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
   const bool causal = p.causal != 0;
   const int pq = cq - 1, pk = (ck - 1) / 2;
   // band mode: entries with query - key >= pad_q + pad_k belong to the stacked tensor-core kernels
-  const bool band_only = (p.kmode == kBandTiles);
 
   // ---- 1. S on the large region ----
   {
@@ -167,7 +166,7 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int kj = j0 - HC + s * 16 + i;
-        const bool ok = (qi < N) && (kj >= 0) && (kj < N) && !(causal && kj > qi) && !(band_only && qi - kj >= pq + pk);
+        const bool ok = (qi < N) && (kj >= 0) && (kj < N) && !(causal && kj > qi);
         acc[i] = ok ? exp2f((acc[i] - lse) * kLog2e) : 0.f;
       }
     }
@@ -198,7 +197,7 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int kj = j0 - HC + s * 16 + i;
-        const bool ok = (qi < N) && (kj >= 0) && (kj < N) && !(causal && kj > qi) && !(band_only && qi - kj >= pq + pk);
+        const bool ok = (qi < N) && (kj >= 0) && (kj < N) && !(causal && kj > qi);
         acc[i] = ok ? exp2f((acc[i] - lse) * kLog2e) : 0.f;
       }
       float4* o = reinterpret_cast<float4*>(sm.sE + r * E_LD + s * 16);
@@ -289,10 +288,6 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
       const float4* src = reinterpret_cast<const float4*>(dcfin + r * E_LD + HC + s * 16);
 #pragma unroll
       for (int i = 0; i < 4; ++i) { float4 v = src[i]; dcv[4*i] = v.x; dcv[4*i+1] = v.y; dcv[4*i+2] = v.z; dcv[4*i+3] = v.w; }
-      if (r >= own_rows) {   // band mode: rows past the owned ones belong to the next CTA
-#pragma unroll
-        for (int i = 0; i < 16; ++i) dcv[i] = 0.f;
-      }
     }
     float* dth = sm.sDTh + warp * (kMaxCQ * kThetaLd);
     if constexpr (CQ > 0) {
@@ -400,12 +395,10 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
   BwdSmem<D, CQ, CK, MIX> sm(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = p.N, H = p.H;
-  const bool band_only = (p.kmode == kBandTiles);
-  const int own_rows = band_only ? p.band_ownq : BR;      // dQ rows this CTA stores
-  const int nQB = (N + own_rows - 1) / own_rows, nKB = (N + BC - 1) / BC;
+  const int nQB = (N + BR - 1) / BR, nKB = (N + BC - 1) / BC;
   const int qb = nQB - 1 - (int)blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
-  const int i0 = qb * own_rows;
+  const int i0 = qb * BR;
   const int cq = (CQ > 0) ? CQ : p.cq, ck = (CQ > 0) ? CK : p.ck;
   const bool causal = p.causal != 0;
   const size_t bh = (size_t)b * H + h;
@@ -421,22 +414,19 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
   load_rows_async<D, Cfg::NT>(sm.sdO, QK_LD, dOg, i0, Cfg::ER, N, tid);
   cp_async_commit();
 
-  // Band mode: one tile, starting band_off keys before the first owned row, holds every band entry
-  // that reaches the owned dQ rows (through the adjoint conv) -- see band_geometry().
-  int kb_begin = 0, kb_end = causal ? min(nKB - 1, (i0 + BR - 1) / BC) : nKB - 1;
-  if (band_only) { kb_begin = 0; kb_end = causal ? 0 : -1; }
+  const int kb_begin = 0, kb_end = causal ? min(nKB - 1, (i0 + BR - 1) / BC) : nKB - 1;
   constexpr int ONT = D / 16;
   float accQ[ONT][4] = {};
   const int mt = warp & 3, nh = warp >> 2;
 
   for (int kb = kb_begin; kb <= kb_end; ++kb) {
-    const int j0 = band_only ? (i0 - p.band_off) : kb * BC;
+    const int j0 = kb * BC;
     load_rows_async<D, Cfg::NT>(sm.sK, QK_LD, Kg, j0 - 2 * HC, Cfg::SR, N, tid);
     load_rows_async<D, Cfg::NT>(sm.sV, QK_LD, Vg, j0 - HC, Cfg::ER, N, tid);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    bwd_tile<D, CQ, CK, MIX, true>(sm, p, i0, j0, cq, ck, G, grank, tid, own_rows);
+    bwd_tile<D, CQ, CK, MIX, true>(sm, p, i0, j0, cq, ck, G, grank, tid);
     // dQ += dS K   (K rows of the owned key block start at row 2*HC of sK)
     warp_gemm<ONT, false, true>(accQ, sm.sDS + mt * 16 * B_LD, B_LD, sm.sK + (2 * HC) * QK_LD + nh * (D / 2), QK_LD, BC, lane);
     __syncthreads();
@@ -449,16 +439,14 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
 #pragma unroll
     for (int j = 0; j < ONT; ++j) {
       const int col = nh * (D / 2) + j * 8 + (lane & 3) * 2;
-      if (i0 + r0 < N && r0 < own_rows) {
+      if (i0 + r0 < N) {
         float2* o = reinterpret_cast<float2*>(p.dQ + (bh * N + i0 + r0) * D + col);
         float2 v = make_float2(accQ[j][0] * p.scale, accQ[j][1] * p.scale);
-        if (p.accumulate) { const float2 u = *o; v.x += u.x; v.y += u.y; }
         *o = v;
       }
-      if (i0 + r1 < N && r1 < own_rows) {
+      if (i0 + r1 < N) {
         float2* o = reinterpret_cast<float2*>(p.dQ + (bh * N + i0 + r1) * D + col);
         float2 v = make_float2(accQ[j][2] * p.scale, accQ[j][3] * p.scale);
-        if (p.accumulate) { const float2 u = *o; v.x += u.x; v.y += u.y; }
         *o = v;
       }
     }
@@ -497,12 +485,10 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
   BwdSmem<D, CQ, CK, MIX> sm(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = p.N, H = p.H;
-  const bool band_only = (p.kmode == kBandTiles);
-  const int own_keys = band_only ? p.band_ownk : BC;      // dK / dV rows this CTA stores
   const int nQB = (N + BR - 1) / BR;
   const int kb = blockIdx.x;  // early key blocks see the most query blocks -> already longest first
   const int h = blockIdx.y, b = blockIdx.z;
-  const int j0 = kb * own_keys;
+  const int j0 = kb * BC;
   const int cq = (CQ > 0) ? CQ : p.cq, ck = (CQ > 0) ? CK : p.ck;
   const bool causal = p.causal != 0;
   const size_t bh = (size_t)b * H + h;
@@ -517,23 +503,20 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
   load_rows_async<D, Cfg::NT>(sm.sV, QK_LD, Vg, j0 - HC, Cfg::ER, N, tid);
   cp_async_commit();
 
-  // Band mode: the single query block that starts at the first owned key holds every band entry
-  // whose gradient reaches the owned keys -- see band_geometry().
-  int qb_begin = causal ? (j0 / BR) : 0, qb_end = nQB - 1;
-  if (band_only) { qb_begin = 0; qb_end = causal ? 0 : -1; }
+  const int qb_begin = causal ? (j0 / BR) : 0, qb_end = nQB - 1;
   constexpr int ONT = D / 16;
   float accK[ONT][4] = {}, accV[ONT][4] = {};
   const int mt = warp & 3, nh = warp >> 2;
 
   for (int qb = qb_begin; qb <= qb_end; ++qb) {
-    const int i0 = band_only ? j0 : qb * BR;
+    const int i0 = qb * BR;
     bwd_load_rowstats<D, CQ, CK, MIX>(sm, p, bh, i0, tid);
     load_rows_async<D, Cfg::NT>(sm.sQ, QK_LD, Qg, i0 - H1, Cfg::SR, N, tid);
     load_rows_async<D, Cfg::NT>(sm.sdO, QK_LD, dOg, i0, Cfg::ER, N, tid);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    bwd_tile<D, CQ, CK, MIX, false>(sm, p, i0, j0, cq, ck, G, grank, tid, BR);
+    bwd_tile<D, CQ, CK, MIX, false>(sm, p, i0, j0, cq, ck, G, grank, tid);
     // dV += P^T dO ; dK += dS^T Q   (A operands stored [query][key] -> transposed loads)
     warp_gemm<ONT, true, true>(accV, sm.sPb + mt * 16, B_LD, sm.sdO + nh * (D / 2), QK_LD, BR, lane);
     warp_gemm<ONT, true, true>(accK, sm.sDS + mt * 16, B_LD, sm.sQ + H1 * QK_LD + nh * (D / 2), QK_LD, BR, lane);
@@ -548,15 +531,11 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const int r = hh ? r1 : r0;
-      if (j0 + r < N && r < own_keys) {
+      if (j0 + r < N) {
         float2* ok_ = reinterpret_cast<float2*>(p.dK + (bh * N + j0 + r) * D + col);
         float2* ov_ = reinterpret_cast<float2*>(p.dV + (bh * N + j0 + r) * D + col);
         float2 vk = make_float2(accK[j][2 * hh] * p.scale, accK[j][2 * hh + 1] * p.scale);
         float2 vv = make_float2(accV[j][2 * hh], accV[j][2 * hh + 1]);
-        if (p.accumulate) {
-          const float2 uk = *ok_, uv = *ov_;
-          vk.x += uk.x; vk.y += uk.y; vv.x += uv.x; vv.y += uv.y;
-        }
         *ok_ = vk; *ov_ = vv;
       }
     }

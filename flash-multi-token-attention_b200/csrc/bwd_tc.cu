@@ -6,8 +6,8 @@
 //     dQ[i'] = ln2 * sum_a sum_j dC[i' + pad_q - a, j] Kt_a[j]
 //     dKt_a  = dC^T Q^(a)  (gradient w.r.t. Kt_a / (scale*log2e) ... i.e. before the pre-pass scaling)     dV = P^T dO
 // and dK / dTheta follow from dKt_a by the adjoint of the pre-pass (dk_post_kernel).
-// The band entries are handled by the exact kernels (bwd_exact.cuh, kmode = kBandTiles), which
-// accumulate into the same outputs.
+// The band entries are handled by bwd_band_kernel (bwd_band.cu), which adds its part to the same
+// outputs afterwards.
 //
 //   bwd_dq_tc_kernel   : CTA = NT query-row tiles, loops key blocks.  A tile computes dC for
 //                        128 rows but owns only the first 112 of them as dQ rows: dQ row i'

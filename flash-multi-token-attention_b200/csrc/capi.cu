@@ -84,11 +84,9 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
     return n * sizeof(float);
   }
   if (op == FMTA_OP_BWD_TC) {
-    // dTheta partials of the exact band kernel and of the tensor-core post-pass (one contiguous
-    // slot array, rounded up), followed by the tensor-core backward's buffers
-    int off, ownq, ownk;
-    band_geometry(cq, ck, &off, &ownq, &ownk);
-    const size_t slots = (size_t)B * ((N + ownq - 1) / ownq) + (size_t)bwd_tc_theta_slots(B, N, ck);
+    // dTheta partials of the band kernel and of the tensor-core post-pass (one contiguous slot
+    // array, rounded up), followed by the tensor-core backward's buffers
+    const size_t slots = (size_t)bwd_band_theta_slots(B, N, cq, ck) + (size_t)bwd_tc_theta_slots(B, N, ck);
     const size_t part = (slots * H * (size_t)(cq * ck) * sizeof(float) + 1023) / 1024 * 1024;
     return part + bwd_tc_workspace_bytes(B, H, N, d, cq);
   }
@@ -114,7 +112,6 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
   p.B = B; p.H = H; p.N = N; p.d = d;
   p.cq = theta ? cq : 1; p.ck = theta ? ck : 1; p.G = (wmix && G > 1) ? G : 1;
   p.scale = scale; p.causal = causal; p.o_bf16 = (o_dtype == FMTA_DTYPE_BF16);
-  p.kmode = kAllTiles;
   // a 1x1 mixing "group" is a per-head scalar; fold it away by treating it as no mix only
   // when W is absent -- with G == 1 and W given the scalar still applies:
   if (wmix && G == 1) return FMTA_ERR_UNSUPPORTED;
@@ -132,9 +129,7 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
     // stacked tensor-core kernel off the causal band, then the band kernel, which continues the
     // online softmax from the un-normalised partial and writes the final O, M, L
     if (int s = check_cuda(launch_fwd_tc(p, workspace, &p.Opart, &p.Mpart, &p.Lpart, (cudaStream_t)stream))) return s;
-    if (fwd_band_supported(p)) return check_cuda(launch_fwd_band(p, (cudaStream_t)stream));
-    p.kmode = kBandTiles;
-    band_geometry(p.cq, p.ck, &p.band_off, &p.band_ownq, &p.band_ownk);
+    return check_cuda(launch_fwd_band(p, (cudaStream_t)stream));
   }
   return check_cuda(launch_fwd_exact(p, (cudaStream_t)stream));
 }
@@ -159,7 +154,7 @@ static int fill_bwd(TrainParams& p, const void* Q, const void* K, const void* V,
   p.theta = theta; p.Wmix = wmix;
   p.B = B; p.H = H; p.N = N; p.d = d;
   p.cq = theta ? cq : 1; p.ck = theta ? ck : 1; p.G = wmix ? G : 1;
-  p.scale = scale; p.causal = causal; p.kmode = kAllTiles;
+  p.scale = scale; p.causal = causal;
   return FMTA_OK;
 }
 
@@ -239,10 +234,7 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
     return FMTA_OK;
   }
   // tensor-core kernels for the entries off the causal band, then the band kernel adds its part
-  const bool lean_band = bwd_band_supported(p);
-  band_geometry(p.cq, p.ck, &p.band_off, &p.band_ownq, &p.band_ownk);
-  slots_ex = lean_band ? bwd_band_theta_slots(B, N, p.cq, p.ck)
-                       : B * ((N + p.band_ownq - 1) / p.band_ownq);   // one dTheta partial per band CTA
+  slots_ex = bwd_band_theta_slots(B, N, p.cq, p.ck);            // one dTheta partial per band CTA
   const int slots_tc = bwd_tc_theta_slots(B, N, p.ck);
   float* part = reinterpret_cast<float*>(workspace);
   const size_t part_bytes = ((size_t)(slots_ex + slots_tc) * n_theta * sizeof(float) + 1023) / 1024 * 1024;
@@ -251,15 +243,10 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
   if (int s = check_cuda(launch_bwd_dkdv_tc(p, tcw, part + (size_t)slots_ex * n_theta, st))) return s;
   p.n_slots = slots_ex;
   p.dTheta_part = part;
-  if (lean_band && causal) {
+  if (causal) {
     if (int s = check_cuda(launch_bwd_band(p, st))) return s;
-  } else if (lean_band) {
+  } else {   // no causal mask: no band
     if (int s = check_cuda(cudaMemsetAsync(part, 0, (size_t)slots_ex * n_theta * sizeof(float), st))) return s;
-  } else {
-    p.kmode = kBandTiles;
-    p.accumulate = 1;
-    if (int s = check_cuda(launch_bwd_dq(p, st))) return s;
-    if (int s = check_cuda(launch_bwd_dkdv(p, st))) return s;
   }
   return check_cuda(launch_reduce_partials(part, dTheta, slots_ex + slots_tc, (int)n_theta, st));
 }

@@ -6,12 +6,6 @@
 
 namespace fmta {
 
-// Which key blocks of a query block a kernel walks.
-enum KMode : int {
-  kAllTiles = 0,      // every (causally reachable) key block
-  kBandTiles = 1,     // only key blocks that touch the causal band i-j < pad_q+pad_k
-};
-
 struct TrainParams {
   const __nv_bfloat16* Q;
   const __nv_bfloat16* K;
@@ -25,7 +19,7 @@ struct TrainParams {
   float* M;                  // forward: [B,H,N] row max
   float* L;                  // forward: [B,H,N] row sum of exp(C - M)
   float* LSEout;             // forward (optional): M + log L
-  const float* Opart;        // forward (optional): un-normalised partial O to start from
+  const float* Opart;        // forward band kernel: un-normalised partial (O, m, l) left by the tensor-core kernel
   const float* Mpart;
   const float* Lpart;
   float* dQ;                 // backward outputs, fp32
@@ -37,27 +31,8 @@ struct TrainParams {
   float scale;
   int causal;
   int o_bf16;
-  int kmode;
-  int accumulate;            // backward: add into dQ/dK/dV instead of overwriting
   int n_slots;
-  // band mode (kmode == kBandTiles): one 64x64 tile per CTA, placed so that it holds every band entry
-  // of the rows (keys) the CTA owns: key tile starts band_off before the first owned row
-  int band_off;              // 16 or 32
-  int band_ownq;             // query rows owned per CTA (forward, dQ kernel)
-  int band_ownk;             // keys owned per CTA (dK/dV kernel)
 };
-
-// Geometry of the band tiles for a filter shape (see TrainParams::band_*).
-inline void band_geometry(int cq, int ck, int* off, int* ownq, int* ownk) {
-  const int pq = cq - 1, pk = (ck - 1) / 2, band = pq + pk;
-  *off = (band + pk <= 17) ? 16 : 32;
-  int oq = 64 - *off;
-  if (72 - *off - pq < oq) oq = 72 - *off - pq;
-  *ownq = oq;
-  int ok = 65 - band - pq;
-  if (ok > 48) ok = 48;
-  *ownk = ok;
-}
 
 struct DecodeParams {
   const __nv_bfloat16* Q;    // [B,H,q_len,d]

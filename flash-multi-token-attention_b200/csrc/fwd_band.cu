@@ -226,11 +226,6 @@ __global__ void __launch_bounds__(FwdBandCfg<D>::NT, 2) fwd_band_kernel(const Tr
   }
 }
 
-bool fwd_band_supported(const TrainParams& p) {
-  return p.theta != nullptr && p.Wmix == nullptr && (p.d == 64 || p.d == 128) && p.cq <= 16 && p.ck <= 17 &&
-         p.Opart != nullptr && p.Mpart != nullptr && p.Lpart != nullptr;
-}
-
 template <int D>
 static cudaError_t launch_fwd_band_t(const TrainParams& p, cudaStream_t stream) {
   using Cfg = FwdBandCfg<D>;

@@ -6,7 +6,7 @@ namespace fmta {
 
 template <int D, int CQ, int CK>
 static cudaError_t launch_fwd_exact_t(const TrainParams& p, cudaStream_t stream) {
-  const int own = (p.kmode == kBandTiles) ? p.band_ownq : 64;
+  const int own = 64;
   const int nQB = (p.N + own - 1) / own;
   dim3 grid(nQB, p.H, p.B), block(256);
   const bool mix = (p.Wmix != nullptr) && p.G > 1;

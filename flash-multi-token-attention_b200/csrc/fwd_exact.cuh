@@ -10,8 +10,8 @@
 // trip through HBM inside the key loop.
 //
 // This kernel is exact for every tile, including the causal band where the stacked-GEMM
-// formulation (fwd_tc.cu) does not apply; with kmode == kBandTiles it walks only those key
-// blocks and continues an online softmax started by the stacked kernel (Opart/Mpart/Lpart).
+// formulation (fwd_tc.cu) does not apply.  It is the path for head mixing, d = 32, calls
+// without a workspace and `path = 0`; the tensor-core path handles the band in fwd_band.cu.
 #pragma once
 #include <cooperative_groups.h>
 
@@ -68,12 +68,10 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = p.N, H = p.H;
-  const bool band_only = (p.kmode == kBandTiles);
-  const int own_rows = band_only ? p.band_ownq : BR;      // rows this CTA stores
-  const int nQB = (N + own_rows - 1) / own_rows, nKB = (N + BC - 1) / BC;
+  const int nQB = (N + BR - 1) / BR, nKB = (N + BC - 1) / BC;
   const int qb = nQB - 1 - (int)blockIdx.x;  // long (late) query blocks first
   const int h = blockIdx.y, b = blockIdx.z;
-  const int i0 = qb * own_rows;
+  const int i0 = qb * BR;
   const int cq = (CQ > 0) ? CQ : p.cq, ck = (CQ > 0) ? CK : p.ck;
   const int pq = cq - 1, pk = (ck - 1) / 2;
   const bool causal = p.causal != 0;
@@ -93,47 +91,22 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
     if (tid < G * G) sW[tid] = p.Wmix[(size_t)(h / G) * G * G + tid];
   }
 
-  // key-block range.  Band mode: the entries with query - key >= pad_q + pad_k were done by the
-  // stacked tensor-core kernel; the band entries of the own_rows rows owned here all lie in the
-  // single 64-key tile that starts band_off keys before the first owned row.
-  int kb_begin = 0, kb_end = nKB - 1;
-  if (band_only) {
-    kb_begin = 0;
-    kb_end = causal ? 0 : -1;      // no causal band: nothing to do here but finalise
-  } else if (causal) {
-    kb_end = min(nKB - 1, (i0 + BR - 1) / BC);
-  }
+  const int kb_begin = 0, kb_end = causal ? min(nKB - 1, (i0 + BR - 1) / BC) : nKB - 1;
 
   // running softmax state and output accumulators
   constexpr int ONT = D / 16;  // n8-tiles per warp (half of the head dim)
   float accO[ONT][4];
   const int mt = warp & 3, nh = warp >> 2;
   const int fr0 = mt * 16 + (lane >> 2), fr1 = fr0 + 8;
-  {
-    const bool part = (p.Opart != nullptr);
-    if (tid < BR) {
-      const int gi = i0 + tid;
-      float m0 = -INFINITY, l0 = 0.f;
-      if (part && gi < N) { m0 = p.Mpart[bh * N + gi]; l0 = p.Lpart[bh * N + gi]; }
-      sM[tid] = m0; sL[tid] = l0;
-    }
+  if (tid < BR) { sM[tid] = -INFINITY; sL[tid] = 0.f; }
 #pragma unroll
-    for (int j = 0; j < ONT; ++j) {
-      const int col = nh * (D / 2) + j * 8 + (lane & 3) * 2;
-      float2 v0 = make_float2(0.f, 0.f), v1 = v0;
-      if (part) {
-        if (i0 + fr0 < N) v0 = *reinterpret_cast<const float2*>(p.Opart + (bh * N + i0 + fr0) * D + col);
-        if (i0 + fr1 < N) v1 = *reinterpret_cast<const float2*>(p.Opart + (bh * N + i0 + fr1) * D + col);
-      }
-      accO[j][0] = v0.x; accO[j][1] = v0.y; accO[j][2] = v1.x; accO[j][3] = v1.y;
-    }
-  }
+  for (int j = 0; j < ONT; ++j) { accO[j][0] = accO[j][1] = accO[j][2] = accO[j][3] = 0.f; }
 
   load_rows_async<D, Cfg::NT>(sQ, QK_LD, Qg, i0 - HR, SR, N, tid);
   cp_async_commit();
 
   for (int kb = kb_begin; kb <= kb_end; ++kb) {
-    const int j0 = band_only ? (i0 - p.band_off) : kb * BC;
+    const int j0 = kb * BC;
     load_rows_async<D, Cfg::NT>(sK, QK_LD, Kg, j0 - HC, SC, N, tid);
     load_rows_async<D, Cfg::NT>(sV, QK_LD, Vg, j0, BC, N, tid);
     cp_async_commit();
@@ -212,8 +185,8 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
       const int c = 2 * lane;
       float2 v = *reinterpret_cast<const float2*>(cbuf + r * C_LD + c);
       const int qi = i0 + r, kj = j0 + c;
-      if (kj < 0 || kj >= N || (causal && kj > qi) || (band_only && qi - kj >= pq + pk)) v.x = -INFINITY;
-      if (kj + 1 < 0 || kj + 1 >= N || (causal && kj + 1 > qi) || (band_only && qi - (kj + 1) >= pq + pk)) v.y = -INFINITY;
+      if (kj < 0 || kj >= N || (causal && kj > qi)) v.x = -INFINITY;
+      if (kj + 1 < 0 || kj + 1 >= N || (causal && kj + 1 > qi)) v.y = -INFINITY;
       const float mx = warp_max(fmaxf(v.x, v.y));
       const float m_old = sM[r];
       const float m_new = fmaxf(m_old, mx);
@@ -254,15 +227,15 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
       const float o00 = accO[j][0] * inv0, o01 = accO[j][1] * inv0, o10 = accO[j][2] * inv1, o11 = accO[j][3] * inv1;
       if (p.o_bf16) {
         bf16* O = reinterpret_cast<bf16*>(p.O);
-        if (i0 + fr0 < N && fr0 < own_rows) *reinterpret_cast<uint32_t*>(O + (bh * N + i0 + fr0) * D + col) = pack_bf16(o00, o01);
-        if (i0 + fr1 < N && fr1 < own_rows) *reinterpret_cast<uint32_t*>(O + (bh * N + i0 + fr1) * D + col) = pack_bf16(o10, o11);
+        if (i0 + fr0 < N) *reinterpret_cast<uint32_t*>(O + (bh * N + i0 + fr0) * D + col) = pack_bf16(o00, o01);
+        if (i0 + fr1 < N) *reinterpret_cast<uint32_t*>(O + (bh * N + i0 + fr1) * D + col) = pack_bf16(o10, o11);
       } else {
         float* O = reinterpret_cast<float*>(p.O);
-        if (i0 + fr0 < N && fr0 < own_rows) *reinterpret_cast<float2*>(O + (bh * N + i0 + fr0) * D + col) = make_float2(o00, o01);
-        if (i0 + fr1 < N && fr1 < own_rows) *reinterpret_cast<float2*>(O + (bh * N + i0 + fr1) * D + col) = make_float2(o10, o11);
+        if (i0 + fr0 < N) *reinterpret_cast<float2*>(O + (bh * N + i0 + fr0) * D + col) = make_float2(o00, o01);
+        if (i0 + fr1 < N) *reinterpret_cast<float2*>(O + (bh * N + i0 + fr1) * D + col) = make_float2(o10, o11);
       }
     }
-    if (tid < own_rows && i0 + tid < N) {
+    if (tid < BR && i0 + tid < N) {
       const float m = sM[tid], l = sL[tid];
       if (p.M) p.M[bh * N + i0 + tid] = m;
       if (p.L) p.L[bh * N + i0 + tid] = l;
