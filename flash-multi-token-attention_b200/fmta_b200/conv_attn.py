@@ -103,7 +103,7 @@ def dkdv_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
 def backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, path=-1):
     """(dQ, dK, dV, dconv_kernel), all fp32, in one call (`fmta_bwd`): what the reference obtains
     from `dq_backward` + `dkdv_backward` (conv_attention_cuda.py:147-152).  ``path`` as in the C ABI:
-    0 exact kernels, 1 tensor-core kernels + exact band, -1 library default."""
+    0 exact kernels, 1 tensor-core kernels + band kernel, -1 library default."""
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (dO, "dO")):
         require_cuda_bf16(t, n)
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
