@@ -135,13 +135,14 @@ def test_rejects_bad_inputs():
     (1, 2, 520, 64, 6, 11, True),     # several 224-row dQ tiles and 128-key dK tiles, ragged N
     (2, 1, 300, 64, 3, 5, False),     # no causal band: everything on the tensor-core kernels
     (1, 1, 100, 64, 6, 11, True),     # shorter than one tile
-    (1, 2, 400, 64, 6, 17, True),     # wide key filter: band tiles placed 32 keys back
+    (1, 2, 400, 64, 6, 17, True),     # wide key filter (W = 21): three key tiles per row tile, FMA output phase
+    (1, 2, 700, 64, 3, 5, True),      # run-time filter shape in the band kernels, mma output phase
     (1, 1, 333, 64, 2, 3, True),      # tiny filter, band of 2
     (1, 1, 1500, 64, 6, 11, True),    # many key blocks per tile
 ])
 def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
     """fmta_bwd with the exact kernels (path 0) and with the stacked-GEMM tensor-core kernels plus
-    exact band (path 1) against the oracle; forward run on both paths as well."""
+    the band kernel (path 1) against the oracle; forward run on both paths as well."""
     import fmta_b200 as F
     Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=17 + N, dtype=torch.bfloat16)
     scale = 1.0 / math.sqrt(d)
