@@ -169,7 +169,8 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     cfg = dict(CFG)
     dec = dict(DEC)
     if args.small:
@@ -237,10 +238,19 @@ def main():
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    t_w = time.perf_counter()
     for _ in range(args.warmup):
         step(q, k, v, do)
-    while time.perf_counter() - t_w < 0.3:      # keep the GPU under load until nvidia-smi has sampled it
+    # keep the GPU under load for about 0.3 s more, so that nvidia-smi samples it before the timed
+    # region; every rank must run the SAME number of steps (each holds an all-reduce), so rank 0
+    # measures one step and the count is broadcast
+    torch.cuda.synchronize()
+    t_w = time.perf_counter()
+    step(q, k, v, do)
+    torch.cuda.synchronize()
+    n_extra = torch.tensor([min(400, int(0.3 / max(time.perf_counter() - t_w, 1e-4)) + 1)], device=dev)
+    if world > 1:
+        dist.broadcast(n_extra, src=0)
+    for _ in range(int(n_extra.item())):
         step(q, k, v, do)
     ms = timed(lambda: step(q, k, v, do, record=True), args.steps)
     clocks = sampler.stop() if sampler else None
