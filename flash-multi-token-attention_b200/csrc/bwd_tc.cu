@@ -74,7 +74,7 @@ struct DqCfg {
   static constexpr int oRing = ((odC + NT * (BC / 8) * DR * 16 + 1023) / 1024) * 1024;
   static constexpr int oBar = oRing + NSLOT * TILE_BYTES;
   static constexpr int kSmemBytes = oBar + 512 + 1024;
-  static constexpr int kTmemCols = 512;        // per tile t: S at 192t, dP at 192t+64, dQ at 192t+128
+  static constexpr int kTmemCols = 512;        // per tile t: S (two buffers) at 256t and 256t+64, dP at 256t+128, dQ at 256t+192
   static constexpr int kThreads = (NT * 4 + 1 + 2 * NT) * 32;   // element-wise warps, TMA warp, two MMA issuer warps per tile
 };
 
@@ -97,8 +97,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* empty = bars + NSLOT;        // [NSLOT]  count 2 NT
   uint64_t* q_full = bars + 2 * NSLOT;   // Q and dO staged
   uint64_t* sdp_full = q_full + 1;       // [NT] S and dP of the block complete
-  uint64_t* s_free = sdp_full + 2;       // [NT] S and dP taken into registers (128 arrivals)
-  uint64_t* dc_full = s_free + 2;        // [NT] dC tile written to shared memory (128 arrivals)
+  uint64_t* s_free = sdp_full + 2;       // [NT][2] S buffer b and dP of a block taken into registers (128 arrivals)
+  uint64_t* dc_full = s_free + 4;        // [NT] dC tile written to shared memory (128 arrivals)
   uint64_t* dq_done = dc_full + 2;       // [NT] dQ MMAs of the block complete (dC buffer reusable)
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(dq_done + 2);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -133,9 +133,10 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 2 * NT); }   // every issuer releases every tile
     tc::mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(&sdp_full[i], 1); tc::mbar_init(&s_free[i], BM); tc::mbar_init(&dc_full[i], BM);
+      tc::mbar_init(&sdp_full[i], 1); tc::mbar_init(&dc_full[i], BM);
       tc::mbar_init(&dq_done[i], 1);
     }
+    for (int i = 0; i < 4; ++i) tc::mbar_init(&s_free[i], BM);
     *s_abort = 0;
     tc::mbar_fence_init();
   }
@@ -193,7 +194,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t o_hi = (uint32_t)(dOa >> 32), o_lo = (uint32_t)dOa;
       const uint32_t c_hi = (uint32_t)(dCa >> 32), c_lo = (uint32_t)dCa;
       const uint32_t k_hi = (uint32_t)(dKb >> 32), k_lo0 = (uint32_t)dKb;
-      const uint32_t tS = tmem + t * 192, tP = tS + 64, tQ = tS + 128;
+      const uint32_t tS = tmem + t * 256, tP = tS + 128, tQ = tS + 192;   // S is double-buffered: tS + 64 * (kb & 1)
       const int my_nkb = nkb_t[t];
       const int per = cq + 1;                                // ring tiles per key block
       bool ok = tc::mbar_wait_warp(q_full, 0, s_abort);
@@ -201,8 +202,9 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int kb = 0; kb < nkb && ok; ++kb) {
           const bool active = kb < my_nkb;
           if (t == 0) TRACEQ(kb * 8 + 0);
-          if (active && kb > 0) {
-            ok = tc::mbar_wait_warp(&s_free[t], (kb - 1) & 1, s_abort);
+          const uint32_t tSb = tS + 64 * (kb & 1);
+          if (active && kb > 1) {      // the element-wise warps have taken S(kb-2) out of this buffer
+            ok = tc::mbar_wait_warp(&s_free[2 * t + (kb & 1)], ((kb >> 1) - 1) & 1, s_abort);
             tc::tc_fence_after();
           }
           if (t == 0) TRACEQ(kb * 8 + 1);
@@ -213,16 +215,20 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               tc::tc_fence_after();
               const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
               const uint32_t a_lo = q_lo + (uint32_t)a;
-              tc::mma_ss2pe(tS, a_lo, q_hi, b_lo, k_hi, idescS, a != 0);
+              tc::mma_ss2pe(tSb, a_lo, q_hi, b_lo, k_hi, idescS, a != 0);
 #pragma unroll
               for (int k = 1; k < D / 16; ++k)
-                tc::mma_ss2e<1>(tS, a_lo + (uint32_t)(2 * k * QR), q_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
+                tc::mma_ss2e<1>(tSb, a_lo + (uint32_t)(2 * k * QR), q_hi, b_lo + (uint32_t)(2 * k), k_hi, idescS);
             }
             tc::mma_commit_e(&empty[slot]);      // (the dQ issuers hold the Kt tile until dQ(kb) is done)
           }
           if (!ok) break;
           const int id = kb * per + cq, slot = id % NSLOT, ph = (id / NSLOT) & 1;
           if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
+          if (active && kb > 0) {      // dP is single-buffered: block kb-1 must have left it
+            ok = tc::mbar_wait_warp(&s_free[2 * t + ((kb - 1) & 1)], ((kb - 1) >> 1) & 1, s_abort);
+            if (!ok) break;
+          }
           if (active) {
             tc::tc_fence_after();
             const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
@@ -275,7 +281,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int m = tid & (BM - 1);
     const int gi = R0 + t * OWN + m;                    // query index of this dC row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + t * 192 + lane_base, tP = tS + 64, tQ = tS + 128;
+    const uint32_t tS = tmem + t * 256 + lane_base, tP = tS + 128, tQ = tS + 192;
     const int my_nkb = nkb_t[t];
     const bool row_ok = gi < N;
     const float lse2 = row_ok ? p.LSE[(size_t)bh * N + gi] * kLog2e : 0.f;
@@ -291,14 +297,15 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float s[BC], dp[BC];
       {
         float t0[32], t1[32], t2[32], t3[32];
-        tc::tmem_ld32_nowait(tS, t0); tc::tmem_ld32_nowait(tS + 32, t1);
+        const uint32_t tSb = tS + 64 * (kb & 1);
+        tc::tmem_ld32_nowait(tSb, t0); tc::tmem_ld32_nowait(tSb + 32, t1);
         tc::tmem_ld32_nowait(tP, t2); tc::tmem_ld32_nowait(tP + 32, t3);
         tc::tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; dp[i] = t2[i]; dp[32 + i] = t3[i]; }
       }
       tc::tc_fence_before();
-      tc::mbar_arrive(&s_free[t]);
+      tc::mbar_arrive(&s_free[2 * t + (kb & 1)]);
       if (tid == 0) TRACEQ(1024 + kb * 8 + 2);
       const int j0 = kb * BC;
       const int jlim = row_ok ? (p.causal ? min(N - 1, gi - band) : N - 1) : -1;   // last key owned here

@@ -251,9 +251,9 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
   return check_cuda(launch_reduce_partials(part, dTheta, slots_ex + slots_tc, (int)n_theta, st));
 }
 
-int fmta_decode(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
-                float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
-                int ck, int k_splits, float scale, void* stream) {
+static int decode_impl(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
+                       float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
+                       int ck, int k_splits, float scale, int offset_causal, void* stream) {
   if (!Q || !K || !V || !theta || !O_splits || !M_splits || !L_splits) return FMTA_ERR_NULL;
   if (B < 1 || H < 1 || Nk < 1 || B > 65535 || H > 65535) return FMTA_ERR_SHAPE;
   if (q_len < 1 || q_len > 16) return FMTA_ERR_SHAPE;          // flash_conv_attention_inference.py:66-67
@@ -267,7 +267,20 @@ int fmta_decode(const void* Q, const void* K, const void* V, const float* theta,
   p.theta = theta; p.O_splits = O_splits; p.M_splits = M_splits; p.L_splits = L_splits;
   p.B = B; p.H = H; p.q_len = q_len; p.Nk = Nk; p.d = d; p.cq = cq; p.ck = ck; p.k_splits = k_splits;
   p.scale = scale;
+  p.offset_causal = offset_causal;
   return check_cuda(launch_decode(p, (cudaStream_t)stream));
+}
+
+int fmta_decode(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
+                float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
+                int ck, int k_splits, float scale, void* stream) {
+  return decode_impl(Q, K, V, theta, O_splits, M_splits, L_splits, B, H, q_len, Nk, d, cq, ck, k_splits, scale, 0, stream);
+}
+
+int fmta_decode_offset_causal(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
+                              float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
+                              int ck, int k_splits, float scale, void* stream) {
+  return decode_impl(Q, K, V, theta, O_splits, M_splits, L_splits, B, H, q_len, Nk, d, cq, ck, k_splits, scale, 1, stream);
 }
 
 }  // extern "C"

@@ -10,7 +10,9 @@
 // The MMA contraction index is permuted so that each lane's B fragment is one contiguous
 // 16-byte piece of a K row (A = Q is laid out to match once, in registers).
 // Warps are merged in shared memory, splits by combine_splits_kernel on the same stream
-// (result normalised into split 0, as the reference leaves it).
+// (result normalised into split 0, as the reference leaves it).  With `offset_causal` the score of
+// a key later than a query row's own position is zeroed before the conv, as in the training
+// forward, so that the result equals the last row of the training forward over the same sequence.
 #pragma once
 #include "fmta_common.cuh"
 #include "fmta_params.h"
@@ -140,8 +142,16 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeP
           }
         }
         const int kcol = (kb + 8 * j + 2 * t) & (kDecRing - 1);
-        *reinterpret_cast<float2*>(ring + g * kDecRing + kcol) = make_float2(acc[0] * p.scale, acc[1] * p.scale);
-        if (R16) *reinterpret_cast<float2*>(ring + (g + 8) * kDecRing + kcol) = make_float2(acc[2] * p.scale, acc[3] * p.scale);
+        float v0 = acc[0] * p.scale, v1 = acc[1] * p.scale, v2 = acc[2] * p.scale, v3 = acc[3] * p.scale;
+        if (p.offset_causal && kb + 16 > Nk - rows) {   // only the last keys of the cache can lie in a row's future
+          const int key0 = kb + 8 * j + 2 * t, lim = Nk - rows + g;
+          if (key0 > lim) v0 = 0.f;
+          if (key0 + 1 > lim) v1 = 0.f;
+          if (key0 > lim + 8) v2 = 0.f;
+          if (key0 + 1 > lim + 8) v3 = 0.f;
+        }
+        *reinterpret_cast<float2*>(ring + g * kDecRing + kcol) = make_float2(v0, v1);
+        if (R16) *reinterpret_cast<float2*>(ring + (g + 8) * kDecRing + kcol) = make_float2(v2, v3);
       }
       __syncwarp();
       // ---- conv + softmax + PV for the previous block [kb-16, kb) ----

@@ -44,6 +44,7 @@ struct DecodeParams {
   float* L_splits;
   int B, H, q_len, Nk, d, cq, ck, k_splits;
   float scale;
+  int offset_causal;         // zero the scores of keys later than each query row's position (row r sits at Nk - rows + r)
 };
 
 }  // namespace fmta

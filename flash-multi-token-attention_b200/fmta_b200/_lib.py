@@ -55,9 +55,11 @@ lib.fmta_bwd_dkdv.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, 
                               _vp]
 lib.fmta_decode.restype = _i
 lib.fmta_decode.argtypes = [_vp, _vp, _vp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
+lib.fmta_decode_offset_causal.restype = _i
+lib.fmta_decode_offset_causal.argtypes = lib.fmta_decode.argtypes
 
 EXPORTS = ["fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
-           "fmta_bwd_prep_D", "fmta_bwd", "fmta_set_path", "fmta_profile_kernel", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode"]
+           "fmta_bwd_prep_D", "fmta_bwd", "fmta_set_path", "fmta_profile_kernel", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode", "fmta_decode_offset_causal"]
 
 
 def check(status, what):

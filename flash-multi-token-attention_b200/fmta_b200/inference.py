@@ -6,11 +6,14 @@ import torch
 from ._lib import lib, check, ptr, stream_ptr, require_cuda_bf16, as_f32
 
 
-def forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal, num_k_blocks=None):
+def forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal, num_k_blocks=None,
+                      offset_causal=False):
     """(O_splits [B,H,k_splits,d], M_splits, L_splits [B,H,k_splits]) fp32 with the merged,
     normalised result in split 0 (fwd_inference.cu:359-368).  ``causal`` is accepted and has no
     effect, exactly as in the reference kernel (fwd_inference.cu:36 is never read);
-    ``num_k_blocks`` is accepted for signature compatibility and ignored."""
+    ``num_k_blocks`` is accepted for signature compatibility and ignored.  ``offset_causal=True``
+    (an addition) applies the training forward's mask with query row r placed at position
+    Nk - rows + r, so that the result equals the last row of the causal training forward."""
     for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
         require_cuda_bf16(t, n)
     B, H, q_len, d = Q.shape
@@ -30,17 +33,19 @@ def forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causa
     O = torch.empty((B, H, k_splits, d), dtype=torch.float32, device=Q.device)
     M = torch.empty((B, H, k_splits), dtype=torch.float32, device=Q.device)
     L = torch.empty_like(M)
-    st = lib.fmta_decode(ptr(Q), ptr(K), ptr(V), ptr(theta), ptr(O), ptr(M), ptr(L), B, H, q_len, Nk, d, cq, ck,
-                         int(k_splits), float(scale), stream_ptr())
+    fn = lib.fmta_decode_offset_causal if offset_causal else lib.fmta_decode
+    st = fn(ptr(Q), ptr(K), ptr(V), ptr(theta), ptr(O), ptr(M), ptr(L), B, H, q_len, Nk, d, cq, ck,
+            int(k_splits), float(scale), stream_ptr())
     check(st, "fmta_decode")
     return O, M, L
 
 
-def fwd_conv_attn_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal):
+def fwd_conv_attn_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal, offset_causal=False):
     """(O [B,H,1,d], M [B,H,1], L [B,H,1]) for the last query row
     (flash_conv_attention_inference.py:33-93).  The reference front-pads Q to 16 rows with
     zeros; zero rows contribute nothing, so Q is passed as is."""
     if Q.shape[2] > 16:
         raise ValueError(f"Q sequence length must be <= 16 for inference, got {Q.shape[2]}")
-    O, M, L = forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal)
+    O, M, L = forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal,
+                                offset_causal=offset_causal)
     return O[:, :, 0:1, :], M[:, :, 0:1], L[:, :, 0:1]

@@ -155,6 +155,19 @@ int fmta_decode(const void* Q, const void* K, const void* V, const float* theta,
                 int ck, int k_splits, float scale, void* stream);
 
 /*
+ * Decode with the causal mask of the training forward ("offset-causal").  No counterpart in the
+ * reference, whose decode kernel accepts `causal` and never reads it (kernels/fwd_inference.cu:36).
+ * Query row r of the `rows = min(q_len, c_q)` most recent rows sits at sequence position
+ * Nk - rows + r; the score of a key later than that position is set to zero before the conv,
+ * exactly as the training forward zeroes future scores.  With q_len >= min(c_q, Nk) the merged
+ * result in split 0 equals row Nk-1 of `fmta_fwd` (causal) over the same Nk-long sequence.
+ * Arguments and outputs as `fmta_decode`.
+ */
+int fmta_decode_offset_causal(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
+                              float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
+                              int ck, int k_splits, float scale, void* stream);
+
+/*
  * Allocation-free variant of fmta_bwd_dq_dw (no counterpart in the reference, whose wrappers
  * always allocate with torch).  Same arguments without the workspace: the per-CTA partial sums
  * of dTheta / dW go to a 4 MiB array that lives inside the library's device image.  Meant for

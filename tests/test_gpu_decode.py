@@ -73,3 +73,33 @@ def test_rejects_bad_inputs():
         F.fwd_conv_attn_inference(Q[:, :, :4], K, K, th, 65, 1.0, 2, 1, False)   # k_splits > Nk
     with pytest.raises(RuntimeError):
         F.fwd_conv_attn_inference(Q[:, :, :4], K, K, th, 0, 1.0, 2, 1, False)
+
+
+@pytest.mark.parametrize("B,H,q_len,Nk,d,cq,ck,k_splits", [
+    (1, 2, 6, 300, 64, 6, 11, 1),
+    (2, 2, 6, 1000, 128, 6, 11, 4),
+    (1, 1, 16, 257, 64, 6, 11, 3),     # more rows than filter taps
+    (1, 2, 3, 129, 32, 3, 5, 2),
+    (1, 1, 4, 4, 64, 6, 11, 1),        # cache shorter than the filter
+])
+def test_offset_causal_matches_oracle_and_training_forward(B, H, q_len, Nk, d, cq, ck, k_splits):
+    """Decode with the training forward's mask: against its own oracle, and (the property it exists for)
+    against row Nk-1 of the causal training forward run by the library over the same sequence."""
+    import fmta_b200 as F
+    Q, K, V, _, theta = orc.make_inputs(B, H, 0, d, cq, ck, seed=5 + Nk, dtype=torch.bfloat16, Nk=Nk, q_len=Nk)
+    scale = 1.0 / math.sqrt(d)
+    Qr = Q[:, :, Nk - q_len:, :].contiguous()
+    Or, Mr, Lr = orc.decode_last_row_offset_causal(Qr, K, V, theta, scale)
+    qb, kb, vb = (t.cuda().to(torch.bfloat16).contiguous() for t in (Qr, K, V))
+    O, M, L = F.fwd_conv_attn_inference(qb, kb, vb, theta.cuda(), k_splits, scale, cq - 1, (ck - 1) // 2, True,
+                                        offset_causal=True)
+    assert maxabs(O, Or) <= TOL_BF16
+    assert maxabs(M, Mr) <= TOL_BF16
+    assert maxabs(M + torch.log(L), Mr + torch.log(Lr)) <= TOL_BF16
+    Of, Mf, Lf = F.forward(Q.cuda().to(torch.bfloat16).contiguous(), kb, vb, theta.cuda(), scale, cq - 1, (ck - 1) // 2, True)
+    assert maxabs(O[:, :, 0], Of[:, :, -1]) <= TOL_BF16
+    assert maxabs((M + torch.log(L))[:, :, 0], (Mf + torch.log(Lf))[:, :, -1]) <= TOL_BF16
+    # the mask matters: without it the last keys' scores differ
+    O0, _, _ = F.fwd_conv_attn_inference(qb, kb, vb, theta.cuda(), k_splits, scale, cq - 1, (ck - 1) // 2, False)
+    if Nk > 16 and cq > 1:
+        assert maxabs(O0, O) > 0

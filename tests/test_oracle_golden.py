@@ -117,3 +117,19 @@ def test_adjoint_identity():
     lhs = (orc.conv_scores_shift(S, th) * dC).sum()
     rhs = (S * orc.conv_scores_transposed(dC, th)).sum()
     assert abs(float(lhs - rhs)) < 1e-9
+
+
+def test_offset_causal_decode_is_last_row_of_causal_forward():
+    """The offset-causal decode oracle has no reference counterpart; it is pinned by composition with
+    the (pinned) training forward: same sequence, last row."""
+    torch.manual_seed(3)
+    for (N, cq, ck, q_len) in [(50, 6, 11, 6), (40, 3, 5, 8), (33, 2, 3, 2), (5, 6, 11, 5), (64, 6, 11, 16)]:
+        B, H, d = 1, 2, 16
+        Q, K, V = (torch.randn(B, H, N, d) for _ in range(3))
+        th = torch.randn(H, cq, ck) * 0.1
+        th[:, cq - 1, ck // 2] += 1
+        O, M, L = orc.conv_attn_fwd(Q, K, V, th, None, True)
+        Od, Md, Ld = orc.decode_last_row_offset_causal(Q[:, :, N - q_len:], K, V, th)
+        assert maxabs(O[:, :, -1:], Od) <= 1e-5
+        assert maxabs(M[:, :, -1:], Md) <= 1e-5
+        assert maxabs(L[:, :, -1:], Ld) <= 1e-4
