@@ -137,6 +137,13 @@ def test_rejects_bad_inputs():
     (1, 1, 100, 64, 6, 11, True),     # shorter than one tile
     (1, 2, 400, 64, 6, 17, True),     # wide key filter (W = 21): three key tiles per row tile, FMA output phase
     (1, 2, 700, 64, 3, 5, True),      # run-time filter shape in the band kernels, mma output phase
+    (1, 1, 611, 64, 6, 13, True),     # W = 17: widest filter on the two-key-tile / mma output path
+    (1, 1, 389, 64, 6, 15, True),     # W = 19: three key tiles, FMA output phase
+    (1, 2, 257, 64, 1, 3, True),      # single query tap: band of 1
+    (1, 1, 450, 64, 4, 7, True),
+    (2, 1, 200, 64, 5, 9, True),
+    (1, 1, 77, 64, 6, 11, True),      # exactly one band CTA
+    (1, 1, 78, 64, 6, 11, True),      # one position into the second band CTA
     (1, 1, 333, 64, 2, 3, True),      # tiny filter, band of 2
     (1, 1, 1500, 64, 6, 11, True),    # many key blocks per tile
 ])
@@ -155,7 +162,11 @@ def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
     Or, Mr, Lr = orc.conv_attn_fwd(Q, K, V, theta, scale, causal)
     rq, rk, rv, rt = orc.conv_attn_bwd_autograd(Q, K, V, theta, dO, scale, causal)
     _check(dict(O=O, M=M, L=L, LSE=LSE, dQ=dQ, dK=dK, dV=dV, dTheta=dTh),
-           dict(O=Or, M=Mr, L=Lr, dQ=rq, dK=rk, dV=rv, dTheta=rt), dtheta_rel=5e-3)
+           dict(O=Or, M=Mr, L=Lr, dQ=rq, dK=rk, dV=rv, dTheta=rt),
+           # dTheta is a heavily cancelling sum over all score entries; on the tensor-core path both of
+           # its factors (dC and the stacked keys) have been rounded to bf16, and for filters with one
+           # or two query taps the error reaches 1e-2 of max|dTheta| (5e-3 for the exact kernels)
+           dtheta_rel=5e-3 if path == 0 else 1.5e-2)
 
 
 def test_tensor_core_path_rejected_when_unsupported():
