@@ -253,7 +253,9 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
 
 static int decode_impl(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,
                        float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
-                       int ck, int k_splits, float scale, int offset_causal, void* stream) {
+                       int ck, int k_splits, float scale, int offset_causal, void* stream,
+                       const int* block_table = nullptr, const int* seq_lens = nullptr, int page_size = 0,
+                       int max_pages = 0) {
   if (!Q || !K || !V || !theta || !O_splits || !M_splits || !L_splits) return FMTA_ERR_NULL;
   if (B < 1 || H < 1 || Nk < 1 || B > 65535 || H > 65535) return FMTA_ERR_SHAPE;
   if (q_len < 1 || q_len > 16) return FMTA_ERR_SHAPE;          // flash_conv_attention_inference.py:66-67
@@ -268,6 +270,14 @@ static int decode_impl(const void* Q, const void* K, const void* V, const float*
   p.B = B; p.H = H; p.q_len = q_len; p.Nk = Nk; p.d = d; p.cq = cq; p.ck = ck; p.k_splits = k_splits;
   p.scale = scale;
   p.offset_causal = offset_causal;
+  if (block_table) {
+    int shift = 0;
+    while ((1 << shift) < page_size) ++shift;
+    if (page_size < 16 || (1 << shift) != page_size) return FMTA_ERR_SHAPE;      // power of two, >= one 16-key step
+    if (max_pages < (Nk + page_size - 1) / page_size || max_pages > 2048) return FMTA_ERR_SHAPE;
+    p.block_table = block_table; p.seq_lens = seq_lens;
+    p.page_size = page_size; p.page_shift = shift; p.max_pages = max_pages;
+  }
   return check_cuda(launch_decode(p, (cudaStream_t)stream));
 }
 
@@ -281,6 +291,29 @@ int fmta_decode_offset_causal(const void* Q, const void* K, const void* V, const
                               float* M_splits, float* L_splits, int B, int H, int q_len, int Nk, int d, int cq,
                               int ck, int k_splits, float scale, void* stream) {
   return decode_impl(Q, K, V, theta, O_splits, M_splits, L_splits, B, H, q_len, Nk, d, cq, ck, k_splits, scale, 1, stream);
+}
+
+int fmta_decode_paged(const void* Q, const void* K_pool, const void* V_pool, const int* block_table,
+                      const int* seq_lens, const float* theta, float* O_splits, float* M_splits, float* L_splits,
+                      int B, int H, int q_len, int Nk_max, int d, int cq, int ck, int k_splits, float scale,
+                      int page_size, int max_pages, int offset_causal, void* stream) {
+  if (!block_table) return FMTA_ERR_NULL;
+  return decode_impl(Q, K_pool, V_pool, theta, O_splits, M_splits, L_splits, B, H, q_len, Nk_max, d, cq, ck, k_splits,
+                     scale, offset_causal ? 1 : 0, stream, block_table, seq_lens, page_size, max_pages);
+}
+
+int fmta_kv_append_paged(void* K_pool, void* V_pool, const int* block_table, const int* seq_lens, const void* K_new,
+                         const void* V_new, int B, int H, int n_new, int d, int page_size, int max_pages,
+                         void* stream) {
+  if (!K_pool || !V_pool || !block_table || !seq_lens || !K_new || !V_new) return FMTA_ERR_NULL;
+  if (B < 1 || H < 1 || n_new < 1 || B > 65535 || H > 65535 || max_pages < 1) return FMTA_ERR_SHAPE;
+  if (d != 32 && d != 64 && d != 128) return FMTA_ERR_UNSUPPORTED;
+  int shift = 0;
+  while ((1 << shift) < page_size) ++shift;
+  if (page_size < 16 || (1 << shift) != page_size) return FMTA_ERR_SHAPE;
+  if (!aligned16(K_pool) || !aligned16(V_pool) || !aligned16(K_new) || !aligned16(V_new)) return FMTA_ERR_ALIGN;
+  return check_cuda(launch_kv_append_paged(K_pool, V_pool, block_table, seq_lens, K_new, V_new, B, H, n_new, d,
+                                           page_size, shift, max_pages, (cudaStream_t)stream));
 }
 
 }  // extern "C"

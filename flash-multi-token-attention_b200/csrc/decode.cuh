@@ -21,6 +21,7 @@ namespace fmta {
 
 constexpr int kDecWarps = 4;
 constexpr int kDecRing = 64;   // keys kept per warp for the conv window
+constexpr int kDecMaxPages = 2048;   // block-table entries of one sequence kept in shared memory (paged cache)
 
 FMTA_DEVINL uint4 ldg_nc_v4(const void* p) {
   uint4 v;
@@ -38,7 +39,7 @@ __host__ __device__ inline int decode_keys_per_split(int Nk, int k_splits) {
   return ((per + 16 * kDecWarps - 1) / (16 * kDecWarps)) * (16 * kDecWarps);
 }
 
-template <int D, bool R16>
+template <int D, bool R16, bool PAGED>
 __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeParams p) {
   constexpr int KS = D / 16;       // k-steps of the MMA
   constexpr int CH = D / 32;       // 32-element chunks per row (one 16-byte load per lane each)
@@ -49,15 +50,29 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeP
   __shared__ float sTheta[16 * 20];
   __shared__ float sMergeO[kDecWarps][D];
   __shared__ float sMergeML[kDecWarps][2];
+  __shared__ int sTable[PAGED ? kDecMaxPages : 1];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int Nk = p.Nk, cq = p.cq, ck = p.ck, pk = (ck - 1) / 2;
+  const int Nk = (PAGED && p.seq_lens) ? p.seq_lens[b] : p.Nk;
+  const int cq = p.cq, ck = p.ck, pk = (ck - 1) / 2;
   const int rows = min(p.q_len, cq);          // query rows that the last output row sees
   const size_t bh = (size_t)b * p.H + h;
-  const bf16* Kg = p.K + bh * (size_t)Nk * D;
-  const bf16* Vg = p.V + bh * (size_t)Nk * D;
+  const bf16* Kg = PAGED ? p.K : p.K + bh * (size_t)Nk * D;
+  const bf16* Vg = PAGED ? p.V : p.V + bh * (size_t)Nk * D;
+  // element offset of a key's row inside Kg / Vg
+  auto row_off = [&](int key) -> size_t {
+    if (PAGED) {
+      const int pg = key >> p.page_shift, in = key & (p.page_size - 1);
+      return (((size_t)sTable[pg] * p.H + h) * p.page_size + in) * D;
+    }
+    return (size_t)key * D;
+  };
+  if (PAGED) {
+    const int npg = (Nk + p.page_size - 1) >> p.page_shift;
+    for (int i = tid; i < npg; i += kDecWarps * 32) sTable[i] = p.block_table[(size_t)b * p.max_pages + i];
+  }
   const bf16* Qg = p.Q + (bh * p.q_len + (p.q_len - rows)) * (size_t)D;
 
   // theta rows that see a real query row: tap a = cq - rows + r  <->  ring row r
@@ -88,7 +103,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeP
   }
   __syncthreads();
 
-  const int keys_per_split = decode_keys_per_split(Nk, p.k_splits);
+  const int keys_per_split = decode_keys_per_split(Nk, p.k_splits);   // (per sequence when lengths differ)
   const int keys_per_warp = keys_per_split / kDecWarps;
   const int k_lo = split * keys_per_split + warp * keys_per_warp;
   const int k_hi = min(k_lo + keys_per_warp, ((Nk + 15) / 16) * 16);
@@ -112,7 +127,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeP
         const bool ok = key >= 0 && key < Nk;
 #pragma unroll
         for (int c = 0; c < CH; ++c)
-          kf[j][c] = ok ? ldg_nc_v4(Kg + (size_t)key * D + c * 32 + t * 8) : make_uint4(0u, 0u, 0u, 0u);
+          kf[j][c] = ok ? ldg_nc_v4(Kg + row_off(key) + c * 32 + t * 8) : make_uint4(0u, 0u, 0u, 0u);
       }
       const bool do_pv = (kb - 16 >= k_lo);
       uint4 vf[VL];
@@ -120,7 +135,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeP
 #pragma unroll
         for (int i = 0; i < VL; ++i) {
           const int key = kb - 16 + i * KPL + vrow;
-          vf[i] = (key < Nk) ? ldg_nc_v4(Vg + (size_t)key * D + vcol) : make_uint4(0u, 0u, 0u, 0u);
+          vf[i] = (key < Nk) ? ldg_nc_v4(Vg + row_off(key) + vcol) : make_uint4(0u, 0u, 0u, 0u);
         }
       }
       // ---- S for the K block -> ring ----
@@ -243,6 +258,26 @@ __global__ void combine_splits_kernel(float* __restrict__ O_splits, float* __res
   }
   __syncthreads();
   if (threadIdx.x == 0) { Ms[0] = m; Ls[0] = l; }
+}
+
+// Append n_new key/value rows per sequence to a paged cache: row r of sequence b goes to position
+// seq_lens[b] + r (seq_lens is not modified; the caller advances it).  One 16-byte chunk per thread.
+template <int D>
+__global__ void kv_append_paged_kernel(bf16* __restrict__ Kpool, bf16* __restrict__ Vpool,
+                                       const int* __restrict__ block_table, const int* __restrict__ seq_lens,
+                                       const bf16* __restrict__ Knew, const bf16* __restrict__ Vnew, int H, int n_new,
+                                       int page_size, int page_shift, int max_pages) {
+  constexpr int CPR = D / 8;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_new * CPR) return;
+  const int r = idx / CPR, c = idx % CPR;
+  const int pos = seq_lens[b] + r;
+  const int pg = block_table[(size_t)b * max_pages + (pos >> page_shift)], in = pos & (page_size - 1);
+  const size_t dst = (((size_t)pg * H + h) * page_size + in) * D + c * 8;
+  const size_t src = (((size_t)b * H + h) * n_new + r) * D + c * 8;
+  *reinterpret_cast<uint4*>(Kpool + dst) = *reinterpret_cast<const uint4*>(Knew + src);
+  *reinterpret_cast<uint4*>(Vpool + dst) = *reinterpret_cast<const uint4*>(Vnew + src);
 }
 
 }  // namespace fmta

@@ -45,6 +45,11 @@ struct DecodeParams {
   int B, H, q_len, Nk, d, cq, ck, k_splits;
   float scale;
   int offset_causal;         // zero the scores of keys later than each query row's position (row r sits at Nk - rows + r)
+  // paged cache (block_table != nullptr): K and V point at pools [n_pages, H, page_size, d]; page p of
+  // sequence b is pool page block_table[b * max_pages + p]; seq_lens (optional) gives Nk per sequence
+  const int* block_table;
+  const int* seq_lens;
+  int page_size, page_shift, max_pages;
 };
 
 }  // namespace fmta

@@ -71,6 +71,9 @@ cudaError_t launch_bwd_dkdv(const TrainParams& p, cudaStream_t stream);
 cudaError_t launch_reduce_partials(const float* part, float* out, int n_slots, int n, cudaStream_t stream);
 cudaError_t launch_rowdot(const void* dO, const void* O, int o_bf16, float* Dv, size_t rows, int d, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams& p, cudaStream_t stream);
+cudaError_t launch_kv_append_paged(void* Kpool, void* Vpool, const int* block_table, const int* seq_lens,
+                                   const void* Knew, const void* Vnew, int B, int H, int n_new, int d, int page_size,
+                                   int page_shift, int max_pages, cudaStream_t stream);
 bool fwd_tc_supported(const TrainParams& p);
 size_t fwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
 bool bwd_tc_supported(const TrainParams& p);

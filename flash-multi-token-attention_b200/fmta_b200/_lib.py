@@ -57,9 +57,13 @@ lib.fmta_decode.restype = _i
 lib.fmta_decode.argtypes = [_vp, _vp, _vp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]
 lib.fmta_decode_offset_causal.restype = _i
 lib.fmta_decode_offset_causal.argtypes = lib.fmta_decode.argtypes
+lib.fmta_decode_paged.restype = _i
+lib.fmta_decode_paged.argtypes = [_vp, _vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp]
+lib.fmta_kv_append_paged.restype = _i
+lib.fmta_kv_append_paged.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
 
 EXPORTS = ["fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
-           "fmta_bwd_prep_D", "fmta_bwd", "fmta_set_path", "fmta_profile_kernel", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode", "fmta_decode_offset_causal"]
+           "fmta_bwd_prep_D", "fmta_bwd", "fmta_set_path", "fmta_profile_kernel", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode", "fmta_decode_offset_causal", "fmta_decode_paged", "fmta_kv_append_paged"]
 
 
 def check(status, what):

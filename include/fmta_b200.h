@@ -168,6 +168,30 @@ int fmta_decode_offset_causal(const void* Q, const void* K, const void* V, const
                               int ck, int k_splits, float scale, void* stream);
 
 /*
+ * Decode over a PAGED key/value cache (no counterpart in the reference, whose cache is one
+ * contiguous [B,H,Nk,d] tensor).  K_pool / V_pool are bf16 [n_pages, H, page_size, d]; page p of
+ * sequence b is pool page block_table[b * max_pages + p] (int32).  page_size is a power of two
+ * >= 16, max_pages <= 2048.  seq_lens (int32 [B], device memory, may be NULL) gives the cache
+ * length of each sequence (>= 1); without it every sequence has Nk_max keys.  Nk_max bounds the
+ * lengths (max_pages * page_size >= Nk_max).  offset_causal as in fmta_decode_offset_causal.
+ * Outputs as `fmta_decode`.  The result is that of `fmta_decode` on the gathered cache.
+ */
+int fmta_decode_paged(const void* Q, const void* K_pool, const void* V_pool, const int* block_table,
+                      const int* seq_lens, const float* theta, float* O_splits, float* M_splits,
+                      float* L_splits, int B, int H, int q_len, int Nk_max, int d, int cq, int ck,
+                      int k_splits, float scale, int page_size, int max_pages, int offset_causal,
+                      void* stream);
+
+/*
+ * Incremental append to a paged cache (no reference counterpart): rows K_new / V_new, bf16
+ * [B,H,n_new,d], go to positions seq_lens[b] .. seq_lens[b] + n_new - 1 of sequence b; the pages
+ * they land on must already be listed in block_table.  seq_lens is read, not advanced.
+ */
+int fmta_kv_append_paged(void* K_pool, void* V_pool, const int* block_table, const int* seq_lens,
+                         const void* K_new, const void* V_new, int B, int H, int n_new, int d,
+                         int page_size, int max_pages, void* stream);
+
+/*
  * Allocation-free variant of fmta_bwd_dq_dw (no counterpart in the reference, whose wrappers
  * always allocate with torch).  Same arguments without the workspace: the per-CTA partial sums
  * of dTheta / dW go to a 4 MiB array that lives inside the library's device image.  Meant for

@@ -103,3 +103,79 @@ def test_offset_causal_matches_oracle_and_training_forward(B, H, q_len, Nk, d, c
     O0, _, _ = F.fwd_conv_attn_inference(qb, kb, vb, theta.cuda(), k_splits, scale, cq - 1, (ck - 1) // 2, False)
     if Nk > 16 and cq > 1:
         assert maxabs(O0, O) > 0
+
+
+def _paged_from_contiguous(K, V, page_size, n_extra_pages=3, seed=0):
+    """Scatter contiguous caches [B,H,Nk,d] into pools [n_pages,H,page_size,d] through a random page
+    permutation; returns (K_pool, V_pool, block_table)."""
+    B, H, Nk, d = K.shape
+    ppb = (Nk + page_size - 1) // page_size
+    n_pages = B * ppb + n_extra_pages
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g)[: B * ppb].view(B, ppb)
+    Kp = torch.randn(n_pages, H, page_size, d, generator=g).to(torch.bfloat16)      # junk in unused slots
+    Vp = torch.randn(n_pages, H, page_size, d, generator=g).to(torch.bfloat16)
+    for b in range(B):
+        for pgi in range(ppb):
+            lo, hi = pgi * page_size, min(Nk, (pgi + 1) * page_size)
+            Kp[perm[b, pgi], :, : hi - lo] = K[b, :, lo:hi].to(torch.bfloat16)
+            Vp[perm[b, pgi], :, : hi - lo] = V[b, :, lo:hi].to(torch.bfloat16)
+    return Kp.cuda(), Vp.cuda(), perm.to(torch.int32).cuda()
+
+
+@pytest.mark.parametrize("B,H,q_len,Nk,d,cq,ck,k_splits,page", [
+    (2, 2, 6, 1000, 128, 6, 11, 4, 64),
+    (1, 3, 6, 333, 64, 6, 11, 1, 16),
+    (2, 1, 4, 2048, 64, 3, 5, 3, 256),
+])
+def test_paged_cache_equals_contiguous(B, H, q_len, Nk, d, cq, ck, k_splits, page):
+    """Same keys through a paged pool with a shuffled block table: bit-identical to the contiguous
+    kernel (same arithmetic order), within tolerance of the oracle; with and without the causal mask."""
+    import fmta_b200 as F
+    Q, K, V, _, theta = orc.make_inputs(B, H, 0, d, cq, ck, seed=11 + Nk, dtype=torch.bfloat16, Nk=Nk, q_len=q_len)
+    scale = 1.0 / math.sqrt(d)
+    qb, kb, vb = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V))
+    Kp, Vp, table = _paged_from_contiguous(K, V, page)
+    th = theta.cuda()
+    for oc in (False, True):
+        Oc, Mc, Lc = F.forward_inference(qb, kb, vb, th, k_splits, scale, cq - 1, (ck - 1) // 2, False, offset_causal=oc)
+        Op, Mp, Lp = F.forward_inference_paged(qb, Kp, Vp, table, th, k_splits, scale, cq - 1, (ck - 1) // 2,
+                                               max_seq_len=Nk, offset_causal=oc)
+        assert torch.equal(Oc[:, :, 0], Op[:, :, 0]) and torch.equal(Mc[:, :, 0], Mp[:, :, 0]) and torch.equal(Lc[:, :, 0], Lp[:, :, 0])
+    Or, Mr, Lr = orc.decode_last_row(Q, K, V, theta, scale)
+    Op, Mp, Lp = F.forward_inference_paged(qb, Kp, Vp, table, th, k_splits, scale, cq - 1, (ck - 1) // 2, max_seq_len=Nk)
+    assert maxabs(Op[:, :, 0:1], Or) <= TOL_BF16
+
+
+def test_paged_cache_ragged_lengths_and_append():
+    """Sequences of different length in one call (seq_lens), and rows appended with kv_append_paged:
+    each sequence must equal the contiguous decode of its own prefix."""
+    import fmta_b200 as F
+    B, H, q_len, d, cq, ck, page, Nmax = 3, 2, 6, 64, 6, 11, 32, 500
+    Q, K, V, _, theta = orc.make_inputs(B, H, 0, d, cq, ck, seed=77, dtype=torch.bfloat16, Nk=Nmax, q_len=q_len)
+    scale = 1.0 / math.sqrt(d)
+    lens = [500, 123, 257]
+    n_new = 5
+    Kp, Vp, table = _paged_from_contiguous(K, V, page)
+    th = theta.cuda()
+    qb = Q.cuda().to(torch.bfloat16).contiguous()
+    # start 5 rows short, then append the missing rows
+    start = torch.tensor([l - n_new for l in lens], dtype=torch.int32).cuda()
+    Knew = torch.stack([K[b, :, lens[b] - n_new:lens[b]] for b in range(B)]).to(torch.bfloat16).cuda().contiguous()
+    Vnew = torch.stack([V[b, :, lens[b] - n_new:lens[b]] for b in range(B)]).to(torch.bfloat16).cuda().contiguous()
+    # overwrite the rows to be appended with junk first, so that the append is what makes them right
+    for b in range(B):
+        for pos in range(lens[b] - n_new, lens[b]):
+            Kp[table[b, pos // page].item(), :, pos % page] = 7.0
+            Vp[table[b, pos // page].item(), :, pos % page] = -7.0
+    F.kv_append_paged(Kp, Vp, table, start, Knew, Vnew)
+    seq = torch.tensor(lens, dtype=torch.int32).cuda()
+    for ks in (1, 4):
+        Op, Mp, Lp = F.forward_inference_paged(qb, Kp, Vp, table, th, ks, scale, cq - 1, (ck - 1) // 2,
+                                               seq_lens=seq, max_seq_len=Nmax, offset_causal=True)
+        for b in range(B):
+            kb = K[b:b + 1, :, :lens[b]].cuda().to(torch.bfloat16).contiguous()
+            vb = V[b:b + 1, :, :lens[b]].cuda().to(torch.bfloat16).contiguous()
+            Oc, Mc, Lc = F.forward_inference(qb[b:b + 1], kb, vb, th, 1, scale, cq - 1, (ck - 1) // 2, False, offset_causal=True)
+            assert maxabs(Op[b:b + 1, :, 0], Oc[:, :, 0]) <= 1e-5
+            assert maxabs((Mp + torch.log(Lp))[b:b + 1, :, 0], (Mc + torch.log(Lc))[:, :, 0]) <= 1e-5
