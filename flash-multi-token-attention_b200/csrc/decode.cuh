@@ -61,14 +61,18 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeP
   const size_t bh = (size_t)b * p.H + h;
   const bf16* Kg = PAGED ? p.K : p.K + bh * (size_t)Nk * D;
   const bf16* Vg = PAGED ? p.V : p.V + bh * (size_t)Nk * D;
-  // element offset of a key's row inside Kg / Vg
-  auto row_off = [&](int key) -> size_t {
+  // A 16-key step never straddles a page (pages hold a multiple of 16 keys), so the page lookup is
+  // done once per step: step_base(kb) is the element offset of key (kb rounded down to its page),
+  // and a key's row follows at (key - that) * D.
+  const int page_mask = PAGED ? p.page_size - 1 : 0;
+  auto step_base = [&](int kb) -> size_t {
     if (PAGED) {
-      const int pg = key >> p.page_shift, in = key & (p.page_size - 1);
-      return (((size_t)sTable[pg] * p.H + h) * p.page_size + in) * D;
+      const int pg = max(kb, 0) >> p.page_shift;
+      return ((size_t)sTable[pg] * p.H + h) * p.page_size * D;
     }
-    return (size_t)key * D;
+    return 0;
   };
+  auto row_in = [&](int key) -> size_t { return PAGED ? (size_t)(key & page_mask) * D : (size_t)key * D; };
   if (PAGED) {
     const int npg = (Nk + p.page_size - 1) >> p.page_shift;
     for (int i = tid; i < npg; i += kDecWarps * 32) sTable[i] = p.block_table[(size_t)b * p.max_pages + i];
@@ -121,21 +125,23 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeP
     for (int kb = k_lo - 16; kb <= k_hi; kb += 16) {
       // ---- issue loads: K block [kb, kb+16), V block [kb-16, kb) ----
       uint4 kf[2][CH];
+      const bf16* Kst = Kg + step_base(kb);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int key = kb + 8 * j + g;
         const bool ok = key >= 0 && key < Nk;
 #pragma unroll
         for (int c = 0; c < CH; ++c)
-          kf[j][c] = ok ? ldg_nc_v4(Kg + row_off(key) + c * 32 + t * 8) : make_uint4(0u, 0u, 0u, 0u);
+          kf[j][c] = ok ? ldg_nc_v4(Kst + row_in(key) + c * 32 + t * 8) : make_uint4(0u, 0u, 0u, 0u);
       }
       const bool do_pv = (kb - 16 >= k_lo);
       uint4 vf[VL];
       if (do_pv) {
+        const bf16* Vst = Vg + step_base(kb - 16);
 #pragma unroll
         for (int i = 0; i < VL; ++i) {
           const int key = kb - 16 + i * KPL + vrow;
-          vf[i] = (key < Nk) ? ldg_nc_v4(Vg + row_off(key) + vcol) : make_uint4(0u, 0u, 0u, 0u);
+          vf[i] = (key < Nk) ? ldg_nc_v4(Vst + row_in(key) + vcol) : make_uint4(0u, 0u, 0u, 0u);
         }
       }
       // ---- S for the K block -> ring ----
