@@ -826,11 +826,13 @@ __global__ void __launch_bounds__(256) dk_post_window_kernel(const float* __rest
   for (int i = tid; i < cq * CK; i += 256) sTh[i] = theta[(size_t)h * cq * CK + i] * scale;
   const int run = tid / CPR, c = tid % CPR;
   const int r0 = run * RR;                                 // first row of this thread inside the tile (before the halo shift)
-  uint2 kw[WIN];                                           // the key rows of this thread's window, read once
+  float4 kw[WIN];                                          // the key rows of this thread's window, read and widened once
 #pragma unroll
   for (int i = 0; i < WIN; ++i) {
     const int jj = J0 - PK + r0 + i;
-    kw[i] = (jj >= 0 && jj < N) ? *reinterpret_cast<const uint2*>(K + ((size_t)bh * N + jj) * D + c * 4) : make_uint2(0u, 0u);
+    const uint2 kk = (jj >= 0 && jj < N) ? *reinterpret_cast<const uint2*>(K + ((size_t)bh * N + jj) * D + c * 4) : make_uint2(0u, 0u);
+    kw[i] = make_float4(__uint_as_float(kk.x << 16), __uint_as_float(kk.x & 0xffff0000u),
+                        __uint_as_float(kk.y << 16), __uint_as_float(kk.y & 0xffff0000u));
   }
   float dk[RR][4];
 #pragma unroll
@@ -855,18 +857,33 @@ __global__ void __launch_bounds__(256) dk_post_window_kernel(const float* __rest
         dk[r][0] = fmaf(w, u.x, dk[r][0]); dk[r][1] = fmaf(w, u.y, dk[r][1]);
         dk[r][2] = fmaf(w, u.z, dk[r][2]); dk[r][3] = fmaf(w, u.w, dk[r][3]);
         const float4 own = dw[r + PK];                   // dKt_a[j]
-        const uint2 kk = kw[r + bb];                     // k_{j + bb - pad_k}
-        tb = fmaf(own.x, __uint_as_float(kk.x << 16), tb);
-        tb = fmaf(own.y, __uint_as_float(kk.x & 0xffff0000u), tb);
-        tb = fmaf(own.z, __uint_as_float(kk.y << 16), tb);
-        tb = fmaf(own.w, __uint_as_float(kk.y & 0xffff0000u), tb);
+        const float4 kk = kw[r + bb];                    // k_{j + bb - pad_k}
+        tb = fmaf(own.x, kk.x, tb);
+        tb = fmaf(own.y, kk.y, tb);
+        tb = fmaf(own.z, kk.z, tb);
+        tb = fmaf(own.w, kk.w, tb);
       }
       t[bb] = tb;
     }
+    {
+      // reduce-scatter over the warp: 16 shuffles instead of 5 per value; afterwards the even lane
+      // 2 * i holds the warp total of value i
+      float v[16];
 #pragma unroll
-    for (int bb = 0; bb < CK; ++bb) {
-      const float v = warp_sum(t[bb]);
-      if (lane == 0) sRed[warp][a * CK + bb] = v;
+      for (int i = 0; i < 16; ++i) v[i] = i < CK ? t[i] : 0.f;
+#pragma unroll
+      for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
+        const bool up = (lane & bit) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+          const float send = up ? v[i] : v[i + half];
+          const float keep = up ? v[i + half] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+        }
+      }
+      const float tot = v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+      const int idx = lane >> 1;                             // bits 4..1 of the lane select the value
+      if ((lane & 1) == 0 && idx < CK) sRed[warp][a * CK + idx] = tot;
     }
     __syncthreads();                                       // the buffer of tap a is staged again for tap a+2
   }
