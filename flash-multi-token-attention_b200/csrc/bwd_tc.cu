@@ -800,7 +800,7 @@ __global__ void __launch_bounds__(256) dk_post_kernel(const float* __restrict__ 
 // (bf16, read once from global memory) in registers; the dTheta terms are summed per thread over its rows and leave the warp through
 // one reduction per filter row.
 template <int D, int CK, int RR>
-__global__ void __launch_bounds__(256) dk_post_window_kernel(const float* __restrict__ dKt, const bf16* __restrict__ K,
+__global__ void __launch_bounds__(256, 2) dk_post_window_kernel(const float* __restrict__ dKt, const bf16* __restrict__ K,
                                                              const float* __restrict__ theta, float* __restrict__ dK,
                                                              float* __restrict__ dTheta_part, int H, int N, int cq,
                                                              float scale, int n_jblocks) {
