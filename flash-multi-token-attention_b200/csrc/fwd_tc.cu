@@ -529,7 +529,7 @@ cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t 
   const size_t BH = (size_t)p.B * p.H;
   const float sc = p.scale * kLog2e;
   if (p.ck == 11 && p.cq <= 16) {
-    constexpr int RR = 8;
+    constexpr int RR = 4;
     if (p.d == 64) {
       constexpr int RUNS = 256 / (64 / 8);
       dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);
