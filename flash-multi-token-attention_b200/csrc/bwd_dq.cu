@@ -5,13 +5,25 @@
 
 namespace fmta {
 
-// Sum per-slot partials in slot order: out[i] = sum_s part[s * n + i].
-__global__ void reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int n_slots, int n) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
+// Sum per-slot partials: out[i] = sum_s part[s * n + i].  32 outputs per CTA, 8 threads per output;
+// thread k adds the slots s = k, k+8, ... in order, then the 8 sub-sums are added in order of k:
+// a fixed summation tree, so the result is bit-reproducible.
+__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                              int n_slots, int n) {
+  __shared__ float sSub[8][33];
+  const int col = threadIdx.x & 31, k = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + col;
   float t = 0.f;
-  for (int s = 0; s < n_slots; ++s) t += part[(size_t)s * n + i];
-  out[i] = t;
+  if (i < n)
+    for (int s = k; s < n_slots; s += 8) t += part[(size_t)s * n + i];
+  sSub[k][col] = t;
+  __syncthreads();
+  if (k == 0 && i < n) {
+    float r = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) r += sSub[q][col];
+    out[i] = r;
+  }
 }
 
 // D[row] = sum_d dO[row,d] * O[row,d]; one warp per row.  O may be fp32 or bf16.
@@ -67,7 +79,7 @@ cudaError_t launch_bwd_dq(const TrainParams& p, cudaStream_t stream) {
 }
 
 cudaError_t launch_reduce_partials(const float* part, float* out, int n_slots, int n, cudaStream_t stream) {
-  reduce_partials_kernel<<<(n + 127) / 128, 128, 0, stream>>>(part, out, n_slots, n);
+  reduce_partials_kernel<<<(n + 31) / 32, 256, 0, stream>>>(part, out, n_slots, n);
   return cudaGetLastError();
 }
 
