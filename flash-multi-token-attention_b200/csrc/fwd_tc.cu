@@ -197,8 +197,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
   const int band = pq + pk;              // entries with query - key < band belong to the exact kernel
   const int nQB = (N + NT * BM - 1) / (NT * BM);
-  const int qb = nQB - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // CTAs are dispatched in linear block order; walk it length-major (all (batch, head) pairs of the
+  // longest row block first) so that the greedy hardware scheduler ends with the short CTAs
+  const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const int nBH = gridDim.y * gridDim.z;
+  const int qb = nQB - 1 - lin / nBH;
+  const int h = (lin % nBH) % (int)gridDim.y, b = (lin % nBH) / (int)gridDim.y;
   const int bh = b * p.H + h;
   const int i0 = qb * NT * BM;
   const int nKB = (N + BC - 1) / BC;
