@@ -315,9 +315,14 @@ def main():
     if kms:
         ach = 8.0 * d * E / (kms * 1e-3) / 1e12
         exe = 2.0 * d * (2 * cq + 2) * E / (kms * 1e-3) / 1e12
+        # DRAM bytes per launch from the committed ncu capture at B=2,H=16,N=4096 (152.2 MB read + 181.0 MB
+        # written, profiles/tensor_core_kernels_ncu_full_B2_H16_N4096_d64.md), scaled by the (batch, head)
+        # units; only quoted for that sequence length and head dimension
+        traffic = (152.18e6 + 181.01e6) * (B * H) / 32.0 if (N == 4096 and d == 64 and cq == 6) else None
         roof = dict(bound="tensor", kernel=KERNELS[DOMINANT], achieved=ach, peak=peaks["tflops_sustained"],
                     unit="TFLOP/s", frac=ach / peaks["tflops_sustained"], peak_source=peaks["source"] + " (sustained)",
-                    traffic=None, ms_per_launch=kms, executed_tflops=exe,
+                    traffic=traffic, traffic_unit="bytes per launch (ncu capture of a smaller case, scaled)",
+                    ms_per_launch=kms, executed_tflops=exe,
                     executed_frac=exe / peaks["tflops_sustained"],
                     note="achieved counts 8*d*E algorithmic FLOPs; the kernel executes 2*d*(2*c_q+2)*E "
                          "(stacked filter taps on the tensor cores) = executed_tflops")
@@ -387,8 +392,11 @@ def bench_decode(F, dev, dec, peaks, world, timed):
     return dict(metric="decode HBM GB/s", value=world * gbs, unit="GB/s", ms_per_step=ms, paged=paged,
                 config=dict(workload="fwd_inference bf16 B=%d(per GPU),H=%d,d=%d,Nk=%d,q_len=%d,theta(%d,%d),k_splits=%d"
                             % (B, H, d, Nk, ql, cq, ck, ks), l2="17 GB of K/V per step >> L2"),
+                # DRAM traffic: the committed ncu capture at B=4,H=32,Nk=16384 read+wrote 1.02x its algorithmic
+                # bytes (profiles/decode_kernel_ncu_full_B4_H32_Nk16384_d128.md); it grows with the (b,h) x key units
                 roofline=dict(bound="hbm", kernel="decode_kernel", achieved=gbs, peak=peaks["hbm"], unit="GB/s",
-                              frac=gbs / peaks["hbm"], peak_source=peaks["source"], traffic=None),
+                              frac=gbs / peaks["hbm"], peak_source=peaks["source"], traffic=1.02 * by,
+                              traffic_unit="bytes per launch (ncu capture of a smaller case, scaled)"),
                 gpu_launches=4 * steps)
 
 
