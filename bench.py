@@ -316,7 +316,7 @@ def main():
         ach = 8.0 * d * E / (kms * 1e-3) / 1e12
         exe = 2.0 * d * (2 * cq + 2) * E / (kms * 1e-3) / 1e12
         # DRAM bytes per launch from the committed ncu capture at B=2,H=16,N=4096 (152.2 MB read + 181.0 MB
-        # written, profiles/tensor_core_kernels_ncu_full_B2_H16_N4096_d64.md), scaled by the (batch, head)
+        # written; summary under profiles/), scaled by the (batch, head)
         # units; only quoted for that sequence length and head dimension
         traffic = (152.18e6 + 181.01e6) * (B * H) / 32.0 if (N == 4096 and d == 64 and cq == 6) else None
         roof = dict(bound="tensor", kernel=KERNELS[DOMINANT], achieved=ach, peak=peaks["tflops_sustained"],
@@ -393,7 +393,7 @@ def bench_decode(F, dev, dec, peaks, world, timed):
                 config=dict(workload="fwd_inference bf16 B=%d(per GPU),H=%d,d=%d,Nk=%d,q_len=%d,theta(%d,%d),k_splits=%d"
                             % (B, H, d, Nk, ql, cq, ck, ks), l2="17 GB of K/V per step >> L2"),
                 # DRAM traffic: the committed ncu capture at B=4,H=32,Nk=16384 read+wrote 1.02x its algorithmic
-                # bytes (profiles/decode_kernel_ncu_full_B4_H32_Nk16384_d128.md); it grows with the (b,h) x key units
+                # bytes (summary under profiles/); it grows with the (b,h) x key units
                 roofline=dict(bound="hbm", kernel="decode_kernel", achieved=gbs, peak=peaks["hbm"], unit="GB/s",
                               frac=gbs / peaks["hbm"], peak_source=peaks["source"], traffic=1.02 * by,
                               traffic_unit="bytes per launch (ncu capture of a smaller case, scaled)"),

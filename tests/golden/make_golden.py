@@ -101,7 +101,7 @@ def head_case(refh, name, B, H, N, d, causal, seed, w_kind):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     a = ap.parse_args()
     base = os.path.join(a.reference, "flash_multi_token_attention")
     ref = _load(os.path.join(base, "conv_attn", "conv_attention_pytorch.py"), "ref_conv_attention_pytorch")
