@@ -55,6 +55,17 @@ def test_host_validation_needs_no_gpu():
     dec = lambda q_len=6, ks=1, Nk=64: lib.fmta_decode(good, good, good, good, good, good, good, 1, 1, q_len, Nk,
                                                         64, 3, 3, ks, 1.0, None)
     assert dec(q_len=17) == -2 and dec(ks=0) == -2 and dec(ks=65) == -2
+    assert lib.fmta_decode_offset_causal(good, good, good, good, good, good, good, 1, 1, 17, 64, 64, 3, 3, 1, 1.0,
+                                         None) == -2
+    pag = lambda table=good, page=64, max_pages=4, Nk=200: lib.fmta_decode_paged(
+        good, good, good, table, None, good, good, good, good, 1, 1, 6, Nk, 64, 3, 3, 1, 1.0, page, max_pages, 0, None)
+    assert pag(table=None) == -1
+    assert pag(page=48) == -2 and pag(page=8) == -2          # power of two, at least one 16-key step
+    assert pag(max_pages=3) == -2                            # 200 keys need 4 pages of 64
+    assert pag(max_pages=4096, Nk=64) == -2                  # block-table row longer than the kernel stages
+    app = lambda kp=good, page=64, n_new=1: lib.fmta_kv_append_paged(kp, good, good, good, good, good, 1, 1, n_new,
+                                                                     64, page, 4, None)
+    assert app(kp=None) == -1 and app(page=24) == -2 and app(n_new=0) == -2
     assert lib.fmta_bwd_dq_dw(good, good, good, good, good, good, good, None, good, good, None, 1, 2, 64, 64, 3, 3,
                               1, 1.0, 1, None, 0, None) == -5     # workspace missing
     assert lib.fmta_workspace_bytes(1, 4, 16, 4096, 64, 6, 11, 1) == 4 * 64 * 16 * 66 * 4
