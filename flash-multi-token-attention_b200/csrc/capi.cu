@@ -11,7 +11,7 @@ using namespace fmta;
 namespace {
 
 thread_local int g_last_cuda_error = 0;
-int g_path = -1;   // process-wide default: -1 auto, 0 exact kernels only, 1 tensor-core kernels + exact band
+int g_path = -1;   // process-wide default: -1 auto, 0 exact kernels only, 1 tensor-core kernels + band kernel
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

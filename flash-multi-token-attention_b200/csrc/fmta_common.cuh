@@ -1,7 +1,7 @@
 // Shared device helpers for the conv-attention kernels (sm_100a).
 //
 // Register-fragment tensor-core helpers (ldmatrix + mma.sync m16n8k16 bf16, fp32
-// accumulate) used by the exact ("band") tile path and the decode kernel, cp.async
+// accumulate) used by the exact tile kernels, the band kernels and the decode kernel, cp.async
 // tile loaders with zero fill, and small warp utilities.  The TMA / tcgen05 / TMEM
 // helpers used by the stacked-GEMM forward live in fmta_tc.cuh.
 #pragma once

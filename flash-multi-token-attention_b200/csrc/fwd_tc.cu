@@ -9,8 +9,8 @@
 //   fwd_tc_kernel : the warp-specialised main kernel (1 TMA warp, 1 MMA warp, 2 softmax warpgroups);
 //   launch_fwd_tc : tensor maps + launches.
 // Ownership is per score entry: the stacked kernel takes every entry with query - key >= pad_q +
-// pad_k (masking the rest of a diagonal tile), the exact tile kernel takes the band entries.  The
-// kernel leaves an UN-normalised partial (O, m, l) per query row; the exact kernel continues the
+// pad_k (masking the rest of a diagonal tile), the band kernel (fwd_band.cu) takes the band entries.  The
+// kernel leaves an UN-normalised partial (O, m, l) per query row; the band kernel continues the
 // online softmax from that state over the band and writes the final O, M, L.
 //
 // Row-shifted A operands without copies: Q is staged in the no-swizzle K-major core-matrix
@@ -195,7 +195,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
-  const int band = pq + pk;              // entries with query - key < band belong to the exact kernel
+  const int band = pq + pk;              // entries with query - key < band belong to the band kernel
   const int nQB = (N + NT * BM - 1) / (NT * BM);
   // CTAs are dispatched in linear block order; walk it length-major (all (batch, head) pairs of the
   // longest row block first) so that the greedy hardware scheduler ends with the short CTAs
@@ -378,7 +378,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tc::mbar_arrive(&s_free[t]);
       if (tid == 0) TRACE(kb * 8 + 1);
       const int j0 = kb * BC;
-      // mask: keys past N, and (causal) entries on or above the band, which the exact kernel owns
+      // mask: keys past N, and (causal) entries on or above the band, which the band kernel owns
       const int jlim = p.causal ? min(N - 1, gi - band) : N - 1;   // last key this row may see here
       if (j0 + BC - 1 > jlim) {
 #pragma unroll
@@ -597,7 +597,7 @@ size_t fwd_tc_workspace_bytes(int B, int H, int N, int d, int cq) {
   return up(rows * cq * d * 2) + up(rows * d * 4) + 2 * up(rows * 4) + 1024;
 }
 
-// Runs the pre-pass and the stacked kernel; on return p_out describes where the exact band kernel
+// Runs the pre-pass and the stacked kernel; on return p_out describes where the band kernel
 // must pick up (Opart / Mpart / Lpart).
 cudaError_t launch_fwd_tc(const TrainParams& p, void* workspace, const float** Opart, const float** Mpart,
                           const float** Lpart, cudaStream_t stream) {
