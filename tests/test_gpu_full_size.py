@@ -97,3 +97,35 @@ def test_decode_full_cache_length():
         assert maxabs(O, Or) <= TOL_BF16
         assert maxabs(M, Mr) <= TOL_BF16
         assert maxabs(M + torch.log(L), Mr + torch.log(Lr)) <= TOL_BF16
+
+
+def test_head_mix_configuration_identity_mix_N8192_d128():
+    """Head-mixing configuration (N=8192, d=128, theta (6,11), groups of 4) on a 2-group slice.  With
+    identity mixing matrices the cluster kernels must reproduce plain conv attention (computed by the
+    default tensor-core + band forward and the exact backward): a size-independent property where the
+    O(N^2) oracle cannot go.  Then a non-trivial mix: everything finite, dW of the right shape."""
+    import fmta_b200 as F
+    B, H, N, d, cq, ck, G = 1, 8, 8192, 128, 6, 11, 4
+    g = torch.Generator(device="cuda").manual_seed(8192)
+    q, k, v, do = (torch.randn(B, H, N, d, device="cuda", generator=g).to(torch.bfloat16) for _ in range(4))
+    th = torch.randn(H, cq, ck, device="cuda", generator=g) * 0.02
+    th[:, cq - 1, ck // 2] += 1.0
+    scale = 1.0 / math.sqrt(d)
+    eye = torch.eye(G, device="cuda").repeat(H // G, 1, 1).contiguous()
+    o, l, m, lse = F.conv_headmix_forward(q, k, v, eye, th, scale, True, out_dtype=torch.float32)
+    O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True)
+    assert maxabs(o, O) <= TOL_BF16
+    assert maxabs(m + torch.log(l), LSE) <= TOL_BF16
+    dq, dw, dth = F.conv_headmix_bwd_dq_dw(q, k, v, eye, o, do, l, m, th, True, scale)
+    dk, dv = F.conv_headmix_bwd_dkdv(q, k, v, eye, o, do, l, m, th, True, scale)
+    Dv = F.rowdot(do, O)
+    rq, rk, rv, rth = F.backward(q, k, v, do, Dv, LSE, th, scale, cq - 1, (ck - 1) // 2, True)
+    assert maxabs(dq, rq) <= TOL_BF16 and maxabs(dk, rk) <= TOL_BF16 and maxabs(dv, rv) <= TOL_BF16
+    assert maxabs(dth, rth) <= max(TOL_BF16, 5e-3 * float(rth.abs().max()))
+    w = (eye + 0.02 * torch.randn(H // G, G, G, device="cuda", generator=g)).contiguous()
+    o2, l2, m2, _ = F.conv_headmix_forward(q, k, v, w, th, scale, True, out_dtype=torch.float32)
+    dq2, dw2, dth2 = F.conv_headmix_bwd_dq_dw(q, k, v, w, o2, do, l2, m2, th, True, scale)
+    assert dw2.shape == (H // G, G, G)
+    for t in (o2, dq2, dw2, dth2):
+        assert torch.isfinite(t).all()
+    assert 0 < maxabs(o2, o) < 1.0          # the mix changes the result, mildly
