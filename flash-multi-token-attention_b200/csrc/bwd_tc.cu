@@ -394,8 +394,8 @@ struct DkvCfg {
   static_assert(D == 64, "the dK/dV tensor-core kernel is instantiated for d = 64");
   static constexpr int BK = 128;               // keys per CTA (= TMEM lanes)
   static constexpr int BR = 64;                // query rows per block
-  static constexpr int HALO = 16;
-  static constexpr int QR = BR + HALO;         // 80 rows of Q per stage
+  static constexpr int HALO = 8;               // rows of Q staged above the block (pad_q <= 5)
+  static constexpr int QR = BR + HALO;         // 72 rows of Q per stage
   static constexpr int MAXCQ = 6;              // dV + 6 dKt accumulators of 64 columns + 64 scratch = 512
   static constexpr int NSTG = 3;
   static constexpr int KT_BYTES = BK * 128;    // one resident Kt / V tile
@@ -403,13 +403,14 @@ struct DkvCfg {
   static constexpr int oV = oKt + MAXCQ * KT_BYTES;
   static constexpr int oStage = oV + KT_BYTES;
   static constexpr int sgdO = 0;                                  // [64 rows][128 B], 128B swizzle
-  static constexpr int sgQ = BR * 128;                            // [D/8][QR][16 B]
-  static constexpr int sgLD = sgQ + QR * D * 2;                   // LSE*log2e [64], D [64]
+  static constexpr int sgQ = BR * 128;                            // [D/8][QR][16 B], then the same again one row later
+  static constexpr int sgLD = sgQ + 2 * QR * D * 2;               // LSE*log2e [64], D [64]
   static constexpr int STAGE_BYTES = ((sgLD + 2 * BR * 4 + 1023) / 1024) * 1024;
   static constexpr int oPT = oStage + NSTG * STAGE_BYTES;         // P^T : [BR/8][128 keys][16 B] (K-major A operand)
   static constexpr int oDCT = oPT + (BR / 8) * BK * 16;           // dC^T: same layout
   static constexpr int oBar = oDCT + (BR / 8) * BK * 16;
   static constexpr int kSmemBytes = oBar + 512 + 1024;
+  static_assert(kSmemBytes <= 227 * 1024, "dK/dV kernel: shared memory budget");
   static constexpr int kTmemCols = 512;        // dV at 0, dKt_a at 64*(1+a), scratch X at 448
   static constexpr int colX = 448;
   static constexpr int kEwWarps = 16;
@@ -503,10 +504,14 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         __syncwarp();
         if (lane == 0) {
-          tc::mbar_expect_tx(&full[st], BR * 128 + QR * D * 2);
+          tc::mbar_expect_tx(&full[st], BR * 128 + 2 * QR * D * 2);
           tc::tma_load_3d(sg + Cfg::sgdO, &tmdO, &full[st], 0, i0, bh);
-          for (int kc = 0; kc < D / 8; ++kc)
-            tc::tma_load_3d(sg + Cfg::sgQ + kc * (QR * 16), &tmQ, &full[st], kc * 8, i0 - HALO, bh);
+          // Q twice: the second copy starts one row later and sits where the column chunks 8..15 of a
+          // 128-wide MN-major operand fall, so that ONE 128 x 128 MMA accumulates two adjacent filter
+          // taps (dKt_a | dKt_{a+1}) += dC^T [Q^(a) | Q^(a+1)]
+          for (int cp = 0; cp < 2; ++cp)
+            for (int kc = 0; kc < D / 8; ++kc)
+              tc::tma_load_3d(sg + Cfg::sgQ + (cp * (D / 8) + kc) * (QR * 16), &tmQ, &full[st], kc * 8, i0 - HALO + cp, bh);
         }
       }
     }
@@ -568,8 +573,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int ai = warp - (Cfg::kEwWarps + 2);
     if (nblk > 0) {   // all lanes run the loop; one elected lane issues (see tc::elect_one)
       constexpr uint32_t idescA = tc::make_idesc(BK, D, 0, 1);     // 128 x D, B MN-major
-      const int a_half = cq / 2;
-      const int a_begin = ai == 0 ? 0 : a_half, a_end = ai == 0 ? a_half : cq;
+      constexpr uint32_t idescA2 = tc::make_idesc(BK, 2 * D, 0, 1); // 128 x 2D: two adjacent taps at once
+      const int pairs = cq / 2, p_half = pairs / 2;
+      const int p_begin = ai == 0 ? 0 : p_half, p_end = ai == 0 ? p_half : pairs;
+      const bool single = (ai == 1) && (cq & 1);                   // odd c_q: the last tap on its own
       const uint64_t dPTa = tc::make_sdesc(smem_u32(smem + Cfg::oPT), BK * 16, 128, tc::kLayoutNone);
       const uint64_t dDCa = tc::make_sdesc(smem_u32(smem + Cfg::oDCT), BK * 16, 128, tc::kLayoutNone);
       const uint32_t pt_hi = (uint32_t)(dPTa >> 32), pt_lo = (uint32_t)dPTa, dc_lo = (uint32_t)dDCa;
@@ -591,7 +598,17 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           for (int k = 1; k < BR / 16; ++k)
             tc::mma_ss2e<1>(tmem, pt_lo + (uint32_t)(2 * k * BK), pt_hi, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
         }
-        for (int a = a_begin; a < a_end; ++a) {
+        for (int pr = p_begin; pr < p_end; ++pr) {
+          const int a = 2 * pr;
+          const uint32_t dacc = tmem + 64 * (1 + a);
+          const uint32_t b_lo = qm_lo + (uint32_t)a;
+          tc::mma_ss2pe(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA2, acc_on);
+#pragma unroll
+          for (int k = 1; k < BR / 16; ++k)
+            tc::mma_ss2e<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idescA2);
+        }
+        if (single) {
+          const int a = cq - 1;
           const uint32_t dacc = tmem + 64 * (1 + a);
           const uint32_t b_lo = qm_lo + (uint32_t)a;
           tc::mma_ss2pe(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA, acc_on);
