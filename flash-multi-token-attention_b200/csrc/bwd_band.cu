@@ -25,17 +25,17 @@ namespace bandcfg {
 constexpr int kThetaLdBand = 20;                     // filter row stride in shared memory (c_k <= 17)
 constexpr int D = 64;
 constexpr int NT = 256;
-constexpr int MAXPQ = 5, MAXPK = 8;                 // c_q <= 6, c_k <= 17
-constexpr int MAXBAND = MAXPQ + MAXPK;              // 13
-constexpr int MAXW = MAXBAND + MAXPK;               // 21
+constexpr int MAXPQ = 6, MAXPK = 8;                 // c_q <= 7, c_k <= 17
+constexpr int MAXBAND = MAXPQ + MAXPK;              // 14
+constexpr int MAXW = MAXBAND + MAXPK;               // 22
 constexpr int RC = 96;                              // dC rows computed per CTA (6 tiles of 16)
 constexpr int RS = RC + 16;                         // Sb / Q rows: start 16 rows earlier
 constexpr int RK = RC + 48;                         // K rows: start 48 rows earlier
 constexpr int LD = D + 8;                           // bf16 row stride (ldmatrix without bank conflicts)
 constexpr int SB_LD = 37;                           // band (zero pad for e < 0) + W columns, odd
-constexpr int DC_LD = 43;                           // pad_k + band + pad_q + 2 pad_k columns, odd
-constexpr int P_LD = 13;
-constexpr int DS_LD = 21;
+constexpr int DC_LD = 45;                           // pad_k + band + pad_q + 2 pad_k columns (<= 44), odd
+constexpr int P_LD = 15;
+constexpr int DS_LD = 23;
 constexpr int A_LD = 40;                            // bf16 operand tiles of the output GEMMs: 32 columns + 8 (ldmatrix)
 constexpr int oQ = 0;
 constexpr int oK = oQ + RS * LD * 2;
@@ -47,7 +47,7 @@ constexpr int oP = oSb + RS * SB_LD * 4;            // dPb, overwritten in place
 constexpr int odS = oP + RC * P_LD * 4;
 constexpr int oLD = odS + RC * DS_LD * 4;           // LSE*log2e [RC], D [RC]
 constexpr int oTheta = oLD + 2 * RC * 4;
-constexpr int oRed = oTheta + 6 * kThetaLdBand * 4;
+constexpr int oRed = oTheta + 7 * kThetaLdBand * 4;
 constexpr int kSmemBytes = oRed + NT * 4;
 }  // namespace bandcfg
 
@@ -494,6 +494,8 @@ cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream) {
   ScopedKernelTimer timer_(kKernBwdBand, stream);
   if (p.cq == 6 && p.ck == 11)
     return launch_kernel<TrainParams>(bwd_band_kernel<6, 11>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
+  if (p.cq == 7 && p.ck == 7)
+    return launch_kernel<TrainParams>(bwd_band_kernel<7, 7>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
   return launch_kernel<TrainParams>(bwd_band_kernel<0, 0>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
 }
 

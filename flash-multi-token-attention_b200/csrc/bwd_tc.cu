@@ -51,6 +51,9 @@ struct BwdTcParams {
   float* dKt;         // [B,H,cq,N,D] (dkdv kernel: overwritten)
   int* status;
   int H, N, cq, ck, causal;
+  // dK/dV kernel: the filter taps whose dKt this launch accumulates ([tap0, tap0 + ntap)) and whether it
+  // accumulates dV as well; seven taps do not fit the tensor memory at once and take two launches
+  int tap0, ntap, with_dv;
 };
 
 // ==========================================================================================
@@ -67,7 +70,8 @@ struct DqCfg {
   static constexpr int QR = HALO + OWN * (NT - 1) + BM;   // 256 rows of Q
   static constexpr int DR = BM + 16;           // rows of a dC buffer (16 zero rows below)
   static constexpr int TILE_BYTES = BC * 128;  // Kt / V ring tile: 64 keys x 64 elements
-  static constexpr int NSLOT = 14;             // two key blocks of (cq <= 6) Kt tiles + V
+  static constexpr int NSLOT = 15;             // the Kt tiles of one key block held for its dQ MMAs (cq <= 7) while the
+                                               // next block's cq + 1 tiles stream in: 2 cq + 1 slots
   static constexpr int oQ = 0;                                  // [D/8][QR][16 B]
   static constexpr int odO = oQ + QR * D * 2;                   // NT x [128 rows][128 B], 128B swizzle
   static constexpr int odC = odO + NT * BM * 128;               // NT x [BC/8][DR][16 B]
@@ -389,14 +393,14 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // ==========================================================================================
 // dK-tilde / dV
 // ==========================================================================================
-template <int D>
+template <int D, int CQMAX, bool PAIR>   // PAIR: stage Q twice so that two adjacent taps share one 128-wide MMA
 struct DkvCfg {
   static_assert(D == 64, "the dK/dV tensor-core kernel is instantiated for d = 64");
   static constexpr int BK = 128;               // keys per CTA (= TMEM lanes)
   static constexpr int BR = 64;                // query rows per block
   static constexpr int HALO = 8;               // rows of Q staged above the block (pad_q <= 5)
   static constexpr int QR = BR + HALO;         // 72 rows of Q per stage
-  static constexpr int MAXCQ = 6;              // dV + 6 dKt accumulators of 64 columns + 64 scratch = 512
+  static constexpr int MAXCQ = CQMAX;          // resident Kt tiles; at most 7 accumulators of 64 columns + 64 scratch = 512
   static constexpr int NSTG = 3;
   static constexpr int KT_BYTES = BK * 128;    // one resident Kt / V tile
   static constexpr int oKt = 0;                                   // MAXCQ x [128 keys][128 B], 128B swizzle
@@ -404,7 +408,7 @@ struct DkvCfg {
   static constexpr int oStage = oV + KT_BYTES;
   static constexpr int sgdO = 0;                                  // [64 rows][128 B], 128B swizzle
   static constexpr int sgQ = BR * 128;                            // [D/8][QR][16 B], then the same again one row later
-  static constexpr int sgLD = sgQ + 2 * QR * D * 2;               // LSE*log2e [64], D [64]
+  static constexpr int sgLD = sgQ + (PAIR ? 2 : 1) * QR * D * 2;  // LSE*log2e [64], D [64]
   static constexpr int STAGE_BYTES = ((sgLD + 2 * BR * 4 + 1023) / 1024) * 1024;
   static constexpr int oPT = oStage + NSTG * STAGE_BYTES;         // P^T : [BR/8][128 keys][16 B] (K-major A operand)
   static constexpr int oDCT = oPT + (BR / 8) * BK * 16;           // dC^T: same layout
@@ -417,12 +421,12 @@ struct DkvCfg {
   static constexpr int kThreads = (kEwWarps + 4) * 32;   // + producer, issuer S, issuers A0 and A1
 };
 
-template <int D>
-__global__ void __launch_bounds__(DkvCfg<D>::kThreads, 1)
+template <int D, int CQMAX, bool PAIR>
+__global__ void __launch_bounds__(DkvCfg<D, CQMAX, PAIR>::kThreads, 1)
 bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmKt, const __grid_constant__ CUtensorMap tmV,
                    const BwdTcParams p) {
-  using Cfg = DkvCfg<D>;
+  using Cfg = DkvCfg<D, CQMAX, PAIR>;
   constexpr int BK = Cfg::BK, BR = Cfg::BR, HALO = Cfg::HALO, QR = Cfg::QR, NSTG = Cfg::NSTG;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -504,12 +508,12 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         __syncwarp();
         if (lane == 0) {
-          tc::mbar_expect_tx(&full[st], BR * 128 + 2 * QR * D * 2);
+          tc::mbar_expect_tx(&full[st], BR * 128 + (PAIR ? 2 : 1) * QR * D * 2);
           tc::tma_load_3d(sg + Cfg::sgdO, &tmdO, &full[st], 0, i0, bh);
           // Q twice: the second copy starts one row later and sits where the column chunks 8..15 of a
           // 128-wide MN-major operand fall, so that ONE 128 x 128 MMA accumulates two adjacent filter
           // taps (dKt_a | dKt_{a+1}) += dC^T [Q^(a) | Q^(a+1)]
-          for (int cp = 0; cp < 2; ++cp)
+          for (int cp = 0; cp < (PAIR ? 2 : 1); ++cp)
             for (int kc = 0; kc < D / 8; ++kc)
               tc::tma_load_3d(sg + Cfg::sgQ + (cp * (D / 8) + kc) * (QR * 16), &tmQ, &full[st], kc * 8, i0 - HALO + cp, bh);
         }
@@ -574,9 +578,13 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (nblk > 0) {   // all lanes run the loop; one elected lane issues (see tc::elect_one)
       constexpr uint32_t idescA = tc::make_idesc(BK, D, 0, 1);     // 128 x D, B MN-major
       constexpr uint32_t idescA2 = tc::make_idesc(BK, 2 * D, 0, 1); // 128 x 2D: two adjacent taps at once
-      const int pairs = cq / 2, p_half = pairs / 2;
-      const int p_begin = ai == 0 ? 0 : p_half, p_end = ai == 0 ? p_half : pairs;
-      const bool single = (ai == 1) && (cq & 1);                   // odd c_q: the last tap on its own
+      // this launch accumulates taps [tap0, tap0 + ntap) (accumulator i at column 64 * (with_dv + i)) and
+      // dV (column 0) when with_dv; A0 takes dV and the first half of the tap groups, A1 the rest.  With
+      // PAIR a group is two adjacent taps in one 128-wide MMA (an odd last tap goes alone).
+      const int ntap = p.ntap, tap0 = p.tap0, accb = p.with_dv ? 1 : 0;
+      const int pairs = PAIR ? ntap / 2 : 0, singles = ntap - 2 * pairs;     // groups: `pairs` pairs, then `singles` single taps
+      const int ngrp = pairs + singles, g_half = ngrp / 2;
+      const int g_begin = ai == 0 ? 0 : g_half, g_end = ai == 0 ? g_half : ngrp;
       const uint64_t dPTa = tc::make_sdesc(smem_u32(smem + Cfg::oPT), BK * 16, 128, tc::kLayoutNone);
       const uint64_t dDCa = tc::make_sdesc(smem_u32(smem + Cfg::oDCT), BK * 16, 128, tc::kLayoutNone);
       const uint32_t pt_hi = (uint32_t)(dPTa >> 32), pt_lo = (uint32_t)dPTa, dc_lo = (uint32_t)dDCa;
@@ -592,29 +600,22 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!tc::mbar_wait_warp(&full[st], ph, s_abort)) { ok = false; break; }
         if (!tc::mbar_wait_warp(pdc_full, it & 1, s_abort)) { ok = false; break; }
         tc::tc_fence_after();
-        if (ai == 0) {
+        if (ai == 0 && p.with_dv) {
           tc::mma_ss2pe(tmem, pt_lo, pt_hi, o_lo, o_hi, idescA, acc_on);
 #pragma unroll
           for (int k = 1; k < BR / 16; ++k)
             tc::mma_ss2e<1>(tmem, pt_lo + (uint32_t)(2 * k * BK), pt_hi, o_lo + (uint32_t)(k * (2048 / 16)), o_hi, idescA);
         }
-        for (int pr = p_begin; pr < p_end; ++pr) {
-          const int a = 2 * pr;
-          const uint32_t dacc = tmem + 64 * (1 + a);
-          const uint32_t b_lo = qm_lo + (uint32_t)a;
-          tc::mma_ss2pe(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA2, acc_on);
+        for (int gi = g_begin; gi < g_end; ++gi) {
+          const bool pair = gi < pairs;
+          const int i = pair ? 2 * gi : 2 * pairs + (gi - pairs);        // first accumulator / tap of the group
+          const uint32_t dacc = tmem + 64 * (accb + i);
+          const uint32_t b_lo = qm_lo + (uint32_t)(tap0 + i);
+          const uint32_t idg = pair ? idescA2 : idescA;
+          tc::mma_ss2pe(dacc, dc_lo, pt_hi, b_lo, qm_hi, idg, acc_on);
 #pragma unroll
           for (int k = 1; k < BR / 16; ++k)
-            tc::mma_ss2e<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idescA2);
-        }
-        if (single) {
-          const int a = cq - 1;
-          const uint32_t dacc = tmem + 64 * (1 + a);
-          const uint32_t b_lo = qm_lo + (uint32_t)a;
-          tc::mma_ss2pe(dacc, dc_lo, pt_hi, b_lo, qm_hi, idescA, acc_on);
-#pragma unroll
-          for (int k = 1; k < BR / 16; ++k)
-            tc::mma_ss2e<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idescA);
+            tc::mma_ss2e<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idg);
         }
         tc::mma_commit_e(&empty[st]);
         tc::mma_commit_e(pdc_free);
@@ -715,7 +716,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const bool have = (nblk > 0) && ok;
     const bool store = key < N;
     const size_t krow = (size_t)(store ? key : 0);
-    for (int ch = cg; ch < 2 * (cq + 1); ch += NCG) {
+    const int nacc = (p.with_dv ? 1 : 0) + p.ntap;
+    for (int ch = cg; ch < 2 * nacc; ch += NCG) {
       const int acc = ch >> 1, half = ch & 1;
       float o[32];
       if (have) {
@@ -726,8 +728,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       if (store) {
         float* dst;
-        if (acc == 0) dst = p.dV + ((size_t)bh * N + krow) * D + half * 32;
-        else dst = p.dKt + (((size_t)bh * cq + (acc - 1)) * N + krow) * D + half * 32;
+        if (p.with_dv && acc == 0) dst = p.dV + ((size_t)bh * N + krow) * D + half * 32;
+        else dst = p.dKt + (((size_t)bh * cq + (p.tap0 + acc - (p.with_dv ? 1 : 0))) * N + krow) * D + half * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
       }
@@ -754,8 +756,8 @@ __global__ void __launch_bounds__(256) dk_post_kernel(const float* __restrict__ 
                                                       float* __restrict__ dTheta_part, int H, int N, int cq, int ck,
                                                       float scale, int n_jblocks) {
   constexpr int CPR = D / 8, RPB = 256 / CPR;
-  __shared__ float sTh[6 * 20];
-  __shared__ float sRed[8][6 * 17];
+  __shared__ float sTh[7 * 20];
+  __shared__ float sRed[8][7 * 17];
   const int bh = blockIdx.y, h = bh % H, b = bh / H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < cq * ck; i += 256) sTh[(i / ck) * 20 + (i % ck)] = theta[(size_t)h * cq * ck + i] * scale;
@@ -830,8 +832,8 @@ __global__ void __launch_bounds__(256, 2) dk_post_window_kernel(const float* __r
   constexpr int CPR = D / 4, RUNS = 256 / CPR, PK = (CK - 1) / 2, WIN = RR + CK - 1;
   constexpr int ROWS = RUNS * RR, TR = ROWS + CK - 1;     // keys per CTA, rows staged
   __shared__ __align__(16) float sT[2][TR * D];
-  __shared__ float sTh[6 * CK];
-  __shared__ float sRed[8][6 * CK];
+  __shared__ float sTh[7 * CK];
+  __shared__ float sRed[8][7 * CK];
   const int bh = blockIdx.y, h = bh % H, b = bh / H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int J0 = blockIdx.x * ROWS;
@@ -931,10 +933,10 @@ bool tensor_maps_available();
 cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream);
 
 // keys per CTA of the dKt adjoint kernel chosen for a filter width
-static int dk_post_rows_per_cta(int ck) { return ck == 11 ? 64 : 32; }
+static int dk_post_rows_per_cta(int ck) { return (ck == 11 || ck == 7) ? 64 : 32; }   // window kernel : generic kernel
 
 bool bwd_tc_supported(const TrainParams& p) {
-  return p.theta != nullptr && p.Wmix == nullptr && p.d == 64 && p.cq >= 1 && p.cq <= 6 && tensor_maps_available();
+  return p.theta != nullptr && p.Wmix == nullptr && p.d == 64 && p.cq >= 1 && p.cq <= 7 && tensor_maps_available();
 }
 
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq) {
@@ -976,15 +978,13 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t
 }
 
 
-cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream) {
+// One launch of the dK/dV kernel for the taps [tap0, tap0 + ntap) (and dV).
+template <int CQMAX, bool PAIR>
+static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* Kt, float* dKt, int* status, int tap0,
+                                    int ntap, int with_dv, cudaStream_t stream) {
   constexpr int D = 64;
-  using Cfg = DkvCfg<D>;
-  const size_t rows = (size_t)p.B * p.H * p.N, BH = (size_t)p.B * p.H;
-  auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
-  unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
-  __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
-  float* dKt = reinterpret_cast<float*>(w); w += up(rows * p.cq * D * 4);
-  int* status = reinterpret_cast<int*>(w);
+  using Cfg = DkvCfg<D, CQMAX, PAIR>;
+  const size_t BH = (size_t)p.B * p.H;
   alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV;
   if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR, false)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmdO, p.dO, D, p.N, BH, 64, Cfg::BR, true)) return cudaErrorInvalidValue;
@@ -993,13 +993,33 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   BwdTcParams bp = {};
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dV = p.dV; bp.dKt = dKt; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
-  auto kern = bwd_dkdv_tc_kernel<D>;
+  bp.tap0 = tap0; bp.ntap = ntap; bp.with_dv = with_dv;
+  auto kern = bwd_dkdv_tc_kernel<D, CQMAX, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((p.N + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream) {
+  constexpr int D = 64;
+  const size_t rows = (size_t)p.B * p.H * p.N, BH = (size_t)p.B * p.H;
+  auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+  unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
+  __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
+  float* dKt = reinterpret_cast<float*>(w); w += up(rows * p.cq * D * 4);
+  int* status = reinterpret_cast<int*>(w);
+  cudaError_t e;
   { ScopedKernelTimer timer_(kKernBwdDkdvTc, stream);
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp); }
-  e = cudaGetLastError();
+    if (p.cq <= 6) {
+      e = launch_dkdv_pass<6, true>(p, Kt, dKt, status, 0, p.cq, 1, stream);
+    } else {
+      // seven taps: dV + 7 accumulators + the scratch columns exceed the tensor memory, so the taps are
+      // split over two launches (each recomputes S^T and dP^T)
+      e = launch_dkdv_pass<7, false>(p, Kt, dKt, status, 0, 4, 1, stream);
+      if (e == cudaSuccess) e = launch_dkdv_pass<7, false>(p, Kt, dKt, status, 4, p.cq - 4, 0, stream);
+    } }
   if (e != cudaSuccess) return e;
   const int rpb = dk_post_rows_per_cta(p.ck);
   const int njb = (p.N + rpb - 1) / rpb;
@@ -1007,6 +1027,8 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   ScopedKernelTimer timer2_(kKernDkPost, stream);
   if (p.ck == 11)
     dk_post_window_kernel<D, 11, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
+  else if (p.ck == 7)
+    dk_post_window_kernel<D, 7, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
   else
     dk_post_kernel<D><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.ck, p.scale, njb);
   return cudaGetLastError();

@@ -532,16 +532,18 @@ cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t 
   ScopedKernelTimer timer_(kKernKtilde, stream);
   const size_t BH = (size_t)p.B * p.H;
   const float sc = p.scale * kLog2e;
-  if (p.ck == 11 && p.cq <= 16) {
+  if ((p.ck == 11 || p.ck == 7) && p.cq <= 16) {      // filter widths with a register-window instantiation
     constexpr int RR = 4;
     if (p.d == 64) {
       constexpr int RUNS = 256 / (64 / 8);
       dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);
-      ktilde_window_kernel<64, 11, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
+      if (p.ck == 11) ktilde_window_kernel<64, 11, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
+      else ktilde_window_kernel<64, 7, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
     } else {
       constexpr int RUNS = 256 / (128 / 8);
       dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);
-      ktilde_window_kernel<128, 11, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
+      if (p.ck == 11) ktilde_window_kernel<128, 11, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
+      else ktilde_window_kernel<128, 7, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
     }
     return cudaGetLastError();
   }

@@ -142,6 +142,9 @@ def test_rejects_bad_inputs():
     (1, 2, 257, 64, 1, 3, True),      # single query tap: band of 1
     (1, 1, 450, 64, 4, 7, True),
     (2, 1, 200, 64, 5, 9, True),
+    (1, 2, 900, 64, 7, 7, True),      # seven query taps: two launches of the dK/dV kernel (the reference's 7x7 filter)
+    (1, 1, 300, 64, 7, 17, True),     # largest filter of the tensor-core backward
+    (2, 1, 260, 64, 7, 11, False),
     (1, 1, 77, 64, 6, 11, True),      # exactly one band CTA
     (1, 1, 78, 64, 6, 11, True),      # one position into the second band CTA
     (1, 1, 333, 64, 2, 3, True),      # tiny filter, band of 2
