@@ -80,7 +80,13 @@ def ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr():
+    """torch's current stream on the current device, as the `cudaStream_t` the C ABI takes."""
+    if _raw_stream is not None:     # same handle as current_stream().cuda_stream, without building a Stream object
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -6,6 +6,14 @@ import torch
 from ._lib import lib, check, ptr, stream_ptr, require_cuda_bf16, as_f32
 
 
+def _split_outputs(B, H, k_splits, d, device):
+    """O_splits [B,H,k_splits,d], M_splits, L_splits [B,H,k_splits] carved out of one allocation."""
+    n = B * H * k_splits
+    buf = torch.empty(n * (d + 2), dtype=torch.float32, device=device)
+    return (buf[: n * d].view(B, H, k_splits, d), buf[n * d: n * (d + 1)].view(B, H, k_splits),
+            buf[n * (d + 1):].view(B, H, k_splits))
+
+
 def forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causal, num_k_blocks=None,
                       offset_causal=False):
     """(O_splits [B,H,k_splits,d], M_splits, L_splits [B,H,k_splits]) fp32 with the merged,
@@ -30,9 +38,7 @@ def forward_inference(Q, K, V, conv_kernel, k_splits, scale, pad_q, pad_k, causa
     if k_splits > Nk:
         raise RuntimeError("k_splits cannot be larger than seq_len_k")
     theta = as_f32(conv_kernel)
-    O = torch.empty((B, H, k_splits, d), dtype=torch.float32, device=Q.device)
-    M = torch.empty((B, H, k_splits), dtype=torch.float32, device=Q.device)
-    L = torch.empty_like(M)
+    O, M, L = _split_outputs(B, H, k_splits, d, Q.device)
     fn = lib.fmta_decode_offset_causal if offset_causal else lib.fmta_decode
     st = fn(ptr(Q), ptr(K), ptr(V), ptr(theta), ptr(O), ptr(M), ptr(L), B, H, q_len, Nk, d, cq, ck,
             int(k_splits), float(scale), stream_ptr())
@@ -78,9 +84,7 @@ def forward_inference_paged(Q, K_pool, V_pool, block_table, conv_kernel, k_split
     if pad_q != cq - 1 or pad_k != (ck - 1) // 2:
         raise RuntimeError("pad_q/pad_k must be (kx-1, (ky-1)//2)")
     theta = as_f32(conv_kernel)
-    O = torch.empty((B, H, k_splits, d), dtype=torch.float32, device=Q.device)
-    M = torch.empty((B, H, k_splits), dtype=torch.float32, device=Q.device)
-    L = torch.empty_like(M)
+    O, M, L = _split_outputs(B, H, k_splits, d, Q.device)
     st = lib.fmta_decode_paged(ptr(Q), ptr(K_pool), ptr(V_pool), ptr(block_table), ptr(seq_lens), ptr(theta), ptr(O),
                                ptr(M), ptr(L), B, H, q_len, Nk, d, cq, ck, int(k_splits), float(scale), page_size,
                                max_pages, int(bool(offset_causal)), stream_ptr())
