@@ -496,6 +496,8 @@ cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream) {
     return launch_kernel<TrainParams>(bwd_band_kernel<6, 11>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
   if (p.cq == 7 && p.ck == 7)
     return launch_kernel<TrainParams>(bwd_band_kernel<7, 7>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
+  if (p.cq == 3 && p.ck == 5)
+    return launch_kernel<TrainParams>(bwd_band_kernel<3, 5>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
   return launch_kernel<TrainParams>(bwd_band_kernel<0, 0>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
 }
 

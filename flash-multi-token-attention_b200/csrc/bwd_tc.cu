@@ -933,7 +933,7 @@ bool tensor_maps_available();
 cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream);
 
 // keys per CTA of the dKt adjoint kernel chosen for a filter width
-static int dk_post_rows_per_cta(int ck) { return (ck == 11 || ck == 7) ? 64 : 32; }   // window kernel : generic kernel
+static int dk_post_rows_per_cta(int ck) { return (ck == 11 || ck == 7 || ck == 5 || ck == 3) ? 64 : 32; }   // window kernel : generic kernel
 
 bool bwd_tc_supported(const TrainParams& p) {
   return p.theta != nullptr && p.Wmix == nullptr && p.d == 64 && p.cq >= 1 && p.cq <= 7 && tensor_maps_available();
@@ -1029,6 +1029,10 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
     dk_post_window_kernel<D, 11, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
   else if (p.ck == 7)
     dk_post_window_kernel<D, 7, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
+  else if (p.ck == 5)
+    dk_post_window_kernel<D, 5, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
+  else if (p.ck == 3)
+    dk_post_window_kernel<D, 3, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
   else
     dk_post_kernel<D><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.ck, p.scale, njb);
   return cudaGetLastError();

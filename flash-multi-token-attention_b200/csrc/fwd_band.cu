@@ -234,6 +234,8 @@ static cudaError_t launch_fwd_band_t(const TrainParams& p, cudaStream_t stream) 
     return launch_kernel<TrainParams>(fwd_band_kernel<D, 6, 11>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
   if (p.cq == 7 && p.ck == 7)
     return launch_kernel<TrainParams>(fwd_band_kernel<D, 7, 7>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
+  if (p.cq == 3 && p.ck == 5)
+    return launch_kernel<TrainParams>(fwd_band_kernel<D, 3, 5>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
   return launch_kernel<TrainParams>(fwd_band_kernel<D, 0, 0>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
 }
 

@@ -532,19 +532,18 @@ cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t 
   ScopedKernelTimer timer_(kKernKtilde, stream);
   const size_t BH = (size_t)p.B * p.H;
   const float sc = p.scale * kLog2e;
-  if ((p.ck == 11 || p.ck == 7) && p.cq <= 16) {      // filter widths with a register-window instantiation
+  if ((p.ck == 11 || p.ck == 7 || p.ck == 5 || p.ck == 3) && p.cq <= 16) {      // filter widths with a register-window instantiation
     constexpr int RR = 4;
+#define FMTA_KT_WIN(DD, CKK)                                                                                      \
+    { constexpr int RUNS = 256 / (DD / 8);                                                                        \
+      dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);                                               \
+      ktilde_window_kernel<DD, CKK, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc); }
     if (p.d == 64) {
-      constexpr int RUNS = 256 / (64 / 8);
-      dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);
-      if (p.ck == 11) ktilde_window_kernel<64, 11, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
-      else ktilde_window_kernel<64, 7, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
+      if (p.ck == 11) FMTA_KT_WIN(64, 11) else if (p.ck == 7) FMTA_KT_WIN(64, 7) else if (p.ck == 5) FMTA_KT_WIN(64, 5) else FMTA_KT_WIN(64, 3)
     } else {
-      constexpr int RUNS = 256 / (128 / 8);
-      dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);
-      if (p.ck == 11) ktilde_window_kernel<128, 11, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
-      else ktilde_window_kernel<128, 7, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc);
+      if (p.ck == 11) FMTA_KT_WIN(128, 11) else if (p.ck == 7) FMTA_KT_WIN(128, 7) else if (p.ck == 5) FMTA_KT_WIN(128, 5) else FMTA_KT_WIN(128, 3)
     }
+#undef FMTA_KT_WIN
     return cudaGetLastError();
   }
   if (p.d == 64) {
