@@ -48,7 +48,7 @@ struct BwdTcParams {
   const float* Dvec;  // [B,H,N]
   float* dQ;          // [B,H,N,D]   (dq kernel: overwritten)
   float* dV;          // [B,H,N,D]   (dkdv kernel: overwritten)
-  float* dKt;         // [B,H,cq,N,D] (dkdv kernel: overwritten)
+  bf16* dKt;          // [B,H,cq,N,D] bf16 (dkdv kernel: overwritten)
   int* status;
   int H, N, cq, ck, causal;
   // dK/dV kernel: the filter taps whose dKt this launch accumulates ([tap0, tap0 + ntap)) and whether it
@@ -425,7 +425,7 @@ template <int D, int CQMAX, bool PAIR>
 __global__ void __launch_bounds__(DkvCfg<D, CQMAX, PAIR>::kThreads, 1)
 bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmKt, const __grid_constant__ CUtensorMap tmV,
-                   const BwdTcParams p) {
+                   const __grid_constant__ CUtensorMap tmdKt, const BwdTcParams p) {
   using Cfg = DkvCfg<D, CQMAX, PAIR>;
   constexpr int BK = Cfg::BK, BR = Cfg::BR, HALO = Cfg::HALO, QR = Cfg::QR, NSTG = Cfg::NSTG;
   extern __shared__ unsigned char smem_raw[];
@@ -726,13 +726,32 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = 0.f;
       }
-      if (store) {
-        float* dst;
-        if (p.with_dv && acc == 0) dst = p.dV + ((size_t)bh * N + krow) * D + half * 32;
-        else dst = p.dKt + (((size_t)bh * cq + (p.tap0 + acc - (p.with_dv ? 1 : 0))) * N + krow) * D + half * 32;
+      if (p.with_dv && acc == 0) {
+        if (store) {
+          float* dst = p.dV + ((size_t)bh * N + krow) * D + half * 32;
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+        }
+      } else {
+        // dKt_a leaves as bf16 (its adjoint kernel feeds it to mma.sync as it is), through the shared
+        // memory of the Kt tiles, which no MMA reads any more: [128 keys][128 B] with the 128-byte
+        // swizzle, so that the lanes of a warp (one key row each) store without bank conflicts and the
+        // tile goes out as whole lines
+        const int row = qtr * 32 + lane;
+        unsigned char* tile = sKt + (acc - (p.with_dv ? 1 : 0)) * Cfg::KT_BYTES + row * 128;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(tile + (((half * 4 + i) ^ (row & 7)) << 4)) =
+              make_uint4(pack_bf16(o[8 * i], o[8 * i + 1]), pack_bf16(o[8 * i + 2], o[8 * i + 3]),
+                         pack_bf16(o[8 * i + 4], o[8 * i + 5]), pack_bf16(o[8 * i + 6], o[8 * i + 7]));
       }
+    }
+    tc::fence_proxy_async_smem();
+    tc::named_bar_sync(1, Cfg::kEwWarps * 32);
+    if (warp == 0 && tc::elect_one()) {
+      for (int t = 0; t < p.ntap; ++t) tc::tma_store_3d(&tmdKt, sKt + t * Cfg::KT_BYTES, 0, j0, bh * cq + p.tap0 + t);
+      tc::tma_store_commit();
+      tc::tma_store_wait_read();
     }
   }
   __syncwarp();
@@ -749,179 +768,171 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // ------------------------------------------------------------------------------------------
 // Adjoint of the Kt pre-pass:   dK[j] = sum_{a,b} scale*theta[a,b] * dKt_a[j - b + pad_k]
 //                      dTheta[a,b]   += scale * sum_j <dKt_a[j], k_{j+b-pad_k}>
-// One CTA per (32 keys, batch*head); dTheta leaves as one partial per CTA.
-template <int D>
-__global__ void __launch_bounds__(256) dk_post_kernel(const float* __restrict__ dKt, const bf16* __restrict__ K,
-                                                      const float* __restrict__ theta, float* __restrict__ dK,
-                                                      float* __restrict__ dTheta_part, int H, int N, int cq, int ck,
-                                                      float scale, int n_jblocks) {
-  constexpr int CPR = D / 8, RPB = 256 / CPR;
-  __shared__ float sTh[7 * 20];
-  __shared__ float sRed[8][7 * 17];
+// Both are small GEMMs on mma.sync, fed straight from the bf16 dKt_a rows in shared memory:
+//   dK tile (16 keys x 64) = sum_a T_a (16 x 32) X_a (32 rows x 64), T_a[x, r] = scale*theta[a, x + pad_k + 8 - r]
+//       the banded Toeplitz form of filter row a, held as a bf16 (hi, lo) pair so that theta keeps
+//       16 mantissa bits, X_a the dKt_a rows from 8 above the tile's first key on;
+//   dTheta (taps x filter columns) = A B with the contraction over (key, column) pairs:
+//       A[a, (j, d)] = dKt_a[j, d],  B[(j, d), b] = k_{j + b - pad_k}[d]  -- for a fixed key the 16
+//       contraction steps are 16 consecutive columns, so every fragment row is 32 contiguous bytes
+//       of shared memory and the products land in the accumulator already summed per (a, b).
+// One CTA per (64 keys, batch*head); dTheta leaves as one partial per CTA.
+#ifndef FMTA_DKPOST_THETA_LO
+#define FMTA_DKPOST_THETA_LO 1
+#endif
+constexpr bool kThetaLo = FMTA_DKPOST_THETA_LO != 0;
+struct DkPostCfg {
+  static constexpr int D = 64, NT = 256;
+  static constexpr int KEYS = 64, HALO = 8, ROWS = KEYS + 2 * HALO;   // c_k <= 17
+  static constexpr int LD = D + 8;                   // bf16 row stride (ldmatrix without bank conflicts)
+  static constexpr int XT = ROWS * LD + 8;           // elements per staged tap tile; + 16 bytes: the dTheta A fragments take one row per tap
+  static constexpr int T_LD = 40, T_ELEMS = 16 * T_LD;
+  static constexpr int RED_LD = 7 * 24;              // floats per warp in the dTheta reduction buffer
+  static constexpr int smem_bytes(int cq) {           // key rows + c_q tap tiles + max(Toeplitz tiles, reduction buffer)
+    return (cq + 1) * XT * 2 + (2 * cq * T_ELEMS * 2 > 8 * RED_LD * 4 ? 2 * cq * T_ELEMS * 2 : 8 * RED_LD * 4) + 7 * 17 * 4;
+  }
+};
+
+__global__ void __launch_bounds__(DkPostCfg::NT, 2) dk_post_mma_kernel(const bf16* __restrict__ dKt, const bf16* __restrict__ K,
+                                                                      const float* __restrict__ theta, float* __restrict__ dK,
+                                                                      float* __restrict__ dTheta_part, int H, int N, int cq,
+                                                                      int ck, float scale, int n_jblocks) {
+  using Cfg = DkPostCfg;
+  constexpr int D = Cfg::D, NT = Cfg::NT, KEYS = Cfg::KEYS, HALO = Cfg::HALO, ROWS = Cfg::ROWS, LD = Cfg::LD, XT = Cfg::XT;
+  constexpr int T_LD = Cfg::T_LD, T_ELEMS = Cfg::T_ELEMS, RED_LD = Cfg::RED_LD;
+  extern __shared__ __align__(16) unsigned char smem[];
+  bf16* sK = reinterpret_cast<bf16*>(smem);
+  bf16* sX = sK + XT;                                // [cq][ROWS][LD]
+  bf16* sThi = sX + cq * XT;                         // [cq][16][T_LD]
+  bf16* sTlo = sThi + cq * T_ELEMS;
+  float* sRed = reinterpret_cast<float*>(sThi);      // takes the place of the Toeplitz tiles once the dK GEMMs are done
   const int bh = blockIdx.y, h = bh % H, b = bh / H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < cq * ck; i += 256) sTh[(i / ck) * 20 + (i % ck)] = theta[(size_t)h * cq * ck + i] * scale;
-  __syncthreads();
-  const int j = blockIdx.x * RPB + tid / CPR, c = tid % CPR;
   const int pk = (ck - 1) / 2;
-  const bool valid = j < N;
-  float acc[8];
+  const int J0 = blockIdx.x * KEYS;
+
+  // one cp.async group per tap (the key rows travel with tap 0), always seven groups
+  load_rows_async<D, NT>(sK, LD, K + (size_t)bh * N * D, J0 - HALO, ROWS, N, tid);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  for (int a = 0; a < cq; ++a) {
-    const float* base = dKt + (((size_t)bh * cq + a) * N) * D + c * 8;
-    float own[8];   // dKt_a[j] chunk, for the dTheta term
+  for (int a = 0; a < 7; ++a) {
+    if (a < cq) load_rows_async<D, NT>(sX + a * XT, LD, dKt + ((size_t)bh * cq + a) * N * D, J0 - HALO, ROWS, N, tid);
+    cp_async_commit();
+  }
+  float* sTheta = reinterpret_cast<float*>(sTlo + cq * T_ELEMS);
+  if (tid < cq * ck) sTheta[tid] = theta[(size_t)h * cq * ck + tid] * scale;
+  __syncthreads();
+  for (int i = tid; i < cq * 16 * 32; i += NT) {
+    const int a = i >> 9, x = (i >> 5) & 15, r = i & 31;
+    const int bb = x + pk + HALO - r;
+    const float w = (bb >= 0 && bb < ck) ? sTheta[a * ck + bb] : 0.f;
+    const bf16 hi = __float2bfloat16_rn(w);
+    sThi[a * T_ELEMS + x * T_LD + r] = hi;
+    sTlo[a * T_ELEMS + x * T_LD + r] = __float2bfloat16_rn(w - __bfloat162float(hi));
+  }
+
+  // ---- dK: warp = (32 keys, 16 columns).  Its two 16-key tiles share the middle one of their three
+  // 16-row steps through X_a, and the Toeplitz fragments are the same for every tile ----
+  const int cgp = warp & 3, kh = warp >> 2;
+  float acc[2][2][4] = {};
+  {
+    const int l8 = lane & 7, q = lane >> 3;
+    const int t_off = (l8 + (q & 1) * 8) * T_LD + (q >> 1) * 8;
+    const int x_off = (32 * kh + l8 + (q & 1) * 8) * LD + 16 * cgp + (q >> 1) * 8;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) own[e] = 0.f;
-    if (valid) {
-      const float4 u0 = *reinterpret_cast<const float4*>(base + (size_t)j * D), u1 = *reinterpret_cast<const float4*>(base + (size_t)j * D + 4);
-      own[0] = u0.x; own[1] = u0.y; own[2] = u0.z; own[3] = u0.w; own[4] = u1.x; own[5] = u1.y; own[6] = u1.z; own[7] = u1.w;
-    }
-    for (int bb = 0; bb < ck; ++bb) {
-      // dK: source row j - bb + pk
-      const int js = j - bb + pk;
-      if (valid && js >= 0 && js < N) {
-        const float w = sTh[a * 20 + bb];
-        const float4 u0 = *reinterpret_cast<const float4*>(base + (size_t)js * D), u1 = *reinterpret_cast<const float4*>(base + (size_t)js * D + 4);
-        acc[0] = fmaf(w, u0.x, acc[0]); acc[1] = fmaf(w, u0.y, acc[1]); acc[2] = fmaf(w, u0.z, acc[2]); acc[3] = fmaf(w, u0.w, acc[3]);
-        acc[4] = fmaf(w, u1.x, acc[4]); acc[5] = fmaf(w, u1.y, acc[5]); acc[6] = fmaf(w, u1.z, acc[6]); acc[7] = fmaf(w, u1.w, acc[7]);
-      }
-      // dTheta[a,bb]: <dKt_a[j], k_{j+bb-pk}>
-      float t = 0.f;
-      const int jk = j + bb - pk;
-      if (valid && jk >= 0 && jk < N) {
-        const uint4 kv = *reinterpret_cast<const uint4*>(K + ((size_t)bh * N + jk) * D + c * 8);
-        const uint32_t w32[4] = {kv.x, kv.y, kv.z, kv.w};
+    for (int a = 0; a < 7; ++a) {
+      if (a < cq) {
+        cp_async_wait_dyn(6 - a);
+        __syncthreads();
+        uint32_t ah[2][4], al[2][4];
+        ldsm_x4(ah[0], sThi + a * T_ELEMS + t_off);
+        ldsm_x4(ah[1], sThi + a * T_ELEMS + t_off + 16);
+        if (kThetaLo) {
+          ldsm_x4(al[0], sTlo + a * T_ELEMS + t_off);
+          ldsm_x4(al[1], sTlo + a * T_ELEMS + t_off + 16);
+        }
+        const bf16* X = sX + a * XT + x_off;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          t = fmaf(own[2 * e], __uint_as_float(w32[e] << 16), t);
-          t = fmaf(own[2 * e + 1], __uint_as_float(w32[e] & 0xffff0000u), t);
+        for (int st = 0; st < 3; ++st) {
+          uint32_t bfr[4];
+          ldsm_x4_t(bfr, X + 16 * st * LD);
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            const int m = st - ks;                           // the tile whose step ks these rows are
+            if (m >= 0 && m < 2) {
+              mma_bf16(acc[m][0], ah[ks], bfr[0], bfr[1]);
+              mma_bf16(acc[m][1], ah[ks], bfr[2], bfr[3]);
+              if (kThetaLo) {
+                mma_bf16(acc[m][0], al[ks], bfr[0], bfr[1]);
+                mma_bf16(acc[m][1], al[ks], bfr[2], bfr[3]);
+              }
+            }
+          }
         }
       }
-      t = warp_sum(t);
-      if (lane == 0) sRed[warp][a * 17 + bb] = t;
     }
   }
-  if (valid) {
-    float* o = dK + ((size_t)bh * N + j) * D + c * 8;
-    *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  {
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int key = J0 + 32 * kh + 16 * m + g + 8 * hh;
+          if (key < N)
+            *reinterpret_cast<float2*>(dK + ((size_t)bh * N + key) * D + 16 * cgp + 8 * j + 2 * t4) = make_float2(acc[m][j][2 * hh], acc[m][j][2 * hh + 1]);
+        }
+  }
+
+  // ---- dTheta^T (filter columns x taps): warp = 8 keys, two 32-column contraction steps each ----
+  float th[2][2][4] = {};                                    // [16 filter columns][even / odd step]
+  {
+    const int l8 = lane & 7, q = lane >> 3;
+    const int m0 = l8 + (q & 1) * 8;                         // A fragment row = filter column (past c_k: column 0, unused results)
+    const int sA0 = (m0 < ck ? m0 : 0) - pk, sA1 = (m0 + 16 < ck ? m0 + 16 : 0) - pk;
+    const bf16* Bp = sX + (l8 < cq ? l8 : 0) * XT + q * 8;   // B fragment row = tap (past c_q: tap 0); four 8-column slabs
+    const bool wide = ck > 16;
+    for (int kk = 0; kk < 8; ++kk) {
+      const int row = HALO + 8 * warp + kk;                  // shared-memory row of this key
+#pragma unroll
+      for (int d0 = 0; d0 < D; d0 += 32) {
+        uint32_t bfr[4], a0[4], a1[4];
+        ldsm_x4(bfr, Bp + row * LD + d0);
+        ldsm_x4(a0, sK + (row + sA0) * LD + d0 + (q >> 1) * 8);
+        ldsm_x4(a1, sK + (row + sA0) * LD + d0 + 16 + (q >> 1) * 8);
+        mma_bf16(th[0][0], a0, bfr[0], bfr[1]);
+        mma_bf16(th[0][1], a1, bfr[2], bfr[3]);
+        if (wide) {
+          ldsm_x4(a0, sK + (row + sA1) * LD + d0 + (q >> 1) * 8);
+          ldsm_x4(a1, sK + (row + sA1) * LD + d0 + 16 + (q >> 1) * 8);
+          mma_bf16(th[1][0], a0, bfr[0], bfr[1]);
+          mma_bf16(th[1][1], a1, bfr[2], bfr[3]);
+        }
+      }
+    }
+  }
+  __syncthreads();                                           // every warp is done with the Toeplitz tiles
+  {
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int bb = 16 * m + 8 * hh + g, a = 2 * t4 + u;
+          if (a < cq && bb < 24) sRed[warp * RED_LD + a * 24 + bb] = th[m][0][2 * hh + u] + th[m][1][2 * hh + u];
+        }
   }
   __syncthreads();
   const int slot = b * n_jblocks + blockIdx.x;
-  for (int i = tid; i < cq * ck; i += 256) {
+  for (int i = tid; i < cq * ck; i += NT) {
     const int a = i / ck, bb = i % ck;
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) t += sRed[w][a * 17 + bb];
+    for (int w = 0; w < 8; ++w) t += sRed[w * RED_LD + a * 24 + bb];
     dTheta_part[((size_t)slot * H + h) * (cq * ck) + i] = t * scale;
-  }
-}
-
-// Same adjoint with the filter width known at compile time.  A CTA owns 64 keys; the dKt_a rows
-// it needs (64 + CK - 1, fp32) are staged in shared memory with cp.async, double-buffered over
-// the filter rows a, so the loads of tap a+1 overlap the arithmetic of tap a.  One thread owns a
-// 4-float column chunk of RR consecutive keys and keeps its RR + CK - 1 rows of dKt_a and of K
-// (bf16, read once from global memory) in registers; the dTheta terms are summed per thread over its rows and leave the warp through
-// one reduction per filter row.
-template <int D, int CK, int RR>
-__global__ void __launch_bounds__(256, 2) dk_post_window_kernel(const float* __restrict__ dKt, const bf16* __restrict__ K,
-                                                             const float* __restrict__ theta, float* __restrict__ dK,
-                                                             float* __restrict__ dTheta_part, int H, int N, int cq,
-                                                             float scale, int n_jblocks) {
-  constexpr int CPR = D / 4, RUNS = 256 / CPR, PK = (CK - 1) / 2, WIN = RR + CK - 1;
-  constexpr int ROWS = RUNS * RR, TR = ROWS + CK - 1;     // keys per CTA, rows staged
-  __shared__ __align__(16) float sT[2][TR * D];
-  __shared__ float sTh[7 * CK];
-  __shared__ float sRed[8][7 * CK];
-  const int bh = blockIdx.y, h = bh % H, b = bh / H;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int J0 = blockIdx.x * ROWS;
-  auto stage = [&](int a, int buf) {
-    const float* src = dKt + (((size_t)bh * cq + a) * N) * D;
-    for (int i = tid; i < TR * (D / 4); i += 256) {
-      const int r = i / (D / 4), ch = i % (D / 4);
-      const int jj = J0 - PK + r;
-      const bool ok = jj >= 0 && jj < N;
-      cp_async16(&sT[buf][r * D + ch * 4], src + (size_t)(ok ? jj : 0) * D + ch * 4, ok);
-    }
-  };
-  stage(0, 0);
-  cp_async_commit();
-  for (int i = tid; i < cq * CK; i += 256) sTh[i] = theta[(size_t)h * cq * CK + i] * scale;
-  const int run = tid / CPR, c = tid % CPR;
-  const int r0 = run * RR;                                 // first row of this thread inside the tile (before the halo shift)
-  float4 kw[WIN];                                          // the key rows of this thread's window, read and widened once
-#pragma unroll
-  for (int i = 0; i < WIN; ++i) {
-    const int jj = J0 - PK + r0 + i;
-    const uint2 kk = (jj >= 0 && jj < N) ? *reinterpret_cast<const uint2*>(K + ((size_t)bh * N + jj) * D + c * 4) : make_uint2(0u, 0u);
-    kw[i] = make_float4(__uint_as_float(kk.x << 16), __uint_as_float(kk.x & 0xffff0000u),
-                        __uint_as_float(kk.y << 16), __uint_as_float(kk.y & 0xffff0000u));
-  }
-  float dk[RR][4];
-#pragma unroll
-  for (int r = 0; r < RR; ++r) { dk[r][0] = dk[r][1] = dk[r][2] = dk[r][3] = 0.f; }
-  for (int a = 0; a < cq; ++a) {
-    if (a + 1 < cq) stage(a + 1, (a + 1) & 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-    const float* tile = sT[a & 1];
-    float4 dw[WIN];
-#pragma unroll
-    for (int i = 0; i < WIN; ++i) dw[i] = *reinterpret_cast<const float4*>(&tile[(r0 + i) * D + c * 4]);
-    float t[CK];
-#pragma unroll
-    for (int bb = 0; bb < CK; ++bb) {
-      const float w = sTh[a * CK + bb];
-      float tb = 0.f;
-#pragma unroll
-      for (int r = 0; r < RR; ++r) {
-        const float4 u = dw[r - bb + 2 * PK];            // dKt_a[j - bb + pad_k]
-        dk[r][0] = fmaf(w, u.x, dk[r][0]); dk[r][1] = fmaf(w, u.y, dk[r][1]);
-        dk[r][2] = fmaf(w, u.z, dk[r][2]); dk[r][3] = fmaf(w, u.w, dk[r][3]);
-        const float4 own = dw[r + PK];                   // dKt_a[j]
-        const float4 kk = kw[r + bb];                    // k_{j + bb - pad_k}
-        tb = fmaf(own.x, kk.x, tb);
-        tb = fmaf(own.y, kk.y, tb);
-        tb = fmaf(own.z, kk.z, tb);
-        tb = fmaf(own.w, kk.w, tb);
-      }
-      t[bb] = tb;
-    }
-    {
-      // reduce-scatter over the warp: 16 shuffles instead of 5 per value; afterwards the even lane
-      // 2 * i holds the warp total of value i
-      float v[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = i < CK ? t[i] : 0.f;
-#pragma unroll
-      for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
-        const bool up = (lane & bit) != 0;
-#pragma unroll
-        for (int i = 0; i < half; ++i) {
-          const float send = up ? v[i] : v[i + half];
-          const float keep = up ? v[i + half] : v[i];
-          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
-        }
-      }
-      const float tot = v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
-      const int idx = lane >> 1;                             // bits 4..1 of the lane select the value
-      if ((lane & 1) == 0 && idx < CK) sRed[warp][a * CK + idx] = tot;
-    }
-    __syncthreads();                                       // the buffer of tap a is staged again for tap a+2
-  }
-  const int j0 = J0 + r0;
-#pragma unroll
-  for (int r = 0; r < RR; ++r)
-    if (j0 + r < N) *reinterpret_cast<float4*>(dK + ((size_t)bh * N + j0 + r) * D + c * 4) = make_float4(dk[r][0], dk[r][1], dk[r][2], dk[r][3]);
-  const int slot = b * n_jblocks + blockIdx.x;
-  for (int i = tid; i < cq * CK; i += 256) {
-    float t = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) t += sRed[w][i];
-    dTheta_part[((size_t)slot * H + h) * (cq * CK) + i] = t * scale;
   }
 }
 
@@ -932,9 +943,6 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, s
 bool tensor_maps_available();
 cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream);
 
-// keys per CTA of the dKt adjoint kernel chosen for a filter width
-static int dk_post_rows_per_cta(int ck) { return (ck == 11 || ck == 7 || ck == 5 || ck == 3) ? 64 : 32; }   // window kernel : generic kernel
-
 bool bwd_tc_supported(const TrainParams& p) {
   return p.theta != nullptr && p.Wmix == nullptr && p.d == 64 && p.cq >= 1 && p.cq <= 7 && tensor_maps_available();
 }
@@ -942,8 +950,8 @@ bool bwd_tc_supported(const TrainParams& p) {
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq) {
   const size_t rows = (size_t)B * H * N;
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
-  // Kt (bf16) + dKt (fp32) + status
-  return up(rows * cq * d * 2) + up(rows * cq * d * 4) + 2048;
+  // Kt (bf16) + dKt (bf16) + status
+  return up(rows * cq * d * 2) + up(rows * cq * d * 2) + 2048;
 }
 
 cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t stream) {
@@ -953,7 +961,7 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
   __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
-  w += up(rows * p.cq * D * 4);
+  w += up(rows * p.cq * D * 2);
   int* status = reinterpret_cast<int*>(w);
   cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
   if (e != cudaSuccess) return e;
@@ -980,12 +988,13 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t
 
 // One launch of the dK/dV kernel for the taps [tap0, tap0 + ntap) (and dV).
 template <int CQMAX, bool PAIR>
-static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* Kt, float* dKt, int* status, int tap0,
+static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* Kt, __nv_bfloat16* dKt, int* status, int tap0,
                                     int ntap, int with_dv, cudaStream_t stream) {
   constexpr int D = 64;
   using Cfg = DkvCfg<D, CQMAX, PAIR>;
   const size_t BH = (size_t)p.B * p.H;
-  alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV;
+  alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV, tmdKt;
+  if (!make_tensor_map_bf16(&tmdKt, dKt, D, p.N, BH * p.cq, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR, false)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmdO, p.dO, D, p.N, BH, 64, Cfg::BR, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
@@ -998,7 +1007,7 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((p.N + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, tmdKt, bp);
   return cudaGetLastError();
 }
 
@@ -1008,7 +1017,7 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
   __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
-  float* dKt = reinterpret_cast<float*>(w); w += up(rows * p.cq * D * 4);
+  __nv_bfloat16* dKt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
   int* status = reinterpret_cast<int*>(w);
   cudaError_t e;
   { ScopedKernelTimer timer_(kKernBwdDkdvTc, stream);
@@ -1021,27 +1030,20 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
       if (e == cudaSuccess) e = launch_dkdv_pass<7, false>(p, Kt, dKt, status, 4, p.cq - 4, 0, stream);
     } }
   if (e != cudaSuccess) return e;
-  const int rpb = dk_post_rows_per_cta(p.ck);
-  const int njb = (p.N + rpb - 1) / rpb;
+  const int njb = (p.N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS;
   dim3 g2(njb, (unsigned)BH);
+  const int smem = DkPostCfg::smem_bytes(p.cq);
+  e = cudaFuncSetAttribute(dk_post_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
   ScopedKernelTimer timer2_(kKernDkPost, stream);
-  if (p.ck == 11)
-    dk_post_window_kernel<D, 11, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
-  else if (p.ck == 7)
-    dk_post_window_kernel<D, 7, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
-  else if (p.ck == 5)
-    dk_post_window_kernel<D, 5, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
-  else if (p.ck == 3)
-    dk_post_window_kernel<D, 3, 4><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.scale, njb);
-  else
-    dk_post_kernel<D><<<g2, 256, 0, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.ck, p.scale, njb);
+  dk_post_mma_kernel<<<g2, DkPostCfg::NT, smem, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.ck, p.scale, njb);
   return cudaGetLastError();
 }
 
 // slots of dTheta partials written by the dKt adjoint kernel: one per CTA
 int bwd_tc_theta_slots(int B, int N, int ck) {
-  const int rpb = dk_post_rows_per_cta(ck);
-  return B * ((N + rpb - 1) / rpb);
+  (void)ck;
+  return B * ((N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS);
 }
 
 #ifdef FMTA_TC_TRACE

@@ -32,6 +32,19 @@ FMTA_DEVINL void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+// wait until at most n (0..6) of this thread's cp.async groups are pending
+FMTA_DEVINL void cp_async_wait_dyn(int n) {
+  switch (n) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 3: cp_async_wait<3>(); break;
+    case 4: cp_async_wait<4>(); break;
+    case 5: cp_async_wait<5>(); break;
+    default: cp_async_wait<6>(); break;
+  }
+}
+
 // Copy rows [row0, row0+nrows) of a row-major [n_rows_total, D] bf16 matrix into shared
 // memory with row stride `ld` elements.  Rows outside [0, n_rows_total) become zero.
 template <int D, int NT>
