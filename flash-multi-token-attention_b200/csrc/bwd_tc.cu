@@ -37,7 +37,9 @@ __device__ long long g_trace_bwd[16384];
 #define TRACEE(slot) do { if (trace_on && tid == 0) g_trace_bwd[4096 + (slot)] = clock64(); } while (0)
 __device__ long long g_cta_times[3 * 8192];
 #define TRACEQ(slot) do { if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) g_trace_bwd[8192 + (slot)] = clock64(); } while (0)
+#define TRACEP(slot) do { if (blockIdx.x == 30 && (blockIdx.y == 5 || blockIdx.y == 40)) g_trace_bwd[12288 + (blockIdx.y == 40 ? 2048 : 0) + 16 * (threadIdx.x >> 5) + (slot)] = clock64(); } while (0)
 #else
+#define TRACEP(slot) do {} while (0)
 #define TRACEB(slot) do {} while (0)
 #define TRACEE(slot) do {} while (0)
 #define TRACEQ(slot) do {} while (0)
@@ -784,52 +786,82 @@ constexpr bool kThetaLo = FMTA_DKPOST_THETA_LO != 0;
 struct DkPostCfg {
   static constexpr int D = 64, NT = 256;
   static constexpr int KEYS = 64, HALO = 8, ROWS = KEYS + 2 * HALO;   // c_k <= 17
-  static constexpr int LD = D + 8;                   // bf16 row stride (ldmatrix without bank conflicts)
-  static constexpr int XT = ROWS * LD + 8;           // elements per staged tap tile; + 16 bytes: the dTheta A fragments take one row per tap
-  static constexpr int T_LD = 40, T_ELEMS = 16 * T_LD;
+  // A staged tile is [ROWS][128 B] as TMA writes it with the 128-byte swizzle: the 16-byte chunk c of
+  // a row sits at chunk c ^ (address bits 7..9).  Consecutive tiles start 128 bytes further along that
+  // pattern, so that the same row of the c_q tap tiles (one dTheta fragment) covers all banks.
+  static constexpr int TILE_BYTES = ROWS * 128;
+  static constexpr int TILE_STRIDE = TILE_BYTES + 128;
+  static constexpr int T_LD = 40, T_ELEMS = 16 * T_LD;        // one 16 x 32 Toeplitz tile (bf16), rows 80 bytes apart
   static constexpr int RED_LD = 7 * 24;              // floats per warp in the dTheta reduction buffer
-  static constexpr int smem_bytes(int cq) {           // key rows + c_q tap tiles + max(Toeplitz tiles, reduction buffer)
-    return (cq + 1) * XT * 2 + (2 * cq * T_ELEMS * 2 > 8 * RED_LD * 4 ? 2 * cq * T_ELEMS * 2 : 8 * RED_LD * 4) + 7 * 17 * 4;
+  __host__ __device__ static constexpr int t_bytes(int cq) { return 2 * cq * T_ELEMS * 2; }
+  static constexpr int smem_bytes(int cq) {           // alignment slack + key rows + c_q tap tiles + max(Toeplitz tiles, reduction buffer) + barriers
+    return 1024 + (cq + 1) * TILE_STRIDE + (t_bytes(cq) > 8 * RED_LD * 4 ? t_bytes(cq) : 8 * RED_LD * 4) + 64;
   }
 };
 
-__global__ void __launch_bounds__(DkPostCfg::NT, 2) dk_post_mma_kernel(const bf16* __restrict__ dKt, const bf16* __restrict__ K,
-                                                                      const float* __restrict__ theta, float* __restrict__ dK,
-                                                                      float* __restrict__ dTheta_part, int H, int N, int cq,
-                                                                      int ck, float scale, int n_jblocks) {
+// The Toeplitz tiles of every head, [H][c_q][hi, lo][16][T_LD] bf16: T[x, r] = scale * theta[a, x + pad_k + 8 - r].
+__global__ void dk_post_toeplitz_kernel(const float* __restrict__ theta, bf16* __restrict__ Tg, int cq, int ck, float scale) {
+  constexpr int T_LD = DkPostCfg::T_LD, T_ELEMS = DkPostCfg::T_ELEMS, HALO = DkPostCfg::HALO;
+  const int h = blockIdx.x, pk = (ck - 1) / 2;
+  for (int i = threadIdx.x; i < cq * 16 * T_LD; i += blockDim.x) {
+    const int a = i / (16 * T_LD), x = (i / T_LD) % 16, r = i % T_LD;
+    const int bb = x + pk + HALO - r;
+    const float w = (r < 32 && bb >= 0 && bb < ck) ? theta[((size_t)h * cq + a) * ck + bb] * scale : 0.f;
+    const bf16 hi = __float2bfloat16_rn(w);
+    bf16* dst = Tg + ((size_t)h * cq + a) * 2 * T_ELEMS + x * T_LD + r;
+    dst[0] = hi;
+    dst[T_ELEMS] = __float2bfloat16_rn(w - __bfloat162float(hi));
+  }
+}
+
+__global__ void __launch_bounds__(DkPostCfg::NT, 2)
+dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmX,
+                   const bf16* __restrict__ Tg, float* __restrict__ dK, float* __restrict__ dTheta_part, int* status,
+                   int H, int N, int cq, int ck, float scale, int n_jblocks) {
   using Cfg = DkPostCfg;
-  constexpr int D = Cfg::D, NT = Cfg::NT, KEYS = Cfg::KEYS, HALO = Cfg::HALO, ROWS = Cfg::ROWS, LD = Cfg::LD, XT = Cfg::XT;
+  constexpr int D = Cfg::D, NT = Cfg::NT, KEYS = Cfg::KEYS, HALO = Cfg::HALO;
   constexpr int T_LD = Cfg::T_LD, T_ELEMS = Cfg::T_ELEMS, RED_LD = Cfg::RED_LD;
-  extern __shared__ __align__(16) unsigned char smem[];
-  bf16* sK = reinterpret_cast<bf16*>(smem);
-  bf16* sX = sK + XT;                                // [cq][ROWS][LD]
-  bf16* sThi = sX + cq * XT;                         // [cq][16][T_LD]
-  bf16* sTlo = sThi + cq * T_ELEMS;
-  float* sRed = reinterpret_cast<float*>(sThi);      // takes the place of the Toeplitz tiles once the dK GEMMs are done
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // tile 0: key rows, tile 1 + a: dKt_a rows; row r of a tile is key J0 - HALO + r
+  unsigned char* sTb = smem + (cq + 1) * Cfg::TILE_STRIDE;
+  bf16* sT = reinterpret_cast<bf16*>(sTb);                  // [cq][hi, lo][16][T_LD]
+  float* sRed = reinterpret_cast<float*>(sTb);               // takes the place of the Toeplitz tiles once the dK GEMMs are done
+  const int t_or_red = Cfg::t_bytes(cq) > 8 * RED_LD * 4 ? Cfg::t_bytes(cq) : 8 * RED_LD * 4;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sTb + t_or_red);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2);
   const int bh = blockIdx.y, h = bh % H, b = bh / H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pk = (ck - 1) / 2;
   const int J0 = blockIdx.x * KEYS;
+  const int half = (cq + 1) / 2;                             // the taps arrive in two batches
+  // 16-byte chunk c of row r of tile t
+  auto at = [&](int t, int r, int c) -> const void* {
+    return smem + t * Cfg::TILE_STRIDE + r * 128 + (((c ^ (r + t)) & 7) << 4);
+  };
 
-  // one cp.async group per tap (the key rows travel with tap 0), always seven groups
-  load_rows_async<D, NT>(sK, LD, K + (size_t)bh * N * D, J0 - HALO, ROWS, N, tid);
-#pragma unroll
-  for (int a = 0; a < 7; ++a) {
-    if (a < cq) load_rows_async<D, NT>(sX + a * XT, LD, dKt + ((size_t)bh * cq + a) * N * D, J0 - HALO, ROWS, N, tid);
-    cp_async_commit();
+  TRACEP(0);
+  if (tid == 0) {
+    tc::tma_prefetch_desc(&tmK); tc::tma_prefetch_desc(&tmX);
+    tc::mbar_init(&bars[0], 1); tc::mbar_init(&bars[1], 1);
+    *s_abort = 0;
+    tc::mbar_fence_init();
   }
-  float* sTheta = reinterpret_cast<float*>(sTlo + cq * T_ELEMS);
-  if (tid < cq * ck) sTheta[tid] = theta[(size_t)h * cq * ck + tid] * scale;
   __syncthreads();
-  for (int i = tid; i < cq * 16 * 32; i += NT) {
-    const int a = i >> 9, x = (i >> 5) & 15, r = i & 31;
-    const int bb = x + pk + HALO - r;
-    const float w = (bb >= 0 && bb < ck) ? sTheta[a * ck + bb] : 0.f;
-    const bf16 hi = __float2bfloat16_rn(w);
-    sThi[a * T_ELEMS + x * T_LD + r] = hi;
-    sTlo[a * T_ELEMS + x * T_LD + r] = __float2bfloat16_rn(w - __bfloat162float(hi));
+  if (tid == 0) {
+    tc::mbar_expect_tx(&bars[0], (1 + half) * Cfg::TILE_BYTES + Cfg::t_bytes(cq));
+    tc::tma_load_3d(smem, &tmK, &bars[0], 0, J0 - HALO, bh);
+    tc::bulk_load(sTb, Tg + (size_t)h * cq * 2 * T_ELEMS, Cfg::t_bytes(cq), &bars[0]);
+    for (int a = 0; a < half; ++a) tc::tma_load_3d(smem + (a + 1) * Cfg::TILE_STRIDE, &tmX, &bars[0], 0, J0 - HALO, bh * cq + a);
+    if (cq > half) {
+      tc::mbar_expect_tx(&bars[1], (cq - half) * Cfg::TILE_BYTES);
+      for (int a = half; a < cq; ++a) tc::tma_load_3d(smem + (a + 1) * Cfg::TILE_STRIDE, &tmX, &bars[1], 0, J0 - HALO, bh * cq + a);
+    }
   }
+  TRACEP(1);
+  bool ok = true;
 
+  TRACEP(2);
   // ---- dK: warp = (32 keys, 16 columns).  Its two 16-key tiles share the middle one of their three
   // 16-row steps through X_a, and the Toeplitz fragments are the same for every tile ----
   const int cgp = warp & 3, kh = warp >> 2;
@@ -837,24 +869,25 @@ __global__ void __launch_bounds__(DkPostCfg::NT, 2) dk_post_mma_kernel(const bf1
   {
     const int l8 = lane & 7, q = lane >> 3;
     const int t_off = (l8 + (q & 1) * 8) * T_LD + (q >> 1) * 8;
-    const int x_off = (32 * kh + l8 + (q & 1) * 8) * LD + 16 * cgp + (q >> 1) * 8;
+    const int x_row = 32 * kh + l8 + (q & 1) * 8, x_chunk = 2 * cgp + (q >> 1);
 #pragma unroll
     for (int a = 0; a < 7; ++a) {
       if (a < cq) {
-        cp_async_wait_dyn(6 - a);
-        __syncthreads();
-        uint32_t ah[2][4], al[2][4];
-        ldsm_x4(ah[0], sThi + a * T_ELEMS + t_off);
-        ldsm_x4(ah[1], sThi + a * T_ELEMS + t_off + 16);
-        if (kThetaLo) {
-          ldsm_x4(al[0], sTlo + a * T_ELEMS + t_off);
-          ldsm_x4(al[1], sTlo + a * T_ELEMS + t_off + 16);
+        if (a == 0 || a == half) {
+          ok = ok && tc::mbar_wait(&bars[a == 0 ? 0 : 1], 0, s_abort);
+          if (a == 0) TRACEP(3); else TRACEP(4);
         }
-        const bf16* X = sX + a * XT + x_off;
+        uint32_t ah[2][4], al[2][4];
+        ldsm_x4(ah[0], sT + 2 * a * T_ELEMS + t_off);
+        ldsm_x4(ah[1], sT + 2 * a * T_ELEMS + t_off + 16);
+        if (kThetaLo) {
+          ldsm_x4(al[0], sT + (2 * a + 1) * T_ELEMS + t_off);
+          ldsm_x4(al[1], sT + (2 * a + 1) * T_ELEMS + t_off + 16);
+        }
 #pragma unroll
         for (int st = 0; st < 3; ++st) {
           uint32_t bfr[4];
-          ldsm_x4_t(bfr, X + 16 * st * LD);
+          ldsm_x4_t(bfr, at(a + 1, x_row + 16 * st, x_chunk));
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks) {
             const int m = st - ks;                           // the tile whose step ks these rows are
@@ -871,6 +904,7 @@ __global__ void __launch_bounds__(DkPostCfg::NT, 2) dk_post_mma_kernel(const bf1
       }
     }
   }
+  TRACEP(5);
   {
     const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
@@ -885,33 +919,37 @@ __global__ void __launch_bounds__(DkPostCfg::NT, 2) dk_post_mma_kernel(const bf1
         }
   }
 
+  TRACEP(6);
   // ---- dTheta^T (filter columns x taps): warp = 8 keys, two 32-column contraction steps each ----
-  float th[2][2][4] = {};                                    // [16 filter columns][even / odd step]
+  float th[2][4][4] = {};                                    // [16 filter columns][four independent accumulation chains]
   {
     const int l8 = lane & 7, q = lane >> 3;
     const int m0 = l8 + (q & 1) * 8;                         // A fragment row = filter column (past c_k: column 0, unused results)
     const int sA0 = (m0 < ck ? m0 : 0) - pk, sA1 = (m0 + 16 < ck ? m0 + 16 : 0) - pk;
-    const bf16* Bp = sX + (l8 < cq ? l8 : 0) * XT + q * 8;   // B fragment row = tap (past c_q: tap 0); four 8-column slabs
+    const int bt = 1 + (l8 < cq ? l8 : 0);                   // B fragment row = tap (past c_q: tap 0); four 8-column slabs
     const bool wide = ck > 16;
+#pragma unroll 2
     for (int kk = 0; kk < 8; ++kk) {
       const int row = HALO + 8 * warp + kk;                  // shared-memory row of this key
 #pragma unroll
-      for (int d0 = 0; d0 < D; d0 += 32) {
+      for (int c0 = 0; c0 < D / 8; c0 += 4) {
         uint32_t bfr[4], a0[4], a1[4];
-        ldsm_x4(bfr, Bp + row * LD + d0);
-        ldsm_x4(a0, sK + (row + sA0) * LD + d0 + (q >> 1) * 8);
-        ldsm_x4(a1, sK + (row + sA0) * LD + d0 + 16 + (q >> 1) * 8);
-        mma_bf16(th[0][0], a0, bfr[0], bfr[1]);
-        mma_bf16(th[0][1], a1, bfr[2], bfr[3]);
+        ldsm_x4(bfr, at(bt, row, c0 + q));
+        ldsm_x4(a0, at(0, row + sA0, c0 + (q >> 1)));
+        ldsm_x4(a1, at(0, row + sA0, c0 + 2 + (q >> 1)));
+        const int ch = (c0 >> 1) & 2;                        // chains 0, 1 for columns 0..31, 2, 3 for columns 32..63
+        mma_bf16(th[0][ch], a0, bfr[0], bfr[1]);
+        mma_bf16(th[0][ch + 1], a1, bfr[2], bfr[3]);
         if (wide) {
-          ldsm_x4(a0, sK + (row + sA1) * LD + d0 + (q >> 1) * 8);
-          ldsm_x4(a1, sK + (row + sA1) * LD + d0 + 16 + (q >> 1) * 8);
-          mma_bf16(th[1][0], a0, bfr[0], bfr[1]);
-          mma_bf16(th[1][1], a1, bfr[2], bfr[3]);
+          ldsm_x4(a0, at(0, row + sA1, c0 + (q >> 1)));
+          ldsm_x4(a1, at(0, row + sA1, c0 + 2 + (q >> 1)));
+          mma_bf16(th[1][ch], a0, bfr[0], bfr[1]);
+          mma_bf16(th[1][ch + 1], a1, bfr[2], bfr[3]);
         }
       }
     }
   }
+  TRACEP(7);
   __syncthreads();                                           // every warp is done with the Toeplitz tiles
   {
     const int g = lane >> 2, t4 = lane & 3;
@@ -922,10 +960,11 @@ __global__ void __launch_bounds__(DkPostCfg::NT, 2) dk_post_mma_kernel(const bf1
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int bb = 16 * m + 8 * hh + g, a = 2 * t4 + u;
-          if (a < cq && bb < 24) sRed[warp * RED_LD + a * 24 + bb] = th[m][0][2 * hh + u] + th[m][1][2 * hh + u];
+          if (a < cq && bb < 24) sRed[warp * RED_LD + a * 24 + bb] = (th[m][0][2 * hh + u] + th[m][1][2 * hh + u]) + (th[m][2][2 * hh + u] + th[m][3][2 * hh + u]);
         }
   }
   __syncthreads();
+  TRACEP(8);
   const int slot = b * n_jblocks + blockIdx.x;
   for (int i = tid; i < cq * ck; i += NT) {
     const int a = i / ck, bb = i % ck;
@@ -934,6 +973,7 @@ __global__ void __launch_bounds__(DkPostCfg::NT, 2) dk_post_mma_kernel(const bf1
     for (int w = 0; w < 8; ++w) t += sRed[w * RED_LD + a * 24 + bb];
     dTheta_part[((size_t)slot * H + h) * (cq * ck) + i] = t * scale;
   }
+  if (!ok) atomicExch(status, 1);
 }
 
 // ==========================================================================================
@@ -950,8 +990,8 @@ bool bwd_tc_supported(const TrainParams& p) {
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq) {
   const size_t rows = (size_t)B * H * N;
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
-  // Kt (bf16) + dKt (bf16) + status
-  return up(rows * cq * d * 2) + up(rows * cq * d * 2) + 2048;
+  // Kt (bf16) + dKt (bf16) + status + the Toeplitz tiles of the dKt adjoint
+  return up(rows * cq * d * 2) + up(rows * cq * d * 2) + 2048 + up((size_t)H * DkPostCfg::t_bytes(cq));
 }
 
 cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t stream) {
@@ -1035,8 +1075,13 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   const int smem = DkPostCfg::smem_bytes(p.cq);
   e = cudaFuncSetAttribute(dk_post_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
+  __nv_bfloat16* Tg = reinterpret_cast<__nv_bfloat16*>(w + 1024);   // status word first
+  alignas(64) CUtensorMap tmK, tmX;
+  if (!make_tensor_map_bf16(&tmK, p.K, D, p.N, BH, 64, DkPostCfg::ROWS, true)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmX, dKt, D, p.N, BH * p.cq, 64, DkPostCfg::ROWS, true)) return cudaErrorInvalidValue;
   ScopedKernelTimer timer2_(kKernDkPost, stream);
-  dk_post_mma_kernel<<<g2, DkPostCfg::NT, smem, stream>>>(dKt, p.K, p.theta, p.dK, dTheta_part_tc, p.H, p.N, p.cq, p.ck, p.scale, njb);
+  dk_post_toeplitz_kernel<<<p.H, 256, 0, stream>>>(p.theta, Tg, p.cq, p.ck, p.scale);
+  dk_post_mma_kernel<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb);
   return cudaGetLastError();
 }
 

@@ -69,6 +69,12 @@ FMTA_DEVINL void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* b
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// Contiguous copy global -> shared (both addresses and the size multiples of 16 bytes), completing on an mbarrier.
+FMTA_DEVINL void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 // Tile store shared -> global (bulk async-group).  c0 = 0 and c1 >= 0 at every call: a store must not
 // start at a negative coordinate; rows past the tensor's extent are clipped.
 FMTA_DEVINL void tma_store_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
