@@ -830,7 +830,8 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const int t_or_red = Cfg::t_bytes(cq) > 8 * RED_LD * 4 ? Cfg::t_bytes(cq) : 8 * RED_LD * 4;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sTb + t_or_red);
   volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2);
-  const int bh = blockIdx.y, h = bh % H, b = bh / H;
+  // last (batch, head) first: the dK/dV kernel wrote its dKt rows most recently, so they are still in L2
+  const int bh = gridDim.y - 1 - blockIdx.y, h = bh % H, b = bh / H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pk = (ck - 1) / 2;
   const int J0 = blockIdx.x * KEYS;
