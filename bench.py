@@ -315,10 +315,10 @@ def main():
     if kms:
         ach = 8.0 * d * E / (kms * 1e-3) / 1e12
         exe = 2.0 * d * (2 * cq + 2) * E / (kms * 1e-3) / 1e12
-        # DRAM bytes per launch from the committed ncu capture at B=2,H=16,N=4096 (152.2 MB read + 181.0 MB
+        # DRAM bytes per launch from the committed ncu capture at B=2,H=16,N=4096 (152.1 MB read + 89.3 MB
         # written; summary under profiles/), scaled by the (batch, head)
         # units; only quoted for that sequence length and head dimension
-        traffic = (152.18e6 + 181.01e6) * (B * H) / 32.0 if (N == 4096 and d == 64 and cq == 6) else None
+        traffic = (152.12e6 + 89.30e6) * (B * H) / 32.0 if (N == 4096 and d == 64 and cq == 6) else None
         roof = dict(bound="tensor", kernel=KERNELS[DOMINANT], achieved=ach, peak=peaks["tflops_sustained"],
                     unit="TFLOP/s", frac=ach / peaks["tflops_sustained"], peak_source=peaks["source"] + " (sustained)",
                     traffic=traffic, traffic_unit="bytes per launch (ncu capture of a smaller case, scaled)",
@@ -335,8 +335,8 @@ def main():
                             l2="inputs+outputs per step (%.0f MB) exceed the 126 MB L2" % ((4 * 2 + 4 * 4) * B * H * N * d / 1e6),
                             flops_attn_gflop=fl / 1e9, flops_conv_gflop=8 * cq * ck * E / 1e9),
                 # kernels of this library per step: forward = stacked-key pre-pass, fwd_tc, fwd_band; rowdot;
-                # backward = pre-pass, dq_tc, dkdv_tc, dKt adjoint, bwd_band, partial reduction
-                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=10 * args.steps)
+                # backward = pre-pass, dq_tc, dkdv_tc, Toeplitz tiles + dKt adjoint, bwd_band, partial reduction
+                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=11 * args.steps)
 
     # ---- decode (HBM-bound), rank-local, reported beside the headline ----
     if not args.no_decode:

@@ -814,11 +814,13 @@ __global__ void dk_post_toeplitz_kernel(const float* __restrict__ theta, bf16* _
   }
 }
 
+template <int CQ>   // taps at compile time (straight-line tap loop), or 0: read from the argument
 __global__ void __launch_bounds__(DkPostCfg::NT, 2)
 dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmX,
                    const bf16* __restrict__ Tg, float* __restrict__ dK, float* __restrict__ dTheta_part, int* status,
-                   int H, int N, int cq, int ck, float scale, int n_jblocks) {
+                   int H, int N, int cq_arg, int ck, float scale, int n_jblocks) {
   using Cfg = DkPostCfg;
+  const int cq = CQ > 0 ? CQ : cq_arg;
   constexpr int D = Cfg::D, NT = Cfg::NT, KEYS = Cfg::KEYS, HALO = Cfg::HALO;
   constexpr int T_LD = Cfg::T_LD, T_ELEMS = Cfg::T_ELEMS, RED_LD = Cfg::RED_LD;
   extern __shared__ unsigned char smem_raw[];
@@ -929,7 +931,7 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const int sA0 = (m0 < ck ? m0 : 0) - pk, sA1 = (m0 + 16 < ck ? m0 + 16 : 0) - pk;
     const int bt = 1 + (l8 < cq ? l8 : 0);                   // B fragment row = tap (past c_q: tap 0); four 8-column slabs
     const bool wide = ck > 16;
-#pragma unroll 2
+#pragma unroll 4
     for (int kk = 0; kk < 8; ++kk) {
       const int row = HALO + 8 * warp + kk;                  // shared-memory row of this key
 #pragma unroll
@@ -1074,7 +1076,8 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   const int njb = (p.N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS;
   dim3 g2(njb, (unsigned)BH);
   const int smem = DkPostCfg::smem_bytes(p.cq);
-  e = cudaFuncSetAttribute(dk_post_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  auto kern = p.cq == 6 ? dk_post_mma_kernel<6> : p.cq == 7 ? dk_post_mma_kernel<7> : p.cq == 3 ? dk_post_mma_kernel<3> : dk_post_mma_kernel<0>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   __nv_bfloat16* Tg = reinterpret_cast<__nv_bfloat16*>(w + 1024);   // status word first
   alignas(64) CUtensorMap tmK, tmX;
@@ -1082,7 +1085,7 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   if (!make_tensor_map_bf16(&tmX, dKt, D, p.N, BH * p.cq, 64, DkPostCfg::ROWS, true)) return cudaErrorInvalidValue;
   ScopedKernelTimer timer2_(kKernDkPost, stream);
   dk_post_toeplitz_kernel<<<p.H, 256, 0, stream>>>(p.theta, Tg, p.cq, p.ck, p.scale);
-  dk_post_mma_kernel<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb);
+  kern<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb);
   return cudaGetLastError();
 }
 
