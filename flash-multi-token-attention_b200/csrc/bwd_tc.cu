@@ -814,13 +814,11 @@ __global__ void dk_post_toeplitz_kernel(const float* __restrict__ theta, bf16* _
   }
 }
 
-template <int CQ>   // taps at compile time (straight-line tap loop), or 0: read from the argument
 __global__ void __launch_bounds__(DkPostCfg::NT, 2)
 dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmX,
                    const bf16* __restrict__ Tg, float* __restrict__ dK, float* __restrict__ dTheta_part, int* status,
-                   int H, int N, int cq_arg, int ck, float scale, int n_jblocks) {
+                   int H, int N, int cq, int ck, float scale, int n_jblocks) {
   using Cfg = DkPostCfg;
-  const int cq = CQ > 0 ? CQ : cq_arg;
   constexpr int D = Cfg::D, NT = Cfg::NT, KEYS = Cfg::KEYS, HALO = Cfg::HALO;
   constexpr int T_LD = Cfg::T_LD, T_ELEMS = Cfg::T_ELEMS, RED_LD = Cfg::RED_LD;
   extern __shared__ unsigned char smem_raw[];
@@ -1076,7 +1074,7 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   const int njb = (p.N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS;
   dim3 g2(njb, (unsigned)BH);
   const int smem = DkPostCfg::smem_bytes(p.cq);
-  auto kern = p.cq == 6 ? dk_post_mma_kernel<6> : p.cq == 7 ? dk_post_mma_kernel<7> : p.cq == 3 ? dk_post_mma_kernel<3> : dk_post_mma_kernel<0>;
+  auto kern = dk_post_mma_kernel;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   __nv_bfloat16* Tg = reinterpret_cast<__nv_bfloat16*>(w + 1024);   // status word first
