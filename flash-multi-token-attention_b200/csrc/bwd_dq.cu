@@ -50,6 +50,40 @@ __global__ void rowdot_kernel(const bf16* __restrict__ dO, const void* __restric
   if (lane == 0) Dv[row] = t;
 }
 
+// The same with TPR = d / 8 threads per row, 16 bytes of dO (and 16 or 32 of O) per thread: one load
+// instruction per operand and thread, 256 / TPR rows per block.
+template <bool O_BF16, int TPR>
+__global__ void __launch_bounds__(256) rowdot_vec_kernel(const bf16* __restrict__ dO, const void* __restrict__ O,
+                                                         float* __restrict__ Dv, size_t rows) {
+  constexpr int D = TPR * 8;
+  const size_t row = (size_t)blockIdx.x * (256 / TPR) + threadIdx.x / TPR;
+  const int c = (threadIdx.x % TPR) * 8;
+  float t = 0.f;
+  if (row < rows) {
+    const uint4 g = *reinterpret_cast<const uint4*>(dO + row * D + c);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+    float o[8];
+    if (O_BF16) {
+      const uint4 ov = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(O) + row * D + c);
+      const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { o[2 * e] = __uint_as_float(ow[e] << 16); o[2 * e + 1] = __uint_as_float(ow[e] & 0xffff0000u); }
+    } else {
+      const float4 o0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(O) + row * D + c);
+      const float4 o1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(O) + row * D + c + 4);
+      o[0] = o0.x; o[1] = o0.y; o[2] = o0.z; o[3] = o0.w; o[4] = o1.x; o[5] = o1.y; o[6] = o1.z; o[7] = o1.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      t = fmaf(__uint_as_float(gw[e] << 16), o[2 * e], t);
+      t = fmaf(__uint_as_float(gw[e] & 0xffff0000u), o[2 * e + 1], t);
+    }
+  }
+#pragma unroll
+  for (int off = TPR / 2; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+  if (row < rows && c == 0) Dv[row] = t;
+}
+
 template <int D, int CQ, int CK>
 static cudaError_t launch_bwd_dq_t(const TrainParams& p, cudaStream_t stream) {
   const int own = 64;
@@ -84,6 +118,17 @@ cudaError_t launch_reduce_partials(const float* part, float* out, int n_slots, i
 }
 
 cudaError_t launch_rowdot(const void* dO, const void* O, int o_bf16, float* Dv, size_t rows, int d, cudaStream_t stream) {
+  const bf16* g = reinterpret_cast<const bf16*>(dO);
+#define FMTA_ROWDOT(TPR)                                                                                   \
+  { const unsigned nb = (unsigned)((rows + 256 / TPR - 1) / (256 / TPR));                                  \
+    if (o_bf16) rowdot_vec_kernel<true, TPR><<<nb, 256, 0, stream>>>(g, O, Dv, rows);                      \
+    else rowdot_vec_kernel<false, TPR><<<nb, 256, 0, stream>>>(g, O, Dv, rows);                            \
+    return cudaGetLastError(); }
+  const bool al = (reinterpret_cast<uintptr_t>(dO) % 16 == 0) && (reinterpret_cast<uintptr_t>(O) % 16 == 0);
+  if (al && d == 64) FMTA_ROWDOT(8)
+  if (al && d == 128) FMTA_ROWDOT(16)
+  if (al && d == 32) FMTA_ROWDOT(4)
+#undef FMTA_ROWDOT
   const unsigned blocks = (unsigned)((rows + 7) / 8);
   if (o_bf16) rowdot_kernel<true><<<blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(dO), O, Dv, rows, d);
   else rowdot_kernel<false><<<blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(dO), O, Dv, rows, d);
