@@ -5,7 +5,7 @@
 //     C = sum_a Q^(a) Kt_a^T,   P = exp2(C - LSE*log2e),   dP = dO V^T,   dC = P * (dP - D)
 //     dQ[i'] = ln2 * sum_a sum_j dC[i' + pad_q - a, j] Kt_a[j]
 //     dKt_a  = dC^T Q^(a)  (gradient w.r.t. Kt_a / (scale*log2e) ... i.e. before the pre-pass scaling)     dV = P^T dO
-// and dK / dTheta follow from dKt_a by the adjoint of the pre-pass (dk_post_kernel).
+// and dK / dTheta follow from dKt_a by the adjoint of the pre-pass (dk_post_mma_kernel).
 // The band entries are handled by bwd_band_kernel (bwd_band.cu), which adds its part to the same
 // outputs afterwards.
 //
@@ -774,10 +774,11 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 //   dK tile (16 keys x 64) = sum_a T_a (16 x 32) X_a (32 rows x 64), T_a[x, r] = scale*theta[a, x + pad_k + 8 - r]
 //       the banded Toeplitz form of filter row a, held as a bf16 (hi, lo) pair so that theta keeps
 //       16 mantissa bits, X_a the dKt_a rows from 8 above the tile's first key on;
-//   dTheta (taps x filter columns) = A B with the contraction over (key, column) pairs:
-//       A[a, (j, d)] = dKt_a[j, d],  B[(j, d), b] = k_{j + b - pad_k}[d]  -- for a fixed key the 16
-//       contraction steps are 16 consecutive columns, so every fragment row is 32 contiguous bytes
+//   dTheta^T (filter columns x taps) = A B with the contraction over (key, column) pairs:
+//       A[b, (j, d)] = k_{j + b - pad_k}[d],  B[(j, d), a] = dKt_a[j, d]  -- for a fixed key the 16
+//       contraction steps are 16 consecutive columns, so every fragment row is 16 contiguous bytes
 //       of shared memory and the products land in the accumulator already summed per (a, b).
+// The rows are staged by TMA (two mbarrier batches, bounded waits), the Toeplitz tiles by one bulk copy.
 // One CTA per (64 keys, batch*head); dTheta leaves as one partial per CTA.
 #ifndef FMTA_DKPOST_THETA_LO
 #define FMTA_DKPOST_THETA_LO 1
