@@ -149,6 +149,11 @@ def test_rejects_bad_inputs():
     (1, 1, 78, 64, 6, 11, True),      # one position into the second band CTA
     (1, 1, 333, 64, 2, 3, True),      # tiny filter, band of 2
     (1, 1, 1500, 64, 6, 11, True),    # many key blocks per tile
+    (1, 1, 63, 64, 6, 11, True),      # one key short of the 64-key tile of the dK~ adjoint kernel
+    (1, 1, 64, 64, 6, 11, True),      # exactly one tile
+    (1, 2, 65, 64, 6, 11, True),      # one key into the second tile: its halo rows are mostly past the end
+    (1, 2, 129, 64, 7, 17, True),     # the same with the widest filter (halo of 8 rows fully used)
+    (1, 1, 130, 64, 1, 3, False),     # one tap, no band
 ])
 def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
     """fmta_bwd with the exact kernels (path 0) and with the stacked-GEMM tensor-core kernels plus
