@@ -58,12 +58,6 @@ inline int bwd_band_positions(int cq, int ck) {
   return r < bandcfg::RC ? r : bandcfg::RC;
 }
 
-#ifdef FMTA_TC_TRACE
-__device__ long long g_trace_band[16];
-#define TRACEK(slot) do { if (blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_trace_band[(slot)] = clock64(); } while (0)
-#else
-#define TRACEK(slot) do {} while (0)
-#endif
 
 template <int CQ, int CK>   // filter shape at compile time, or (0, 0): read from the parameters
 __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainParams p) {
@@ -100,7 +94,6 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   const bf16* Vg = p.V + bh * (size_t)N * D;
   const bf16* dOg = p.dO + bh * (size_t)N * D;
 
-  TRACEK(0);
   load_rows_async<D, NT>(sQ, LD, Qg, t0 - 16, RS, N, tid);
   load_rows_async<D, NT>(sK, LD, Kg, t0 - 48, RK, N, tid);
   load_rows_async<D, NT>(sV, LD, Vg, t0 - 16, RS, N, tid);
@@ -116,7 +109,6 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   }
   cp_async_wait<0>();
   __syncthreads();
-  TRACEK(1);
 
   // ---- Sb and dPb on 16 x 16 tiles along the diagonal ----
   {
@@ -157,12 +149,10 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
     }
   }
   __syncthreads();
-  TRACEK(2);
 
   // ---- the padded dC rows take over the V buffer ----
   for (int i = tid; i < RC * DC_LD; i += NT) sdC[i] = 0.f;
   __syncthreads();
-  TRACEK(3);
 
   // ---- conv, P and dC ----
   if constexpr (CQ > 0) {
@@ -250,7 +240,6 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
     }
   }
   __syncthreads();
-  TRACEK(4);
 
   // ---- dTheta ----
   if constexpr (CQ > 0) {
@@ -306,7 +295,6 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
     }
     sRed[tid] = t0s + t1s;
   }
-  TRACEK(5);
   if (mma_out) {      // Sb is dead now: its place takes the two dense arrangements of dS
     __syncthreads();
     for (int i = tid; i < 2 * RC * A_LD / 2; i += NT) reinterpret_cast<uint32_t*>(sAQ)[i] = 0u;
@@ -393,7 +381,6 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
     }
   }
   __syncthreads();
-  TRACEK(6);
   {
     const int ntaps = cq * ck;
     if (tid < ntaps) {
@@ -404,7 +391,6 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
       p.dTheta_part[((size_t)slot * H + h) * ntaps + tid] = t;
     }
   }
-  TRACEK(7);
 
   if (mma_out) {
     // ---- dQ, dK, dV on mma.sync: 16 positions x 32 head dims per job, accumulating onto the values in memory ----
@@ -472,14 +458,8 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
       if (two) { *reinterpret_cast<float2*>(gb) = aq1; *reinterpret_cast<float2*>(gb + kofs) = ak1; *reinterpret_cast<float2*>(gb + vofs) = av1; }
     }
   }
-  TRACEK(8);
 }
 
-#ifdef FMTA_TC_TRACE
-extern "C" int fmta_debug_trace_band(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace_band, sizeof(long long) * n);
-}
-#endif
 
 int bwd_band_theta_slots(int B, int N, int cq, int ck) {
   const int R = bwd_band_positions(cq, ck);

@@ -31,19 +31,6 @@ namespace fmta {
 
 constexpr float kLn2 = 0.6931471805599453f;
 
-#ifdef FMTA_TC_TRACE
-__device__ long long g_trace_bwd[16384];
-#define TRACEB(slot) do { if (trace_on) g_trace_bwd[(slot)] = clock64(); } while (0)
-#define TRACEE(slot) do { if (trace_on && tid == 0) g_trace_bwd[4096 + (slot)] = clock64(); } while (0)
-__device__ long long g_cta_times[3 * 8192];
-#define TRACEQ(slot) do { if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0) g_trace_bwd[8192 + (slot)] = clock64(); } while (0)
-#define TRACEP(slot) do { if (blockIdx.x == 30 && (blockIdx.y == 5 || blockIdx.y == 40)) g_trace_bwd[12288 + (blockIdx.y == 40 ? 2048 : 0) + 16 * (threadIdx.x >> 5) + (slot)] = clock64(); } while (0)
-#else
-#define TRACEP(slot) do {} while (0)
-#define TRACEB(slot) do {} while (0)
-#define TRACEE(slot) do {} while (0)
-#define TRACEQ(slot) do {} while (0)
-#endif
 
 struct BwdTcParams {
   const float* LSE;   // [B,H,N] natural log
@@ -56,6 +43,7 @@ struct BwdTcParams {
   // dK/dV kernel: the filter taps whose dKt this launch accumulates ([tap0, tap0 + ntap)) and whether it
   // accumulates dV as well; seven taps do not fit the tensor memory at once and take two launches
   int tap0, ntap, with_dv;
+  int selftest_expire;   // failure-detection self-test: the element-wise warps' first wait is on a barrier nothing arrives at
 };
 
 // ==========================================================================================
@@ -106,14 +94,13 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* s_free = sdp_full + 2;       // [NT][2] S buffer b and dP of a block taken into registers (128 arrivals)
   uint64_t* dc_full = s_free + 4;        // [NT] dC tile written to shared memory (128 arrivals)
   uint64_t* dq_done = dc_full + 2;       // [NT] dQ MMAs of the block complete (dC buffer reusable)
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(dq_done + 2);
+  uint64_t* never_bar = dq_done + 2;     // nothing arrives here (expiry self-test)
+  uint64_t* mma_drain = never_bar + 1;   // abort path: every issuer's MMAs have completed (2 NT arrivals)
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(mma_drain + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  volatile int* s_issued = s_abort + 1;  // ring tiles the producer has issued
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef FMTA_TC_TRACE
-  long long cta_t0 = 0;
-  if (tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t0));
-#endif
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
   const int band = pq + pk;
   const int rows_per_cta = OWN * NT;
@@ -147,7 +134,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc::mbar_init(&dq_done[i], 1);
     }
     for (int i = 0; i < 4; ++i) tc::mbar_init(&s_free[i], BM);
-    *s_abort = 0;
+    tc::mbar_init(never_bar, 1); tc::mbar_init(mma_drain, 2 * NT);
+    *s_abort = 0; *s_issued = 0;
     tc::mbar_fence_init();
   }
   if (warp == NT * 4 + 1) {
@@ -180,6 +168,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc::mbar_expect_tx(&full[slot], Cfg::TILE_BYTES);
         tc::tma_load_3d(sRing + slot * Cfg::TILE_BYTES, map, &full[slot], 0, y, z);
         ++id;
+        *s_issued = id;
       };
       for (int kb = 0; kb < nkb && ok; ++kb) {
         for (int a = 0; a < cq && ok; ++a) put(&tmKt, kb * BC, bh * cq + a);
@@ -211,13 +200,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!is_dq) {
         for (int kb = 0; kb < nkb && ok; ++kb) {
           const bool active = kb < my_nkb;
-          if (t == 0) TRACEQ(kb * 8 + 0);
           const uint32_t tSb = tS + 64 * (kb & 1);
           if (active && kb > 1) {      // the element-wise warps have taken S(kb-2) out of this buffer
             ok = tc::mbar_wait_warp(&s_free[2 * t + (kb & 1)], ((kb >> 1) - 1) & 1, s_abort);
             tc::tc_fence_after();
           }
-          if (t == 0) TRACEQ(kb * 8 + 1);
           for (int a = 0; a < cq && ok; ++a) {
             const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
             if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
@@ -249,17 +236,14 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
           tc::mma_commit_e(&empty[slot]);
           if (active) tc::mma_commit_e(&sdp_full[t]);
-          if (t == 0) TRACEQ(kb * 8 + 2);
         }
       } else {
         for (int kb = 0; kb < nkb && ok; ++kb) {
           const bool active = kb < my_nkb;
-          if (t == 0) TRACEQ(kb * 8 + 3);
           if (active) {
             ok = tc::mbar_wait_warp(&dc_full[t], kb & 1, s_abort);
             tc::tc_fence_after();
           }
-          if (t == 0) TRACEQ(kb * 8 + 4);
           for (int a = 0; a < cq && ok; ++a) {
             const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
             if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
@@ -281,7 +265,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (tc::elect_one()) tc::mbar_arrive(&empty[slot]);
           }
           if (active) tc::mma_commit_e(&dq_done[t]);
-          if (t == 0) TRACEQ(kb * 8 + 5);
         }
       }
     }
@@ -299,11 +282,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     unsigned char* cbuf = sdC + t * ((BC / 8) * DR * 16) + m * 16;
     bool ok = true;
     for (int kb = 0; kb < my_nkb && ok; ++kb) {
-      if (tid == 0) TRACEQ(1024 + kb * 8 + 0);
-      ok = __all_sync(0xffffffffu, tc::mbar_wait(&sdp_full[t], kb & 1, s_abort));
+      ok = __all_sync(0xffffffffu, (p.selftest_expire && kb == 0)
+                                       ? tc::mbar_wait(never_bar, 0, s_abort, tc::kSelfTestSpinLimit)
+                                       : tc::mbar_wait(&sdp_full[t], kb & 1, s_abort));
       if (!ok) break;
       tc::tc_fence_after();
-      if (tid == 0) TRACEQ(1024 + kb * 8 + 1);
       float s[BC], dp[BC];
       {
         float t0[32], t1[32], t2[32], t3[32];
@@ -316,7 +299,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       tc::tc_fence_before();
       tc::mbar_arrive(&s_free[2 * t + (kb & 1)]);
-      if (tid == 0) TRACEQ(1024 + kb * 8 + 2);
       const int j0 = kb * BC;
       const int jlim = row_ok ? (p.causal ? min(N - 1, gi - band) : N - 1) : -1;   // last key owned here
       uint32_t pk32[BC / 2];
@@ -337,18 +319,15 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           pk32[i / 2] = pack_bf16(c0, c1);
         }
       }
-      if (tid == 0) TRACEQ(1024 + kb * 8 + 3);
       if (kb > 0) {   // dQ(kb-1) has finished reading the dC buffer
         ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (kb - 1) & 1, s_abort));
         if (!ok) break;
       }
-      if (tid == 0) TRACEQ(1024 + kb * 8 + 4);
 #pragma unroll
       for (int kc = 0; kc < BC / 8; ++kc)
         *reinterpret_cast<uint4*>(cbuf + kc * (DR * 16)) = make_uint4(pk32[4 * kc], pk32[4 * kc + 1], pk32[4 * kc + 2], pk32[4 * kc + 3]);
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(&dc_full[t]);
-      if (tid == 0) TRACEQ(1024 + kb * 8 + 5);
     }
     // ---- epilogue: the 112 owned dQ rows of this tile ----
     if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (my_nkb - 1) & 1, s_abort));
@@ -376,16 +355,21 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   tc::tc_fence_before();
   __syncthreads();
-#ifdef FMTA_TC_TRACE
-  if (tid == 0) {
-    long long cta_t1; unsigned smid;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t1));
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    const int cid = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-    if (cid < 8192) { g_cta_times[3 * cid] = cta_t0; g_cta_times[3 * cid + 1] = cta_t1; g_cta_times[3 * cid + 2] = smid; }
+  if (*s_abort) {
+    if (tid == 0) atomicExch(p.status, 1);
+    // nothing of this CTA may still be in flight when its shared and tensor memory are given up: every
+    // issuer commits behind its last MMA; one thread waits (bounded) for those commits, for the Q / dO
+    // copies and for the latest copy issued into each ring slot
+    if (warp > NT * 4) tc::mma_commit_e(mma_drain);
+    if (tid == NT * 4 * 32 && nkb > 0) {
+      volatile int never = 0;
+      tc::mbar_wait(q_full, 0, &never);
+      const int issued = *s_issued;
+      for (int id = max(0, issued - NSLOT); id < issued; ++id) tc::mbar_wait(&full[id % NSLOT], (id / NSLOT) & 1, &never);
+    }
+    if (tid == NT * 4 * 32) { volatile int never = 0; tc::mbar_wait(mma_drain, 0, &never); }
+    __syncthreads();
   }
-#endif
-  if (*s_abort && tid == 0) atomicExch(p.status, 1);
   if (warp == NT * 4 + 1) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, Cfg::kTmemCols);
@@ -446,8 +430,11 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* pdc_full = xd_free + 1;      // P^T and dC^T (bf16) written to shared memory (256 arrivals)
   uint64_t* pdc_free = pdc_full + 1;     // the dV / dKt MMAs that read them have completed
   uint64_t* all_done = pdc_free + 1;
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(all_done + 1);
+  uint64_t* never_bar = all_done + 1;    // nothing arrives here (expiry self-test)
+  uint64_t* mma_drain = never_bar + 1;   // abort path: every issuer's MMAs have completed (3 arrivals)
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(mma_drain + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  volatile int* s_issued = s_abort + 1;  // stages the producer has issued
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
@@ -468,7 +455,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc::mbar_init(dpt_full, 1); tc::mbar_init(xd_free, Cfg::kEwWarps * 32);
     tc::mbar_init(pdc_full, Cfg::kEwWarps * 32); tc::mbar_init(pdc_free, 2);
     tc::mbar_init(all_done, 2);
-    *s_abort = 0;
+    tc::mbar_init(never_bar, 1); tc::mbar_init(mma_drain, 3);
+    *s_abort = 0; *s_issued = 0;
     tc::mbar_fence_init();
   }
   if (warp == Cfg::kEwWarps + 1) {
@@ -480,9 +468,6 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc::tc_fence_after();
   const uint32_t tmem = *s_tmem;
   const uint32_t tX = tmem + Cfg::colX;
-#ifdef FMTA_TC_TRACE
-  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
-#endif
 
   if (warp == Cfg::kEwWarps) {
     // ===================== producer warp (TMA + row statistics) =====================
@@ -518,6 +503,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           for (int cp = 0; cp < (PAIR ? 2 : 1); ++cp)
             for (int kc = 0; kc < D / 8; ++kc)
               tc::tma_load_3d(sg + Cfg::sgQ + (cp * (D / 8) + kc) * (QR * 16), &tmQ, &full[st], kc * 8, i0 - HALO + cp, bh);
+          *s_issued = it + 1;
         }
       }
     }
@@ -551,10 +537,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
         const uint64_t dQk = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);   // K-major, N = rows
         const uint32_t qk_hi = (uint32_t)(dQk >> 32), qk_lo = (uint32_t)dQk;
-        TRACEB(it * 8 + 0);
         if (!tc::mbar_wait_warp(xd_free, it & 1, s_abort)) { ok = false; break; }   // dP^T(it) has left X
         tc::tc_fence_after();
-        TRACEB(it * 8 + 1);
         // S^T = sum_a Kt_a Q^(a)T
         for (int a = 0; a < cq; ++a) {
           const uint32_t a_lo = kt_lo + (uint32_t)(a * (Cfg::KT_BYTES >> 4));
@@ -566,12 +550,9 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         tc::mma_commit_e(st_full);
         tc::mma_commit_e(&empty[st]);        // this issuer's reads of the stage (dO for dP^T, Q for S^T) are done then
-        TRACEB(it * 8 + 2);
         if (!tc::mbar_wait_warp(xs_free, it & 1, s_abort)) { ok = false; break; }   // S^T(it) has left X
         tc::tc_fence_after();
-        TRACEB(it * 8 + 4);
         if (it + 1 < nblk) issue_dPT(it + 1);
-        TRACEB(it * 8 + 5);
       }
     }
   } else if (warp >= Cfg::kEwWarps + 2) {
@@ -634,7 +615,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     bool ok = true;
     float dpc[CW];                                      // dP^T of the block about to be processed
     if (nblk > 0) {
-      ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, 0, s_abort));
+      ok = __all_sync(0xffffffffu, p.selftest_expire ? tc::mbar_wait(never_bar, 0, s_abort, tc::kSelfTestSpinLimit)
+                                                     : tc::mbar_wait(dpt_full, 0, s_abort));
       if (ok) {
         tc::tc_fence_after();
         tc::tmem_ldn(tXl, dpc);
@@ -648,11 +630,9 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const float* ld = reinterpret_cast<const float*>(sStage + st * Cfg::STAGE_BYTES + Cfg::sgLD) + CW * cg;
       ok = __all_sync(0xffffffffu, tc::mbar_wait(&full[st], ph, s_abort));
       if (!ok) break;
-      TRACEE(it * 8 + 0);
       ok = __all_sync(0xffffffffu, tc::mbar_wait(st_full, it & 1, s_abort));
       if (!ok) break;
       tc::tc_fence_after();
-      TRACEE(it * 8 + 1);
       float s[CW];
       tc::tmem_ldn(tXl, s);
       tc::tc_fence_before();
@@ -660,7 +640,6 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // take the next block's dP^T out of X right away, so that its S^T can start while this
       // block's arithmetic runs
       float dpn[CW];
-      TRACEE(it * 8 + 2);
       if (it + 1 < nblk) {
         ok = __all_sync(0xffffffffu, tc::mbar_wait(dpt_full, (it + 1) & 1, s_abort));
         if (!ok) break;
@@ -669,7 +648,6 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc::tc_fence_before();
         tc::mbar_arrive(xd_free);
       }
-      TRACEE(it * 8 + 3);
       // P^T[key, i] = exp2(S^T - LSE_i), kept only where this kernel owns the entry; dC^T = P^T (dP^T - D_i)
       uint32_t pp[CW / 2], cc[CW / 2];
       if ((j0 + BK <= N) && (i0 + BR <= N) && (!p.causal || j0 + BK - 1 + band <= i0)) {   // block owned entirely
@@ -693,12 +671,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
 #pragma unroll
       for (int c = 0; c < CW; ++c) dpc[c] = dpn[c];
-      TRACEE(it * 8 + 4);
       if (it > 0) {   // the MMAs of block it-1 have finished reading the P^T / dC^T buffers
         ok = __all_sync(0xffffffffu, tc::mbar_wait(pdc_free, (it - 1) & 1, s_abort));
         if (!ok) break;
       }
-      TRACEE(it * 8 + 5);
       {
         unsigned char* pt = smem + Cfg::oPT + (qtr * 32 + lane) * 16;
         unsigned char* dc = smem + Cfg::oDCT + (qtr * 32 + lane) * 16;
@@ -710,7 +686,6 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(pdc_full);
-      TRACEE(it * 8 + 6);
     }
     // ---- epilogue: dV and dKt_a rows of this key; 14 chunks of 32 columns dealt round-robin to the column groups ----
     if (nblk > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(all_done, 0, s_abort));
@@ -760,7 +735,21 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   tc::tc_fence_before();
   __syncthreads();
-  if (*s_abort && tid == 0) atomicExch(p.status, 1);
+  if (*s_abort) {
+    if (tid == 0) atomicExch(p.status, 1);
+    // as in the dQ kernel: MMAs and copies of this CTA are waited for (bounded) before its memories go
+    if (warp > Cfg::kEwWarps) tc::mma_commit_e(mma_drain);
+    if (tid == Cfg::kEwWarps * 32) {
+      volatile int never = 0;
+      if (nblk > 0) {
+        tc::mbar_wait(kv_full, 0, &never);
+        const int issued = *s_issued;
+        for (int it = max(0, issued - NSTG); it < issued; ++it) tc::mbar_wait(&full[it % NSTG], (it / NSTG) & 1, &never);
+      }
+      tc::mbar_wait(mma_drain, 0, &never);
+    }
+    __syncthreads();
+  }
   if (warp == Cfg::kEwWarps + 1) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, Cfg::kTmemCols);
@@ -842,7 +831,6 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     return smem + t * Cfg::TILE_STRIDE + r * 128 + (((c ^ (r + t)) & 7) << 4);
   };
 
-  TRACEP(0);
   if (tid == 0) {
     tc::tma_prefetch_desc(&tmK); tc::tma_prefetch_desc(&tmX);
     tc::mbar_init(&bars[0], 1); tc::mbar_init(&bars[1], 1);
@@ -860,10 +848,8 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       for (int a = half; a < cq; ++a) tc::tma_load_3d(smem + (a + 1) * Cfg::TILE_STRIDE, &tmX, &bars[1], 0, J0 - HALO, bh * cq + a);
     }
   }
-  TRACEP(1);
   bool ok = true;
 
-  TRACEP(2);
   // ---- dK: warp = (32 keys, 16 columns).  Its two 16-key tiles share the middle one of their three
   // 16-row steps through X_a, and the Toeplitz fragments are the same for every tile ----
   const int cgp = warp & 3, kh = warp >> 2;
@@ -877,7 +863,6 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       if (a < cq) {
         if (a == 0 || a == half) {
           ok = ok && tc::mbar_wait(&bars[a == 0 ? 0 : 1], 0, s_abort);
-          if (a == 0) TRACEP(3); else TRACEP(4);
         }
         uint32_t ah[2][4], al[2][4];
         ldsm_x4(ah[0], sT + 2 * a * T_ELEMS + t_off);
@@ -906,7 +891,6 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
     }
   }
-  TRACEP(5);
   {
     const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
@@ -921,7 +905,6 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
   }
 
-  TRACEP(6);
   // ---- dTheta^T (filter columns x taps): warp = 8 keys, two 32-column contraction steps each ----
   float th[2][4][4] = {};                                    // [16 filter columns][four independent accumulation chains]
   {
@@ -951,7 +934,6 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
     }
   }
-  TRACEP(7);
   __syncthreads();                                           // every warp is done with the Toeplitz tiles
   {
     const int g = lane >> 2, t4 = lane & 3;
@@ -966,7 +948,6 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
   }
   __syncthreads();
-  TRACEP(8);
   const int slot = b * n_jblocks + blockIdx.x;
   for (int i = tid; i < cq * ck; i += NT) {
     const int a = i / ck, bb = i % ck;
@@ -1017,6 +998,7 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t
   BwdTcParams bp = {};
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dQ = p.dQ; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
+  bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
   auto kern = bwd_dq_tc_kernel<D>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
@@ -1045,6 +1027,7 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dV = p.dV; bp.dKt = dKt; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.tap0 = tap0; bp.ntap = ntap; bp.with_dv = with_dv;
+  bp.selftest_expire = take_selftest_expire(kKernBwdDkdvTc);
   auto kern = bwd_dkdv_tc_kernel<D, CQMAX, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
@@ -1085,7 +1068,9 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   ScopedKernelTimer timer2_(kKernDkPost, stream);
   dk_post_toeplitz_kernel<<<p.H, 256, 0, stream>>>(p.theta, Tg, p.cq, p.ck, p.scale);
   kern<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb);
-  return cudaGetLastError();
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  return launch_fold_status(status, stream);
 }
 
 // slots of dTheta partials written by the dKt adjoint kernel: one per CTA
@@ -1094,13 +1079,5 @@ int bwd_tc_theta_slots(int B, int N, int ck) {
   return B * ((N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS);
 }
 
-#ifdef FMTA_TC_TRACE
-extern "C" int fmta_debug_cta_times(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_cta_times, sizeof(long long) * n);
-}
-extern "C" int fmta_debug_trace_bwd(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace_bwd, sizeof(long long) * n);
-}
-#endif
 
 }  // namespace fmta

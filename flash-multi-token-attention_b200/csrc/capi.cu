@@ -38,7 +38,34 @@ int check_train_dims(int B, int H, int N, int d, int cq, int ck, int G, bool has
 
 }  // namespace
 
-namespace fmta { ProfileHook g_profile_hook = {0, nullptr, nullptr}; }
+namespace {
+constexpr int kMaxDevices = 64;
+int* g_status_word[kMaxDevices] = {};   // caller-owned device word per device (fmta_set_status_word)
+int g_selftest_kernel = 0;              // kernel id whose next launch runs the expiry self-test
+
+__global__ void fold_status_kernel(const int* __restrict__ status, int* __restrict__ sink) {
+  if (*status != 0) atomicOr(sink, *status);
+}
+}  // namespace
+
+namespace fmta {
+ProfileHook g_profile_hook = {0, nullptr, nullptr};
+
+cudaError_t launch_fold_status(const int* status, cudaStream_t stream) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaSuccess;
+  int* sink = g_status_word[dev];
+  if (sink == nullptr) return cudaSuccess;
+  fold_status_kernel<<<1, 1, 0, stream>>>(status, sink);
+  return cudaGetLastError();
+}
+
+int take_selftest_expire(int kernel_id) {
+  if (g_selftest_kernel != kernel_id) return 0;
+  g_selftest_kernel = 0;
+  return 1;
+}
+}  // namespace fmta
 
 extern "C" {
 
@@ -53,6 +80,7 @@ const char* fmta_strerror(int status) {
     case FMTA_ERR_ALIGN: return "a tensor pointer is not 16-byte aligned";
     case FMTA_ERR_WORKSPACE: return "workspace missing or too small (see fmta_workspace_bytes)";
     case FMTA_ERR_CUDA: return "the CUDA runtime rejected a launch (see fmta_last_cuda_error)";
+    case FMTA_ERR_DEVICE_WAIT: return "a bounded wait inside a tensor-core kernel ran out (device status word set); the outputs of that call are invalid";
     case FMTA_ERR_SCRATCH_LIMIT: return "problem too large for the built-in 4 MiB scratch of fmta_bwd_dq_dw_static; use fmta_bwd_dq_dw with a workspace";
     default: return "unknown status";
   }
@@ -71,8 +99,23 @@ int fmta_profile_kernel(int kernel_id, void* start_event, void* stop_event) {
 
 int fmta_set_path(int path) {
   const int old = g_path;
-  if (path >= -1 && path <= 2) g_path = path;
+  if (path >= -1 && path <= 1) g_path = path;
   return old;
+}
+
+int fmta_set_status_word(int* device_word) {
+  int dev = -1;
+  if (int s = check_cuda(cudaGetDevice(&dev))) return s;
+  if (dev < 0 || dev >= kMaxDevices) return FMTA_ERR_SHAPE;
+  g_status_word[dev] = device_word;
+  return FMTA_OK;
+}
+
+int fmta_selftest_expire_next(int kernel_id) {
+  if (kernel_id != 0 && kernel_id != kKernFwdTc && kernel_id != kKernBwdDqTc && kernel_id != kKernBwdDkdvTc)
+    return FMTA_ERR_UNSUPPORTED;
+  g_selftest_kernel = kernel_id;
+  return FMTA_OK;
 }
 
 size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, int G) {

@@ -55,7 +55,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) decode_kernel(const DecodeP
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int Nk = (PAGED && p.seq_lens) ? p.seq_lens[b] : p.Nk;
+  // a per-sequence length comes from device memory the caller may have left stale: clamp it to the range the
+  // block table (and the shared-memory copy of its row) was sized for
+  const int Nk = (PAGED && p.seq_lens) ? min(max(p.seq_lens[b], 1), p.Nk) : p.Nk;
   const int cq = p.cq, ck = p.ck, pk = (ck - 1) / 2;
   const int rows = min(p.q_len, cq);          // query rows that the last output row sees
   const size_t bh = (size_t)b * p.H + h;
@@ -279,6 +281,7 @@ __global__ void kv_append_paged_kernel(bf16* __restrict__ Kpool, bf16* __restric
   if (idx >= n_new * CPR) return;
   const int r = idx / CPR, c = idx % CPR;
   const int pos = seq_lens[b] + r;
+  if (pos < 0 || (pos >> page_shift) >= max_pages) return;   // past the block table: the row is dropped, nothing is written
   const int pg = block_table[(size_t)b * max_pages + (pos >> page_shift)], in = pos & (page_size - 1);
   const size_t dst = (((size_t)pg * H + h) * page_size + in) * D + c * 8;
   const size_t src = (((size_t)b * H + h) * n_new + r) * D + c * 8;

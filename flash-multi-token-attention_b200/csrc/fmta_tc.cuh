@@ -38,14 +38,17 @@ FMTA_DEVINL bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // CTA's abort flag) and returns false; the caller then leaves its loop and the kernel tears
 // down normally.  No trap, no endless spin.
 constexpr uint32_t kSpinLimit = 1u << 22;
-FMTA_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+FMTA_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
 }
+// Poll limit of the wait that the expiry self-test makes run out: it waits on a barrier nothing
+// ever arrives at, so a few hundred polls are enough to prove the point.
+constexpr uint32_t kSelfTestSpinLimit = 256;
 
 // ---------------------------------------------------------------- fences
 FMTA_DEVINL void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

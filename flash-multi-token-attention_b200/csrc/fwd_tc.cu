@@ -32,12 +32,6 @@
 
 namespace fmta {
 
-#ifdef FMTA_TC_TRACE
-__device__ long long g_trace[16384];
-#define TRACE(slot) do { if (trace_on) g_trace[(slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot) do {} while (0)
-#endif
 
 // ------------------------------------------------------------------------------------------
 // Kt[bh, a, j, :] = scale * sum_b theta[h, a, b] * K[bh, j + b - pad_k, :]   (bf16, zero beyond ends)
@@ -135,6 +129,7 @@ struct TcParams {
   float* Lpart;
   int* status;    // device word: set non-zero when a bounded wait expired
   int H, N, cq, ck, causal;
+  int selftest_expire;   // failure-detection self-test: the softmax warps' first wait is on a barrier nothing arrives at
 };
 
 // One CTA owns NT row tiles of 128 query rows (one softmax warpgroup and one TMEM lane per row);
@@ -188,7 +183,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint64_t* s_free = s_full + 2;         // [NT]  S[t] loaded into registers (128 arrivals)
   uint64_t* p_full = s_free + 2;         // [NT]  P[t] written to tensor memory (128 arrivals)
   uint64_t* o_full = p_full + 2;         // [NT]  PV(t, kb) completed
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(o_full + 2);
+  uint64_t* never_bar = o_full + 2;      // nothing arrives here (expiry self-test)
+  uint64_t* mma_drain = never_bar + 1;   // abort path: every issuer's MMAs have completed (NT arrivals)
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(mma_drain + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   volatile int* s_issued = s_abort + 1;
   volatile int* s_consumed = s_abort + 2;
@@ -218,13 +215,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     } else nkb_t[t] = nKB;
   }
   const int nkb = max(nkb_t[0], nkb_t[1]);
-#ifdef FMTA_TC_TRACE
-  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
-#endif
 
   if (tid == 0) {
     for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], NT); }   // every MMA warp releases a slot
     tc::mbar_init(q_full, 1);
+    tc::mbar_init(never_bar, 1); tc::mbar_init(mma_drain, NT);
     for (int i = 0; i < 2; ++i) { tc::mbar_init(&s_full[i], 1); tc::mbar_init(&s_free[i], BM); tc::mbar_init(&p_full[i], BM); tc::mbar_init(&o_full[i], 1); }
     *s_abort = 0; *s_issued = 0; *s_consumed = 0;
     tc::mbar_fence_init();
@@ -338,11 +333,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       };
       if (ok) issue_S(0);
       for (int kb = 0; kb < nkb && ok; ++kb) {
-        if (t == 0) TRACE(8192 + kb * 4 + 0);
         if (kb + 1 < nkb) issue_S(kb + 1);
-        if (t == 0) TRACE(8192 + kb * 4 + 1);
         if (ok) issue_PV(kb);
-        if (t == 0) TRACE(8192 + kb * 4 + 2);
       }
       if (t == 0) *s_consumed = id;
     }
@@ -360,8 +352,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     float m_true = -INFINITY;                           // true row max (m_run lags it by up to tau)
     bool ok = true;
     for (int kb = 0; kb < my_nkb && ok; ++kb) {
-      if (tid == 0) TRACE(kb * 8 + 0);
-      ok = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[t], kb & 1, s_abort));
+      ok = __all_sync(0xffffffffu, (p.selftest_expire && kb == 0)
+                                       ? tc::mbar_wait(never_bar, 0, s_abort, tc::kSelfTestSpinLimit)
+                                       : tc::mbar_wait(&s_full[t], kb & 1, s_abort));
       if (!ok) break;   // warp-uniform: the TMEM accesses below are warp-collective
       tc::tc_fence_after();
       float s[BC];
@@ -376,7 +369,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // S[t] is in registers: let the MMA warp overwrite it with the next key block
       tc::tc_fence_before();
       tc::mbar_arrive(&s_free[t]);
-      if (tid == 0) TRACE(kb * 8 + 1);
       const int j0 = kb * BC;
       // mask: keys past N, and (causal) entries on or above the band, which the band kernel owns
       const int jlim = p.causal ? min(N - 1, gi - band) : N - 1;   // last key this row may see here
@@ -413,7 +405,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         pk32[i / 2] = pack_bf16(p0, p1); pk32[i / 2 + 1] = pack_bf16(p2, p3);
       }
       l_run = l_run * alpha + (sum0 + sum1);
-      if (tid == 0) TRACE(kb * 8 + 2);
       if (kb > 0) {
         // PV(kb-1) complete: P[t] may be overwritten and O touched.  Waited for on every block
         // (not only when O is rescaled) so that the parity wait never aliases an older phase.
@@ -421,7 +412,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (!ok) break;
         tc::tc_fence_after();
       }
-      if (tid == 0) TRACE(kb * 8 + 3);
       if (__any_sync(0xffffffffu, need)) {   // O *= alpha (need is false on the first block)
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -442,7 +432,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tc::tmem_wait_st();
       tc::tc_fence_before();
       tc::mbar_arrive(&p_full[t]);
-      if (tid == 0) TRACE(kb * 8 + 5);
     }
     // ---- epilogue: un-normalised partial row ----
     if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (my_nkb - 1) & 1, s_abort));
@@ -478,9 +467,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   if (*s_abort) {
     if (tid == 0) atomicExch(p.status, 1);
-    if (tid == NT * 4 * 32) {   // drain copies that were issued but never consumed, with a bounded wait
+    // nothing of this CTA may still be in flight when its shared and tensor memory are given up: every
+    // issuer commits behind its last MMA, one thread waits (bounded) for those commits and for the
+    // copies that were issued but never consumed
+    if (warp > NT * 4) tc::mma_commit_e(mma_drain);
+    if (tid == NT * 4 * 32) {
       volatile int never = 0;
       for (int id = *s_consumed; id < *s_issued; ++id) tc::mbar_wait(&full[id % NSLOT], (id / NSLOT) & 1, &never);
+      tc::mbar_wait(mma_drain, 0, &never);
     }
     __syncthreads();
   }
@@ -576,6 +570,7 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
   TcParams tp;
   tp.Opart = Opart; tp.Mpart = Mpart; tp.Lpart = Lpart; tp.status = status;
   tp.H = p.H; tp.N = p.N; tp.cq = p.cq; tp.ck = p.ck; tp.causal = p.causal;
+  tp.selftest_expire = take_selftest_expire(kKernFwdTc);
   auto kern = fwd_tc_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
@@ -615,13 +610,9 @@ cudaError_t launch_fwd_tc(const TrainParams& p, void* workspace, const float** O
   if (p.d == 64) e = launch_tc_t<64>(p, Kt, Op, Mp, Lp, status, stream);
   else e = launch_tc_t<128>(p, Kt, Op, Mp, Lp, status, stream);
   *Opart = Op; *Mpart = Mp; *Lpart = Lp;
-  return e;
+  if (e != cudaSuccess) return e;
+  return launch_fold_status(status, stream);
 }
 
-#ifdef FMTA_TC_TRACE
-extern "C" int fmta_debug_trace(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n);
-}
-#endif
 
 }  // namespace fmta

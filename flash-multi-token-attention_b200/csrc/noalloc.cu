@@ -53,11 +53,28 @@ extern "C" int fmta_bwd_dq_dw_static(const void* Q, const void* K, const void* V
                                      const float* wmix, float* dQ, float* dTheta, float* dW, int B,
                                      int H, int N, int d, int cq, int ck, int G, float scale,
                                      int causal, void* stream) {
-  // Size check first, so an over-limit problem is rejected before anything touches the device.
-  if (B < 1 || H < 1 || N < 1 || cq < 1 || ck < 1 || G < 1) return FMTA_ERR_SHAPE;
-  const size_t need = fmta_workspace_bytes(FMTA_OP_BWD_DQ, B, H, N, d, theta ? cq : 1, theta ? ck : 1,
-                                           wmix ? G : 1);
+  // Range checks first (the same ones fmta_bwd_dq_dw applies), so that the size below is computed from
+  // sane values; the filter shape and the group size only count when theta / wmix are given.
+  if (B < 1 || H < 1 || N < 1 || B > 65535 || H > 65535) return FMTA_ERR_SHAPE;
+  if (theta && (cq < 1 || ck < 1)) return FMTA_ERR_SHAPE;
+  if (theta && (cq > 16 || ck > 17 || (ck % 2) == 0)) return FMTA_ERR_UNSUPPORTED;
+  if (wmix) {
+    if (G < 1) return FMTA_ERR_SHAPE;
+    if (G != 2 && G != 4 && G != 8 && G != 16) return FMTA_ERR_UNSUPPORTED;
+    if (H % G != 0) return FMTA_ERR_SHAPE;
+  }
+  // Scratch is needed only for the filter / mixing gradients; an over-limit problem is rejected before
+  // anything touches the device.
+  size_t need = 0;
+  if (theta || wmix) {
+    const size_t slots = (size_t)B * (size_t)((N + 63) / 64);
+    if (theta) need += slots * (size_t)H * (size_t)cq * (size_t)ck * sizeof(float);
+    if (wmix) need += slots * (size_t)H * (size_t)G * sizeof(float);
+  }
   if (need > FMTA_STATIC_SCRATCH_BYTES) return FMTA_ERR_SCRATCH_LIMIT;
+  if (need == 0)   // no partial sums to keep: the plain entry point needs no workspace either
+    return fmta_bwd_dq_dw(Q, K, V, dO, D, LSE, theta, wmix, dQ, dTheta, dW, B, H, N, d, cq, ck, G, scale, causal,
+                          nullptr, 0, stream);
   float* scratch = nullptr;
   if (int s = scratch_for_current_device(&scratch)) return s;
   // Every partial slot is overwritten by the CTA that owns it before the reduction reads it, so

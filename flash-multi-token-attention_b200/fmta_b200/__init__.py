@@ -6,7 +6,7 @@ Same operator API as the reference package (``ConvAttentionCUDA``,
 ``HeadConvAttention``, ``head_conv_attention``), backed by hand-written sm_100a CUDA behind a
 C ABI (libfmta_b200.so).  Importing fails if the library has not been built.
 """
-from ._lib import lib as _c_lib, LIB_PATH  # noqa: F401  (raises ImportError when missing)
+from ._lib import lib as _c_lib, LIB_PATH, check_device_status  # noqa: F401  (raises ImportError when missing)
 from .conv_attn import (ConvAttentionCUDA, FlashConvAttentionCUDAFunction, forward, dq_backward,  # noqa: F401
                         dkdv_backward, backward, rowdot)
 from .inference import (forward_inference, fwd_conv_attn_inference, forward_inference_paged,  # noqa: F401

@@ -62,7 +62,12 @@ lib.fmta_decode_paged.argtypes = [_vp, _vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _
 lib.fmta_kv_append_paged.restype = _i
 lib.fmta_kv_append_paged.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]
 
-EXPORTS = ["fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
+lib.fmta_set_status_word.restype = _i
+lib.fmta_set_status_word.argtypes = [_vp]
+lib.fmta_selftest_expire_next.restype = _i
+lib.fmta_selftest_expire_next.argtypes = [_i]
+
+EXPORTS = ["fmta_set_status_word", "fmta_selftest_expire_next", "fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
            "fmta_bwd_prep_D", "fmta_bwd", "fmta_set_path", "fmta_profile_kernel", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode", "fmta_decode_offset_causal", "fmta_decode_paged", "fmta_kv_append_paged"]
 
 
@@ -102,3 +107,47 @@ def require_cuda_bf16(t, name):
 
 def as_f32(t):
     return t if (t.dtype == torch.float32 and t.is_contiguous()) else t.to(torch.float32).contiguous()
+
+
+def require_on(ref, t, name, shape=None):
+    """Every tensor whose address goes to a kernel must live on the device of ``ref`` (a CPU
+    tensor would hand the kernel a host pointer) and, where given, have exactly ``shape``."""
+    if not t.is_cuda or t.device != ref.device:
+        raise RuntimeError("%s must be a CUDA tensor on %s (got %s)" % (name, ref.device, t.device))
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise RuntimeError("%s must have shape %s (got %s)" % (name, tuple(shape), tuple(t.shape)))
+
+
+# ---- failure detection: one int32 status word per device, registered with the library ----
+_status_words = {}
+
+
+def _status_word(device):
+    """The status word of ``device`` (created, zeroed and registered on first use)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        with torch.cuda.device(idx):
+            w = torch.zeros(1, dtype=torch.int32, device="cuda:%d" % idx)
+            check(lib.fmta_set_status_word(ctypes.c_void_p(w.data_ptr())), "fmta_set_status_word")
+        _status_words[idx] = w
+    return w
+
+
+def arm_status(device):
+    """Called by the op wrappers before they launch: makes sure the library folds the status of its
+    tensor-core kernels into this device's status word."""
+    _status_word(device)
+
+
+def check_device_status(device=None):
+    """Synchronises ``device`` and raises RuntimeError if a bounded wait inside one of the
+    tensor-core kernels ran out since the last check (the outputs of that call are invalid).
+    The word is cleared, so the next check reports only newer failures."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    w = _status_word(torch.device(device))
+    v = int(w.item())          # synchronises
+    if v != 0:
+        w.zero_()
+        check(-8, "fmta_b200 device status")

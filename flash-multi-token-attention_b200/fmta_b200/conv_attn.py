@@ -15,7 +15,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from ._lib import lib, check, ptr, stream_ptr, require_cuda_bf16, as_f32
+from ._lib import lib, check, ptr, stream_ptr, require_cuda_bf16, as_f32, require_on, arm_status
 
 
 def _dims(Q, conv_kernel, pad_q, pad_k):
@@ -41,6 +41,8 @@ def forward(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, out_dtype=torch.f
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
     if K.shape != Q.shape or V.shape != Q.shape:
         raise RuntimeError("Q, K, V must have the same shape [batch, heads, seq, d_head]")
+    require_on(Q, K, "K"); require_on(Q, V, "V"); require_on(Q, conv_kernel, "conv_kernel")
+    arm_status(Q.device)
     theta = as_f32(conv_kernel)
     O = torch.empty((B, H, N, d), dtype=out_dtype, device=Q.device)
     M = torch.empty((B, H, N), dtype=torch.float32, device=Q.device)
@@ -61,11 +63,22 @@ def rowdot(dO, O):
     require_cuda_bf16(dO, "dO")
     if O.dtype not in (torch.float32, torch.bfloat16) or not O.is_contiguous():
         raise RuntimeError("O must be contiguous fp32 or bf16")
+    require_on(dO, O, "O", dO.shape)
     D = torch.empty(dO.shape[:-1], dtype=torch.float32, device=dO.device)
     st = lib.fmta_bwd_prep_D(ptr(dO), ptr(O), 1 if O.dtype == torch.bfloat16 else 0, ptr(D),
                              D.numel(), dO.shape[-1], stream_ptr())
     check(st, "fmta_bwd_prep_D")
     return D
+
+
+def _check_bwd_args(Q, K, V, dO, D, L, conv_kernel):
+    """Same device and the expected shape for every tensor whose address goes to the backward kernels."""
+    for t, n in ((K, "K"), (V, "V"), (dO, "dO")):
+        require_on(Q, t, n, Q.shape)
+    require_on(Q, D, "D", Q.shape[:-1])
+    require_on(Q, L, "L (log-sum-exp)", Q.shape[:-1])
+    require_on(Q, conv_kernel, "conv_kernel")
+    arm_status(Q.device)
 
 
 def dq_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
@@ -74,6 +87,7 @@ def dq_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (dO, "dO")):
         require_cuda_bf16(t, n)
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
+    _check_bwd_args(Q, K, V, dO, D, L, conv_kernel)
     theta, Dv, LSE = as_f32(conv_kernel), as_f32(D), as_f32(L)
     dQ = torch.empty((B, H, N, d), dtype=torch.float32, device=Q.device)
     dTheta = torch.empty((H, cq, ck), dtype=torch.float32, device=Q.device)
@@ -91,6 +105,7 @@ def dkdv_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (dO, "dO")):
         require_cuda_bf16(t, n)
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
+    _check_bwd_args(Q, K, V, dO, D, L, conv_kernel)
     theta, Dv, LSE = as_f32(conv_kernel), as_f32(D), as_f32(L)
     dK = torch.empty((B, H, N, d), dtype=torch.float32, device=Q.device)
     dV = torch.empty_like(dK)
@@ -107,6 +122,7 @@ def backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, path=-
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (dO, "dO")):
         require_cuda_bf16(t, n)
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
+    _check_bwd_args(Q, K, V, dO, D, L, conv_kernel)
     theta, Dv, LSE = as_f32(conv_kernel), as_f32(D), as_f32(L)
     dQ = torch.empty((B, H, N, d), dtype=torch.float32, device=Q.device)
     dK = torch.empty_like(dQ)

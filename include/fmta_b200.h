@@ -41,6 +41,7 @@ extern "C" {
 #define FMTA_ERR_WORKSPACE (-5)   /* workspace missing or too small */
 #define FMTA_ERR_CUDA (-6)        /* the CUDA runtime rejected a launch (see fmta_last_cuda_error) */
 #define FMTA_ERR_SCRATCH_LIMIT (-7) /* problem needs more than FMTA_STATIC_SCRATCH_BYTES of built-in scratch */
+#define FMTA_ERR_DEVICE_WAIT (-8) /* a bounded wait inside a kernel ran out (status word, see fmta_set_status_word) */
 
 /* Size of the library's built-in scratch array used by fmta_bwd_dq_dw_static (4 MiB per GPU). */
 #define FMTA_STATIC_SCRATCH_BYTES ((size_t)4 << 20)
@@ -64,6 +65,28 @@ const char* fmta_strerror(int status);
  * plus exact kernels on it.  Returns the previous value.
  */
 int fmta_set_path(int path);
+
+/*
+ * Failure detection.  Every wait inside the tensor-core kernels (on an mbarrier fed by TMA, by the
+ * tensor cores or by other warps) is bounded; a kernel whose wait runs out stops issuing work, waits
+ * (bounded) for what it has in flight, frees its tensor memory and sets a status word, and the
+ * outputs of that call are invalid.  The reference has no counterpart (its forward only prints a
+ * launch error, conv_attn/kernels/fwd.cu:306-309; its backward throws on one, dq_bwd.cu:585-586).
+ * fmta_set_status_word registers, for the CURRENT device, a caller-owned int32 in device memory
+ * (zeroed by the caller); from then on every tensor-core entry point ends by OR-ing its kernels'
+ * status into that word on its stream.  The caller reads the word after a synchronisation it does
+ * anyway: non-zero = FMTA_ERR_DEVICE_WAIT.  NULL unregisters.  Process-wide per device, not thread-safe.
+ */
+int fmta_set_status_word(int* device_word);
+
+/*
+ * Self-test of the above: the next launch of the named tensor-core kernel (ids as in
+ * fmta_profile_kernel: 1 forward, 3 dQ, 4 dK/dV; 0 cancels) points its first consumer wait at a
+ * barrier that nothing arrives at, with a limit of a few hundred polls, so that the wait runs out
+ * and the kernel takes its abort path.  Nothing faults or spins without bound; the call's outputs
+ * are garbage and the status word reads non-zero.
+ */
+int fmta_selftest_expire_next(int kernel_id);
 
 /*
  * Timing hook for benchmarks: while armed, every launch of the chosen kernel is bracketed by

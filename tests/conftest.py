@@ -17,3 +17,16 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden_dir():
     return os.path.join(ROOT, "tests", "golden")
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean(request):
+    """After every GPU test: no bounded wait inside a tensor-core kernel may have run out unnoticed."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    import fmta_b200
+    fmta_b200.check_device_status()

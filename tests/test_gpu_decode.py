@@ -179,3 +179,32 @@ def test_paged_cache_ragged_lengths_and_append():
             Oc, Mc, Lc = F.forward_inference(qb[b:b + 1], kb, vb, th, 1, scale, cq - 1, (ck - 1) // 2, False, offset_causal=True)
             assert maxabs(Op[b:b + 1, :, 0], Oc[:, :, 0]) <= 1e-5
             assert maxabs((Mp + torch.log(Lp))[b:b + 1, :, 0], (Mc + torch.log(Lc))[:, :, 0]) <= 1e-5
+
+
+def test_paged_lengths_beyond_the_table_are_clamped_not_followed():
+    """A stale or oversized seq_lens entry must not walk the kernels off the block table: the decode
+    treats it as max_seq_len, and the append drops rows whose page index lies past the table."""
+    import fmta_b200 as F
+    B, H, q_len, d, cq, ck, page, Nmax = 2, 2, 6, 64, 6, 11, 32, 160
+    Q, K, V, _, theta = orc.make_inputs(B, H, 0, d, cq, ck, seed=5, dtype=torch.bfloat16, Nk=Nmax, q_len=q_len)
+    scale = 1.0 / math.sqrt(d)
+    Kp, Vp, table = _paged_from_contiguous(K, V, page)
+    th = theta.cuda()
+    qb = Q.cuda().to(torch.bfloat16).contiguous()
+    full = torch.tensor([Nmax, Nmax], dtype=torch.int32).cuda()
+    wild = torch.tensor([Nmax + 100000, 2 ** 30], dtype=torch.int32).cuda()
+    zero = torch.tensor([0, -7], dtype=torch.int32).cuda()
+    ref = F.forward_inference_paged(qb, Kp, Vp, table, th, 2, scale, cq - 1, (ck - 1) // 2, seq_lens=full, max_seq_len=Nmax)
+    got = F.forward_inference_paged(qb, Kp, Vp, table, th, 2, scale, cq - 1, (ck - 1) // 2, seq_lens=wild, max_seq_len=Nmax)
+    torch.cuda.synchronize()
+    for a, b in zip(ref, got):
+        assert torch.equal(a[:, :, 0], b[:, :, 0])
+    one = F.forward_inference_paged(qb, Kp, Vp, table, th, 1, scale, cq - 1, (ck - 1) // 2, seq_lens=zero, max_seq_len=Nmax)
+    torch.cuda.synchronize()
+    assert torch.isfinite(one[0][:, :, 0]).all()          # lengths below 1 are read as 1
+    # append: positions past max_pages * page_size are dropped, the pools stay as they were
+    Kp0, Vp0 = Kp.clone(), Vp.clone()
+    Knew = torch.ones(B, H, 3, d, dtype=torch.bfloat16, device="cuda")
+    F.kv_append_paged(Kp, Vp, table, wild, Knew, Knew)
+    torch.cuda.synchronize()
+    assert torch.equal(Kp, Kp0) and torch.equal(Vp, Vp0)

@@ -37,10 +37,13 @@ def test_static_scratch_matches_workspace_variant_twice():
                                 B, H, N, d, cq, ck, 1, scale, 1, _p(ws), nbytes, st)
         assert rc == 0
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.fmta_bwd_dq_dw_static(_p(q), _p(k), _p(v), _p(do), _p(D), _p(LSE), _p(th), None, _p(dQ_b), _p(dT_b),
                                        None, B, H, N, d, cq, ck, 1, scale, 1, st)
         assert rc == 0, lib.fmta_strerror(rc)
         torch.cuda.synchronize()
+        if call == 1:   # once the first call has looked up the array's address, a call leaves the device's free memory as it was
+            assert torch.cuda.mem_get_info()[0] == free_before
         # same kernels, same summation order: identical results (the suite's tolerance is 2e-2)
         assert torch.equal(dQ_a, dQ_b)
         assert torch.equal(dT_a, dT_b)
@@ -57,3 +60,8 @@ def test_static_scratch_rejects_oversized_problems():
                                    64, 32, 4096, 64, 6, 11, 1, 0.125, 1, None)
     assert rc == -7
     assert b"4 MiB" in lib.fmta_strerror(rc)
+    # without a filter or a mixing matrix there are no partial sums: no size limit applies, and the
+    # filter-shape arguments are ignored as fmta_bwd_dq_dw ignores them (the NULL dQ is what is refused)
+    rc = lib.fmta_bwd_dq_dw_static(good, good, good, good, good, good, None, None, None, None, None,
+                                   64, 32, 4096, 64, 0, 0, 0, 0.125, 1, None)
+    assert rc == -1
