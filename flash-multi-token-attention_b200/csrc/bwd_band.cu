@@ -23,7 +23,6 @@ namespace fmta {
 
 namespace bandcfg {
 constexpr int kThetaLdBand = 20;                     // filter row stride in shared memory (c_k <= 17)
-constexpr int D = 64;
 constexpr int NT = 256;
 constexpr int MAXPQ = 6, MAXPK = 8;                 // c_q <= 7, c_k <= 17
 constexpr int MAXBAND = MAXPQ + MAXPK;              // 14
@@ -31,24 +30,29 @@ constexpr int MAXW = MAXBAND + MAXPK;               // 22
 constexpr int RC = 96;                              // dC rows computed per CTA (6 tiles of 16)
 constexpr int RS = RC + 16;                         // Sb / Q rows: start 16 rows earlier
 constexpr int RK = RC + 48;                         // K rows: start 48 rows earlier
-constexpr int LD = D + 8;                           // bf16 row stride (ldmatrix without bank conflicts)
 constexpr int SB_LD = 37;                           // band (zero pad for e < 0) + W columns, odd
 constexpr int DC_LD = 45;                           // pad_k + band + pad_q + 2 pad_k columns (<= 44), odd
 constexpr int P_LD = 15;
 constexpr int DS_LD = 23;
 constexpr int A_LD = 40;                            // bf16 operand tiles of the output GEMMs: 32 columns + 8 (ldmatrix)
-constexpr int oQ = 0;
-constexpr int oK = oQ + RS * LD * 2;
-constexpr int oV = oK + RK * LD * 2;                // V rows; later reused for the padded dC rows
-constexpr int kVBytes = (RS * LD * 2 > RC * DC_LD * 4) ? RS * LD * 2 : RC * DC_LD * 4;
-constexpr int odO = oV + kVBytes;
-constexpr int oSb = odO + RC * LD * 2;
-constexpr int oP = oSb + RS * SB_LD * 4;            // dPb, overwritten in place by P
-constexpr int odS = oP + RC * P_LD * 4;
-constexpr int oLD = odS + RC * DS_LD * 4;           // LSE*log2e [RC], D [RC]
-constexpr int oTheta = oLD + 2 * RC * 4;
-constexpr int oRed = oTheta + 7 * kThetaLdBand * 4;
-constexpr int kSmemBytes = oRed + NT * 4;
+// shared-memory layout for head dim D
+template <int D>
+struct Layout {
+  static constexpr int LD = D + 8;                  // bf16 row stride (ldmatrix without bank conflicts)
+  static constexpr int oQ = 0;
+  static constexpr int oK = oQ + RS * LD * 2;
+  static constexpr int oV = oK + RK * LD * 2;       // V rows; later reused for the padded dC rows
+  static constexpr int kVBytes = (RS * LD * 2 > RC * DC_LD * 4) ? RS * LD * 2 : RC * DC_LD * 4;
+  static constexpr int odO = oV + kVBytes;
+  static constexpr int oSb = odO + RC * LD * 2;
+  static constexpr int oP = oSb + RS * SB_LD * 4;   // dPb, overwritten in place by P
+  static constexpr int odS = oP + RC * P_LD * 4;
+  static constexpr int oLD = odS + RC * DS_LD * 4;  // LSE*log2e [RC], D [RC]
+  static constexpr int oTheta = oLD + 2 * RC * 4;
+  static constexpr int oRed = oTheta + 7 * kThetaLdBand * 4;
+  static constexpr int kSmemBytes = oRed + NT * 4;
+  static constexpr int kCtasPerSm = (2 * kSmemBytes <= 225 * 1024) ? 2 : 1;
+};
 }  // namespace bandcfg
 
 // positions owned per CTA for a filter shape
@@ -59,9 +63,12 @@ inline int bwd_band_positions(int cq, int ck) {
 }
 
 
-template <int CQ, int CK>   // filter shape at compile time, or (0, 0): read from the parameters
-__global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainParams p) {
+template <int D, int CQ, int CK>   // head dim; filter shape at compile time, or (0, 0): read from the parameters
+__global__ void __launch_bounds__(bandcfg::NT, bandcfg::Layout<D>::kCtasPerSm) bwd_band_kernel(const TrainParams p) {
   using namespace bandcfg;
+  using BL = Layout<D>;
+  constexpr int LD = BL::LD, oQ = BL::oQ, oK = BL::oK, oV = BL::oV, odO = BL::odO, oSb = BL::oSb, oP = BL::oP;
+  constexpr int odS = BL::odS, oLD = BL::oLD, oTheta = BL::oTheta, oRed = BL::oRed;
   extern __shared__ __align__(16) unsigned char smem[];
   bf16* sQ = reinterpret_cast<bf16*>(smem + oQ);
   bf16* sK = reinterpret_cast<bf16*>(smem + oK);
@@ -395,8 +402,9 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
   if (mma_out) {
     // ---- dQ, dK, dV on mma.sync: 16 positions x 32 head dims per job, accumulating onto the values in memory ----
     const int ntile = (R + 15) / 16;
-    for (int job = warp; job < ntile * 6; job += NT / 32) {
-      const int m = job / 6, which = (job % 6) >> 1, ch = job & 1;      // which: 0 dQ, 1 dK, 2 dV
+    constexpr int NCH = D / 32;                                          // 32-column chunks of the head dim
+    for (int job = warp; job < ntile * 3 * NCH; job += NT / 32) {
+      const int m = job / (3 * NCH), which = (job % (3 * NCH)) / NCH, ch = job % NCH;      // which: 0 dQ, 1 dK, 2 dV
       const int x0 = 16 * m + (lane >> 2), x1 = x0 + 8;
       const bool ok0 = (x0 < R) && (t0 + x0 < N), ok1 = (x1 < R) && (t0 + x1 < N);
       float* gout = (which == 0) ? p.dQ : (which == 1) ? p.dK : p.dV;
@@ -428,8 +436,10 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
       if (ta >= N) break;
       const bool two = (xr1 < R) && (tb < N);
       const int xb = two ? xr1 : xr0;                       // second position (a repeat of the first when absent)
-      float* ga = p.dQ + (bh * N + ta) * D + 2 * lane;
-      float* gb = p.dQ + (bh * N + t0 + xb) * D + 2 * lane;
+     for (int c0 = 0; c0 < D; c0 += 64) {                   // 64 head dims per pass of the warp
+      const int col = c0 + 2 * lane;
+      float* ga = p.dQ + (bh * N + ta) * D + col;
+      float* gb = p.dQ + (bh * N + t0 + xb) * D + col;
       const ptrdiff_t kofs = p.dK - p.dQ, vofs = p.dV - p.dQ;  // element offsets between the three outputs
       float2 aq0 = *reinterpret_cast<const float2*>(ga), ak0 = *reinterpret_cast<const float2*>(ga + kofs), av0 = *reinterpret_cast<const float2*>(ga + vofs);
       float2 aq1 = *reinterpret_cast<const float2*>(gb), ak1 = *reinterpret_cast<const float2*>(gb + kofs), av1 = *reinterpret_cast<const float2*>(gb + vofs);
@@ -437,10 +447,10 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
       for (int e = 0; e < W; ++e) {
         const float s10 = sdS[xr0 * DS_LD + e], s11 = sdS[xb * DS_LD + e];
         const float s20 = sdS[(xr0 + e) * DS_LD + e], s21 = sdS[(xb + e) * DS_LD + e];
-        const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xr0 + 48 - e) * LD + 2 * lane);
-        const __nv_bfloat162 k1 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xb + 48 - e) * LD + 2 * lane);
-        const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xr0 + 16 + e) * LD + 2 * lane);
-        const __nv_bfloat162 q1 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xb + 16 + e) * LD + 2 * lane);
+        const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xr0 + 48 - e) * LD + col);
+        const __nv_bfloat162 k1 = *reinterpret_cast<const __nv_bfloat162*>(sK + (xb + 48 - e) * LD + col);
+        const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xr0 + 16 + e) * LD + col);
+        const __nv_bfloat162 q1 = *reinterpret_cast<const __nv_bfloat162*>(sQ + (xb + 16 + e) * LD + col);
         aq0.x = fmaf(s10, __low2float(k0), aq0.x); aq0.y = fmaf(s10, __high2float(k0), aq0.y);
         aq1.x = fmaf(s11, __low2float(k1), aq1.x); aq1.y = fmaf(s11, __high2float(k1), aq1.y);
         ak0.x = fmaf(s20, __low2float(q0), ak0.x); ak0.y = fmaf(s20, __high2float(q0), ak0.y);
@@ -449,13 +459,14 @@ __global__ void __launch_bounds__(bandcfg::NT, 2) bwd_band_kernel(const TrainPar
 #pragma unroll 2
       for (int dd = 0; dd < band; ++dd) {
         const float p0 = sP[(xr0 + dd) * P_LD + dd], p1 = sP[(xb + dd) * P_LD + dd];
-        const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xr0 + dd) * LD + 2 * lane);
-        const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xb + dd) * LD + 2 * lane);
+        const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xr0 + dd) * LD + col);
+        const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(sdO + (xb + dd) * LD + col);
         av0.x = fmaf(p0, __low2float(o0), av0.x); av0.y = fmaf(p0, __high2float(o0), av0.y);
         av1.x = fmaf(p1, __low2float(o1), av1.x); av1.y = fmaf(p1, __high2float(o1), av1.y);
       }
       *reinterpret_cast<float2*>(ga) = aq0; *reinterpret_cast<float2*>(ga + kofs) = ak0; *reinterpret_cast<float2*>(ga + vofs) = av0;
       if (two) { *reinterpret_cast<float2*>(gb) = aq1; *reinterpret_cast<float2*>(gb + kofs) = ak1; *reinterpret_cast<float2*>(gb + vofs) = av1; }
+     }
     }
   }
 }
@@ -468,17 +479,24 @@ int bwd_band_theta_slots(int B, int N, int cq, int ck) {
 
 // Adds the band part of dQ/dK/dV and writes one dTheta partial per CTA into p.dTheta_part
 // ([slots][H][cq*ck]).  Nothing to do when the filter has no band (pad_q + pad_k == 0).
+template <int D>
+static cudaError_t launch_bwd_band_d(const TrainParams& p, dim3 grid, cudaStream_t stream) {
+  constexpr int smem = bandcfg::Layout<D>::kSmemBytes;
+  if (p.cq == 6 && p.ck == 11)
+    return launch_kernel<TrainParams>(bwd_band_kernel<D, 6, 11>, grid, dim3(bandcfg::NT), smem, stream, 1, p);
+  if (p.cq == 7 && p.ck == 7 && D == 64)
+    return launch_kernel<TrainParams>(bwd_band_kernel<D, 7, 7>, grid, dim3(bandcfg::NT), smem, stream, 1, p);
+  if (p.cq == 3 && p.ck == 5)
+    return launch_kernel<TrainParams>(bwd_band_kernel<D, 3, 5>, grid, dim3(bandcfg::NT), smem, stream, 1, p);
+  return launch_kernel<TrainParams>(bwd_band_kernel<D, 0, 0>, grid, dim3(bandcfg::NT), smem, stream, 1, p);
+}
+
 cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream) {
   const int R = bwd_band_positions(p.cq, p.ck);
   dim3 grid((p.N + R - 1) / R, p.H, p.B);
   ScopedKernelTimer timer_(kKernBwdBand, stream);
-  if (p.cq == 6 && p.ck == 11)
-    return launch_kernel<TrainParams>(bwd_band_kernel<6, 11>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
-  if (p.cq == 7 && p.ck == 7)
-    return launch_kernel<TrainParams>(bwd_band_kernel<7, 7>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
-  if (p.cq == 3 && p.ck == 5)
-    return launch_kernel<TrainParams>(bwd_band_kernel<3, 5>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
-  return launch_kernel<TrainParams>(bwd_band_kernel<0, 0>, grid, dim3(bandcfg::NT), bandcfg::kSmemBytes, stream, 1, p);
+  if (p.d == 128) return launch_bwd_band_d<128>(p, grid, stream);
+  return launch_bwd_band_d<64>(p, grid, stream);
 }
 
 }  // namespace fmta

@@ -24,27 +24,11 @@
 #include <cuda_runtime.h>
 
 #include "fmta_params.h"
+#include "bwd_tc.cuh"
 #include "fmta_tc.cuh"
 #include "launch_util.cuh"
 
 namespace fmta {
-
-constexpr float kLn2 = 0.6931471805599453f;
-
-
-struct BwdTcParams {
-  const float* LSE;   // [B,H,N] natural log
-  const float* Dvec;  // [B,H,N]
-  float* dQ;          // [B,H,N,D]   (dq kernel: overwritten)
-  float* dV;          // [B,H,N,D]   (dkdv kernel: overwritten)
-  bf16* dKt;          // [B,H,cq,N,D] bf16 (dkdv kernel: overwritten)
-  int* status;
-  int H, N, cq, ck, causal;
-  // dK/dV kernel: the filter taps whose dKt this launch accumulates ([tap0, tap0 + ntap)) and whether it
-  // accumulates dV as well; seven taps do not fit the tensor memory at once and take two launches
-  int tap0, ntap, with_dv;
-  int selftest_expire;   // failure-detection self-test: the element-wise warps' first wait is on a barrier nothing arrives at
-};
 
 // ==========================================================================================
 // dQ
@@ -807,7 +791,7 @@ __global__ void dk_post_toeplitz_kernel(const float* __restrict__ theta, bf16* _
 __global__ void __launch_bounds__(DkPostCfg::NT, 2)
 dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmX,
                    const bf16* __restrict__ Tg, float* __restrict__ dK, float* __restrict__ dTheta_part, int* status,
-                   int H, int N, int cq, int ck, float scale, int n_jblocks) {
+                   int H, int N, int cq, int ck, float scale, int n_jblocks, int dfull) {
   using Cfg = DkPostCfg;
   constexpr int D = Cfg::D, NT = Cfg::NT, KEYS = Cfg::KEYS, HALO = Cfg::HALO;
   constexpr int T_LD = Cfg::T_LD, T_ELEMS = Cfg::T_ELEMS, RED_LD = Cfg::RED_LD;
@@ -825,6 +809,7 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pk = (ck - 1) / 2;
   const int J0 = blockIdx.x * KEYS;
+  const int col0 = blockIdx.z * D;                           // a CTA handles 64 of the head's `dfull` columns
   const int half = (cq + 1) / 2;                             // the taps arrive in two batches
   // 16-byte chunk c of row r of tile t
   auto at = [&](int t, int r, int c) -> const void* {
@@ -840,12 +825,12 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   __syncthreads();
   if (tid == 0) {
     tc::mbar_expect_tx(&bars[0], (1 + half) * Cfg::TILE_BYTES + Cfg::t_bytes(cq));
-    tc::tma_load_3d(smem, &tmK, &bars[0], 0, J0 - HALO, bh);
+    tc::tma_load_3d(smem, &tmK, &bars[0], col0, J0 - HALO, bh);
     tc::bulk_load(sTb, Tg + (size_t)h * cq * 2 * T_ELEMS, Cfg::t_bytes(cq), &bars[0]);
-    for (int a = 0; a < half; ++a) tc::tma_load_3d(smem + (a + 1) * Cfg::TILE_STRIDE, &tmX, &bars[0], 0, J0 - HALO, bh * cq + a);
+    for (int a = 0; a < half; ++a) tc::tma_load_3d(smem + (a + 1) * Cfg::TILE_STRIDE, &tmX, &bars[0], col0, J0 - HALO, bh * cq + a);
     if (cq > half) {
       tc::mbar_expect_tx(&bars[1], (cq - half) * Cfg::TILE_BYTES);
-      for (int a = half; a < cq; ++a) tc::tma_load_3d(smem + (a + 1) * Cfg::TILE_STRIDE, &tmX, &bars[1], 0, J0 - HALO, bh * cq + a);
+      for (int a = half; a < cq; ++a) tc::tma_load_3d(smem + (a + 1) * Cfg::TILE_STRIDE, &tmX, &bars[1], col0, J0 - HALO, bh * cq + a);
     }
   }
   bool ok = true;
@@ -901,7 +886,7 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         for (int hh = 0; hh < 2; ++hh) {
           const int key = J0 + 32 * kh + 16 * m + g + 8 * hh;
           if (key < N)
-            *reinterpret_cast<float2*>(dK + ((size_t)bh * N + key) * D + 16 * cgp + 8 * j + 2 * t4) = make_float2(acc[m][j][2 * hh], acc[m][j][2 * hh + 1]);
+            *reinterpret_cast<float2*>(dK + ((size_t)bh * N + key) * dfull + col0 + 16 * cgp + 8 * j + 2 * t4) = make_float2(acc[m][j][2 * hh], acc[m][j][2 * hh + 1]);
         }
   }
 
@@ -948,7 +933,7 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
   }
   __syncthreads();
-  const int slot = b * n_jblocks + blockIdx.x;
+  const int slot = (b * (int)gridDim.z + (int)blockIdx.z) * n_jblocks + blockIdx.x;   // one partial per CTA
   for (int i = tid; i < cq * ck; i += NT) {
     const int a = i / ck, bb = i % ck;
     float t = 0.f;
@@ -962,12 +947,13 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 // ==========================================================================================
 // host side
 // ==========================================================================================
-bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128);
-bool tensor_maps_available();
 cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream);
 
 bool bwd_tc_supported(const TrainParams& p) {
-  return p.theta != nullptr && p.Wmix == nullptr && p.d == 64 && p.cq >= 1 && p.cq <= 7 && tensor_maps_available();
+  // head dim 64: up to seven query taps (two launches of the dK/dV kernel for the seventh); head dim 128:
+  // up to six (the resident stacked key tiles of the dK/dV kernel fill its shared memory)
+  const bool shape_ok = (p.d == 64 && p.cq <= 7) || (p.d == 128 && p.cq <= 6);
+  return p.theta != nullptr && p.Wmix == nullptr && shape_ok && p.cq >= 1 && tensor_maps_available();
 }
 
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq) {
@@ -983,13 +969,14 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t
   const size_t rows = (size_t)p.B * p.H * p.N, BH = (size_t)p.B * p.H;
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
-  __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
-  w += up(rows * p.cq * D * 2);
+  __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * p.d * 2);
+  w += up(rows * p.cq * p.d * 2);
   int* status = reinterpret_cast<int*>(w);
   cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
   if (e != cudaSuccess) return e;
   e = launch_ktilde(p, Kt, stream);
   if (e != cudaSuccess) return e;
+  if (p.d == 128) return launch_bwd_dq_tc128(p, Kt, status, stream);
   alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV;
   if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR / 2, false)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmdO, p.dO, D, p.N, BH, 64, Cfg::BM, true)) return cudaErrorInvalidValue;
@@ -1037,7 +1024,7 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
 }
 
 cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream) {
-  constexpr int D = 64;
+  const int D = p.d;
   const size_t rows = (size_t)p.B * p.H * p.N, BH = (size_t)p.B * p.H;
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
@@ -1046,7 +1033,9 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   int* status = reinterpret_cast<int*>(w);
   cudaError_t e;
   { ScopedKernelTimer timer_(kKernBwdDkdvTc, stream);
-    if (p.cq <= 6) {
+    if (D == 128) {
+      e = launch_bwd_dkdv_tc128(p, Kt, dKt, status, stream);
+    } else if (p.cq <= 6) {
       e = launch_dkdv_pass<6, true>(p, Kt, dKt, status, 0, p.cq, 1, stream);
     } else {
       // seven taps: dV + 7 accumulators + the scratch columns exceed the tensor memory, so the taps are
@@ -1056,7 +1045,7 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
     } }
   if (e != cudaSuccess) return e;
   const int njb = (p.N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS;
-  dim3 g2(njb, (unsigned)BH);
+  dim3 g2(njb, (unsigned)BH, D / DkPostCfg::D);      // one CTA per 64 keys and 64 columns of the head dim
   const int smem = DkPostCfg::smem_bytes(p.cq);
   auto kern = dk_post_mma_kernel;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -1065,18 +1054,18 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   alignas(64) CUtensorMap tmK, tmX;
   if (!make_tensor_map_bf16(&tmK, p.K, D, p.N, BH, 64, DkPostCfg::ROWS, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmX, dKt, D, p.N, BH * p.cq, 64, DkPostCfg::ROWS, true)) return cudaErrorInvalidValue;
+  // (the maps span the full head dim; each CTA fetches its 64-column slab)
   ScopedKernelTimer timer2_(kKernDkPost, stream);
   dk_post_toeplitz_kernel<<<p.H, 256, 0, stream>>>(p.theta, Tg, p.cq, p.ck, p.scale);
-  kern<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb);
+  kern<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb, D);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   return launch_fold_status(status, stream);
 }
 
 // slots of dTheta partials written by the dKt adjoint kernel: one per CTA
-int bwd_tc_theta_slots(int B, int N, int ck) {
-  (void)ck;
-  return B * ((N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS);
+int bwd_tc_theta_slots(int B, int N, int d) {
+  return B * (d > DkPostCfg::D ? d / DkPostCfg::D : 1) * ((N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS);
 }
 
 

@@ -1,0 +1,37 @@
+// Parameter block and host-side declarations shared by the tensor-core backward kernels
+// (bwd_tc.cu: head dim 64; bwd_tc128.cu: head dim 128).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "fmta_common.cuh"
+#include "fmta_params.h"
+
+namespace fmta {
+
+constexpr float kLn2 = 0.6931471805599453f;
+
+
+struct BwdTcParams {
+  const float* LSE;   // [B,H,N] natural log
+  const float* Dvec;  // [B,H,N]
+  float* dQ;          // [B,H,N,D]   (dq kernel: overwritten)
+  float* dV;          // [B,H,N,D]   (dkdv kernel: overwritten)
+  bf16* dKt;          // [B,H,cq,N,D] bf16 (dkdv kernel: overwritten)
+  int* status;
+  int H, N, cq, ck, causal;
+  // dK/dV kernel: the filter taps whose dKt this launch accumulates ([tap0, tap0 + ntap)) and whether it
+  // accumulates dV as well; seven taps do not fit the tensor memory at once and take two launches
+  int tap0, ntap, with_dv;
+  int selftest_expire;   // failure-detection self-test: the element-wise warps' first wait is on a barrier nothing arrives at
+};
+
+
+bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128);
+bool tensor_maps_available();
+
+// head dim 128 (bwd_tc128.cu)
+cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, int* status, cudaStream_t stream);
+cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt, __nv_bfloat16* dKt, int* status, cudaStream_t stream);
+
+}  // namespace fmta

@@ -129,7 +129,7 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
   if (op == FMTA_OP_BWD_TC) {
     // dTheta partials of the band kernel and of the tensor-core post-pass (one contiguous slot
     // array, rounded up), followed by the tensor-core backward's buffers
-    const size_t slots = (size_t)bwd_band_theta_slots(B, N, cq, ck) + (size_t)bwd_tc_theta_slots(B, N, ck);
+    const size_t slots = (size_t)bwd_band_theta_slots(B, N, cq, ck) + (size_t)bwd_tc_theta_slots(B, N, d);
     const size_t part = (slots * H * (size_t)(cq * ck) * sizeof(float) + 1023) / 1024 * 1024;
     return part + bwd_tc_workspace_bytes(B, H, N, d, cq);
   }
@@ -278,7 +278,7 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
   }
   // tensor-core kernels for the entries off the causal band, then the band kernel adds its part
   slots_ex = bwd_band_theta_slots(B, N, p.cq, p.ck);            // one dTheta partial per band CTA
-  const int slots_tc = bwd_tc_theta_slots(B, N, p.ck);
+  const int slots_tc = bwd_tc_theta_slots(B, N, d);
   float* part = reinterpret_cast<float*>(workspace);
   const size_t part_bytes = ((size_t)(slots_ex + slots_tc) * n_theta * sizeof(float) + 1023) / 1024 * 1024;
   void* tcw = reinterpret_cast<unsigned char*>(workspace) + part_bytes;

@@ -88,7 +88,7 @@ bool bwd_tc_supported(const TrainParams& p);
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
 cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t stream);
 cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream);
-int bwd_tc_theta_slots(int B, int N, int ck);
+int bwd_tc_theta_slots(int B, int N, int d);
 int bwd_band_theta_slots(int B, int N, int cq, int ck);
 cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream);
 cudaError_t launch_fwd_band(const TrainParams& p, cudaStream_t stream);

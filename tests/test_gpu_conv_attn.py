@@ -154,6 +154,19 @@ def test_rejects_bad_inputs():
     (1, 2, 65, 64, 6, 11, True),      # one key into the second tile: its halo rows are mostly past the end
     (1, 2, 129, 64, 7, 17, True),     # the same with the widest filter (halo of 8 rows fully used)
     (1, 1, 130, 64, 1, 3, False),     # one tap, no band
+    # head dim 128: dQ tile of 120 owned rows, 64-key dK/dV CTAs with 128-row query blocks
+    (1, 2, 520, 128, 6, 11, True),
+    (2, 1, 300, 128, 3, 5, False),    # no causal band: everything on the tensor-core kernels
+    (1, 1, 100, 128, 6, 11, True),    # shorter than one tile
+    (1, 1, 120, 128, 6, 11, True),    # exactly the rows one dQ tile owns
+    (1, 1, 121, 128, 6, 11, True),    # one row into the second dQ tile
+    (1, 2, 257, 128, 1, 3, True),     # single query tap
+    (1, 1, 450, 128, 4, 7, True),
+    (1, 1, 611, 128, 6, 13, True),    # W = 17
+    (1, 1, 389, 128, 6, 15, True),    # W = 19: FMA output phase of the band kernel
+    (1, 1, 1500, 128, 6, 11, True),   # many key blocks per dQ tile, many row blocks per key tile
+    (1, 2, 65, 128, 6, 11, True),     # one key into the second 64-key tile
+    (2, 2, 333, 128, 5, 9, True),
 ])
 def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
     """fmta_bwd with the exact kernels (path 0) and with the stacked-GEMM tensor-core kernels plus
@@ -179,8 +192,10 @@ def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
 
 def test_tensor_core_path_rejected_when_unsupported():
     import fmta_b200 as F
-    Q = torch.zeros(1, 1, 64, 128, device="cuda", dtype=torch.bfloat16)
-    th = torch.zeros(1, 6, 11, device="cuda")
     LSE = torch.zeros(1, 1, 64, device="cuda")
-    with pytest.raises(RuntimeError):   # the tensor-core backward exists for d = 64 only
-        F.backward(Q, Q, Q, Q, LSE, LSE, th, 1.0, 5, 5, True, path=1)
+    Q = torch.zeros(1, 1, 64, 32, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):   # the tensor-core backward exists for d = 64 and d = 128
+        F.backward(Q, Q, Q, Q, LSE, LSE, torch.zeros(1, 6, 11, device="cuda"), 1.0, 5, 5, True, path=1)
+    Q = torch.zeros(1, 1, 64, 128, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):   # ... with up to six query taps at d = 128
+        F.backward(Q, Q, Q, Q, LSE, LSE, torch.zeros(1, 7, 7, device="cuda"), 1.0, 6, 3, True, path=1)
