@@ -15,7 +15,8 @@
 //                           stay resident (112 KB).  The accumulators are kept TRANSPOSED, with the head
 //                           dim on the lanes: dV^T[d, key] += dO^T P and dKt_a^T[d, key] += Q^(a)T dC are
 //                           M = 128 MMAs whose A operand is the staged dO / Q tile read MN-major (for Q
-//                           with the tap's row shift as a start-address offset) and whose B operand is the
+//                           with the tap's row shift as a start-address offset of 128 bytes per row into
+//                           the 128-byte-swizzled tile) and whose B operand is the
 //                           bf16 P / dC tile exactly as the element-wise warps write it (one row per
 //                           thread).  dV^T + 6 dKt^T take 448 columns; S and dP share the last 64
 //                           (dP(0) | S(0) dP(1) | S(1) dP(2) ...), as in the d = 64 kernel.  Scores and dP
@@ -23,6 +24,7 @@
 // Every mbarrier wait is bounded; no TMA multicast, no cluster, cta_group::1 only.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 
 #include "bwd_tc.cuh"
 #include "fmta_tc.cuh"
@@ -33,7 +35,8 @@ namespace fmta {
 // ==========================================================================================
 // dQ, d = 128
 // ==========================================================================================
-struct Dq128Cfg {
+template <int NSLOT_>
+struct Dq128CfgT {
   static constexpr int D = 128;
   static constexpr int BM = 128;               // dC rows per tile (= TMEM lanes)
   static constexpr int OWN = 120;              // dQ rows a tile owns (dQ row i needs dC rows i .. i + pad_q, pad_q <= 8)
@@ -43,7 +46,7 @@ struct Dq128Cfg {
   static constexpr int DR = BM + 16;           // rows of the dC buffer (16 zero rows below)
   static constexpr int SLAB_BYTES = BC * 128;  // 64 keys x 64 elements, 128-byte swizzle
   static constexpr int TILE_BYTES = 2 * SLAB_BYTES;   // one Kt / V ring tile: two column slabs
-  static constexpr int NSLOT = 10;
+  static constexpr int NSLOT = NSLOT_;
   static constexpr int oQ = 0;                                  // [D/8][QR][16 B]
   static constexpr int odC = oQ + QR * D * 2;                   // [BC/8][DR][16 B]
   static constexpr int oRing = ((odC + (BC / 8) * DR * 16 + 1023) / 1024) * 1024;
@@ -55,10 +58,13 @@ struct Dq128Cfg {
   static constexpr int kThreads = (4 + 1 + 2) * 32;   // element-wise warpgroup, TMA warp, two MMA issuer warps
 };
 
-__global__ void __launch_bounds__(Dq128Cfg::kThreads, 1)
+using Dq128Cfg = Dq128CfgT<10>;
+
+template <int NSLOT_>
+__global__ void __launch_bounds__(Dq128CfgT<NSLOT_>::kThreads, 1)
 bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKt,
                     const __grid_constant__ CUtensorMap tmV, const bf16* __restrict__ dO, const BwdTcParams p) {
-  using Cfg = Dq128Cfg;
+  using Cfg = Dq128CfgT<NSLOT_>;
   constexpr int D = Cfg::D, BM = Cfg::BM, OWN = Cfg::OWN, BC = Cfg::BC, HALO = Cfg::HALO, QR = Cfg::QR;
   constexpr int DR = Cfg::DR, NSLOT = Cfg::NSLOT;
   extern __shared__ unsigned char smem_raw[];
@@ -367,14 +373,14 @@ struct Dkv128Cfg {
   static constexpr int DO_SLAB = BR * 128;     // 128 rows x 64 elements, 128-byte swizzle
   static constexpr int oKt = 0;
   static constexpr int oV = oKt + MAXCQ * KT_BYTES;
-  static constexpr int oQ = oV + KT_BYTES;                      // [D/8][QR][16 B]
+  static constexpr int Q_SLAB = QR * 128;      // 144 rows x 64 elements, 128-byte swizzle
+  static constexpr int oQ = oV + KT_BYTES;                      // two slabs
   static constexpr int odO = oQ + QR * D * 2;                   // two slabs
   static constexpr int oP = odO + 2 * DO_SLAB;                  // P  : [BK/8][BR][16 B]  (MN-major B operand)
   static constexpr int oDC = oP + (BK / 8) * BR * 16;           // dC : same layout
-  static constexpr int oLD = oDC + (BK / 8) * BR * 16;          // two buffers of LSE*log2e [BR], D [BR]
-  static constexpr int oBar = oLD + 2 * 2 * BR * 4;
+  static constexpr int oBar = oDC + (BK / 8) * BR * 16;
   static constexpr int kSmemBytes = oBar + 512 + 1024;
-  static_assert(odO % 1024 == 0 && oV % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+  static_assert(odO % 1024 == 0 && oV % 1024 == 0 && oQ % 1024 == 0 && Q_SLAB % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
   static_assert(kSmemBytes <= 227 * 1024, "dK/dV kernel (d = 128): shared memory budget");
   static constexpr int kTmemCols = 512;        // dV^T at 0, dKt_a^T at 64 (1 + a), scratch X (S / dP) at 448
   static constexpr int colX = 448;
@@ -398,7 +404,7 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint64_t* kv_full = bars;
   uint64_t* q_full = kv_full + 1;        // Q of the block staged
   uint64_t* q_free = q_full + 1;         // the three issuers are done with it (3 commits)
-  uint64_t* do_full = q_free + 1;        // dO (and LSE / D) of the block staged
+  uint64_t* do_full = q_free + 1;        // dO of the block staged
   uint64_t* do_free = do_full + 1;       // dP and dV^T of the block have read it (2 commits)
   uint64_t* st_full = do_free + 1;       // S in X
   uint64_t* xs_free = st_full + 1;       // S taken into registers (256 arrivals): X free for the next dP
@@ -447,7 +453,7 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const uint32_t tX = tmem + Cfg::colX;
 
   if (warp == Cfg::kEwWarps) {
-    // ===================== producer warp (TMA + row statistics) =====================
+    // ===================== producer warp (TMA) =====================
     if (nblk > 0) {
       if (lane == 0) {
         tc::tma_prefetch_desc(&tmQ); tc::tma_prefetch_desc(&tmdO); tc::tma_prefetch_desc(&tmKt); tc::tma_prefetch_desc(&tmV);
@@ -462,19 +468,11 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       bool ok = true;
       for (int it = 0; it < nblk && ok; ++it) {
         const int i0 = (qb_begin + it) * BR;
-        // ---- dO and the row statistics of block `it` (free once dP and dV^T of block it-1 are done) ----
+        // ---- dO of block `it` (its buffer is free once dP and dV^T of block it-1 are done) ----
         if (it > 0) {
           ok = __all_sync(0xffffffffu, tc::mbar_wait(do_free, (it - 1) & 1, s_abort));
           if (!ok) break;
         }
-        float* ld = reinterpret_cast<float*>(smem + Cfg::oLD) + (it & 1) * 2 * BR;
-#pragma unroll
-        for (int r = lane; r < BR; r += 32) {
-          const int gi = i0 + r;
-          ld[r] = gi < N ? p.LSE[(size_t)bh * N + gi] * kLog2e : 0.f;
-          ld[BR + r] = gi < N ? p.Dvec[(size_t)bh * N + gi] : 0.f;
-        }
-        __syncwarp();
         if (lane == 0) {
           tc::mbar_expect_tx(do_full, 2 * Cfg::DO_SLAB);
           tc::tma_load_3d(sdO, &tmdO, do_full, 0, i0, bh);
@@ -488,10 +486,8 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         if (lane == 0) {
           tc::mbar_expect_tx(q_full, QR * D * 2);
-          for (int kc = 0; kc < D / 8; ++kc) {
-            tc::tma_load_3d(sQ + kc * (QR * 16), &tmQ, q_full, kc * 8, i0 - HALO, bh);
-            tc::tma_load_3d(sQ + kc * (QR * 16) + (QR / 2) * 16, &tmQ, q_full, kc * 8, i0 - HALO + QR / 2, bh);
-          }
+          tc::tma_load_3d(sQ, &tmQ, q_full, 0, i0 - HALO, bh);
+          tc::tma_load_3d(sQ + Cfg::Q_SLAB, &tmQ, q_full, 64, i0 - HALO, bh);
           *s_q_issued = it + 1;
         }
       }
@@ -505,8 +501,12 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint32_t v_lo = kt_lo + (uint32_t)((Cfg::oV - Cfg::oKt) >> 4);
       const uint64_t dOk = tc::make_sdesc(smem_u32(sdO), 16, 1024, tc::kLayoutSW128);
       const uint32_t o_lo = (uint32_t)dOk;                         // same high word as the Kt tiles
-      const uint64_t dQk = tc::make_sdesc(smem_u32(sQ) + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);   // K-major, M = rows
-      const uint32_t qk_hi = (uint32_t)(dQk >> 32), qk_lo = (uint32_t)dQk;
+      // Q^(a), K-major: the same swizzled tile with the start address moved down by the tap's row shift.  The
+      // tensor core applies the 128-byte swizzle to the absolute shared-memory address, exactly as TMA did when
+      // it wrote the tile, so a start that is a multiple of 128 bytes (not of the 1024-byte pattern) reads the
+      // shifted rows correctly.
+      const uint64_t dQk = tc::make_sdesc(smem_u32(sQ) + (HALO - pq) * 128, 16, 1024, tc::kLayoutSW128);
+      const uint32_t qk_lo = (uint32_t)dQk;                        // same high word as the Kt tiles
       bool ok = tc::mbar_wait_warp(kv_full, 0, s_abort);
       // X holds dP(it) first (taken into registers by the element-wise warps), then S(it):
       //   dP(0) | S(0) dP(1) | S(1) dP(2) | ...
@@ -529,11 +529,11 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // S = sum_a Q^(a) Kt_a^T
         for (int a = 0; a < cq; ++a) {
           const uint32_t b_lo = kt_lo + (uint32_t)(a * (Cfg::KT_BYTES >> 4));
-          const uint32_t a_lo = qk_lo + (uint32_t)a;
-          tc::mma_ss2pe(tX, a_lo, qk_hi, b_lo, kt_hi, idescT, a != 0);
+          const uint32_t a_lo = qk_lo + (uint32_t)(a * (128 >> 4));       // row shift = +128 B per row
+          tc::mma_ss2pe(tX, a_lo, kt_hi, b_lo, kt_hi, idescT, a != 0);
 #pragma unroll
           for (int k = 1; k < D / 16; ++k)
-            tc::mma_ss2e<1>(tX, a_lo + (uint32_t)(2 * k * QR), qk_hi,
+            tc::mma_ss2e<1>(tX, a_lo + (uint32_t)((k >> 2) * (Cfg::Q_SLAB >> 4) + (k & 3) * 2), kt_hi,
                             b_lo + (uint32_t)((k >> 2) * (Cfg::SLAB_BYTES >> 4) + (k & 3) * 2), kt_hi, idescT);
         }
         tc::mma_commit_e(st_full);
@@ -554,8 +554,8 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const int t_begin = ai == 0 ? 0 : t_half, t_end = ai == 0 ? t_half : ntap;
       // dO read MN-major (M = head dim across the two slabs, K = rows): 16 rows = 2048 bytes per step
       const uint64_t dOm = tc::make_sdesc(smem_u32(sdO), Cfg::DO_SLAB, 1024, tc::kLayoutSW128);
-      // Q read MN-major (M = head dim in 8-element chunks QR * 16 bytes apart, K = rows 16 bytes apart)
-      const uint64_t dQm = tc::make_sdesc(smem_u32(sQ) + (HALO - pq) * 16, 128, QR * 16, tc::kLayoutNone);
+      // Q read MN-major (M = head dim across the two slabs, K = rows, shifted by the tap through the start address)
+      const uint64_t dQm = tc::make_sdesc(smem_u32(sQ) + (HALO - pq) * 128, Cfg::Q_SLAB, 1024, tc::kLayoutSW128);
       // P / dC: N = keys in 8-key chunks BR * 16 bytes apart, K = rows 16 bytes apart
       const uint64_t dPb = tc::make_sdesc(smem_u32(smem + Cfg::oP), 128, BR * 16, tc::kLayoutNone);
       const uint64_t dCb = tc::make_sdesc(smem_u32(smem + Cfg::oDC), 128, BR * 16, tc::kLayoutNone);
@@ -580,11 +580,11 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         for (int i = t_begin; i < t_end; ++i) {
           const uint32_t dacc = tmem + 64 * (accb + i);
-          const uint32_t a_lo = qm_lo + (uint32_t)(tap0 + i);
+          const uint32_t a_lo = qm_lo + (uint32_t)((tap0 + i) * (128 >> 4));     // K (row) shift = +128 B per row
           tc::mma_ss2pe(dacc, a_lo, qm_hi, cb_lo, pb_hi, idescA, acc_on);
 #pragma unroll
           for (int k = 1; k < BR / 16; ++k)
-            tc::mma_ss2e<1>(dacc, a_lo + (uint32_t)(k * 16), qm_hi, cb_lo + (uint32_t)(k * 16), pb_hi, idescA);
+            tc::mma_ss2e<1>(dacc, a_lo + (uint32_t)(k * (2048 / 16)), qm_hi, cb_lo + (uint32_t)(k * 16), pb_hi, idescA);
         }
         tc::mma_commit_e(q_free);
         tc::mma_commit_e(pdc_free);
@@ -600,6 +600,12 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t tXl = tX + lane_base + CW * cg;
     bool ok = true;
     float dpc[CW];                                      // dP of the block about to be processed
+    // every thread fetches the statistics of its own row (LSE in log2 units, D), one block ahead
+    float lse2 = 0.f, dvec = 0.f;
+    if (nblk > 0) {
+      const int gi = qb_begin * BR + row;
+      if (gi < N) { lse2 = p.LSE[(size_t)bh * N + gi] * kLog2e; dvec = p.Dvec[(size_t)bh * N + gi]; }
+    }
     if (nblk > 0) {
       ok = __all_sync(0xffffffffu, p.selftest_expire ? tc::mbar_wait(never_bar, 0, s_abort, tc::kSelfTestSpinLimit)
                                                      : tc::mbar_wait(dpt_full, 0, s_abort));
@@ -613,10 +619,11 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int it = 0; it < nblk && ok; ++it) {
       const int i0 = (qb_begin + it) * BR;
       const int gi = i0 + row;
-      ok = __all_sync(0xffffffffu, tc::mbar_wait(do_full, it & 1, s_abort));    // the row statistics travel with dO
-      if (!ok) break;
-      const float* ld = reinterpret_cast<const float*>(smem + Cfg::oLD) + (it & 1) * 2 * BR;
-      const float lse2 = ld[row], dvec = ld[BR + row];
+      float lse2_next = 0.f, dvec_next = 0.f;
+      if (it + 1 < nblk && gi + BR < N) {
+        lse2_next = p.LSE[(size_t)bh * N + gi + BR] * kLog2e;
+        dvec_next = p.Dvec[(size_t)bh * N + gi + BR];
+      }
       ok = __all_sync(0xffffffffu, tc::mbar_wait(st_full, it & 1, s_abort));
       if (!ok) break;
       tc::tc_fence_after();
@@ -669,6 +676,7 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tc::tc_fence_before();
         tc::mbar_arrive(xd_free);
       }
+      lse2 = lse2_next; dvec = dvec_next;
     }
     // ---- epilogue: the accumulators hold dV^T and dKt_a^T (lane = head dim, column = key); chunks of 32
     // keys are dealt round-robin to the two column groups ----
@@ -751,12 +759,16 @@ cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, i
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dQ = p.dQ; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
-  auto kern = bwd_dq_tc128_kernel;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-  if (e != cudaSuccess) return e;
+  const char* ev = getenv("FMTA_DQ128_NSLOT");
+  const int ns = ev ? atoi(ev) : 10;
   dim3 grid((p.N + Cfg::OWN - 1) / Cfg::OWN, p.H, p.B);
-  { ScopedKernelTimer timer_(kKernBwdDqTc, stream);
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, p.dO, bp); }
+  ScopedKernelTimer timer_(kKernBwdDqTc, stream);
+#define FMTA_DQ128_LAUNCH(NS)                                                                                       \
+  { auto kern = bwd_dq_tc128_kernel<NS>;                                                                             \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq128CfgT<NS>::kSmemBytes); \
+    if (e != cudaSuccess) return e;                                                                                   \
+    kern<<<grid, Cfg::kThreads, Dq128CfgT<NS>::kSmemBytes, stream>>>(tmQ, tmKt, tmV, p.dO, bp); }
+  if (ns == 8) FMTA_DQ128_LAUNCH(8) else if (ns == 7) FMTA_DQ128_LAUNCH(7) else FMTA_DQ128_LAUNCH(10)
   return cudaGetLastError();
 }
 
@@ -766,7 +778,7 @@ cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt,
   constexpr int D = Cfg::D;
   const size_t BH = (size_t)p.B * p.H;
   alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV;
-  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR / 2, false)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 64, Cfg::QR, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmdO, p.dO, D, p.N, BH, 64, Cfg::BR, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmV, p.V, D, p.N, BH, 64, Cfg::BK, true)) return cudaErrorInvalidValue;

@@ -119,7 +119,7 @@ def test_head_mix_configuration_identity_mix_N8192_d128():
     dq, dw, dth = F.conv_headmix_bwd_dq_dw(q, k, v, eye, o, do, l, m, th, True, scale)
     dk, dv = F.conv_headmix_bwd_dkdv(q, k, v, eye, o, do, l, m, th, True, scale)
     Dv = F.rowdot(do, O)
-    rq, rk, rv, rth = F.backward(q, k, v, do, Dv, LSE, th, scale, cq - 1, (ck - 1) // 2, True)
+    rq, rk, rv, rth = F.backward(q, k, v, do, Dv, LSE, th, scale, cq - 1, (ck - 1) // 2, True, path=0)
     assert maxabs(dq, rq) <= TOL_BF16 and maxabs(dk, rk) <= TOL_BF16 and maxabs(dv, rv) <= TOL_BF16
     assert maxabs(dth, rth) <= max(TOL_BF16, 5e-3 * float(rth.abs().max()))
     w = (eye + 0.02 * torch.randn(H // G, G, G, device="cuda", generator=g)).contiguous()
