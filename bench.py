@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the conv-attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-decode]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl ours|reference] [--no-decode] [--no-sweep]
 
 One "step" = conv-attention forward + backward (D prep, dQ/dTheta, dK/dV, partial reduction,
 and for N > 1 the all-reduce of dTheta) on the bf16 training configuration
@@ -10,11 +10,17 @@ batch of 4; the only collective is the 4 KB dTheta all-reduce over NCCL).  `valu
 whole-job FlashAttention-convention throughput 14*d*E / t (E = causal score elements); the
 conv's own FLOPs are reported separately and never added to the numerator.
 
+The timed loop of K steps is repeated R times (default 5); `ms_per_step` / `value` are the MEDIAN
+loop, `ms_per_step_min` the fastest, and `ms_x_mhz` = ms_per_step x the median SM clock sampled
+during the loops, so that runs at different power-capped clocks can be compared.
+
 Also reported in the same JSON line: `e2e` (same step with host->device copies of Q,K,V,dO from
 pinned memory and the device->host read of dTheta inside the timed region), `roofline` for the
-dominant kernel, `cpu_baseline` (the CPU oracle -- a port of the reference's PyTorch path -- on
-the host cores, bounded sample), `decode` (fwd_inference over a 32768-long KV cache, HBM GB/s),
-clocks sampled during the timed region.
+dominant kernel with the whole step's fraction of peak beside it, `cpu_baseline` (the reference's
+PyTorch path on the host cores, bounded sample), `decode` (fwd_inference over a 32768-long KV
+cache, HBM GB/s), `sweep` (the d = 128 scaling configuration B=8, H=32, theta (6,11) at
+N = 1024 ... 65536 as ONE fixed problem sharded by (batch, head) over the ranks with the dTheta
+all-reduce: strong scaling), clocks sampled during the timed region.
 
 `--impl reference` times the reference's CPU path (the oracle port, all host threads) on a
 bounded sample of the same workload and prints the same kind of line with "impl": "reference".
@@ -38,6 +44,7 @@ for _p in (ROOT, os.path.join(ROOT, "flash-multi-token-attention_b200")):
 import torch  # noqa: E402
 
 CFG = dict(B=4, H=16, N=4096, d=64, cq=6, ck=11)                 # training configuration (per GPU)
+SWEEP = dict(B=8, H=32, d=128, cq=6, ck=11, Ns=(1024, 4096, 16384, 65536))      # scaling configuration (whole job)
 DEC = dict(B=32, H=32, d=128, Nk=32768, q_len=6, cq=6, ck=11, k_splits=4)   # decode configuration (4 CTAs/SM x 148 SMs: 4096 CTAs = 6.9 waves)
 METRIC = "conv-attn fwd+bwd TFLOP/s"
 
@@ -102,22 +109,56 @@ class ClockSampler:
         return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
 
 
+def _reference_module():
+    """The reference's own ConvAttention class, loaded by file path from the checkout that BASELINE.json
+    names -- when that checkout is present on this machine (it is not on a bare GPU box)."""
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            ref_root = json.load(f).get("reference_path")
+        path = os.path.join(ref_root, "flash_multi_token_attention", "conv_attn", "conv_attention_pytorch.py")
+        if not os.path.exists(path):
+            return None
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("_ref_conv_attention_pytorch", path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod.ConvAttention
+    except Exception:
+        return None
+
+
 def cpu_reference_sample(steps=1, warmup=0):
-    """The reference's CPU path (oracle port: dense scores, conv2d, softmax, autograd backward) on
-    ONE (batch, head) slice of the training configuration, all host threads."""
+    """The reference's CPU path (dense scores, conv2d, softmax, autograd backward) on ONE (batch, head)
+    slice of the training configuration, all host threads: the reference's own module when its checkout
+    is on this machine (kind "reference"), else the oracle's restatement of it (kind "port")."""
     from oracle import conv_attn_oracle as orc
     N, d, cq, ck = CFG["N"], CFG["d"], CFG["cq"], CFG["ck"]
     Q, K, V, dO, th = orc.make_inputs(1, 1, N, d, cq, ck, seed=0, dtype=torch.bfloat16)
     scale = 1.0 / math.sqrt(d)
+    RefCls = _reference_module()
+    kind = "reference" if RefCls is not None else "port"
+    if RefCls is not None:
+        mod = RefCls(1, cq, ck)
+        with torch.no_grad():
+            mod.conv_weight.copy_(th)
+
+        def run():
+            q, k, v = (t.clone().requires_grad_(True) for t in (Q, K, V))
+            mod.conv_weight.grad = None
+            out = mod(q, k, v, causal=True, softmax_scale=scale)
+            (out[0] if isinstance(out, tuple) else out).backward(dO)
+    else:
+        def run():
+            orc.conv_attn_bwd_autograd(Q, K, V, th, dO, scale, True)   # forward + backward
     ts = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        orc.conv_attn_bwd_autograd(Q, K, V, th, dO, scale, True)   # forward + backward
+        run()
         if i >= warmup:
             ts.append(time.perf_counter() - t0)
     t = sum(ts) / len(ts)
     fl, _ = flops_attn(1, 1, N, d)
-    return dict(value=fl / t / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
+    return dict(value=fl / t / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind=kind,
                 sample="1 of %d (batch, head) slices of the workload, fwd+bwd, fp32, %d run(s), %.2f s each; "
                        "slices are independent so the full job is %dx this" % (CFG["B"] * CFG["H"], len(ts), t,
                                                                               CFG["B"] * CFG["H"]),
@@ -149,7 +190,10 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated (median reported)")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--sweep-max-n", type=int, default=65536)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="tiny shapes (profiling / debugging)")
     ap.add_argument("--train-shape", default=None, help="B,H,N,d of the training step (profiling captures)")
@@ -195,7 +239,7 @@ def main():
     # (cudaEventRecord around that one launch, on the launch stream)
     KERNELS = {1: "fwd_tc_kernel", 2: "fwd_band_kernel", 3: "bwd_dq_tc_kernel", 4: "bwd_dkdv_tc_kernel",
                5: "bwd_dq_kernel", 6: "bwd_dkdv_kernel", 8: "bwd_band_kernel", 9: "ktilde_window_kernel",
-               10: "dk_post_window_kernel"}
+               10: "dk_post_mma_kernel"}
     DOMINANT = 4
     kern_ev = []   # (start, end) events around the dominant kernel, per step
 
@@ -252,9 +296,9 @@ def main():
         dist.broadcast(n_extra, src=0)
     for _ in range(int(n_extra.item())):
         step(q, k, v, do)
-    ms = timed(lambda: step(q, k, v, do, record=True), args.steps)
-    clocks = sampler.stop() if sampler else None
-    ms_step = ms / args.steps
+    loops = [timed(lambda: step(q, k, v, do, record=True), args.steps) / args.steps for _ in range(max(1, args.repeats))]
+    F.check_device_status(dev)             # raises if a bounded wait inside a tensor-core kernel ran out
+    ms_step = statistics.median(loops)
     fl, E = flops_attn(B, H, N, d)
     value = world * fl / (ms_step * 1e-3) / 1e12
 
@@ -288,32 +332,39 @@ def main():
             dth_host.copy_(out[4], non_blocking=True)
 
     e2e_run(2)
-    barrier()
-    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    e2e_run(args.steps)
-    e1.record(stream)
-    barrier()
-    ms_e2e = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_e2e], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = float(t.item())
-    ms_e2e /= args.steps
+    e2e_loops = []
+    for _ in range(max(1, args.repeats)):
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        e2e_run(args.steps)
+        e1.record(stream)
+        barrier()
+        t_ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([t_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_ms = float(t.item())
+        e2e_loops.append(t_ms / args.steps)
+    clocks = sampler.stop() if sampler else None
+    ms_e2e = statistics.median(e2e_loops)
     h2d = sum(t.numel() * t.element_size() for t in host)
     e2e = dict(value=world * fl / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", h2d_bytes_per_step=h2d,
-               d2h_bytes_per_step=dth_host.numel() * 4, ms_per_step=ms_e2e,
+               d2h_bytes_per_step=dth_host.numel() * 4, ms_per_step=ms_e2e, ms_per_step_min=min(e2e_loops),
                note="inputs of step i+1 are copied on a second stream while step i computes")
 
     # ---- roofline of the dominant kernel: bwd_dkdv_tc_kernel (dK~/dV on tcgen05) ----
-    # algorithmic work of that kernel per launch (FlashAttention convention): recompute S, dP,
-    # then dV and dK = 4 contractions of 2*d FLOPs per score entry = 8*d*E; the stacked filter taps
-    # make it EXECUTE 2*d*(2*cq + 2) per entry, reported beside it
+    # The step's algorithmic work is 14*d*E (FlashAttention convention: forward S and PV = 4*d*E, backward
+    # S, dP, dV, dK, dQ = 10*d*E).  Both backward kernels recompute S and dP, so each is credited half of
+    # those two contractions: forward 4*d*E, dQ kernel 2*d*E + 2*d*E = 4*d*E, dK/dV kernel 4*d*E + 2*d*E =
+    # 6*d*E -- the three shares add up to the step's 14*d*E.  The stacked filter taps make the dK/dV
+    # kernel EXECUTE 2*d*(2*cq + 2) per entry, reported beside it.  `step_frac` is the whole step against
+    # the same peak.
     peaks = measured_peaks()
     kms = statistics.mean(a_.elapsed_time(b_) for a_, b_ in kern_ev) if kern_ev else None
     roof = None
     if kms:
-        ach = 8.0 * d * E / (kms * 1e-3) / 1e12
+        ach = 6.0 * d * E / (kms * 1e-3) / 1e12
         exe = 2.0 * d * (2 * cq + 2) * E / (kms * 1e-3) / 1e12
         # DRAM bytes per launch from the committed ncu capture at B=2,H=16,N=4096 (152.1 MB read + 89.3 MB
         # written; summary under profiles/), scaled by the (batch, head)
@@ -324,19 +375,26 @@ def main():
                     traffic=traffic, traffic_unit="bytes per launch (ncu capture of a smaller case, scaled)",
                     ms_per_launch=kms, executed_tflops=exe,
                     executed_frac=exe / peaks["tflops_sustained"],
-                    note="achieved counts 8*d*E algorithmic FLOPs; the kernel executes 2*d*(2*c_q+2)*E "
-                         "(stacked filter taps on the tensor cores) = executed_tflops")
+                    step_tflops=fl / (ms_step * 1e-3) / 1e12,
+                    step_frac=fl / (ms_step * 1e-3) / 1e12 / peaks["tflops_sustained"],
+                    step_executed_tflops=(2.0 * d * (cq + 1) + 2.0 * d * (2 * cq + 2) + 2.0 * d * (2 * cq + 2)) * E / (ms_step * 1e-3) / 1e12,
+                    note="achieved counts the kernel's share (6*d*E) of the step's 14*d*E algorithmic FLOPs; it "
+                         "executes 2*d*(2*c_q+2)*E (stacked filter taps on the tensor cores) = executed_tflops; "
+                         "step_frac = 14*d*E / ms_per_step / peak (per GPU)")
 
+    sm_mhz = clocks["sm_mhz"] if clocks else None
     line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
-                ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                repeats=len(loops), ms_per_step=ms_step, ms_per_step_min=min(loops),
+                ms_x_mhz=(ms_step * sm_mhz) if sm_mhz else None, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
                 data="synthetic",
                 config=dict(workload="train fwd+bwd bf16 B=%d(per GPU),H=%d,N=%d,d=%d,theta(%d,%d),causal" % (B, H, N, d, cq, ck),
                             global_batch=B * world, parallelism="batch x head sharding, dTheta all-reduce" if world > 1 else "single GPU",
                             l2="inputs+outputs per step (%.0f MB) exceed the 126 MB L2" % ((4 * 2 + 4 * 4) * B * H * N * d / 1e6),
                             flops_attn_gflop=fl / 1e9, flops_conv_gflop=8 * cq * ck * E / 1e9),
-                # kernels of this library per step: forward = stacked-key pre-pass, fwd_tc, fwd_band; rowdot;
-                # backward = pre-pass, dq_tc, dkdv_tc, Toeplitz tiles + dKt adjoint, bwd_band, partial reduction
-                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=11 * args.steps)
+                # kernels of this library per step: forward = stacked-key pre-pass, fwd_tc, status fold, fwd_band;
+                # rowdot; backward = pre-pass, dq_tc, dkdv_tc, Toeplitz tiles + dKt adjoint, status fold, bwd_band,
+                # partial reduction
+                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=13 * args.steps * len(loops))
 
     # ---- decode (HBM-bound), rank-local, reported beside the headline ----
     if not args.no_decode:
@@ -345,12 +403,98 @@ def main():
         except torch.OutOfMemoryError as e:   # pragma: no cover
             line["decode"] = dict(error="out of memory: %s" % str(e)[:80])
 
+    # ---- the d = 128 scaling configuration: one fixed problem, sharded by (batch, head) ----
+    if not args.no_sweep and not args.small and not args.train_shape:
+        try:
+            line["sweep"] = bench_sweep(F, dev, world, rank, peaks, barrier, args.sweep_max_n)
+        except torch.OutOfMemoryError as e:   # pragma: no cover
+            line["sweep"] = dict(error="out of memory: %s" % str(e)[:80])
+        F.check_device_status(dev)
+
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_reference_sample(steps=3, warmup=1)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_sweep(F, dev, world, rank, peaks, barrier, max_n):
+    """Scaling configuration: conv-attention forward + backward, bf16, d = 128, theta (6,11), causal,
+    B x H = 8 x 32 = 256 (batch, head) units as ONE problem at each sequence length, divided among the
+    ranks by fmta_b200.sharding (a head split here: every rank owns H/world heads of every batch entry),
+    the filter gradient summed by sharding.allreduce_param_grad (NCCL).  Inputs are seeded per
+    (sequence length, batch, head), so the problem is the same for any number of ranks.  A rank walks its
+    slice in batch chunks small enough for about 24 GB of device memory per chunk."""
+    import torch.distributed as dist
+    from fmta_b200 import sharding
+    B, H, d, cq, ck = (SWEEP[k] for k in ("B", "H", "d", "cq", "ck"))
+    scale = 1.0 / math.sqrt(d)
+    plan = sharding.shard_plan(B, H, 1, world, rank)
+    assert plan["mode"] in ("head", "batch")
+    Bl, Hl = plan["b_hi"] - plan["b_lo"], plan["h_hi"] - plan["h_lo"]
+    th_full = torch.randn(H, cq, ck, generator=torch.Generator().manual_seed(11)) * 0.02
+    th_full[:, cq - 1, ck // 2] += 1.0
+    th = th_full[plan["h_lo"]:plan["h_hi"]].contiguous().to(dev)
+    stream = torch.cuda.current_stream()
+    points = []
+    for N in SWEEP["Ns"]:
+        if N > max_n:
+            continue
+        per_bh = N * d * 64                         # inputs, outputs and workspaces of one (batch, head) pair, bytes
+        bchunk = max(1, min(Bl, int(24e9 // (per_bh * Hl))))
+        data = []
+        for b in range(plan["b_lo"], plan["b_hi"]):
+            t4 = []
+            for _ in range(4):
+                t4.append(torch.empty(Hl, N, d, device=dev, dtype=torch.bfloat16))
+            for hi, h in enumerate(range(plan["h_lo"], plan["h_hi"])):
+                g = torch.Generator(device=dev).manual_seed(1000003 * N + 131 * b + h)
+                for t in t4:
+                    t[hi] = torch.randn(N, d, device=dev, generator=g).to(torch.bfloat16)
+            data.append(t4)
+        chunks = []
+        for c0 in range(0, Bl, bchunk):
+            chunks.append([torch.stack([data[b][i] for b in range(c0, min(Bl, c0 + bchunk))]) for i in range(4)])
+        del data
+
+        def step():
+            dth = None
+            for q, k, v, do in chunks:
+                O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True)
+                D = F.rowdot(do, O)
+                dQ, dK, dV, dTh = F.backward(q, k, v, do, D, LSE, th, scale, cq - 1, (ck - 1) // 2, True)
+                dth = dTh if dth is None else dth + dTh
+            return sharding.allreduce_param_grad(dth, plan)      # [H, cq, ck] on every rank
+
+        fl, E = flops_attn(B, H, N, d)
+        est = fl / (150e12 * world)                  # seconds per step at about 150 TFLOP/s per GPU
+        steps = max(1, min(10, int(2.0 / max(est, 1e-4))))
+        step()                                       # warm-up
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            out = step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        tf = fl / (ms * 1e-3) / 1e12
+        points.append(dict(N=N, ms_per_step=ms, steps=steps, value=tf, unit="TFLOP/s", per_gpu_tflops=tf / world,
+                           frac_of_peak=tf / world / peaks["tflops_sustained"], flops_attn_tflop=fl / 1e12,
+                           units_per_rank=Bl * Hl, batch_chunk=bchunk,
+                           dtheta_checksum=float(out.double().abs().sum().item())))
+        del chunks
+        torch.cuda.empty_cache()
+    return dict(metric="conv-attn fwd+bwd TFLOP/s, scaling configuration", scaling="strong",
+                config=dict(workload="train fwd+bwd bf16 B=%d,H=%d,d=%d,theta(%d,%d),causal, one problem per N "
+                                     "sharded by (batch, head)" % (B, H, d, cq, ck), shard_mode=plan["mode"],
+                            collective="all-reduce of dTheta [H,%d,%d] fp32 (NCCL)" % (cq, ck) if world > 1 else "none"),
+                peak=peaks["tflops_sustained"], peak_source=peaks["source"] + " (sustained)", points=points)
 
 
 def bench_decode(F, dev, dec, peaks, world, timed):

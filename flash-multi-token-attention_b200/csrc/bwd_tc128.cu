@@ -24,7 +24,6 @@
 // Every mbarrier wait is bounded; no TMA multicast, no cluster, cta_group::1 only.
 #include <cuda.h>
 #include <cuda_runtime.h>
-#include <cstdlib>
 
 #include "bwd_tc.cuh"
 #include "fmta_tc.cuh"
@@ -35,8 +34,7 @@ namespace fmta {
 // ==========================================================================================
 // dQ, d = 128
 // ==========================================================================================
-template <int NSLOT_>
-struct Dq128CfgT {
+struct Dq128Cfg {
   static constexpr int D = 128;
   static constexpr int BM = 128;               // dC rows per tile (= TMEM lanes)
   static constexpr int OWN = 120;              // dQ rows a tile owns (dQ row i needs dC rows i .. i + pad_q, pad_q <= 8)
@@ -46,9 +44,10 @@ struct Dq128CfgT {
   static constexpr int DR = BM + 16;           // rows of the dC buffer (16 zero rows below)
   static constexpr int SLAB_BYTES = BC * 128;  // 64 keys x 64 elements, 128-byte swizzle
   static constexpr int TILE_BYTES = 2 * SLAB_BYTES;   // one Kt / V ring tile: two column slabs
-  static constexpr int NSLOT = NSLOT_;
-  static constexpr int oQ = 0;                                  // [D/8][QR][16 B]
-  static constexpr int odC = oQ + QR * D * 2;                   // [BC/8][DR][16 B]
+  static constexpr int NSLOT = 10;
+  static constexpr int Q_SLAB = QR * 128;      // 144 rows x 64 elements, 128-byte swizzle
+  static constexpr int oQ = 0;                                  // two slabs
+  static constexpr int odC = oQ + 2 * Q_SLAB;                   // [BC/8][DR][16 B]
   static constexpr int oRing = ((odC + (BC / 8) * DR * 16 + 1023) / 1024) * 1024;
   static constexpr int oBar = oRing + NSLOT * TILE_BYTES;
   static constexpr int kSmemBytes = oBar + 512 + 1024;
@@ -58,13 +57,10 @@ struct Dq128CfgT {
   static constexpr int kThreads = (4 + 1 + 2) * 32;   // element-wise warpgroup, TMA warp, two MMA issuer warps
 };
 
-using Dq128Cfg = Dq128CfgT<10>;
-
-template <int NSLOT_>
-__global__ void __launch_bounds__(Dq128CfgT<NSLOT_>::kThreads, 1)
+__global__ void __launch_bounds__(Dq128Cfg::kThreads, 1)
 bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKt,
                     const __grid_constant__ CUtensorMap tmV, const bf16* __restrict__ dO, const BwdTcParams p) {
-  using Cfg = Dq128CfgT<NSLOT_>;
+  using Cfg = Dq128Cfg;
   constexpr int D = Cfg::D, BM = Cfg::BM, OWN = Cfg::OWN, BC = Cfg::BC, HALO = Cfg::HALO, QR = Cfg::QR;
   constexpr int DR = Cfg::DR, NSLOT = Cfg::NSLOT;
   extern __shared__ unsigned char smem_raw[];
@@ -132,10 +128,8 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0 && nkb > 0) {
       tc::tma_prefetch_desc(&tmQ); tc::tma_prefetch_desc(&tmKt); tc::tma_prefetch_desc(&tmV);
       tc::mbar_expect_tx(q_full, QR * D * 2);
-      for (int kc = 0; kc < D / 8; ++kc) {
-        tc::tma_load_3d(sQ + kc * (QR * 16), &tmQ, q_full, kc * 8, R0 - HALO, bh);
-        tc::tma_load_3d(sQ + kc * (QR * 16) + (QR / 2) * 16, &tmQ, q_full, kc * 8, R0 - HALO + QR / 2, bh);
-      }
+      tc::tma_load_3d(sQ, &tmQ, q_full, 0, R0 - HALO, bh);
+      tc::tma_load_3d(sQ + Cfg::Q_SLAB, &tmQ, q_full, 64, R0 - HALO, bh);
       int id = 0;
       bool ok = true;
       auto put = [&](const CUtensorMap* map, int y, int z) {
@@ -158,7 +152,9 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (nkb > 0) {   // all lanes run the loop; one elected lane issues (see tc::elect_one)
       constexpr uint32_t idescS = tc::make_idesc(BM, BC, 0, 0);    // S, dP: 128 x 64, K-major operands
       constexpr uint32_t idescQ = tc::make_idesc(BM, D, 0, 1);     // dQ: 128 x 128, B (Kt) MN-major
-      const uint64_t dQa = tc::make_sdesc(smem_u32(sQ) + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);
+      // Q^(a): the swizzled tile with its start address moved by the tap's row shift, 128 bytes per row (the
+      // tensor core swizzles the absolute shared-memory address, as TMA did when it wrote the tile)
+      const uint64_t dQa = tc::make_sdesc(smem_u32(sQ) + (HALO - pq) * 128, 16, 1024, tc::kLayoutSW128);
       const uint64_t dCa = tc::make_sdesc(smem_u32(sdC), DR * 16, 128, tc::kLayoutNone);
       const uint64_t dKb = tc::make_sdesc(smem_u32(sRing), 16, 1024, tc::kLayoutSW128);
       // the same tile read MN-major, 128 columns wide: the second 64-column slab starts SLAB_BYTES further
@@ -181,11 +177,11 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
             tc::tc_fence_after();
             const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
-            const uint32_t a_lo = q_lo + (uint32_t)a;
+            const uint32_t a_lo = q_lo + (uint32_t)(a * (128 >> 4));
             tc::mma_ss2pe(tSb, a_lo, q_hi, b_lo, k_hi, idescS, a != 0);
 #pragma unroll
             for (int k = 1; k < D / 16; ++k)
-              tc::mma_ss2e<1>(tSb, a_lo + (uint32_t)(2 * k * QR), q_hi,
+              tc::mma_ss2e<1>(tSb, a_lo + (uint32_t)((k >> 2) * (Cfg::Q_SLAB >> 4) + (k & 3) * 2), q_hi,
                               b_lo + (uint32_t)((k >> 2) * (Cfg::SLAB_BYTES >> 4) + (k & 3) * 2), k_hi, idescS);
             tc::mma_commit_e(&empty[slot]);      // (the dQ issuer holds the Kt tile until dQ(kb) is done)
           }
@@ -752,23 +748,19 @@ cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, i
   constexpr int D = Cfg::D;
   const size_t BH = (size_t)p.B * p.H;
   alignas(64) CUtensorMap tmQ, tmKt, tmV;
-  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR / 2, false)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 64, Cfg::QR, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmV, p.V, D, p.N, BH, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
   BwdTcParams bp = {};
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dQ = p.dQ; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
-  const char* ev = getenv("FMTA_DQ128_NSLOT");
-  const int ns = ev ? atoi(ev) : 10;
+  auto kern = bwd_dq_tc128_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
   dim3 grid((p.N + Cfg::OWN - 1) / Cfg::OWN, p.H, p.B);
-  ScopedKernelTimer timer_(kKernBwdDqTc, stream);
-#define FMTA_DQ128_LAUNCH(NS)                                                                                       \
-  { auto kern = bwd_dq_tc128_kernel<NS>;                                                                             \
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq128CfgT<NS>::kSmemBytes); \
-    if (e != cudaSuccess) return e;                                                                                   \
-    kern<<<grid, Cfg::kThreads, Dq128CfgT<NS>::kSmemBytes, stream>>>(tmQ, tmKt, tmV, p.dO, bp); }
-  if (ns == 8) FMTA_DQ128_LAUNCH(8) else if (ns == 7) FMTA_DQ128_LAUNCH(7) else FMTA_DQ128_LAUNCH(10)
+  { ScopedKernelTimer timer_(kKernBwdDqTc, stream);
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, p.dO, bp); }
   return cudaGetLastError();
 }
 

@@ -30,3 +30,26 @@ def _device_status_clean(request):
         return
     import fmta_b200
     fmta_b200.check_device_status()
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """Per-configuration error table of a GPU session: the largest absolute and relative error of every
+    output over the comparisons made through helpers.check_outputs, printed and (when the folder exists)
+    written to gpurun_out/parity_errors.txt."""
+    try:
+        import helpers
+    except Exception:
+        return
+    if not helpers.ERROR_LOG:
+        return
+    worst = {}
+    for label, key, err, ref in helpers.ERROR_LOG:
+        worst[(label, key)] = (err, ref)
+    lines = ["%-78s %-7s %10s %10s %9s" % ("comparison", "output", "max-abs", "max|ref|", "relative")]
+    for (label, key), (err, ref) in worst.items():
+        lines.append("%-78s %-7s %10.3e %10.3g %9.1e" % (label, key, err, ref, err / ref if ref > 0 else 0.0))
+    text = "\n".join(lines)
+    out = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, "parity_errors.txt"), "w") as f:
+            f.write(text + "\n")

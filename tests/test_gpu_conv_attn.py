@@ -5,7 +5,7 @@ import math
 import pytest
 import torch
 
-from helpers import TOL_BF16, load_golden, maxabs, bf16_round
+from helpers import TOL_BF16, load_golden, maxabs, bf16_round, check_outputs, dtheta_tol
 from oracle import conv_attn_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -25,21 +25,12 @@ def _run_fwd_bwd(Q, K, V, dO, theta, scale, causal):
     return dict(O=O, M=M, L=L, LSE=LSE, dQ=dQ, dK=dK, dV=dV, dTheta=dTh)
 
 
-def _check(got, ref, tol=TOL_BF16, dtheta_rel=None):
-    errs = {}
-    for k in ("O", "dQ", "dK", "dV"):
-        errs[k] = maxabs(got[k], ref[k])
-    errs["LSE"] = maxabs(got["LSE"], ref["M"] + torch.log(ref["L"]))
-    errs["M"] = maxabs(got["M"], ref["M"])
-    errs["dTheta"] = maxabs(got["dTheta"], ref["dTheta"])
-    # L is compared through LSE (it scales with exp(-M)); M and the gradients directly
-    bad = {k: v for k, v in errs.items() if not (v <= tol)}
-    if dtheta_rel is not None and "dTheta" in bad:
-        # the filter gradient is a sum over B*N^2 entries: allow the tolerance relative to its size
-        if errs["dTheta"] <= dtheta_rel * float(ref["dTheta"].abs().max()):
-            bad.pop("dTheta")
-    assert not bad, "max-abs errors above tolerance: %s (all: %s)" % (bad, errs)
-    return errs
+def _check(got, ref, label):
+    """O, M, LSE, dQ, dK, dV within 2e-2 of the oracle; dTheta within the one bound every path is held to
+    (helpers.dtheta_tol).  L is compared through LSE (it scales with exp(-M))."""
+    r = dict(O=ref["O"], M=ref["M"], LSE=ref["M"] + torch.log(ref["L"]), dQ=ref["dQ"], dK=ref["dK"], dV=ref["dV"],
+             dTheta=ref["dTheta"])
+    check_outputs(got, r, label)
 
 
 @pytest.mark.parametrize("name", ["conv_ref_script_3x3", "conv_c0_3x5", "conv_6x11_ragged",
@@ -60,7 +51,7 @@ def test_golden(name):
         dQ, dK, dV, dTh = orc.conv_attn_bwd_autograd(Q, K, V, z["theta"], dO, scale, causal)
         ref = dict(O=O, M=M, L=L, dQ=dQ, dK=dK, dV=dV, dTheta=dTh)
     got = _run_fwd_bwd(Q, K, V, dO, z["theta"], scale, causal)
-    _check(got, ref, dtheta_rel=5e-3)
+    _check(got, ref, "golden %s" % name)
 
 
 @pytest.mark.parametrize("B,H,N,d,cq,ck,causal", [
@@ -80,7 +71,7 @@ def test_oracle_shapes(B, H, N, d, cq, ck, causal):
     O, M, L = orc.conv_attn_fwd(Q, K, V, theta, scale, causal)
     dQ, dK, dV, dTh = orc.conv_attn_bwd_autograd(Q, K, V, theta, dO, scale, causal)
     got = _run_fwd_bwd(Q, K, V, dO, theta, scale, causal)
-    _check(got, dict(O=O, M=M, L=L, dQ=dQ, dK=dK, dV=dV, dTheta=dTh), dtheta_rel=5e-3)
+    _check(got, dict(O=O, M=M, L=L, dQ=dQ, dK=dK, dV=dV, dTheta=dTh), "B%d H%d N%d d%d theta(%d,%d) causal=%d separate calls" % (B, H, N, d, cq, ck, causal))
 
 
 def test_module_autograd_matches_oracle():
@@ -101,7 +92,7 @@ def test_module_autograd_matches_oracle():
     assert maxabs(q.grad, dQ) <= TOL_BF16 and q.grad.dtype == torch.bfloat16
     assert maxabs(k.grad, dK) <= TOL_BF16
     assert maxabs(v.grad, dV) <= TOL_BF16
-    assert maxabs(mod.conv_weight.grad, dTh) <= max(TOL_BF16, 5e-3 * float(dTh.abs().max()))
+    assert maxabs(mod.conv_weight.grad, dTh) <= dtheta_tol(dTh)
 
 
 def test_backward_is_deterministic():
@@ -184,10 +175,25 @@ def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
     rq, rk, rv, rt = orc.conv_attn_bwd_autograd(Q, K, V, theta, dO, scale, causal)
     _check(dict(O=O, M=M, L=L, LSE=LSE, dQ=dQ, dK=dK, dV=dV, dTheta=dTh),
            dict(O=Or, M=Mr, L=Lr, dQ=rq, dK=rk, dV=rv, dTheta=rt),
-           # dTheta is a heavily cancelling sum over all score entries; on the tensor-core path both of
-           # its factors (dC and the stacked keys) have been rounded to bf16, and for filters with one
-           # or two query taps the error reaches 1e-2 of max|dTheta| (5e-3 for the exact kernels)
-           dtheta_rel=5e-3 if path == 0 else 1.5e-2)
+           "B%d H%d N%d d%d theta(%d,%d) causal=%d path %d" % (B, H, N, d, cq, ck, causal, path))
+
+
+def test_fp32_configuration_N256_theta_3x5_both_paths():
+    """The fp32 CPU-path configuration of the benchmark (B=1, H=4, N=256, d=64, theta (3,5), N(0,0.05)
+    filter) run through the bf16 kernels on both paths, against the oracle on the same bf16-rounded inputs."""
+    import fmta_b200 as F
+    B, H, N, d, cq, ck = 1, 4, 256, 64, 3, 5
+    Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=0, theta_std=0.05, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
+    th = theta.cuda()
+    Or, Mr, Lr = orc.conv_attn_fwd(Q, K, V, theta, scale, True)
+    rq, rk, rv, rt = orc.conv_attn_bwd_autograd(Q, K, V, theta, dO, scale, True)
+    for path in (0, 1):
+        O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True, path=path)
+        dQ, dK, dV, dTh = F.backward(q, k, v, do, F.rowdot(do, O), LSE, th, scale, cq - 1, (ck - 1) // 2, True, path=path)
+        _check(dict(O=O, M=M, L=L, LSE=LSE, dQ=dQ, dK=dK, dV=dV, dTheta=dTh),
+               dict(O=Or, M=Mr, L=Lr, dQ=rq, dK=rk, dV=rv, dTheta=rt), "config 0 (N=256, theta (3,5)) path %d" % path)
 
 
 def test_tensor_core_path_rejected_when_unsupported():
