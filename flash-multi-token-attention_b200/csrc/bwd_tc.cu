@@ -363,7 +363,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // ==========================================================================================
 // dK-tilde / dV
 // ==========================================================================================
-template <int D, int CQMAX, bool PAIR>   // PAIR: stage Q twice so that two adjacent taps share one 128-wide MMA
+template <int D, int CQMAX, bool PAIR>   // PAIR: two adjacent taps share one 128-wide MMA
 struct DkvCfg {
   static_assert(D == 64, "the dK/dV tensor-core kernel is instantiated for d = 64");
   static constexpr int BK = 128;               // keys per CTA (= TMEM lanes)
@@ -377,8 +377,8 @@ struct DkvCfg {
   static constexpr int oV = oKt + MAXCQ * KT_BYTES;
   static constexpr int oStage = oV + KT_BYTES;
   static constexpr int sgdO = 0;                                  // [64 rows][128 B], 128B swizzle
-  static constexpr int sgQ = BR * 128;                            // [D/8][QR][16 B], then the same again one row later
-  static constexpr int sgLD = sgQ + (PAIR ? 2 : 1) * QR * D * 2;  // LSE*log2e [64], D [64]
+  static constexpr int sgQ = BR * 128;                            // [QR rows][128 B], 128B swizzle (one TMA copy)
+  static constexpr int sgLD = sgQ + QR * 128;                     // LSE*log2e [64], D [64]
   static constexpr int STAGE_BYTES = ((sgLD + 2 * BR * 4 + 1023) / 1024) * 1024;
   static constexpr int oPT = oStage + NSTG * STAGE_BYTES;         // P^T : [BR/8][128 keys][16 B] (K-major A operand)
   static constexpr int oDCT = oPT + (BR / 8) * BK * 16;           // dC^T: same layout
@@ -479,14 +479,9 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         __syncwarp();
         if (lane == 0) {
-          tc::mbar_expect_tx(&full[st], BR * 128 + (PAIR ? 2 : 1) * QR * D * 2);
+          tc::mbar_expect_tx(&full[st], BR * 128 + QR * 128);
           tc::tma_load_3d(sg + Cfg::sgdO, &tmdO, &full[st], 0, i0, bh);
-          // Q twice: the second copy starts one row later and sits where the column chunks 8..15 of a
-          // 128-wide MN-major operand fall, so that ONE 128 x 128 MMA accumulates two adjacent filter
-          // taps (dKt_a | dKt_{a+1}) += dC^T [Q^(a) | Q^(a+1)]
-          for (int cp = 0; cp < (PAIR ? 2 : 1); ++cp)
-            for (int kc = 0; kc < D / 8; ++kc)
-              tc::tma_load_3d(sg + Cfg::sgQ + (cp * (D / 8) + kc) * (QR * 16), &tmQ, &full[st], kc * 8, i0 - HALO + cp, bh);
+          tc::tma_load_3d(sg + Cfg::sgQ, &tmQ, &full[st], 0, i0 - HALO, bh);
           *s_issued = it + 1;
         }
       }
@@ -519,18 +514,20 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int it = 0; it < nblk && ok; ++it) {
         const int st = it % NSTG;
         const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
-        const uint64_t dQk = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, QR * 16, 128, tc::kLayoutNone);   // K-major, N = rows
+        // Q^(a), K-major, N = rows: the swizzled tile with its start address moved by the tap's row shift,
+        // 128 bytes per row (the tensor core swizzles the absolute shared-memory address, as TMA did)
+        const uint64_t dQk = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 128, 16, 1024, tc::kLayoutSW128);
         const uint32_t qk_hi = (uint32_t)(dQk >> 32), qk_lo = (uint32_t)dQk;
         if (!tc::mbar_wait_warp(xd_free, it & 1, s_abort)) { ok = false; break; }   // dP^T(it) has left X
         tc::tc_fence_after();
         // S^T = sum_a Kt_a Q^(a)T
         for (int a = 0; a < cq; ++a) {
           const uint32_t a_lo = kt_lo + (uint32_t)(a * (Cfg::KT_BYTES >> 4));
-          const uint32_t b_lo = qk_lo + (uint32_t)a;
+          const uint32_t b_lo = qk_lo + (uint32_t)(a * (128 >> 4));
           tc::mma_ss2pe(tX, a_lo, kt_hi, b_lo, qk_hi, idescT, a != 0);
 #pragma unroll
           for (int k = 1; k < D / 16; ++k)
-            tc::mma_ss2e<1>(tX, a_lo + (uint32_t)(2 * k), kt_hi, b_lo + (uint32_t)(2 * k * QR), qk_hi, idescT);
+            tc::mma_ss2e<1>(tX, a_lo + (uint32_t)(2 * k), kt_hi, b_lo + (uint32_t)(2 * k), qk_hi, idescT);
         }
         tc::mma_commit_e(st_full);
         tc::mma_commit_e(&empty[st]);        // this issuer's reads of the stage (dO for dP^T, Q for S^T) are done then
@@ -559,7 +556,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int it = 0; it < nblk && ok; ++it) {
         const int st = it % NSTG, ph = (it / NSTG) & 1;
         const uint32_t sg = smem_u32(sStage + st * Cfg::STAGE_BYTES);
-        const uint64_t dQm = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 16, 128, QR * 16, tc::kLayoutNone);   // MN-major, K = rows
+        // the same tile read MN-major (N = head dim, K = rows shifted by the tap).  A second 64-column atom
+        // placed 128 bytes = ONE ROW after the first is the next tap's operand, so ONE 128 x 128 MMA
+        // accumulates two adjacent filter taps (dKt_a | dKt_{a+1}) += dC^T [Q^(a) | Q^(a+1)] from one copy of Q
+        const uint64_t dQm = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 128, 128, 1024, tc::kLayoutSW128);
         const uint64_t dOk = tc::make_sdesc(sg + Cfg::sgdO, 16, 1024, tc::kLayoutSW128);
         const uint32_t qm_hi = (uint32_t)(dQm >> 32), qm_lo = (uint32_t)dQm;
         const uint32_t o_hi = (uint32_t)(dOk >> 32), o_lo = (uint32_t)dOk;
@@ -577,12 +577,12 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const bool pair = gi < pairs;
           const int i = pair ? 2 * gi : 2 * pairs + (gi - pairs);        // first accumulator / tap of the group
           const uint32_t dacc = tmem + 64 * (accb + i);
-          const uint32_t b_lo = qm_lo + (uint32_t)(tap0 + i);
+          const uint32_t b_lo = qm_lo + (uint32_t)((tap0 + i) * (128 >> 4));
           const uint32_t idg = pair ? idescA2 : idescA;
           tc::mma_ss2pe(dacc, dc_lo, pt_hi, b_lo, qm_hi, idg, acc_on);
 #pragma unroll
           for (int k = 1; k < BR / 16; ++k)
-            tc::mma_ss2e<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * 16), qm_hi, idg);
+            tc::mma_ss2e<1>(dacc, dc_lo + (uint32_t)(2 * k * BK), pt_hi, b_lo + (uint32_t)(k * (2048 / 16)), qm_hi, idg);
         }
         tc::mma_commit_e(&empty[st]);
         tc::mma_commit_e(pdc_free);
@@ -1006,7 +1006,7 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
   const size_t BH = (size_t)p.B * p.H;
   alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV, tmdKt;
   if (!make_tensor_map_bf16(&tmdKt, dKt, D, p.N, BH * p.cq, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
-  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR, false)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 64, Cfg::QR, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmdO, p.dO, D, p.N, BH, 64, Cfg::BR, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmV, p.V, D, p.N, BH, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
