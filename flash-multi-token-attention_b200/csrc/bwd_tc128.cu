@@ -54,7 +54,8 @@ struct Dq128Cfg {
   static_assert(kSmemBytes <= 227 * 1024, "dQ kernel (d = 128): shared memory budget");
   static constexpr int kTmemCols = 512;        // S (two buffers) at 0 and 64, dP at 128, dQ at 192..319, dO (bf16 pairs) at 320..383
   static constexpr int colP = 128, colQ = 192, colO = 320;
-  static constexpr int kThreads = (4 + 1 + 2) * 32;   // element-wise warpgroup, TMA warp, two MMA issuer warps
+  static constexpr int kEwWarps = 8;           // two element-wise warps per lane quarter, 32 key columns each
+  static constexpr int kThreads = (kEwWarps + 1 + 2) * 32;   // element-wise warps, TMA warp, two MMA issuer warps
 };
 
 __global__ void __launch_bounds__(Dq128Cfg::kThreads, 1)
@@ -63,6 +64,8 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   using Cfg = Dq128Cfg;
   constexpr int D = Cfg::D, BM = Cfg::BM, OWN = Cfg::OWN, BC = Cfg::BC, HALO = Cfg::HALO, QR = Cfg::QR;
   constexpr int DR = Cfg::DR, NSLOT = Cfg::NSLOT;
+  constexpr int NEW = Cfg::kEwWarps * 32;      // element-wise threads
+  constexpr int W_TMA = Cfg::kEwWarps, W_S = Cfg::kEwWarps + 1, W_DQ = Cfg::kEwWarps + 2;   // warp roles
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = smem + Cfg::oQ;
@@ -103,14 +106,14 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (tid == 0) {
     for (int i = 0; i < NSLOT; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 2); }
-    tc::mbar_init(q_full, 1); tc::mbar_init(do_full, BM);
-    tc::mbar_init(sdp_full, 1); tc::mbar_init(&s_free[0], BM); tc::mbar_init(&s_free[1], BM);
-    tc::mbar_init(dc_full, BM); tc::mbar_init(dq_done, 1);
+    tc::mbar_init(q_full, 1); tc::mbar_init(do_full, NEW);
+    tc::mbar_init(sdp_full, 1); tc::mbar_init(&s_free[0], NEW); tc::mbar_init(&s_free[1], NEW);
+    tc::mbar_init(dc_full, NEW); tc::mbar_init(dq_done, 1);
     tc::mbar_init(never_bar, 1); tc::mbar_init(mma_drain, 2);
     *s_abort = 0; *s_issued = 0;
     tc::mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == W_S) {
     tc::tmem_alloc(s_tmem, Cfg::kTmemCols);
     tc::tmem_relinquish();
   }
@@ -123,7 +126,7 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tmem = *s_tmem;
   const int per_kb = cq + 1;   // ring tiles per key block
 
-  if (warp == 4) {
+  if (warp == W_TMA) {
     // ===================== TMA producer =====================
     if (lane == 0 && nkb > 0) {
       tc::tma_prefetch_desc(&tmQ); tc::tma_prefetch_desc(&tmKt); tc::tma_prefetch_desc(&tmV);
@@ -146,9 +149,9 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (ok) put(&tmV, kb * BC, bh);
       }
     }
-  } else if (warp > 4) {
-    // ===================== MMA issuers: warp 5 issues S and dP, warp 6 dQ =====================
-    const bool is_dq = warp == 6;
+  } else if (warp > W_TMA) {
+    // ===================== MMA issuers: one warp issues S and dP, the other dQ =====================
+    const bool is_dq = warp == W_DQ;
     if (nkb > 0) {   // all lanes run the loop; one elected lane issues (see tc::elect_one)
       constexpr uint32_t idescS = tc::make_idesc(BM, BC, 0, 0);    // S, dP: 128 x 64, K-major operands
       constexpr uint32_t idescQ = tc::make_idesc(BM, D, 0, 1);     // dQ: 128 x 128, B (Kt) MN-major
@@ -232,29 +235,28 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   } else {
-    // ===================== element-wise warpgroup: one dC row per thread =====================
-    const int m = tid;                                  // row within the tile = TMEM lane
+    // ===================== element-wise warps: one dC row per thread pair, 32 key columns per thread =====================
+    constexpr int CW = BC / 2;                          // key columns per thread
+    const int qtr = warp & 3, cg = warp >> 2;           // TMEM lane quarter, column half
+    const int m = qtr * 32 + lane;                      // row within the tile = TMEM lane
     const int gi = R0 + m;                              // query index of this dC row
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     const uint32_t tS = tmem + lane_base, tP = tS + Cfg::colP, tQ = tS + Cfg::colQ, tO = tS + Cfg::colO;
     const bool row_ok = gi < N;
     const float lse2 = row_ok ? p.LSE[(size_t)bh * N + gi] * kLog2e : 0.f;
     const float dvec = row_ok ? p.Dvec[(size_t)bh * N + gi] : 0.f;
-    unsigned char* cbuf = sdC + m * 16;
+    unsigned char* cbuf = sdC + m * 16 + cg * (CW / 8) * (DR * 16);
     bool ok = true;
     if (nkb > 0) {
-      // this row of dO goes to tensor memory as bf16 pairs (the A operand of dP = dO V^T)
-      const uint4* src = reinterpret_cast<const uint4*>(dO + ((size_t)bh * N + (row_ok ? gi : 0)) * D);
+      // this thread's half of the dO row goes to tensor memory as bf16 pairs (the A operand of dP = dO V^T)
+      const uint4* src = reinterpret_cast<const uint4*>(dO + ((size_t)bh * N + (row_ok ? gi : 0)) * D) + cg * 8;
+      uint32_t w[32];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t w[32];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint4 v = row_ok ? __ldg(src + half * 8 + i) : make_uint4(0u, 0u, 0u, 0u);
-          w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-        }
-        tc::tmem_st32u(tO + 32 * half, w);
+      for (int i = 0; i < 8; ++i) {
+        const uint4 v = row_ok ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
       }
+      tc::tmem_st32u(tO + 32 * cg, w);
       tc::tmem_wait_st();
       tc::tc_fence_before();
       tc::mbar_arrive(do_full);
@@ -265,31 +267,25 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                                        : tc::mbar_wait(sdp_full, kb & 1, s_abort));
       if (!ok) break;
       tc::tc_fence_after();
-      float s[BC], dp[BC];
-      {
-        float t0[32], t1[32], t2[32], t3[32];
-        const uint32_t tSb = tS + 64 * (kb & 1);
-        tc::tmem_ld32_nowait(tSb, t0); tc::tmem_ld32_nowait(tSb + 32, t1);
-        tc::tmem_ld32_nowait(tP, t2); tc::tmem_ld32_nowait(tP + 32, t3);
-        tc::tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; dp[i] = t2[i]; dp[32 + i] = t3[i]; }
-      }
+      float s[CW], dp[CW];
+      tc::tmem_ld32_nowait(tS + 64 * (kb & 1) + CW * cg, s);
+      tc::tmem_ld32_nowait(tP + CW * cg, dp);
+      tc::tmem_wait_ld();
       tc::tc_fence_before();
       tc::mbar_arrive(&s_free[kb & 1]);
-      const int j0 = kb * BC;
+      const int j0 = kb * BC + CW * cg;
       const int jlim = row_ok ? (p.causal ? min(N - 1, gi - band) : N - 1) : -1;   // last key owned here
-      uint32_t pk32[BC / 2];
-      if (__all_sync(0xffffffffu, j0 + BC - 1 <= jlim)) {      // whole block owned by every row of the warp: no masking
+      uint32_t pk32[CW / 2];
+      if (__all_sync(0xffffffffu, j0 + CW - 1 <= jlim)) {      // whole block owned by every row of the warp: no masking
 #pragma unroll
-        for (int i = 0; i < BC; i += 2) {
+        for (int i = 0; i < CW; i += 2) {
           const float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
           const float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
           pk32[i / 2] = pack_bf16(c0, c1);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < BC; i += 2) {
+        for (int i = 0; i < CW; i += 2) {
           float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
           float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
           if (j0 + i > jlim) c0 = 0.f;
@@ -302,22 +298,22 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!ok) break;
       }
 #pragma unroll
-      for (int kc = 0; kc < BC / 8; ++kc)
+      for (int kc = 0; kc < CW / 8; ++kc)
         *reinterpret_cast<uint4*>(cbuf + kc * (DR * 16)) = make_uint4(pk32[4 * kc], pk32[4 * kc + 1], pk32[4 * kc + 2], pk32[4 * kc + 3]);
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(dc_full);
     }
-    // ---- epilogue: the owned dQ rows of this tile ----
+    // ---- epilogue: the owned dQ rows of this tile, 64 of the 128 columns per thread ----
     if (nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(dq_done, (nkb - 1) & 1, s_abort));
     tc::tc_fence_after();
     const bool have = (nkb > 0) && ok;
     const bool store = row_ok && (m < OWN);
-    float* orow = p.dQ + ((size_t)bh * N + (row_ok ? gi : 0)) * D;
+    float* orow = p.dQ + ((size_t)bh * N + (row_ok ? gi : 0)) * D + 64 * cg;
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = 0; c < 2; ++c) {
       float o[32];
       if (have) {
-        tc::tmem_ld32(tQ + c * 32, o);
+        tc::tmem_ld32(tQ + 64 * cg + c * 32, o);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = 0.f;
@@ -336,8 +332,8 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (*s_abort) {
     if (tid == 0) atomicExch(p.status, 1);
     // nothing of this CTA may still be in flight when its shared and tensor memory are given up
-    if (warp > 4) tc::mma_commit_e(mma_drain);
-    if (tid == 4 * 32) {
+    if (warp > W_TMA) tc::mma_commit_e(mma_drain);
+    if (tid == W_TMA * 32) {
       volatile int never = 0;
       if (nkb > 0) {
         tc::mbar_wait(q_full, 0, &never);
@@ -348,7 +344,7 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == W_S) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, Cfg::kTmemCols);
   }
