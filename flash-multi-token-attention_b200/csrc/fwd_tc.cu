@@ -132,33 +132,39 @@ struct TcParams {
   int selftest_expire;   // failure-detection self-test: the softmax warps' first wait is on a barrier nothing arrives at
 };
 
-// One CTA owns NT row tiles of 128 query rows (one softmax warpgroup and one TMEM lane per row);
-// key blocks are 128 wide so that every score MMA is 128 x 128 x 16 -- the 64-wide variant was
-// bound by shared-memory operand fetch (4 KB of A per 2 KB of B).  Every Kt / V tile staged in
-// shared memory feeds the MMAs of all row tiles.  Tensor memory per row tile: S (128 columns,
-// fp32), P (64 columns, bf16 pairs) and O (D columns, fp32); S is released to the next block's
-// MMAs as soon as the softmax threads have loaded it into registers.
+// One CTA owns two row tiles of 128 query rows (one softmax warpgroup and one TMEM lane per row).
+// Every Kt / V tile staged in shared memory feeds the MMAs of both row tiles.  Tensor memory per row
+// tile: S (BC columns, fp32), P (BC / 2 columns, bf16 pairs) and O (D columns, fp32); S is released to
+// the next block's MMAs as soon as the softmax threads have loaded it into registers.
+//   d = 64 : key blocks are 128 wide, so that every score MMA is 128 x 128 x 16 (a 64-wide MMA is bound
+//            by shared-memory operand fetch: 4 KB of A per 2 KB of B);
+//   d = 128: two row tiles only fit the tensor memory with 64-key blocks (2 x (64 + 32 + 128) = 448
+//            columns).  A single 128-row tile with 128-key blocks has the cheaper MMAs, but streams
+//            fourteen 16 KB tiles per block for 128 rows -- 62 bytes per cycle, more than eleven ring
+//            slots cover at the latency of a TMA copy (tensor pipe 42 % busy); sharing every tile between
+//            256 rows halves that.
 template <int D>
 struct TcCfg {
   static constexpr int BM = 128;               // rows per tile (= TMEM lanes)
-  static constexpr int BC = 128;               // keys per block
-  static constexpr int NT = (D == 64) ? 2 : 1; // row tiles per CTA (TMEM: NT * (128 + 64 + D) <= 512)
+  static constexpr int BC = (D == 64) ? 128 : 64;   // keys per block
+  static constexpr int NT = 2;                 // row tiles per CTA (TMEM: NT * (BC + BC / 2 + D) <= 512)
   static constexpr int HALO = 16;              // rows staged above the block (pad_q <= 15)
   static constexpr int QR = NT * BM + HALO;    // rows of Q in shared memory
   static constexpr int QBOX = QR / 2;          // Q is fetched as two boxes per 16-byte column slab
   static constexpr int SLABS = D / 64;         // 64-element (128-byte) column slabs per row
-  static constexpr int TILE_BYTES = BC * 128;  // one ring tile: 128 keys x 64 elements, 128B-swizzled
-  static constexpr int NSLOT = 11;
+  static constexpr int TILE_BYTES = BC * 128;  // one ring tile: BC keys x 64 elements, 128B-swizzled
+  static constexpr int NSLOT = (D == 64) ? 11 : 19;
   static constexpr int oQ = 0;
   static constexpr int oRing = ((oQ + QR * D * 2 + 1023) / 1024) * 1024;
   static constexpr int oBar = oRing + NSLOT * TILE_BYTES;
   static constexpr int kSmemBytes = oBar + 512 + 1024;   // + alignment slack
   static constexpr int kTmemCols = 512;
-  static constexpr int colS = 0;               // S[t] at colS + t*128
-  static constexpr int colP = NT * 128;        // P[t] at colP + t*64
-  static constexpr int colO = NT * 192;        // O[t] at colO + t*D
+  static constexpr int colS = 0;               // S[t] at colS + t*BC
+  static constexpr int colP = NT * BC;         // P[t] at colP + t*BC/2
+  static constexpr int colO = NT * BC + NT * BC / 2;   // O[t] at colO + t*D
   static constexpr int kThreads = (NT * 4 + 1 + NT) * 32;   // softmax warpgroups, TMA warp, one MMA warp per row tile
-  static_assert(NT * (192 + D) <= kTmemCols, "TMEM budget");
+  static_assert(NT * (BC + BC / 2 + D) <= kTmemCols, "TMEM budget");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   static_assert(QR <= 512 && QBOX <= 256, "TMA box limit");
 };
 
@@ -276,8 +282,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const uint64_t dK0 = tc::make_sdesc(smem_u32(sRing), 16, 1024, tc::kLayoutSW128);
       const uint32_t aS_hi = (uint32_t)(dQ0 >> 32), aS_lo = (uint32_t)dQ0;
       const uint32_t b_hi = (uint32_t)(dK0 >> 32), b_lo0 = (uint32_t)dK0;
-      const uint32_t dS = tmem + Cfg::colS + t * 128;
-      const uint32_t aP = tmem + Cfg::colP + t * 64;            // bf16 pairs: 8 columns per 16 keys
+      const uint32_t dS = tmem + Cfg::colS + t * BC;
+      const uint32_t aP = tmem + Cfg::colP + t * (BC / 2);      // bf16 pairs: 8 columns per 16 keys
       const int my_nkb = nkb_t[t];
       int id = 0;
       bool ok = tc::mbar_wait_warp(q_full, 0, s_abort);
@@ -344,8 +350,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int m = tid & (BM - 1);                       // row within the tile = TMEM lane
     const int gi = i0 + t * BM + m;                     // query index
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + Cfg::colS + t * 128 + lane_base;
-    const uint32_t tP = tmem + Cfg::colP + t * 64 + lane_base;
+    const uint32_t tS = tmem + Cfg::colS + t * BC + lane_base;
+    const uint32_t tP = tmem + Cfg::colP + t * (BC / 2) + lane_base;
     const uint32_t tO = tmem + Cfg::colO + t * D + lane_base;
     const int my_nkb = nkb_t[t];
     float m_run = -INFINITY, l_run = 0.f;               // log2 units (Kt carries scale * log2(e))
@@ -358,14 +364,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (!ok) break;   // warp-uniform: the TMEM accesses below are warp-collective
       tc::tc_fence_after();
       float s[BC];
-      {
-        float t0[32], t1[32], t2[32], t3[32];
-        tc::tmem_ld32_nowait(tS, t0); tc::tmem_ld32_nowait(tS + 32, t1);
-        tc::tmem_ld32_nowait(tS + 64, t2); tc::tmem_ld32_nowait(tS + 96, t3);
-        tc::tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; s[64 + i] = t2[i]; s[96 + i] = t3[i]; }
-      }
+      for (int c = 0; c < BC / 32; ++c) tc::tmem_ld32_nowait(tS + 32 * c, reinterpret_cast<float(&)[32]>(s[32 * c]));
+      tc::tmem_wait_ld();
       // S[t] is in registers: let the MMA warp overwrite it with the next key block
       tc::tc_fence_before();
       tc::mbar_arrive(&s_free[t]);
@@ -422,13 +423,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           tc::tmem_st32(tO + c * 32, o);
         }
       }
-      {
-        uint32_t lo[32], hi[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { lo[i] = pk32[i]; hi[i] = pk32[32 + i]; }
-        tc::tmem_st32u(tP, lo);
-        tc::tmem_st32u(tP + 32, hi);
-      }
+      for (int c = 0; c < BC / 64; ++c) tc::tmem_st32u(tP + 32 * c, reinterpret_cast<const uint32_t(&)[32]>(pk32[32 * c]));
       tc::tmem_wait_st();
       tc::tc_fence_before();
       tc::mbar_arrive(&p_full[t]);
