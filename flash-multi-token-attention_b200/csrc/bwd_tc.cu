@@ -10,8 +10,8 @@
 // outputs afterwards.
 //
 //   bwd_dq_tc_kernel   : CTA = NT query-row tiles, loops key blocks.  A tile computes dC for
-//                        128 rows but owns only the first 112 of them as dQ rows: dQ row i'
-//                        needs dC rows i'..i'+pad_q, so consecutive tiles overlap by 16 rows
+//                        128 rows but owns only the first 120 of them as dQ rows: dQ row i'
+//                        needs dC rows i'..i'+pad_q, so consecutive tiles overlap by 8 rows
 //                        (recomputed, like the halo of the exact kernels) and no dQ row is
 //                        ever shared between CTAs.  The row shift of dC is free: dC is staged
 //                        in shared memory in the no-swizzle K-major core-matrix layout whose
@@ -37,11 +37,14 @@ template <int D>
 struct DqCfg {
   static_assert(D == 64, "the dQ tensor-core kernel is instantiated for d = 64");
   static constexpr int BM = 128;               // dC rows per tile (= TMEM lanes)
-  static constexpr int OWN = 112;              // dQ rows a tile owns
+  static constexpr int OWN = 120;              // dQ rows a tile owns (dQ row i needs dC rows i .. i + pad_q, pad_q <= 6)
   static constexpr int BC = 64;                // keys per block
   static constexpr int NT = 2;                 // row tiles per CTA
   static constexpr int HALO = 16;
-  static constexpr int QR = HALO + OWN * (NT - 1) + BM;   // 256 rows of Q
+  // rows of Q staged: 264 are read; the buffer is 272 so that both TMA boxes of QR / 2 rows x 16 bytes land
+  // on 128-byte boundaries of shared memory (a tiled TMA copy needs that of its destination)
+  static constexpr int QR = ((HALO + OWN * (NT - 1) + BM + 15) / 16) * 16;
+  static_assert((QR / 2 * 16) % 128 == 0, "TMA destination alignment");
   static constexpr int DR = BM + 16;           // rows of a dC buffer (16 zero rows below)
   static constexpr int TILE_BYTES = BC * 128;  // Kt / V ring tile: 64 keys x 64 elements
   static constexpr int NSLOT = 15;             // the Kt tiles of one key block held for its dQ MMAs (cq <= 7) while the
@@ -313,7 +316,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(&dc_full[t]);
     }
-    // ---- epilogue: the 112 owned dQ rows of this tile ----
+    // ---- epilogue: the owned dQ rows of this tile ----
     if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (my_nkb - 1) & 1, s_abort));
     tc::tc_fence_after();
     const bool have = (my_nkb > 0) && ok;
@@ -371,7 +374,7 @@ struct DkvCfg {
   static constexpr int HALO = 8;               // rows of Q staged above the block (pad_q <= 5)
   static constexpr int QR = BR + HALO;         // 72 rows of Q per stage
   static constexpr int MAXCQ = CQMAX;          // resident Kt tiles; at most 7 accumulators of 64 columns + 64 scratch = 512
-  static constexpr int NSTG = 3;
+  static constexpr int NSTG = (CQMAX <= 6) ? 4 : 3;   // query-block stages in flight (a seventh resident tile leaves room for three)
   static constexpr int KT_BYTES = BK * 128;    // one resident Kt / V tile
   static constexpr int oKt = 0;                                   // MAXCQ x [128 keys][128 B], 128B swizzle
   static constexpr int oV = oKt + MAXCQ * KT_BYTES;
