@@ -14,7 +14,7 @@ from .inference import (forward_inference, fwd_conv_attn_inference, forward_infe
 from .head_conv import (HeadConvAttentionFunction, HeadConvAttention, head_conv_attention,  # noqa: F401
                         head_conv_attention_forward, head_conv_attention_bwd_dq_dw,
                         head_conv_attention_bwd_dkdv, conv_headmix_attention, conv_headmix_forward,
-                        conv_headmix_bwd_dq_dw, conv_headmix_bwd_dkdv)
+                        conv_headmix_bwd_dq_dw, conv_headmix_bwd_dkdv, conv_headmix_backward)
 from . import sharding  # noqa: F401
 
 __version__ = "0.1.0"

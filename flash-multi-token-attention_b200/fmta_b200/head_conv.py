@@ -14,7 +14,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from ._lib import lib, check, ptr, stream_ptr, as_f32
+from ._lib import lib, check, ptr, stream_ptr, as_f32, require_on
 
 
 def _bf16c(t):
@@ -52,6 +52,9 @@ def conv_headmix_forward(q, k, v, w, conv_kernel=None, scale=1.0, causal=False, 
     qb, kb, vb = _bf16c(q), _bf16c(k), _bf16c(v)
     if not qb.is_cuda:
         raise RuntimeError("q must be a CUDA tensor")
+    require_on(qb, kb, "k", qb.shape); require_on(qb, vb, "v", qb.shape); require_on(qb, w, "w")
+    if conv_kernel is not None:
+        require_on(qb, conv_kernel, "conv_kernel")
     B, H, N, d = qb.shape
     G, wg = _group_of(w, H)
     th, cq, ck = _theta_args(conv_kernel)
@@ -76,14 +79,25 @@ def head_conv_attention_forward(q, k, v, w, scale=1.0, causal=False):
     return o, l, m
 
 
-def _bwd_common(q, k, v, w, o, do, l, m, conv_kernel, causal, scale):
+def _bwd_common(q, k, v, w, o, do, l, m, conv_kernel, causal, scale, lse=None):
     qb, kb, vb, dob = _bf16c(q), _bf16c(k), _bf16c(v), _bf16c(do)
+    if not qb.is_cuda:
+        raise RuntimeError("q must be a CUDA tensor")
     B, H, N, d = qb.shape
+    for t, n in ((kb, "k"), (vb, "v"), (dob, "do"), (o, "o")):
+        require_on(qb, t, n, qb.shape)
+    for t, n in ((l, "l"), (m, "m")):
+        require_on(qb, t, n, (B, H, N))
+    require_on(qb, w, "w")
+    if conv_kernel is not None:
+        require_on(qb, conv_kernel, "conv_kernel")
     if scale is None:
         scale = 1.0 / math.sqrt(d)
     G, wg = _group_of(w, H)
     th, cq, ck = _theta_args(conv_kernel)
-    lse = (m.float() + torch.log(l.float())).contiguous()
+    if lse is None:
+        lse = m.float() + torch.log(l.float())
+    lse = as_f32(lse)
     oc = o.contiguous() if o.dtype in (torch.float32, torch.bfloat16) else o.float().contiguous()
     D = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     st = lib.fmta_bwd_prep_D(ptr(dob), ptr(oc), 1 if oc.dtype == torch.bfloat16 else 0, ptr(D), D.numel(), d,
@@ -118,6 +132,26 @@ def conv_headmix_bwd_dkdv(q, k, v, w, o, do, l, m, conv_kernel=None, causal=Fals
     return dK, dV
 
 
+def conv_headmix_backward(q, k, v, w, o, do, l, m, conv_kernel=None, causal=False, scale=None, lse=None):
+    """(dq, dk, dv, dw shaped like w, dtheta or None), all fp32, from ONE call of the fused backward entry
+    point: D = rowsum(dO * O) and the log-sum-exp are prepared once for both halves (the two host functions
+    above, which mirror the reference's pair of calls, each prepare them again)."""
+    qb, kb, vb, dob, B, H, N, d, G, wg, th, cq, ck, lse, D, scale = _bwd_common(q, k, v, w, o, do, l, m, conv_kernel,
+                                                                                causal, scale, lse)
+    dQ = torch.empty((B, H, N, d), dtype=torch.float32, device=q.device)
+    dK = torch.empty_like(dQ)
+    dV = torch.empty_like(dQ)
+    dW = torch.empty((H // G, G, G), dtype=torch.float32, device=q.device)
+    dTh = torch.empty((H, cq, ck), dtype=torch.float32, device=q.device) if th is not None else None
+    ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_BWD_DQ, B, H, N, d, cq, ck, G)
+    ws = torch.empty(max(int(ws_bytes), 16), dtype=torch.uint8, device=q.device)
+    st = lib.fmta_bwd(ptr(qb), ptr(kb), ptr(vb), ptr(dob), ptr(D), ptr(lse), ptr(th), ptr(wg), ptr(dQ), ptr(dK), ptr(dV),
+                      ptr(dTh), ptr(dW), B, H, N, d, cq, ck, G, scale, int(bool(causal)), 0, ptr(ws), ws_bytes,
+                      stream_ptr())
+    check(st, "fmta_bwd(head mix)")
+    return dQ, dK, dV, dW.reshape(w.shape), dTh
+
+
 def head_conv_attention_bwd_dq_dw(q, k, v, w, o, do, l, m, causal=False, scale=None):
     """(dq in q's dtype, dw) -- bwd_dq_dw.py:373-460."""
     dq, dw, _ = conv_headmix_bwd_dq_dw(q, k, v, w, o, do, l, m, None, causal, scale)
@@ -146,6 +180,11 @@ class HeadConvAttentionFunction(torch.autograd.Function):
     def backward(ctx, grad_output):
         q, k, v, w, output, l, m = ctx.saved_tensors
         grad_q = grad_k = grad_v = grad_w = None
+        need_qw = ctx.needs_input_grad[0] or ctx.needs_input_grad[3]
+        need_kv = ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
+        if need_qw and need_kv:     # the usual case: one fused call, D and the log-sum-exp prepared once
+            dq, dk, dv, dw, _ = conv_headmix_backward(q, k, v, w, output, grad_output, l, m, None, ctx.causal, ctx.scale)
+            return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dw.to(w.dtype), None, None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[3]:
             grad_q, grad_w = head_conv_attention_bwd_dq_dw(q, k, v, w, output, grad_output, l, m,
                                                            causal=ctx.causal, scale=ctx.scale)
@@ -178,16 +217,15 @@ class ConvHeadMixFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, conv_kernel, w, causal, scale):
-        o, l, m, _ = conv_headmix_forward(q, k, v, w, conv_kernel, scale, causal, out_dtype=torch.float32)
-        ctx.save_for_backward(q, k, v, conv_kernel, w, o, l, m)
+        o, l, m, lse = conv_headmix_forward(q, k, v, w, conv_kernel, scale, causal, out_dtype=torch.float32)
+        ctx.save_for_backward(q, k, v, conv_kernel, w, o, l, m, lse)
         ctx.causal, ctx.scale = causal, scale
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, conv_kernel, w, o, l, m = ctx.saved_tensors
-        dq, dw, dth = conv_headmix_bwd_dq_dw(q, k, v, w, o, do, l, m, conv_kernel, ctx.causal, ctx.scale)
-        dk, dv = conv_headmix_bwd_dkdv(q, k, v, w, o, do, l, m, conv_kernel, ctx.causal, ctx.scale)
+        q, k, v, conv_kernel, w, o, l, m, lse = ctx.saved_tensors
+        dq, dk, dv, dw, dth = conv_headmix_backward(q, k, v, w, o, do, l, m, conv_kernel, ctx.causal, ctx.scale, lse=lse)
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dth.to(conv_kernel.dtype), dw.to(w.dtype), None, None
 
 
