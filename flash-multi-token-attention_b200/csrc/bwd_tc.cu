@@ -33,7 +33,7 @@ namespace fmta {
 // ==========================================================================================
 // dQ
 // ==========================================================================================
-template <int D>
+template <int D, bool STREAM = false>   // STREAM: the kernel also leaves P and dC in global memory (see bwd_stream.cu)
 struct DqCfg {
   static_assert(D == 64, "the dQ tensor-core kernel is instantiated for d = 64");
   static constexpr int BM = 128;               // dC rows per tile (= TMEM lanes)
@@ -47,24 +47,29 @@ struct DqCfg {
   static_assert((QR / 2 * 16) % 128 == 0, "TMA destination alignment");
   static constexpr int DR = BM + 16;           // rows of a dC buffer (16 zero rows below)
   static constexpr int TILE_BYTES = BC * 128;  // Kt / V ring tile: 64 keys x 64 elements
-  static constexpr int NSLOT = 15;             // the Kt tiles of one key block held for its dQ MMAs (cq <= 7) while the
-                                               // next block's cq + 1 tiles stream in: 2 cq + 1 slots
+  static constexpr int NSLOT = STREAM ? 11 : 15;   // the Kt tiles of one key block held for its dQ MMAs (cq <= 7) while
+                                               // the next block's cq + 1 tiles stream in: 2 cq + 1 slots (four of them
+                                               // make room for the P tiles when P and dC are streamed out)
   static constexpr int oQ = 0;                                  // [D/8][QR][16 B]
   static constexpr int odO = oQ + QR * D * 2;                   // NT x [128 rows][128 B], 128B swizzle
-  static constexpr int odC = odO + NT * BM * 128;               // NT x [BC/8][DR][16 B]
-  static constexpr int oRing = ((odC + NT * (BC / 8) * DR * 16 + 1023) / 1024) * 1024;
+  static constexpr int DC_BYTES = DR * 128;                     // one dC buffer: [DR rows][128 B], 128B swizzle
+  static constexpr int odC = odO + NT * BM * 128;               // NT buffers
+  static_assert(odC % 1024 == 0 && DC_BYTES % 1024 == 0, "swizzled dC buffers start on 1024-byte boundaries");
+  static constexpr int P_BYTES = BM * 128;                      // STREAM: one P tile, [128 rows][128 B], 128B swizzle
+  static constexpr int oP = odC + NT * DC_BYTES;
+  static constexpr int oRing = ((oP + (STREAM ? NT * P_BYTES : 0) + 1023) / 1024) * 1024;
   static constexpr int oBar = oRing + NSLOT * TILE_BYTES;
   static constexpr int kSmemBytes = oBar + 512 + 1024;
   static constexpr int kTmemCols = 512;        // per tile t: S (two buffers) at 256t and 256t+64, dP at 256t+128, dQ at 256t+192
   static constexpr int kThreads = (NT * 4 + 1 + 2 * NT) * 32;   // element-wise warps, TMA warp, two MMA issuer warps per tile
 };
 
-template <int D>
-__global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
+template <int D, bool STREAM>
+__global__ void __launch_bounds__(DqCfg<D, STREAM>::kThreads, 1)
 bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                  const __grid_constant__ CUtensorMap tmKt, const __grid_constant__ CUtensorMap tmV,
                  const BwdTcParams p) {
-  using Cfg = DqCfg<D>;
+  using Cfg = DqCfg<D, STREAM>;
   constexpr int BM = Cfg::BM, OWN = Cfg::OWN, BC = Cfg::BC, NT = Cfg::NT, HALO = Cfg::HALO, QR = Cfg::QR;
   constexpr int DR = Cfg::DR, NSLOT = Cfg::NSLOT;
   extern __shared__ unsigned char smem_raw[];
@@ -130,7 +135,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc::tmem_relinquish();
   }
   // zero the dC buffers once: the 16 pad rows below each tile are read by the shifted views
-  for (int i = tid; i < NT * (BC / 8) * DR * 4; i += Cfg::kThreads) reinterpret_cast<uint32_t*>(sdC)[i] = 0u;
+  for (int i = tid; i < NT * Cfg::DC_BYTES / 4; i += Cfg::kThreads) reinterpret_cast<uint32_t*>(sdC)[i] = 0u;
   tc::fence_proxy_async_smem();
   tc::tc_fence_before();
   __syncthreads();
@@ -174,7 +179,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idescQ = tc::make_idesc(BM, D, 0, 1);     // dQ: 128 x D, B (Kt) MN-major
       const uint64_t dQa = tc::make_sdesc(smem_u32(sQ) + (HALO + t * OWN - pq) * 16, QR * 16, 128, tc::kLayoutNone);
       const uint64_t dOa = tc::make_sdesc(smem_u32(sdO) + t * (BM * 128), 16, 1024, tc::kLayoutSW128);
-      const uint64_t dCa = tc::make_sdesc(smem_u32(sdC) + t * ((BC / 8) * DR * 16), DR * 16, 128, tc::kLayoutNone);
+      // dC is a 128-byte-swizzled [rows][64 keys] tile; its row-shifted views start 128 bytes per row further
+      const uint64_t dCa = tc::make_sdesc(smem_u32(sdC) + t * Cfg::DC_BYTES, 16, 1024, tc::kLayoutSW128);
       const uint64_t dKb = tc::make_sdesc(smem_u32(sRing), 16, 1024, tc::kLayoutSW128);
       const uint32_t q_hi = (uint32_t)(dQa >> 32), q_lo = (uint32_t)dQa;
       const uint32_t o_hi = (uint32_t)(dOa >> 32), o_lo = (uint32_t)dOa;
@@ -230,6 +236,25 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (active) {
             ok = tc::mbar_wait_warp(&dc_full[t], kb & 1, s_abort);
             tc::tc_fence_after();
+            if constexpr (STREAM) {
+              // P and dC of the tile's owned rows leave as they lie in shared memory (the swizzled image): the
+              // global tensors are tile-major [B*H][row block of 64][key block of 64][64 rows x 128 bytes], a
+              // tile's rows start at a multiple of 8, so a row keeps its swizzle phase and the streaming kernel
+              // gets the same image with a plain copy.  One piece per 64-row block of the global layout.
+              if (ok && tc::elect_one()) {
+                const int r0 = R0 + t * OWN, r1 = min(N, r0 + OWN);
+                const int nkb64 = p.ldp >> 6;
+                const uint64_t pol_ef = tc::l2_policy_evict_first();
+                for (int g = r0; g < r1;) {
+                  const int gend = min(r1, (g | 63) + 1);
+                  const size_t tile = (((size_t)bh * ((N + 63) >> 6) + (g >> 6)) * nkb64 + kb) * 4096 + (size_t)(g & 63) * 64;
+                  tc::bulk_store_hint(p.Pout + tile, smem + Cfg::oP + t * Cfg::P_BYTES + (g - r0) * 128, (uint32_t)(gend - g) * 128, pol_ef);
+                  tc::bulk_store_hint(p.dCout + tile, sdC + t * Cfg::DC_BYTES + (g - r0) * 128, (uint32_t)(gend - g) * 128, pol_ef);
+                  g = gend;
+                }
+                tc::tma_store_commit();
+              }
+            }
           }
           for (int a = 0; a < cq && ok; ++a) {
             const int id = kb * per + a, slot = id % NSLOT, ph = (id / NSLOT) & 1;
@@ -237,11 +262,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (active) {
               tc::tc_fence_after();
               const uint32_t b_lo = k_lo0 + (uint32_t)(slot * (Cfg::TILE_BYTES >> 4));
-              const uint32_t a_lo = c_lo + (uint32_t)(pq - a);       // dC rows i' + pad_q - a
+              const uint32_t a_lo = c_lo + (uint32_t)((pq - a) * (128 >> 4));       // dC rows i' + pad_q - a
               tc::mma_ss2pe(tQ, a_lo, c_hi, b_lo, k_hi, idescQ, (kb != 0) || (a != 0));
 #pragma unroll
               for (int k = 1; k < BC / 16; ++k)
-                tc::mma_ss2e<1>(tQ, a_lo + (uint32_t)(2 * k * DR), c_hi, b_lo + (uint32_t)(k * (2048 / 16)), k_hi, idescQ);
+                tc::mma_ss2e<1>(tQ, a_lo + (uint32_t)(2 * k), c_hi, b_lo + (uint32_t)(k * (2048 / 16)), k_hi, idescQ);
             }
             tc::mma_commit_e(&empty[slot]);
           }
@@ -251,7 +276,15 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (!tc::mbar_wait_warp(&full[slot], ph, s_abort)) { ok = false; break; }
             if (tc::elect_one()) tc::mbar_arrive(&empty[slot]);
           }
+          if constexpr (STREAM) {   // the bulk copies have read their tiles before the buffers are handed back
+            if (active && tc::elect_one()) tc::tma_store_wait_read();
+            __syncwarp();
+          }
           if (active) tc::mma_commit_e(&dq_done[t]);
+        }
+        if constexpr (STREAM) {
+          if (tc::elect_one()) tc::tma_store_wait_all();
+          __syncwarp();
         }
       }
     }
@@ -266,7 +299,10 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool row_ok = gi < N;
     const float lse2 = row_ok ? p.LSE[(size_t)bh * N + gi] * kLog2e : 0.f;
     const float dvec = row_ok ? p.Dvec[(size_t)bh * N + gi] : 0.f;
-    unsigned char* cbuf = sdC + t * ((BC / 8) * DR * 16) + m * 16;
+    unsigned char* ctile = sdC + t * Cfg::DC_BYTES;     // this tile's dC buffer; chunk c of row r at r*128 + ((c ^ (r & 7)) << 4)
+    unsigned char* cbuf = ctile + m * 128;
+    // STREAM: P goes to a second swizzled tile beside dC; the dQ issuer of the tile sends both out with bulk copies
+    unsigned char* pbuf = smem + Cfg::oP + t * Cfg::P_BYTES + m * 128;
     bool ok = true;
     for (int kb = 0; kb < my_nkb && ok; ++kb) {
       ok = __all_sync(0xffffffffu, (p.selftest_expire && kb == 0)
@@ -288,33 +324,64 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc::mbar_arrive(&s_free[2 * t + (kb & 1)]);
       const int j0 = kb * BC;
       const int jlim = row_ok ? (p.causal ? min(N - 1, gi - band) : N - 1) : -1;   // last key owned here
-      uint32_t pk32[BC / 2];
-      if (__all_sync(0xffffffffu, j0 + BC - 1 <= jlim)) {      // whole block owned by every row of the warp: no masking
+      uint32_t pk32[BC / 2], pp32[STREAM ? BC / 2 : 1];
+      if constexpr (!STREAM) {
+        if (__all_sync(0xffffffffu, j0 + BC - 1 <= jlim)) {      // whole block owned by every row of the warp: no masking
 #pragma unroll
-        for (int i = 0; i < BC; i += 2) {
-          const float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
-          const float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
-          pk32[i / 2] = pack_bf16(c0, c1);
+          for (int i = 0; i < BC; i += 2) {
+            const float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
+            const float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
+            pk32[i / 2] = pack_bf16(c0, c1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < BC; i += 2) {
+            float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
+            float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
+            if (j0 + i > jlim) c0 = 0.f;
+            if (j0 + i + 1 > jlim) c1 = 0.f;
+            pk32[i / 2] = pack_bf16(c0, c1);
+          }
         }
-      } else {
+      } else {   // same arithmetic, keeping P as well
 #pragma unroll
         for (int i = 0; i < BC; i += 2) {
-          float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
-          float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
-          if (j0 + i > jlim) c0 = 0.f;
-          if (j0 + i + 1 > jlim) c1 = 0.f;
-          pk32[i / 2] = pack_bf16(c0, c1);
+          float p0 = exp2f(s[i] - lse2), p1 = exp2f(s[i + 1] - lse2);
+          if (j0 + i > jlim) p0 = 0.f;
+          if (j0 + i + 1 > jlim) p1 = 0.f;
+          pp32[i / 2] = pack_bf16(p0, p1);
+          pk32[i / 2] = pack_bf16(p0 * (dp[i] - dvec), p1 * (dp[i + 1] - dvec));
         }
       }
-      if (kb > 0) {   // dQ(kb-1) has finished reading the dC buffer
+      if (kb > 0) {   // dQ(kb-1) has finished reading the dC buffer (STREAM: and the bulk copies of block kb-1 both tiles)
         ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (kb - 1) & 1, s_abort));
         if (!ok) break;
       }
 #pragma unroll
-      for (int kc = 0; kc < BC / 8; ++kc)
-        *reinterpret_cast<uint4*>(cbuf + kc * (DR * 16)) = make_uint4(pk32[4 * kc], pk32[4 * kc + 1], pk32[4 * kc + 2], pk32[4 * kc + 3]);
+      for (int kc = 0; kc < BC / 8; ++kc) {
+        *reinterpret_cast<uint4*>(cbuf + ((kc ^ (m & 7)) << 4)) = make_uint4(pk32[4 * kc], pk32[4 * kc + 1], pk32[4 * kc + 2], pk32[4 * kc + 3]);
+        if constexpr (STREAM)
+          *reinterpret_cast<uint4*>(pbuf + ((kc ^ (m & 7)) << 4)) = make_uint4(pp32[4 * kc], pp32[4 * kc + 1], pp32[4 * kc + 2], pp32[4 * kc + 3]);
+      }
       tc::fence_proxy_async_smem();
       tc::mbar_arrive(&dc_full[t]);
+    }
+    // ---- streaming outputs: zero the key blocks this tile did not visit but a 64-row x 128-key tile of the
+    // dK/dV kernel that holds one of its rows may read: up to the end of the 128-key tile of key
+    // (last row + 63 - band); without a causal mask, up to ldp ----
+    if (STREAM && row_ok && m < OWN) {
+      const int nkb64 = p.ldp >> 6;
+      const size_t tile_row = ((size_t)bh * ((N + 63) >> 6) + (gi >> 6)) * nkb64 * 4096 + (size_t)(gi & 63) * 64;
+      bf16* prow = p.Pout + tile_row;     // key block kz of this row: + kz * 4096
+      bf16* crow = p.dCout + tile_row;
+      const int r_last = R0 + t * OWN + BM - 1;
+      const int fill_end = p.causal ? min(p.ldp, (max(r_last + 63 - band, 0) / 128 + 1) * 128) : p.ldp;
+      for (int kz = my_nkb; kz * BC < fill_end; ++kz)
+#pragma unroll
+        for (int c = 0; c < BC / 8; ++c) {
+          *reinterpret_cast<uint4*>(prow + (size_t)kz * 4096 + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(crow + (size_t)kz * 4096 + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
     // ---- epilogue: the owned dQ rows of this tile ----
     if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (my_nkb - 1) & 1, s_abort));
@@ -966,9 +1033,33 @@ size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq) {
   return up(rows * cq * d * 2) + up(rows * cq * d * 2) + 2048 + up((size_t)H * DkPostCfg::t_bytes(cq));
 }
 
-cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t stream) {
+size_t bwd_tc_stream_workspace_bytes(int B, int H, int N, int d, int cq) {
+  return bwd_tc_workspace_bytes(B, H, N, d, cq) + bwd_stream_extra_bytes(B, H, N);
+}
+
+// where the streamed P / dC tensors sit in a workspace of bwd_tc_stream_workspace_bytes
+static void stream_buffers(const TrainParams& p, void* workspace, __nv_bfloat16** P, __nv_bfloat16** dC, int* ldp) {
+  unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
+  w += bwd_tc_workspace_bytes(p.B, p.H, p.N, p.d, p.cq);
+  *ldp = (p.N + 127) / 128 * 128;
+  const size_t one = ((size_t)p.B * p.H * (size_t)((p.N + 63) / 64 * 64) * (size_t)*ldp * 2 + 1023) / 1024 * 1024;
+  *P = reinterpret_cast<__nv_bfloat16*>(w);
+  *dC = reinterpret_cast<__nv_bfloat16*>(w + one);
+}
+
+// Rows N .. 64*ceil(N/64)-1 of the last row block of the tile-major P / dC tensors are read by the streaming
+// dK/dV kernel (a whole 64-row tile at a time) but written by nobody: zero them (a few KB per (batch, head)).
+__global__ void zero_tail_rows_kernel(bf16* __restrict__ P, bf16* __restrict__ dC, int N, int nkb64) {
+  const int nrb = (N + 63) >> 6, r0 = N & 63;
+  const size_t tile = ((size_t)blockIdx.y * nrb + (nrb - 1)) * nkb64 + blockIdx.x;
+  uint4* p4 = reinterpret_cast<uint4*>(P + tile * 4096 + (size_t)r0 * 64);
+  uint4* c4 = reinterpret_cast<uint4*>(dC + tile * 4096 + (size_t)r0 * 64);
+  for (int i = threadIdx.x; i < (64 - r0) * 8; i += blockDim.x) { p4[i] = make_uint4(0u, 0u, 0u, 0u); c4[i] = make_uint4(0u, 0u, 0u, 0u); }
+}
+
+cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pdc, cudaStream_t stream) {
   constexpr int D = 64;
-  using Cfg = DqCfg<D>;
+  using Cfg = DqCfg<D, false>;
   const size_t rows = (size_t)p.B * p.H * p.N, BH = (size_t)p.B * p.H;
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
@@ -989,11 +1080,22 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dQ = p.dQ; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
-  auto kern = bwd_dq_tc_kernel<D>;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-  if (e != cudaSuccess) return e;
   const int rows_per_cta = Cfg::OWN * Cfg::NT;
   dim3 grid((p.N + rows_per_cta - 1) / rows_per_cta, p.H, p.B);
+  if (keep_pdc) {
+    stream_buffers(p, workspace, &bp.Pout, &bp.dCout, &bp.ldp);
+    if (p.N % 64 != 0) zero_tail_rows_kernel<<<dim3(bp.ldp / 64, (unsigned)BH), 128, 0, stream>>>(bp.Pout, bp.dCout, p.N, bp.ldp / 64);
+    using CfgS = DqCfg<D, true>;
+    auto kern = bwd_dq_tc_kernel<D, true>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgS::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    ScopedKernelTimer timer_(kKernBwdDqTc, stream);
+    kern<<<grid, CfgS::kThreads, CfgS::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
+    return cudaGetLastError();
+  }
+  auto kern = bwd_dq_tc_kernel<D, false>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
   { ScopedKernelTimer timer_(kKernBwdDqTc, stream);
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp); }
   return cudaGetLastError();
@@ -1026,7 +1128,7 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
   return cudaGetLastError();
 }
 
-cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream) {
+cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, bool keep_pdc, cudaStream_t stream) {
   const int D = p.d;
   const size_t rows = (size_t)p.B * p.H * p.N, BH = (size_t)p.B * p.H;
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
@@ -1038,6 +1140,10 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   { ScopedKernelTimer timer_(kKernBwdDkdvTc, stream);
     if (D == 128) {
       e = launch_bwd_dkdv_tc128(p, Kt, dKt, status, stream);
+    } else if (keep_pdc) {
+      __nv_bfloat16 *Pb, *dCb; int ldp;
+      stream_buffers(p, workspace, &Pb, &dCb, &ldp);
+      e = launch_bwd_dkdv_stream(p, Pb, dCb, ldp, dKt, status, stream);
     } else if (p.cq <= 6) {
       e = launch_dkdv_pass<6, true>(p, Kt, dKt, status, 0, p.cq, 1, stream);
     } else {

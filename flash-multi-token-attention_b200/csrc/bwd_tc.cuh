@@ -24,11 +24,22 @@ struct BwdTcParams {
   // accumulates dV as well; seven taps do not fit the tensor memory at once and take two launches
   int tap0, ntap, with_dv;
   int selftest_expire;   // failure-detection self-test: the element-wise warps' first wait is on a barrier nothing arrives at
+  // dQ kernel (optional outputs): the off-band P and dC = P (dP - D) of every entry, bf16, tile-major
+  // [B*H][row block of 64][key block of 64][64 rows][64 keys] with ldp / 64 key blocks (ldp = N rounded up to
+  // 128), so that the dK/dV kernel can stream them instead of recomputing them
+  bf16* Pout;
+  bf16* dCout;
+  int ldp;
 };
 
 
 bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128);
 bool tensor_maps_available();
+
+// streaming dK/dV (bwd_stream.cu): P and dC left in global memory by the dQ kernel
+size_t bwd_stream_extra_bytes(int B, int H, int N);
+cudaError_t launch_bwd_dkdv_stream(const TrainParams& p, const __nv_bfloat16* Pbuf, const __nv_bfloat16* dCbuf, int ldp,
+                                   __nv_bfloat16* dKt, int* status, cudaStream_t stream);
 
 // head dim 128 (bwd_tc128.cu)
 cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, int* status, cudaStream_t stream);

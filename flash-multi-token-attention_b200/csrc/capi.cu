@@ -126,12 +126,13 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
     if (G > 1) n += slots * (size_t)(H / G) * G * G;
     return n * sizeof(float);
   }
-  if (op == FMTA_OP_BWD_TC) {
+  if (op == FMTA_OP_BWD_TC || op == FMTA_OP_BWD_TC_STREAM) {
     // dTheta partials of the band kernel and of the tensor-core post-pass (one contiguous slot
     // array, rounded up), followed by the tensor-core backward's buffers
     const size_t slots = (size_t)bwd_band_theta_slots(B, N, cq, ck) + (size_t)bwd_tc_theta_slots(B, N, d);
     const size_t part = (slots * H * (size_t)(cq * ck) * sizeof(float) + 1023) / 1024 * 1024;
-    return part + bwd_tc_workspace_bytes(B, H, N, d, cq);
+    return part + (op == FMTA_OP_BWD_TC_STREAM && d == 64 ? bwd_tc_stream_workspace_bytes(B, H, N, d, cq)
+                                                          : bwd_tc_workspace_bytes(B, H, N, d, cq));
   }
   if (op == FMTA_OP_FWD_TC) {
     // the stacked key operand (c_q bf16 copies of K) + un-normalised partial O (fp32), M, L
@@ -282,8 +283,12 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
   float* part = reinterpret_cast<float*>(workspace);
   const size_t part_bytes = ((size_t)(slots_ex + slots_tc) * n_theta * sizeof(float) + 1023) / 1024 * 1024;
   void* tcw = reinterpret_cast<unsigned char*>(workspace) + part_bytes;
-  if (int s = check_cuda(launch_bwd_dq_tc(p, tcw, st))) return s;
-  if (int s = check_cuda(launch_bwd_dkdv_tc(p, tcw, part + (size_t)slots_ex * n_theta, st))) return s;
+  // with the larger workspace of FMTA_OP_BWD_TC_STREAM (head dim 64) the dQ kernel leaves P and dC in global
+  // memory and the dK/dV kernel streams them instead of recomputing them
+  const bool keep_pdc = (d == 64) &&
+      workspace_bytes >= fmta_workspace_bytes(FMTA_OP_BWD_TC_STREAM, B, H, N, d, p.cq, p.ck, p.G);
+  if (int s = check_cuda(launch_bwd_dq_tc(p, tcw, keep_pdc, st))) return s;
+  if (int s = check_cuda(launch_bwd_dkdv_tc(p, tcw, part + (size_t)slots_ex * n_theta, keep_pdc, st))) return s;
   p.n_slots = slots_ex;
   p.dTheta_part = part;
   if (causal) {

@@ -85,6 +85,26 @@ FMTA_DEVINL void tma_store_3d(const CUtensorMap* map, const void* smem_src, int 
                ::"l"(map), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
+// Contiguous copy shared -> global (bulk async-group); both addresses and the size multiples of 16 bytes.
+FMTA_DEVINL void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+// Same with an L2 eviction-priority hint: data that is written once and read much later should not push the
+// operands that are being re-read out of the cache.
+FMTA_DEVINL uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+FMTA_DEVINL void bulk_store_hint(void* gdst, const void* smem_src, uint32_t bytes, uint64_t policy) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes), "l"(policy)
+               : "memory");
+}
+// wait until every committed bulk store of this thread has completed (not only read its source)
+FMTA_DEVINL void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 FMTA_DEVINL void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // wait until the committed stores have read their shared-memory source
 FMTA_DEVINL void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

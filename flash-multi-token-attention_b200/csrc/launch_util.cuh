@@ -86,8 +86,11 @@ bool fwd_tc_supported(const TrainParams& p);
 size_t fwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
 bool bwd_tc_supported(const TrainParams& p);
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
-cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, cudaStream_t stream);
-cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, cudaStream_t stream);
+// keep_pdc: the dQ kernel also writes P and dC (workspace of FMTA_OP_BWD_TC_STREAM) and the dK/dV kernel
+// streams them instead of recomputing them (head dim 64)
+cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pdc, cudaStream_t stream);
+cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, bool keep_pdc, cudaStream_t stream);
+size_t bwd_tc_stream_workspace_bytes(int B, int H, int N, int d, int cq);
 int bwd_tc_theta_slots(int B, int N, int d);
 int bwd_band_theta_slots(int B, int N, int cq, int ck);
 cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream);

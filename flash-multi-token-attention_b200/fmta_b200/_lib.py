@@ -16,6 +16,7 @@ FMTA_DTYPE_BF16 = 1
 FMTA_OP_BWD_DQ = 1
 FMTA_OP_FWD_TC = 2
 FMTA_OP_BWD_TC = 3
+FMTA_OP_BWD_TC_STREAM = 4
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(

@@ -52,6 +52,7 @@ extern "C" {
 #define FMTA_OP_BWD_DQ 1 /* for fmta_workspace_bytes */
 #define FMTA_OP_FWD_TC 2
 #define FMTA_OP_BWD_TC 3
+#define FMTA_OP_BWD_TC_STREAM 4 /* FMTA_OP_BWD_TC plus room for P and dC (bf16, 4 * B*H*N*roundup(N,128) bytes) */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int fmta_version(void);
@@ -156,6 +157,11 @@ int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, c
  * mixing, and a workspace of fmta_workspace_bytes(FMTA_OP_BWD_TC, ...); -1 = the process-wide
  * default (fmta_set_path), which picks 1 whenever it is available and the workspace suffices.
  * With path 0 the workspace need is that of FMTA_OP_BWD_DQ.
+ * Head dim 64 with a workspace of fmta_workspace_bytes(FMTA_OP_BWD_TC_STREAM, ...) or more: the dQ kernel
+ * leaves the probabilities P and dC = P (dP - D) of every entry off the causal band in the workspace (bf16),
+ * and the dK/dV kernel streams them through two accumulating GEMMs instead of recomputing scores and
+ * exponentials -- faster whenever the 4*B*H*N^2 bytes fit (1 GiB per 16 (batch, head) pairs at N = 4096);
+ * same numbers as the recomputing kernel (it rounds P and dC to bf16 too).
  */
 int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const float* D,
              const float* LSE, const float* theta, const float* wmix, float* dQ, float* dK, float* dV,

@@ -121,9 +121,9 @@ def test_rejects_bad_inputs():
         F.forward(Q, Q, Q, th, 1.0, 1, 1, True)                    # pads inconsistent with the filter
 
 
-@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("path", [0, 1, 2])
 @pytest.mark.parametrize("B,H,N,d,cq,ck,causal", [
-    (1, 2, 520, 64, 6, 11, True),     # several 224-row dQ tiles and 128-key dK tiles, ragged N
+    (1, 2, 520, 64, 6, 11, True),     # several 240-row dQ tiles and 128-key dK tiles, ragged N
     (2, 1, 300, 64, 3, 5, False),     # no causal band: everything on the tensor-core kernels
     (1, 1, 100, 64, 6, 11, True),     # shorter than one tile
     (1, 2, 400, 64, 6, 17, True),     # wide key filter (W = 21): three key tiles per row tile, FMA output phase
@@ -161,21 +161,29 @@ def test_rejects_bad_inputs():
 ])
 def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
     """fmta_bwd with the exact kernels (path 0) and with the stacked-GEMM tensor-core kernels plus
-    the band kernel (path 1) against the oracle; forward run on both paths as well."""
+    the band kernel (path 1: the dQ kernel keeps P and dC and the dK/dV kernel streams them, head dim 64;
+    "path 2": the dK/dV kernel recomputes them) against the oracle; forward run on both paths as well."""
     import fmta_b200 as F
+    stream_pdc = None if path != 2 else False
+    if path == 2:
+        if d != 64:
+            pytest.skip("the streaming dK/dV kernel exists for head dim 64 only: nothing to switch off")
+        path = 1
     Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=17 + N, dtype=torch.bfloat16)
     scale = 1.0 / math.sqrt(d)
     q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
     th = theta.cuda()
     O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, causal, return_lse=True, path=path)
     Dv = F.rowdot(do, O)
-    dQ, dK, dV, dTh = F.backward(q, k, v, do, Dv, LSE, th, scale, cq - 1, (ck - 1) // 2, causal, path=path)
+    dQ, dK, dV, dTh = F.backward(q, k, v, do, Dv, LSE, th, scale, cq - 1, (ck - 1) // 2, causal, path=path,
+                                 stream_pdc=stream_pdc)
     torch.cuda.synchronize()
     Or, Mr, Lr = orc.conv_attn_fwd(Q, K, V, theta, scale, causal)
     rq, rk, rv, rt = orc.conv_attn_bwd_autograd(Q, K, V, theta, dO, scale, causal)
     _check(dict(O=O, M=M, L=L, LSE=LSE, dQ=dQ, dK=dK, dV=dV, dTheta=dTh),
            dict(O=Or, M=Mr, L=Lr, dQ=rq, dK=rk, dV=rv, dTheta=rt),
-           "B%d H%d N%d d%d theta(%d,%d) causal=%d path %d" % (B, H, N, d, cq, ck, causal, path))
+           "B%d H%d N%d d%d theta(%d,%d) causal=%d path %d%s" % (B, H, N, d, cq, ck, causal, path,
+                                                              " (recomputing dK/dV)" if stream_pdc is False else ""))
 
 
 def test_fp32_configuration_N256_theta_3x5_both_paths():

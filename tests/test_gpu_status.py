@@ -32,8 +32,9 @@ def test_status_is_zero_after_normal_calls():
     F.check_device_status()       # synchronises; raises on a non-zero word
 
 
+@pytest.mark.parametrize("stream_pdc", [None, False])
 @pytest.mark.parametrize("kernel", [KERN_FWD, KERN_DQ, KERN_DKDV])
-def test_expired_wait_is_reported_and_the_next_call_is_clean(kernel):
+def test_expired_wait_is_reported_and_the_next_call_is_clean(kernel, stream_pdc):
     import fmta_b200 as F
     from fmta_b200._lib import lib
     (Q, K, V, dO, theta), (q, k, v, do, th), scale, cq, ck = _inputs()
@@ -44,7 +45,7 @@ def test_expired_wait_is_reported_and_the_next_call_is_clean(kernel):
     if kernel == KERN_FWD:
         F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True, path=1)
     else:
-        F.backward(q, k, v, do, D, LSE, th, scale, cq - 1, (ck - 1) // 2, True, path=1)
+        F.backward(q, k, v, do, D, LSE, th, scale, cq - 1, (ck - 1) // 2, True, path=1, stream_pdc=stream_pdc)
     with pytest.raises(RuntimeError, match="bounded wait"):
         F.check_device_status()
     # the hook is one-shot and the context is intact: the same calls now give the right numbers
