@@ -184,12 +184,77 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_gpu(args):
+    """Same-box GPU baseline: the reference's own CUDA extension, rebuilt for sm_100 by
+    oracle/build_ref_cuda.py (square filters only), next to this library at the shapes of the reference's
+    published benchmark (B=1, H=8, d=64, 7x7 filter, bf16, causal; N = 512 ... 4096).  Context, not the
+    headline: prints one JSON line with the milliseconds of both, forward and backward."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    so = os.path.join(ROOT, "oracle", "_ref", "fmta_reference_cuda_sm100.so")
+    if not os.path.exists(so) or not torch.cuda.is_available():
+        print(json.dumps(dict(impl="reference-gpu", unavailable="oracle/_ref/fmta_reference_cuda_sm100.so has not been built "
+                              "(python oracle/build_ref_cuda.py needs the reference checkout) or no GPU")), flush=True)
+        return
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("fmta_reference_cuda_sm100", so)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    import fmta_b200 as F
+    dev = torch.device("cuda", 0)
+    B, H, d, cq, ck = 1, 8, 64, 7, 7
+    scale, pq, pk = 1.0 / math.sqrt(d), cq - 1, (ck - 1) // 2
+    iters = max(3, min(args.steps, 20))
+
+    def ms_of(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    points = []
+    for N in (512, 1024, 2048, 4096):
+        g = torch.Generator(device=dev).manual_seed(N)
+        q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).to(torch.bfloat16) for _ in range(4))
+        th = torch.randn(H, cq, ck, device=dev, generator=g) * 0.02
+        th[:, cq - 1, ck // 2] += 1.0
+        thb = th.to(torch.bfloat16)
+        # reference: forward(Q,K,V,conv_kernel,scale,pad_q,pad_k,causal); backward takes D and M + log L in bf16
+        O_r, M_r, L_r = ref.forward(q, k, v, thb, scale, pq, pk, True)
+        torch.cuda.synchronize()
+        lse_r = (M_r + torch.log(L_r)).to(torch.bfloat16)
+        D_r = (do.float() * O_r).sum(-1).to(torch.bfloat16)
+        O, M, L, LSE = F.forward(q, k, v, th, scale, pq, pk, True, return_lse=True)
+        Dv = F.rowdot(do, O)
+        pt = dict(N=N, max_abs_O_vs_reference=float((O - O_r).abs().max()),
+                  ref_fwd_ms=ms_of(lambda: ref.forward(q, k, v, thb, scale, pq, pk, True)),
+                  fwd_ms=ms_of(lambda: F.forward(q, k, v, th, scale, pq, pk, True)))
+
+        def ref_bwd():
+            ref.dq_backward(q, k, v, do, D_r, lse_r, thb, scale, pq, pk, True)
+            ref.dkdv_backward(q, k, v, do, D_r, lse_r, thb, scale, pq, pk, True)
+        pt["ref_bwd_ms"] = ms_of(ref_bwd)
+        pt["bwd_ms"] = ms_of(lambda: F.backward(q, k, v, do, Dv, LSE, th, scale, pq, pk, True))
+        points.append(pt)
+    F.check_device_status(dev)
+    print(json.dumps(dict(impl="reference-gpu", metric="ms per call, conv attention 7x7, B=1,H=8,d=64, bf16, causal",
+                          build="reference conv_attn extension compiled with -gencode=arch=compute_100,code=sm_100 "
+                                "(its own sources and flags otherwise)", iters=iters, points=points)), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated (median reported)")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
@@ -200,6 +265,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "reference-gpu":
+        return run_reference_gpu(args)
     args.warmup = max(args.warmup, 3)
 
     import torch.distributed as dist
