@@ -14,11 +14,15 @@
 //                        needs dC rows i'..i'+pad_q, so consecutive tiles overlap by 8 rows
 //                        (recomputed, like the halo of the exact kernels) and no dQ row is
 //                        ever shared between CTAs.  The row shift of dC is free: dC is staged
-//                        in shared memory in the no-swizzle K-major core-matrix layout whose
-//                        M stride is 16 bytes, exactly as Q is in the forward.
+//                        in shared memory as a 128-byte-swizzled [rows][64 keys] tile, and the tensor
+//                        core applies the swizzle to the absolute address, so a view shifted by s
+//                        rows is the same tile with the descriptor start address moved by 128 s bytes.
+//                        With STREAM the kernel also leaves P and dC in global memory (bwd_stream.cu).
 //   bwd_dkdv_tc_kernel : CTA = 128 keys (= TMEM lanes), loops 64-row query blocks; transposed
 //                        scores S^T = Kt_a Q^(a)T so that P^T and dC^T are produced with keys on the
-//                        lanes (rows of the dV / dKt accumulators).
+//                        lanes (rows of the dV / dKt accumulators).  Q is staged once per block as a
+//                        swizzled tile; its row-shifted views are start-address offsets as above.
+// Head dim 64 here; head dim 128 in bwd_tc128.cu.
 // Every mbarrier wait is bounded; no TMA multicast, no cluster, cta_group::1 only.
 #include <cuda.h>
 #include <cuda_runtime.h>

@@ -153,7 +153,7 @@ int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, c
  * Whole backward in one call: dQ, dK, dV, dTheta (and dW).  Replaces the pair of calls made by
  * `FlashConvAttentionCUDAFunction.backward` (conv_attn/conv_attention_cuda.py:147-152).
  * path: 0 = exact tile kernels; 1 = stacked-GEMM tensor-core kernels for the entries off the
- * causal band + the band kernel (accumulating) on the band -- needs d = 64, c_q <= 7, no head
+ * causal band + the band kernel (accumulating) on the band -- needs d = 64 with c_q <= 7 or d = 128 with c_q <= 6, no head
  * mixing, and a workspace of fmta_workspace_bytes(FMTA_OP_BWD_TC, ...); -1 = the process-wide
  * default (fmta_set_path), which picks 1 whenever it is available and the workspace suffices.
  * With path 0 the workspace need is that of FMTA_OP_BWD_DQ.
