@@ -330,22 +330,15 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int jlim = row_ok ? (p.causal ? min(N - 1, gi - band) : N - 1) : -1;   // last key owned here
       uint32_t pk32[BC / 2], pp32[STREAM ? BC / 2 : 1];
       if constexpr (!STREAM) {
-        if (__all_sync(0xffffffffu, j0 + BC - 1 <= jlim)) {      // whole block owned by every row of the warp: no masking
+        // one loop with the ownership mask always applied: two predicated selects per pair cost less than the
+        // registers a separate unmasked copy of the loop takes (this kernel is capped at 128 registers)
 #pragma unroll
-          for (int i = 0; i < BC; i += 2) {
-            const float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
-            const float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
-            pk32[i / 2] = pack_bf16(c0, c1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < BC; i += 2) {
-            float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
-            float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
-            if (j0 + i > jlim) c0 = 0.f;
-            if (j0 + i + 1 > jlim) c1 = 0.f;
-            pk32[i / 2] = pack_bf16(c0, c1);
-          }
+        for (int i = 0; i < BC; i += 2) {
+          float c0 = exp2f(s[i] - lse2) * (dp[i] - dvec);
+          float c1 = exp2f(s[i + 1] - lse2) * (dp[i + 1] - dvec);
+          if (j0 + i > jlim) c0 = 0.f;
+          if (j0 + i + 1 > jlim) c1 = 0.f;
+          pk32[i / 2] = pack_bf16(c0, c1);
         }
       } else {   // same arithmetic, keeping P as well
 #pragma unroll
