@@ -16,8 +16,8 @@ pytestmark = pytest.mark.gpu
 KERN_FWD, KERN_DQ, KERN_DKDV = 1, 3, 4
 
 
-def _inputs(N=400):
-    B, H, d, cq, ck = 1, 2, 64, 6, 11
+def _inputs(N=400, d=64):
+    B, H, cq, ck = 1, 2, 6, 11
     Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=4, dtype=torch.bfloat16)
     q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
     return (Q, K, V, dO, theta), (q, k, v, do, theta.cuda()), 1.0 / math.sqrt(d), cq, ck
@@ -32,12 +32,13 @@ def test_status_is_zero_after_normal_calls():
     F.check_device_status()       # synchronises; raises on a non-zero word
 
 
-@pytest.mark.parametrize("stream_pdc", [None, False])
+@pytest.mark.parametrize("d,stream_pdc", [(64, None), (64, False), (128, None)])
 @pytest.mark.parametrize("kernel", [KERN_FWD, KERN_DQ, KERN_DKDV])
-def test_expired_wait_is_reported_and_the_next_call_is_clean(kernel, stream_pdc):
+def test_expired_wait_is_reported_and_the_next_call_is_clean(kernel, d, stream_pdc):
+    """Every tensor-core kernel family: head dim 64 (recomputing and streaming dK/dV) and head dim 128."""
     import fmta_b200 as F
     from fmta_b200._lib import lib
-    (Q, K, V, dO, theta), (q, k, v, do, th), scale, cq, ck = _inputs()
+    (Q, K, V, dO, theta), (q, k, v, do, th), scale, cq, ck = _inputs(d=d)
     F.check_device_status()
     O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True, path=1)
     D = F.rowdot(do, O)
