@@ -219,6 +219,19 @@ def run_reference_gpu(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters
 
+    def graph_ms_of(fn):
+        """The same call captured once into a CUDA graph and replayed (host launch overhead removed)."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            keep = fn()   # noqa: F841  (outputs stay alive with the graph)
+        return ms_of(graph.replay)
+
     points = []
     for N in (512, 1024, 2048, 4096):
         g = torch.Generator(device=dev).manual_seed(N)
@@ -242,6 +255,8 @@ def run_reference_gpu(args):
             ref.dkdv_backward(q, k, v, do, D_r, lse_r, thb, scale, pq, pk, True)
         pt["ref_bwd_ms"] = ms_of(ref_bwd)
         pt["bwd_ms"] = ms_of(lambda: F.backward(q, k, v, do, Dv, LSE, th, scale, pq, pk, True))
+        pt["fwd_graph_ms"] = graph_ms_of(lambda: F.forward(q, k, v, th, scale, pq, pk, True))
+        pt["bwd_graph_ms"] = graph_ms_of(lambda: F.backward(q, k, v, do, Dv, LSE, th, scale, pq, pk, True))
         points.append(pt)
     F.check_device_status(dev)
     print(json.dumps(dict(impl="reference-gpu", metric="ms per call, conv attention 7x7, B=1,H=8,d=64, bf16, causal",
