@@ -492,9 +492,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int band = pq + pk;
   // (batch, head)-major block order: the key tiles of one (batch, head) run side by side and share its
   // Q / dO stream in L2 (the length-major order of the dQ kernel was 7 % slower here)
-  const int h = blockIdx.y, b = blockIdx.z;
+  // block order: see dkdv_block_order
+  int h, b, j0;
+  dkdv_block_order(BK, h, b, j0);
   const int bh = b * p.H + h;
-  const int j0 = blockIdx.x * BK;        // early key tiles see the most query blocks: longest first
   const int nQB = (N + BR - 1) / BR;
   const int qb_begin = p.causal ? min(nQB, (j0 + band) / BR) : 0;
   const int nblk = nQB - qb_begin;

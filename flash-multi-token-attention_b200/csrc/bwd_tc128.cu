@@ -415,9 +415,9 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
   const int band = pq + pk;
-  const int h = blockIdx.y, b = blockIdx.z;
+  int h, b, j0;
+  dkdv_block_order(BK, h, b, j0);          // (batch, head)-major, key-tile-major tail
   const int bh = b * p.H + h;
-  const int j0 = blockIdx.x * BK;        // early key tiles see the most query blocks: longest first
   const int nQB = (N + BR - 1) / BR;
   const int qb_begin = p.causal ? min(nQB, (j0 + band) / BR) : 0;
   const int nblk = nQB - qb_begin;
