@@ -462,7 +462,8 @@ template <int D, int CQMAX, bool PAIR>
 __global__ void __launch_bounds__(DkvCfg<D, CQMAX, PAIR>::kThreads, 1)
 bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmKt, const __grid_constant__ CUtensorMap tmV,
-                   const __grid_constant__ CUtensorMap tmdKt, const BwdTcParams p) {
+                   const __grid_constant__ CUtensorMap tmdKt, const __grid_constant__ CUtensorMap tmdV,
+                   const BwdTcParams p) {
   using Cfg = DkvCfg<D, CQMAX, PAIR>;
   constexpr int BK = Cfg::BK, BR = Cfg::BR, HALO = Cfg::HALO, QR = Cfg::QR, NSTG = Cfg::NSTG;
   extern __shared__ unsigned char smem_raw[];
@@ -483,9 +484,11 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* all_done = pdc_free + 1;
   uint64_t* never_bar = all_done + 1;    // nothing arrives here (expiry self-test)
   uint64_t* mma_drain = never_bar + 1;   // abort path: every issuer's MMAs have completed (3 arrivals)
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(mma_drain + 1);
+  uint64_t* v_full = mma_drain + 1;      // the V tile alone: dP^T(0) starts on it while the Kt tiles are still in flight
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(v_full + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   volatile int* s_issued = s_abort + 1;  // stages the producer has issued
+  volatile int* s_kt_issued = s_abort + 2;   // the copies of the Kt tiles have been issued
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
@@ -502,13 +505,13 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (tid == 0) {
     for (int i = 0; i < NSTG; ++i) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 3); }   // three issuers release a stage
-    tc::mbar_init(kv_full, 1);
+    tc::mbar_init(kv_full, 1); tc::mbar_init(v_full, 1);
     tc::mbar_init(st_full, 1); tc::mbar_init(xs_free, Cfg::kEwWarps * 32);
     tc::mbar_init(dpt_full, 1); tc::mbar_init(xd_free, Cfg::kEwWarps * 32);
     tc::mbar_init(pdc_full, Cfg::kEwWarps * 32); tc::mbar_init(pdc_free, 2);
     tc::mbar_init(all_done, 2);
     tc::mbar_init(never_bar, 1); tc::mbar_init(mma_drain, 3);
-    *s_abort = 0; *s_issued = 0;
+    *s_abort = 0; *s_issued = 0; *s_kt_issued = 0;
     tc::mbar_fence_init();
   }
   if (warp == Cfg::kEwWarps + 1) {
@@ -526,9 +529,10 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (nblk > 0) {
       if (lane == 0) {
         tc::tma_prefetch_desc(&tmQ); tc::tma_prefetch_desc(&tmdO); tc::tma_prefetch_desc(&tmKt); tc::tma_prefetch_desc(&tmV);
-        tc::mbar_expect_tx(kv_full, (cq + 1) * Cfg::KT_BYTES);
-        for (int a = 0; a < cq; ++a) tc::tma_load_3d(sKt + a * Cfg::KT_BYTES, &tmKt, kv_full, 0, j0, bh * cq + a);
-        tc::tma_load_3d(sV, &tmV, kv_full, 0, j0, bh);
+        // V first, then (below) the first query block, then the Kt tiles: that is the order in which the
+        // first MMAs need them (dP^T(0) = V dO^T, then S^T(0))
+        tc::mbar_expect_tx(v_full, Cfg::KT_BYTES);
+        tc::tma_load_3d(sV, &tmV, v_full, 0, j0, bh);
       }
       bool ok = true;
       for (int it = 0; it < nblk && ok; ++it) {
@@ -551,6 +555,11 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tc::tma_load_3d(sg + Cfg::sgdO, &tmdO, &full[st], 0, i0, bh);
           tc::tma_load_3d(sg + Cfg::sgQ, &tmQ, &full[st], 0, i0 - HALO, bh);
           *s_issued = it + 1;
+          if (it == 0) {
+            tc::mbar_expect_tx(kv_full, cq * Cfg::KT_BYTES);
+            for (int a = 0; a < cq; ++a) tc::tma_load_3d(sKt + a * Cfg::KT_BYTES, &tmKt, kv_full, 0, j0, bh * cq + a);
+            *s_kt_issued = 1;
+          }
         }
       }
     }
@@ -563,7 +572,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint64_t dKtA = tc::make_sdesc(smem_u32(sKt), 16, 1024, tc::kLayoutSW128);
       const uint32_t kt_hi = (uint32_t)(dKtA >> 32), kt_lo = (uint32_t)dKtA;
       const uint32_t v_lo = kt_lo + (uint32_t)((Cfg::oV - Cfg::oKt) >> 4);
-      bool ok = tc::mbar_wait_warp(kv_full, 0, s_abort);
+      bool ok = tc::mbar_wait_warp(v_full, 0, s_abort);
       // X holds dP^T(it) first (taken by the element-wise warps one block ahead), then S^T(it):
       //   dP^T(0) | S^T(0) dP^T(1) | S^T(1) dP^T(2) | ...
       auto issue_dPT = [&](int it) {
@@ -586,6 +595,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // 128 bytes per row (the tensor core swizzles the absolute shared-memory address, as TMA did)
         const uint64_t dQk = tc::make_sdesc(sg + Cfg::sgQ + (HALO - pq) * 128, 16, 1024, tc::kLayoutSW128);
         const uint32_t qk_hi = (uint32_t)(dQk >> 32), qk_lo = (uint32_t)dQk;
+        if (it == 0 && !tc::mbar_wait_warp(kv_full, 0, s_abort)) { ok = false; break; }   // the Kt tiles
         if (!tc::mbar_wait_warp(xd_free, it & 1, s_abort)) { ok = false; break; }   // dP^T(it) has left X
         tc::tc_fence_after();
         // S^T = sum_a Kt_a Q^(a)T
@@ -743,45 +753,57 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (nblk > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(all_done, 0, s_abort));
     tc::tc_fence_after();
     const bool have = (nblk > 0) && ok;
-    const bool store = key < N;
-    const size_t krow = (size_t)(store ? key : 0);
     const int nacc = (p.with_dv ? 1 : 0) + p.ntap;
-    for (int ch = cg; ch < 2 * nacc; ch += NCG) {
-      const int acc = ch >> 1, half = ch & 1;
-      float o[32];
-      if (have) {
-        tc::tmem_ld32(tmem + lane_base + ch * 32, o);
-      } else {
+    // Everything leaves through shared memory and TMA tile stores, as whole lines: dKt_a as bf16 (its adjoint
+    // kernel feeds it to mma.sync as it is) through the Kt tiles, dV as fp32 through the first query-block
+    // stage -- neither is read by an MMA any more.  Tiles are [128 keys][128 B] with the 128-byte swizzle, so
+    // that the lanes of a warp (one key row each) store without bank conflicts.  The 2 * nacc chunks of 32
+    // columns go round by round to the NCG column groups; a round completes two accumulators, whose tiles
+    // are sent off at once, so that only the last round's copies are waited for at the end.
+    unsigned char* sdV = sStage;                       // columns 0-31 | columns 32-63, KT_BYTES each
+    const int row = qtr * 32 + lane;
+    const int nrounds = (2 * nacc + NCG - 1) / NCG;
+    for (int r = 0; r < nrounds; ++r) {
+      const int ch = r * NCG + cg;
+      if (ch < 2 * nacc) {
+        const int acc = ch >> 1, half = ch & 1;
+        float o[32];
+        if (have) {
+          tc::tmem_ld32(tmem + lane_base + ch * 32, o);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0.f;
-      }
-      if (p.with_dv && acc == 0) {
-        if (store) {
-          float* dst = p.dV + ((size_t)bh * N + krow) * D + half * 32;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
         }
-      } else {
-        // dKt_a leaves as bf16 (its adjoint kernel feeds it to mma.sync as it is), through the shared
-        // memory of the Kt tiles, which no MMA reads any more: [128 keys][128 B] with the 128-byte
-        // swizzle, so that the lanes of a warp (one key row each) store without bank conflicts and the
-        // tile goes out as whole lines
-        const int row = qtr * 32 + lane;
-        unsigned char* tile = sKt + (acc - (p.with_dv ? 1 : 0)) * Cfg::KT_BYTES + row * 128;
+        if (p.with_dv && acc == 0) {
+          unsigned char* tile = sdV + half * Cfg::KT_BYTES + row * 128;
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint4*>(tile + (((half * 4 + i) ^ (row & 7)) << 4)) =
-              make_uint4(pack_bf16(o[8 * i], o[8 * i + 1]), pack_bf16(o[8 * i + 2], o[8 * i + 3]),
-                         pack_bf16(o[8 * i + 4], o[8 * i + 5]), pack_bf16(o[8 * i + 6], o[8 * i + 7]));
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(tile + ((i ^ (row & 7)) << 4)) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        } else {
+          unsigned char* tile = sKt + (acc - (p.with_dv ? 1 : 0)) * Cfg::KT_BYTES + row * 128;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(tile + (((half * 4 + i) ^ (row & 7)) << 4)) =
+                make_uint4(pack_bf16(o[8 * i], o[8 * i + 1]), pack_bf16(o[8 * i + 2], o[8 * i + 3]),
+                           pack_bf16(o[8 * i + 4], o[8 * i + 5]), pack_bf16(o[8 * i + 6], o[8 * i + 7]));
+        }
+      }
+      tc::fence_proxy_async_smem();
+      tc::named_bar_sync(1, Cfg::kEwWarps * 32);
+      if (tid == 0) {                                  // one thread owns the bulk group of every round
+        for (int acc = 2 * r; acc < min(2 * r + 2, nacc); ++acc) {
+          if (p.with_dv && acc == 0) {
+            tc::tma_store_3d(&tmdV, sdV, 0, j0, bh);
+            tc::tma_store_3d(&tmdV, sdV + Cfg::KT_BYTES, 32, j0, bh);
+          } else {
+            const int t = acc - (p.with_dv ? 1 : 0);
+            tc::tma_store_3d(&tmdKt, sKt + t * Cfg::KT_BYTES, 0, j0, bh * cq + p.tap0 + t);
+          }
+        }
+        tc::tma_store_commit();
       }
     }
-    tc::fence_proxy_async_smem();
-    tc::named_bar_sync(1, Cfg::kEwWarps * 32);
-    if (warp == 0 && tc::elect_one()) {
-      for (int t = 0; t < p.ntap; ++t) tc::tma_store_3d(&tmdKt, sKt + t * Cfg::KT_BYTES, 0, j0, bh * cq + p.tap0 + t);
-      tc::tma_store_commit();
-      tc::tma_store_wait_read();
-    }
+    if (tid == 0) tc::tma_store_wait_read();
   }
   __syncwarp();
 
@@ -794,7 +816,8 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (tid == Cfg::kEwWarps * 32) {
       volatile int never = 0;
       if (nblk > 0) {
-        tc::mbar_wait(kv_full, 0, &never);
+        tc::mbar_wait(v_full, 0, &never);
+        if (*s_kt_issued) tc::mbar_wait(kv_full, 0, &never);
         const int issued = *s_issued;
         for (int it = max(0, issued - NSTG); it < issued; ++it) tc::mbar_wait(&full[it % NSTG], (it / NSTG) & 1, &never);
       }
@@ -1107,8 +1130,9 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
   constexpr int D = 64;
   using Cfg = DkvCfg<D, CQMAX, PAIR>;
   const size_t BH = (size_t)p.B * p.H;
-  alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV, tmdKt;
+  alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV, tmdKt, tmdV;
   if (!make_tensor_map_bf16(&tmdKt, dKt, D, p.N, BH * p.cq, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
+  if (!make_tensor_map_f32(&tmdV, p.dV, D, p.N, BH, 32, Cfg::BK, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 64, Cfg::QR, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmdO, p.dO, D, p.N, BH, 64, Cfg::BR, true)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BK, true)) return cudaErrorInvalidValue;
@@ -1122,7 +1146,7 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((p.N + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, tmdKt, bp);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, tmdKt, tmdV, bp);
   return cudaGetLastError();
 }
 

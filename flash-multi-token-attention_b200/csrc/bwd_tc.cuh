@@ -34,6 +34,7 @@ struct BwdTcParams {
 
 
 bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128);
+bool make_tensor_map_f32(CUtensorMap* map, const void* base, int D, int rows, size_t outer, int box_x, int box_rows, bool sw128);
 bool tensor_maps_available();
 
 // streaming dK/dV (bwd_stream.cu): P and dC left in global memory by the dQ kernel
