@@ -34,8 +34,8 @@ def _device_status_clean(request):
 
 def pytest_sessionfinish(session, exitstatus):
     """Per-configuration error table of a GPU session: the largest absolute and relative error of every
-    output over the comparisons made through helpers.check_outputs, printed and (when the folder exists)
-    written to gpurun_out/parity_errors.txt."""
+    output over the comparisons made through helpers.check_outputs, written to parity_errors.txt in the
+    folder named by the environment variable FMTA_REPORT_DIR (nothing is written without it)."""
     try:
         import helpers
     except Exception:
@@ -49,7 +49,7 @@ def pytest_sessionfinish(session, exitstatus):
     for (label, key), (err, ref) in worst.items():
         lines.append("%-78s %-7s %10.3e %10.3g %9.1e" % (label, key, err, ref, err / ref if ref > 0 else 0.0))
     text = "\n".join(lines)
-    out = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("FMTA_REPORT_DIR", "")
+    if out and os.path.isdir(out):
         with open(os.path.join(out, "parity_errors.txt"), "w") as f:
             f.write(text + "\n")
