@@ -24,6 +24,7 @@ static cudaError_t launch_bwd_dkdv_t(const TrainParams& p, cudaStream_t stream) 
 
 cudaError_t launch_bwd_dkdv(const TrainParams& p, cudaStream_t stream) {
   ScopedKernelTimer timer_(kKernBwdDkdvExact, stream);
+  if (hm_dense_supported(p)) return launch_hm_bwd_dkdv(p, stream);   // head mix without a conv: all heads of a group in one CTA
   const bool mix = (p.Wmix != nullptr) && p.G > 1;
   int cq = p.cq, ck = p.ck;
   const bool has_theta = p.theta != nullptr;

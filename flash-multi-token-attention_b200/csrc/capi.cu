@@ -30,7 +30,10 @@ int check_train_dims(int B, int H, int N, int d, int cq, int ck, int G, bool has
     if (cq > 16 || ck > 17 || (ck % 2) == 0) return FMTA_ERR_UNSUPPORTED;
   }
   if (has_w) {
-    if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return FMTA_ERR_UNSUPPORTED;
+    // 32 heads per group: only without a key-query conv and up to head dim 64 (the kernels that keep all heads
+    // of a group in one CTA); the cluster kernels behind conv + mix hold one head per CTA of a cluster of <= 16
+    if (G == 32) { if (has_theta || d > 64) return FMTA_ERR_UNSUPPORTED; }
+    else if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return FMTA_ERR_UNSUPPORTED;
     if (H % G != 0) return FMTA_ERR_SHAPE;
   }
   return FMTA_OK;
@@ -121,7 +124,10 @@ int fmta_selftest_expire_next(int kernel_id) {
 size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, int G) {
   (void)d;
   if (op == FMTA_OP_BWD_DQ) {
-    const size_t slots = (size_t)B * ((N + 63) / 64);
+    // one partial per CTA: 64 query rows per CTA in the tile kernels; the all-heads-in-one-CTA kernels of a
+    // head mix without a conv use 16 to 64 rows (the caller need not know which kernel runs: take the larger)
+    size_t slots = (size_t)B * ((N + 63) / 64);
+    if (G > 1 && (size_t)hm_dq_slots(B, N, G) > slots) slots = (size_t)hm_dq_slots(B, N, G);
     size_t n = slots * H * (size_t)(cq * ck);
     if (G > 1) n += slots * (size_t)(H / G) * G * G;
     return n * sizeof(float);
@@ -213,7 +219,7 @@ int fmta_bwd_dq_dw(const void* Q, const void* K, const void* V, const void* dO, 
   const size_t need = fmta_workspace_bytes(FMTA_OP_BWD_DQ, B, H, N, d, p.cq, p.ck, p.G);
   const bool want_part = (theta != nullptr) || (wmix != nullptr);
   if (want_part && (!workspace || workspace_bytes < need)) return FMTA_ERR_WORKSPACE;
-  const int slots = B * ((N + 63) / 64);
+  const int slots = hm_dense_supported(p) ? hm_dq_slots(B, N, p.G) : B * ((N + 63) / 64);   // one partial per CTA of the kernel that runs
   const size_t n_theta = (size_t)H * p.cq * p.ck;
   p.dQ = dQ;
   p.n_slots = slots;
@@ -260,7 +266,7 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
     use_tc = false;
   }
   p.dQ = dQ; p.dK = dK; p.dV = dV;
-  int slots_ex = B * ((N + 63) / 64);
+  int slots_ex = (!use_tc && hm_dense_supported(p)) ? hm_dq_slots(B, N, p.G) : B * ((N + 63) / 64);
   const size_t n_theta = (size_t)H * p.cq * p.ck;
   if (!use_tc) {
     const size_t need = fmta_workspace_bytes(FMTA_OP_BWD_DQ, B, H, N, d, p.cq, p.ck, p.G);

@@ -88,6 +88,12 @@ bool bwd_tc_supported(const TrainParams& p);
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
 // keep_pdc: the dQ kernel also writes P and dC (workspace of FMTA_OP_BWD_TC_STREAM) and the dK/dV kernel
 // streams them instead of recomputing them (head dim 64)
+// dense head mixing without a key-query conv: all heads of a group in one CTA (headmix_dense.cu)
+bool hm_dense_supported(const TrainParams& p);
+int hm_dq_slots(int B, int N, int G);
+cudaError_t launch_hm_fwd(const TrainParams& p, cudaStream_t stream);
+cudaError_t launch_hm_bwd_dq(const TrainParams& p, cudaStream_t stream);
+cudaError_t launch_hm_bwd_dkdv(const TrainParams& p, cudaStream_t stream);
 cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pdc, cudaStream_t stream);
 cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, bool keep_pdc, cudaStream_t stream);
 size_t bwd_tc_stream_workspace_bytes(int B, int H, int N, int d, int cq);

@@ -60,14 +60,16 @@ extern "C" int fmta_bwd_dq_dw_static(const void* Q, const void* K, const void* V
   if (theta && (cq > 16 || ck > 17 || (ck % 2) == 0)) return FMTA_ERR_UNSUPPORTED;
   if (wmix) {
     if (G < 1) return FMTA_ERR_SHAPE;
-    if (G != 2 && G != 4 && G != 8 && G != 16) return FMTA_ERR_UNSUPPORTED;
+    if (G == 32) { if (theta || d > 64) return FMTA_ERR_UNSUPPORTED; }
+    else if (G != 2 && G != 4 && G != 8 && G != 16) return FMTA_ERR_UNSUPPORTED;
     if (H % G != 0) return FMTA_ERR_SHAPE;
   }
   // Scratch is needed only for the filter / mixing gradients; an over-limit problem is rejected before
   // anything touches the device.
   size_t need = 0;
   if (theta || wmix) {
-    const size_t slots = (size_t)B * (size_t)((N + 63) / 64);
+    size_t slots = (size_t)B * (size_t)((N + 63) / 64);
+    if (wmix && !theta) slots = (size_t)hm_dq_slots(B, N, G);   // the kernel of a mix without a conv: finer row tiles
     if (theta) need += slots * (size_t)H * (size_t)cq * (size_t)ck * sizeof(float);
     if (wmix) need += slots * (size_t)H * (size_t)G * sizeof(float);
   }

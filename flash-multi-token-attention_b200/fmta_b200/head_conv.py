@@ -3,10 +3,11 @@
 ``bwd_dq_dw.py:373``, ``bwd_dk_dv.py:407``), plus the composed "key-query conv then grouped
 head mix" operator of the head-mixing training configuration.
 
-The mix runs inside a thread-block cluster: the G heads of a group live in G CTAs that
-exchange their score tiles through distributed shared memory.  A dense [H,H] matrix is the
-single-group case G = H (H in {2,4,8,16}); grouped mixing takes ``w`` as [H/G, G, G].
-H = 32 dense needs a 32-CTA cluster, which the hardware does not offer: it is rejected.
+Without a key-query conv (the reference's operator) all G heads of a mixing group are handled by
+one CTA (G in {2,4,8,16,32}; 32 up to head dim 64).  A mix that follows a key-query conv runs inside
+a thread-block cluster: the G <= 16 heads of a group live in G CTAs that exchange their score tiles
+through distributed shared memory.  A dense [H,H] matrix is the single-group case G = H; grouped
+mixing takes ``w`` as [H/G, G, G].
 """
 import math
 
@@ -21,7 +22,7 @@ def _bf16c(t):
     return t.to(torch.bfloat16).contiguous()
 
 
-def _group_of(w, H):
+def _group_of(w, H, d=0, has_conv=False):
     """(G, w as fp32 [H/G, G, G]) from a dense [H,H] or grouped [H/G,G,G] matrix."""
     if w.dim() == 2:
         if w.shape[0] != H or w.shape[1] != H:
@@ -35,8 +36,10 @@ def _group_of(w, H):
         wg = as_f32(w)
     else:
         raise RuntimeError("w must be [heads, heads] or [heads/G, G, G]")
-    if G not in (2, 4, 8, 16):
-        raise NotImplementedError("head mixing supports group sizes 2, 4, 8, 16 (got %d)" % G)
+    if G == 32 and (has_conv or d > 64):
+        raise NotImplementedError("32 mixed heads are supported without a key-query conv and up to head dim 64")
+    if G not in (2, 4, 8, 16, 32):
+        raise NotImplementedError("head mixing supports group sizes 2, 4, 8, 16, 32 (got %d)" % G)
     return G, wg
 
 
@@ -56,7 +59,7 @@ def conv_headmix_forward(q, k, v, w, conv_kernel=None, scale=1.0, causal=False, 
     if conv_kernel is not None:
         require_on(qb, conv_kernel, "conv_kernel")
     B, H, N, d = qb.shape
-    G, wg = _group_of(w, H)
+    G, wg = _group_of(w, H, d, conv_kernel is not None)
     th, cq, ck = _theta_args(conv_kernel)
     odt = out_dtype or (q.dtype if q.dtype in (torch.float32, torch.bfloat16) else torch.float32)
     O = torch.empty((B, H, N, d), dtype=odt, device=q.device)
@@ -93,7 +96,7 @@ def _bwd_common(q, k, v, w, o, do, l, m, conv_kernel, causal, scale, lse=None):
         require_on(qb, conv_kernel, "conv_kernel")
     if scale is None:
         scale = 1.0 / math.sqrt(d)
-    G, wg = _group_of(w, H)
+    G, wg = _group_of(w, H, d, conv_kernel is not None)
     th, cq, ck = _theta_args(conv_kernel)
     if lse is None:
         lse = m.float() + torch.log(l.float())

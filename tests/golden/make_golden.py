@@ -40,6 +40,8 @@ def _randn(g, *shape):
 
 
 def conv_case(ref, name, B, H, N, d, c_q, c_k, causal, seed, theta_std, identity, dtype_round=None):
+    if ONLY is not None and name != ONLY:
+        return
     g = torch.Generator().manual_seed(seed)
     Q, K, V, dO = (_randn(g, B, H, N, d) for _ in range(4))
     theta = _randn(g, H, c_q, c_k) * theta_std
@@ -62,6 +64,8 @@ def conv_case(ref, name, B, H, N, d, c_q, c_k, causal, seed, theta_std, identity
 
 
 def decode_case(ref, name, B, H, q_len, Nk, d, c_q, c_k, seed, theta_std, identity):
+    if ONLY is not None and name != ONLY:
+        return
     g = torch.Generator().manual_seed(seed)
     Q = _randn(g, B, H, q_len, d).to(torch.bfloat16).float()
     K = _randn(g, B, H, Nk, d).to(torch.bfloat16).float()
@@ -81,6 +85,8 @@ def decode_case(ref, name, B, H, q_len, Nk, d, c_q, c_k, seed, theta_std, identi
 
 
 def head_case(refh, name, B, H, N, d, causal, seed, w_kind):
+    if ONLY is not None and name != ONLY:
+        return
     g = torch.Generator().manual_seed(seed)
     q, k, v, dO = (_randn(g, B, H, N, d) for _ in range(4))
     if w_kind == "dense":
@@ -99,10 +105,16 @@ def head_case(refh, name, B, H, N, d, causal, seed, w_kind):
     print(name, "O", tuple(O.shape))
 
 
+ONLY = None
+
+
 def main():
+    global ONLY
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference repository")
+    ap.add_argument("--only", default=None, help="write only the fixture of this name (default: all)")
     a = ap.parse_args()
+    ONLY = a.only
     base = os.path.join(a.reference, "flash_multi_token_attention")
     ref = _load(os.path.join(base, "conv_attn", "conv_attention_pytorch.py"), "ref_conv_attention_pytorch")
     refh = _load(os.path.join(base, "head_conv_attn", "head_conv_fn_pytorch.py"), "ref_head_conv_fn_pytorch")
@@ -123,6 +135,8 @@ def main():
     head_case(refh, "head_dense16_noncausal", 1, 16, 45, 32, False, 34, "dense")
     head_case(refh, "head_dense16_causal", 1, 16, 40, 32, True, 35, "dense")
     head_case(refh, "head_group4_causal", 2, 8, 50, 32, True, 36, "group4")
+    # 32 heads, the other head count the reference accepts (fwd_kernel.py:300)
+    head_case(refh, "head_dense32_causal", 1, 32, 24, 32, True, 37, "dense")
 
 
 if __name__ == "__main__":

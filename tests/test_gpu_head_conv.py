@@ -28,7 +28,7 @@ def _grads(q, k, v, w, dO, theta, scale, causal):
     return dict(O=o, L=l, M=m, dq=dq, dk=dk, dv=dv, dw=dw, dth=dth)
 
 
-@pytest.mark.parametrize("name", ["head_dense16_noncausal", "head_dense16_causal", "head_group4_causal"])
+@pytest.mark.parametrize("name", ["head_dense16_noncausal", "head_dense16_causal", "head_group4_causal", "head_dense32_causal"])
 def test_golden(name):
     z = load_golden(name)
     scale, causal = float(z["scale"]), bool(z["causal"])
@@ -94,8 +94,49 @@ def test_autograd_function_dropin():
     assert maxabs(o, z["O"]) <= 3 * TOL_BF16
 
 
-def test_dense_32_heads_is_rejected_loudly():
+@pytest.mark.parametrize("B,H,G,N,d,causal", [
+    (2, 16, 16, 201, 32, False),      # the reference's own comparison shape (fwd_kernel.py:381-396)
+    (1, 16, 16, 150, 64, True),
+    (1, 32, 32, 130, 64, True),       # 32 heads: two heads per warp, two output-column passes in the dK/dV kernel
+    (1, 32, 32, 77, 32, False),
+    (1, 16, 16, 100, 128, True),      # head dim 128: two output-column passes
+    (1, 8, 8, 90, 64, True),          # 32-row tiles
+    (2, 8, 4, 133, 128, True),        # grouped, 64-row tiles
+    (1, 4, 2, 200, 64, False),
+    (1, 64, 32, 50, 64, True),        # two groups of 32
+    (1, 16, 8, 300, 128, False),
+    (1, 32, 32, 16, 64, True),        # exactly one tile
+    (1, 16, 16, 1, 64, True),         # single token
+])
+def test_mix_without_conv_all_heads_in_one_cta(B, H, G, N, d, causal):
+    """Dense and grouped mixing for every supported (group size, head dim) family against the oracle."""
+    g = torch.Generator().manual_seed(1000 * G + N + d)
+    q, k, v, dO = (bf16_round(torch.randn(B, H, N, d, generator=g)) for _ in range(4))
+    wk = torch.randn(H // G, G, G, generator=g) / math.sqrt(G) + 0.5 * torch.eye(G)
+    w = torch.block_diag(*[wk[i] for i in range(H // G)])
+    scale = 1.0 / math.sqrt(d)
+    Or, Lr, Mr = orc.head_conv_fwd(q, k, v, w, scale, causal)
+    dq, dk, dv, _, dw = orc.conv_headmix_bwd_autograd(q, k, v, None, w, dO, scale, causal)
+    dw_ref = torch.stack([dw[G * i:G * i + G, G * i:G * i + G] for i in range(H // G)])
+    got = _grads(q, k, v, wk if G < H else wk[0], dO, None, scale, causal)
+    tol = 1.5 * TOL_BF16              # logits with a standard deviation of ~1.5 here: bf16 P / dS rounding shows
+    assert maxabs(got["O"], Or) <= TOL_BF16
+    assert maxabs(got["M"] + torch.log(got["L"]), Mr + torch.log(Lr)) <= TOL_BF16
+    assert maxabs(got["dq"], dq) <= tol
+    assert maxabs(got["dk"], dk) <= tol
+    assert maxabs(got["dv"], dv) <= tol
+    assert maxabs(got["dw"].reshape(dw_ref.shape), dw_ref) <= dtheta_tol(dw_ref)
+
+
+def test_32_heads_limits_are_rejected_loudly():
+    """32 mixed heads run without a key-query conv up to head dim 64; beyond that the call says so."""
     import fmta_b200 as F
-    q = torch.zeros(1, 32, 16, 32, device="cuda", dtype=torch.bfloat16)
+    q = torch.zeros(1, 32, 16, 128, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(NotImplementedError):
         F.head_conv_attention_forward(q, q, q, torch.eye(32, device="cuda"))
+    q = torch.zeros(1, 32, 16, 64, device="cuda", dtype=torch.bfloat16)
+    th = torch.zeros(32, 3, 3, device="cuda")
+    with pytest.raises(NotImplementedError):
+        F.conv_headmix_forward(q, q, q, torch.eye(32, device="cuda"), th, 1.0, True)
+    o, l, m = F.head_conv_attention_forward(q, q, q, torch.eye(32, device="cuda"))
+    assert torch.isfinite(o.float()).all()
