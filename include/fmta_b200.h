@@ -21,7 +21,9 @@
  *   - supported head dims: 32, 64, 128.  Filter shapes: any c_q in [1,16], odd c_k in [1,17]
  *     (c_k must be odd: the reference's own PyTorch path fails for even c_k);
  *   - head mixing: G consecutive heads form a group mixed by a G x G matrix
- *     (W layout [H/G, G, G], row = output head); G in {1,2,4,8,16}, H % G == 0.
+ *     (W layout [H/G, G, G], row = output head); G in {1,2,4,8,16}, H % G == 0; G = 32 as well when
+ *     theta is NULL and d <= 64 (the reference's head-conv operator accepts 16 or 32 heads,
+ *     head_conv_attn/fwd_kernel.py:300).
  */
 #ifndef FMTA_B200_H_
 #define FMTA_B200_H_
