@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the conv-attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl ours|reference] [--no-decode] [--no-sweep]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl ours|reference] [--no-decode] [--no-sweep] [--no-headmix]
 
 One "step" = conv-attention forward + backward (D prep, dQ/dTheta, dK/dV, partial reduction,
 and for N > 1 the all-reduce of dTheta) on the bf16 training configuration
@@ -273,6 +273,8 @@ def main():
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated (median reported)")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-headmix", action="store_true")
+    ap.add_argument("--headmix-shape", default=None, help="B,H,N,d: time only this dense head-mix shape (profiling captures)")
     ap.add_argument("--sweep-max-n", type=int, default=65536)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="tiny shapes (profiling / debugging)")
@@ -493,6 +495,13 @@ def main():
             line["sweep"] = dict(error="out of memory: %s" % str(e)[:80])
         F.check_device_status(dev)
 
+    # ---- head mixing: the reference's head-conv operator (no conv) and the composed conv + mix configuration ----
+    if not args.no_headmix and not args.small and not args.train_shape:
+        try:
+            line["headmix"] = bench_headmix(F, dev, timed, args.headmix_shape)
+        except torch.OutOfMemoryError as e:   # pragma: no cover
+            line["headmix"] = dict(error="out of memory: %s" % str(e)[:80])
+
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_reference_sample(steps=3, warmup=1)
     if rank == 0:
@@ -577,6 +586,48 @@ def bench_sweep(F, dev, world, rank, peaks, barrier, max_n):
                                      "sharded by (batch, head)" % (B, H, d, cq, ck), shard_mode=plan["mode"],
                             collective="all-reduce of dTheta [H,%d,%d] fp32 (NCCL)" % (cq, ck) if world > 1 else "none"),
                 peak=peaks["tflops_sustained"], peak_source=peaks["source"] + " (sustained)", points=points)
+
+
+def bench_headmix(F, dev, timed, shape=None):
+    """Rank-local timings (ms, CUDA events) of the head-mixing operators, forward + dQ/dW + dK/dV, causal, bf16:
+    the reference's head-conv attention (dense W over 16 and 32 heads, no conv) and, unless a shape is given, the
+    head-mixing training configuration (theta (6,11) then groups of 4; B=2,H=32,N=8192,d=128).  TFLOP/s counts
+    the attention products only (14*d per score entry), as the headline does."""
+    pts = []
+    g = torch.Generator(device=dev).manual_seed(11)
+    shapes = [tuple(int(x) for x in shape.split(","))] if shape else [(2, 16, 4096, 64), (2, 32, 4096, 64), (2, 16, 4096, 128)]
+    for (B, H, N, d) in shapes:
+        q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).to(torch.bfloat16) for _ in range(4))
+        w = torch.randn(H, H, device=dev, generator=g) / math.sqrt(H)
+        sc = 1.0 / math.sqrt(d)
+        o, l, m = F.head_conv_attention_forward(q, k, v, w, sc, True)
+        fns = (lambda: F.head_conv_attention_forward(q, k, v, w, sc, True),
+               lambda: F.head_conv_attention_bwd_dq_dw(q, k, v, w, o, do, l, m, True, sc),
+               lambda: F.head_conv_attention_bwd_dkdv(q, k, v, w, o, do, l, m, True, sc))
+        ms = []
+        for fn in fns:
+            fn()
+            ms.append(timed(fn, 3) / 3)
+        E = B * H * N * (N + 1) / 2.0
+        pts.append(dict(workload="head-conv attention (dense %d-head mix, no conv) B=%d,N=%d,d=%d" % (H, B, N, d),
+                        fwd_ms=ms[0], dq_dw_ms=ms[1], dk_dv_ms=ms[2], value=14.0 * d * E / (sum(ms) * 1e-3) / 1e12, unit="TFLOP/s"))
+        del q, k, v, do, o, l, m
+    if not shape:
+        B, H, N, d, G, cq, ck = 2, 32, 8192, 128, 4, 6, 11
+        q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).to(torch.bfloat16) for _ in range(4))
+        th = torch.randn(H, cq, ck, device=dev, generator=g) * 0.02
+        th[:, cq - 1, ck // 2] += 1.0
+        w = (torch.eye(G, device=dev).repeat(H // G, 1, 1) + 0.02 * torch.randn(H // G, G, G, device=dev, generator=g)).contiguous()
+        sc = 1.0 / math.sqrt(d)
+        o, l, m, lse = F.conv_headmix_forward(q, k, v, w, th, sc, True, out_dtype=torch.float32)
+        fns = (lambda: F.conv_headmix_forward(q, k, v, w, th, sc, True, out_dtype=torch.float32),
+               lambda: F.conv_headmix_bwd_dq_dw(q, k, v, w, o, do, l, m, th, True, sc),
+               lambda: F.conv_headmix_bwd_dkdv(q, k, v, w, o, do, l, m, th, True, sc))
+        ms = [timed(fn, 1) for fn in fns]
+        E = B * H * N * (N + 1) / 2.0
+        pts.append(dict(workload="conv (6,11) then mix in groups of 4, B=%d,H=%d,N=%d,d=%d (cluster kernels)" % (B, H, N, d),
+                        fwd_ms=ms[0], dq_dw_ms=ms[1], dk_dv_ms=ms[2], value=14.0 * d * E / (sum(ms) * 1e-3) / 1e12, unit="TFLOP/s"))
+    return dict(metric="head-mix attention fwd+bwd TFLOP/s (per GPU)", points=pts)
 
 
 def bench_decode(F, dev, dec, peaks, world, timed):

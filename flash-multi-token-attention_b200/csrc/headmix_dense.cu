@@ -61,6 +61,12 @@ FMTA_DEVINL void load_set(bf16* dst, int ld, int rows, const bf16* __restrict__ 
   }
 }
 
+// The fp32 score tiles are rows of 16 floats = four 16-byte chunks; chunk c of row r is stored at chunk
+// c ^ ((r >> 1) & 3), so that the eight lanes of a quarter-warp -- four rows, two 8-key strips -- read their
+// chunks from different banks (unswizzled, rows two apart share them: every load took two wavefronts, every
+// fragment store four; the kernels are bound by shared-memory wavefronts).
+FMTA_DEVINL int sw_chunk(int row, int chunk) { return chunk ^ ((row >> 1) & 3); }
+
 // item -> (head, 16-row tile)
 template <int G, int MT>
 FMTA_DEVINL void item_of(int item, int& g, int& mt) {
@@ -86,7 +92,7 @@ FMTA_DEVINL void head_products(float* out, const bf16* sA, int a_rows, const bf1
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int r = mt * 16 + (lane >> 2) + hh * 8, c = j * 8 + (lane & 3) * 2;
-          *reinterpret_cast<float2*>(out + ((size_t)g * a_rows + r) * C::S_LD + c) =
+          *reinterpret_cast<float2*>(out + ((size_t)g * a_rows + r) * C::S_LD + sw_chunk(r, c >> 2) * 4 + (c & 3)) =
               make_float2(acc[j][2 * hh] * alpha, acc[j][2 * hh + 1] * alpha);
         }
     }
@@ -98,11 +104,12 @@ template <int G>
 FMTA_DEVINL void mix_strip(float (&acc)[8], const float* sS, int rows, int row, int half, const float* w, int wstride) {
 #pragma unroll
   for (int c = 0; c < 8; ++c) acc[c] = 0.f;
-  const float* sp = sS + (size_t)row * BC + half * 8;
+  const float* sp = sS + (size_t)row * BC;
+  const int ca = sw_chunk(row, 2 * half) * 4, cb = sw_chunk(row, 2 * half + 1) * 4;
 #pragma unroll 4
   for (int g2 = 0; g2 < G; ++g2) {
-    const float4 a = *reinterpret_cast<const float4*>(sp + (size_t)g2 * rows * BC);
-    const float4 b = *reinterpret_cast<const float4*>(sp + (size_t)g2 * rows * BC + 4);
+    const float4 a = *reinterpret_cast<const float4*>(sp + (size_t)g2 * rows * BC + ca);
+    const float4 b = *reinterpret_cast<const float4*>(sp + (size_t)g2 * rows * BC + cb);
     const float wv = w[g2 * wstride];
     acc[0] = fmaf(wv, a.x, acc[0]); acc[1] = fmaf(wv, a.y, acc[1]); acc[2] = fmaf(wv, a.z, acc[2]); acc[3] = fmaf(wv, a.w, acc[3]);
     acc[4] = fmaf(wv, b.x, acc[4]); acc[5] = fmaf(wv, b.y, acc[5]); acc[6] = fmaf(wv, b.z, acc[6]); acc[7] = fmaf(wv, b.w, acc[7]);
@@ -316,8 +323,10 @@ FMTA_DEVINL void bwd_mix_phase(const float* sS, float* sDC, bf16* sPb, const flo
     const int half = task & 1, outer = (task >> 1) % BR, g = task / (2 * BR);
     float c[8];
     mix_strip<G>(c, sS, BR, outer, half, sW + g * G, 1);
-    float* dc = sDC + ((size_t)g * BR + outer) * BC + half * 8;
-    const float4 d0 = *reinterpret_cast<const float4*>(dc), d1 = *reinterpret_cast<const float4*>(dc + 4);
+    float* dcr = sDC + ((size_t)g * BR + outer) * BC;
+    float* dca = dcr + sw_chunk(outer, 2 * half) * 4;
+    float* dcb = dcr + sw_chunk(outer, 2 * half + 1) * 4;
+    const float4 d0 = *reinterpret_cast<const float4*>(dca), d1 = *reinterpret_cast<const float4*>(dcb);
     const float dp[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
     float pr[8], out[8];
 #pragma unroll
@@ -329,8 +338,8 @@ FMTA_DEVINL void bwd_mix_phase(const float* sS, float* sDC, bf16* sPb, const flo
       pr[k] = ok ? exp2f((c[k] - sLSE[ri]) * kLog2e) : 0.f;
       out[k] = pr[k] * (dp[k] - sDv[ri]);
     }
-    *reinterpret_cast<float4*>(dc) = make_float4(out[0], out[1], out[2], out[3]);
-    *reinterpret_cast<float4*>(dc + 4) = make_float4(out[4], out[5], out[6], out[7]);
+    *reinterpret_cast<float4*>(dca) = make_float4(out[0], out[1], out[2], out[3]);
+    *reinterpret_cast<float4*>(dcb) = make_float4(out[4], out[5], out[6], out[7]);
     if (WANT_P)
       *reinterpret_cast<uint4*>(sPb + ((size_t)g * BR + outer) * (BC + 8) + half * 8) =
           make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
