@@ -99,20 +99,22 @@ FMTA_DEVINL void head_products(float* out, const bf16* sA, int a_rows, const bf1
   }
 }
 
-// acc[8] = sum_g2 w(g2) * S[g2][row][half*8 .. +7]   (the mix of one (row, 8 keys) strip for one output head)
+// The mix of one (row, 4 keys) quad for TWO output heads: acc[h][c] = sum_g2 w2[g2].{x,y} * S[g2][row][4q + c].
+// `w2` points at the pair of weights of input head 0; consecutive input heads are `wstride` floats apart.
+// One 16-byte load of scores and one 8-byte broadcast load of weights feed 8 FMAs.
 template <int G>
-FMTA_DEVINL void mix_strip(float (&acc)[8], const float* sS, int rows, int row, int half, const float* w, int wstride) {
+FMTA_DEVINL void mix_quad(float (&acc)[2][4], const float* sS, int rows, int row, int q, const float* w2, int wstride) {
 #pragma unroll
-  for (int c = 0; c < 8; ++c) acc[c] = 0.f;
-  const float* sp = sS + (size_t)row * BC;
-  const int ca = sw_chunk(row, 2 * half) * 4, cb = sw_chunk(row, 2 * half + 1) * 4;
+  for (int c = 0; c < 4; ++c) acc[0][c] = acc[1][c] = 0.f;
+  const float* sp = sS + (size_t)row * BC + sw_chunk(row, q) * 4;
 #pragma unroll 4
   for (int g2 = 0; g2 < G; ++g2) {
-    const float4 a = *reinterpret_cast<const float4*>(sp + (size_t)g2 * rows * BC + ca);
-    const float4 b = *reinterpret_cast<const float4*>(sp + (size_t)g2 * rows * BC + cb);
-    const float wv = w[g2 * wstride];
-    acc[0] = fmaf(wv, a.x, acc[0]); acc[1] = fmaf(wv, a.y, acc[1]); acc[2] = fmaf(wv, a.z, acc[2]); acc[3] = fmaf(wv, a.w, acc[3]);
-    acc[4] = fmaf(wv, b.x, acc[4]); acc[5] = fmaf(wv, b.y, acc[5]); acc[6] = fmaf(wv, b.z, acc[6]); acc[7] = fmaf(wv, b.w, acc[7]);
+    const float4 a = *reinterpret_cast<const float4*>(sp + (size_t)g2 * rows * BC);
+    const float2 wv = *reinterpret_cast<const float2*>(w2 + g2 * wstride);
+    acc[0][0] = fmaf(wv.x, a.x, acc[0][0]); acc[0][1] = fmaf(wv.x, a.y, acc[0][1]);
+    acc[0][2] = fmaf(wv.x, a.z, acc[0][2]); acc[0][3] = fmaf(wv.x, a.w, acc[0][3]);
+    acc[1][0] = fmaf(wv.y, a.x, acc[1][0]); acc[1][1] = fmaf(wv.y, a.y, acc[1][1]);
+    acc[1][2] = fmaf(wv.y, a.z, acc[1][2]); acc[1][3] = fmaf(wv.y, a.w, acc[1][3]);
   }
 }
 
@@ -125,8 +127,8 @@ struct FwdSmem {
   static constexpr int oS = oKV + C::KSET;
   static constexpr int oP = oS + C::SSET;
   static constexpr int oStat = oP + C::PSET;                 // M, L, alpha: [G][BR] each
-  static constexpr int oW = oStat + 3 * G * C::BR * 4;
-  static constexpr int kBytes = oW + G * G * 4;
+  static constexpr int oWt = oStat + 3 * G * C::BR * 4;        // W transposed: [input head][output head]
+  static constexpr int kBytes = oWt + G * G * 4;
   static_assert(kBytes <= 227 * 1024, "forward: shared memory budget");
 };
 
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(NT, 1) hm_fwd_kernel(const TrainParams p) {
   float* sM = reinterpret_cast<float*>(smem + SM::oStat);
   float* sL = sM + G * BR;
   float* sAlpha = sL + G * BR;
-  float* sW = reinterpret_cast<float*>(smem + SM::oW);
+  float* sWt = reinterpret_cast<float*>(smem + SM::oWt);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = p.N, H = p.H;
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(NT, 1) hm_fwd_kernel(const TrainParams p) {
   const bf16* Kg = p.K + bh0 * hs;
   const bf16* Vg = p.V + bh0 * hs;
 
-  for (int i = tid; i < G * G; i += NT) sW[i] = p.Wmix[(size_t)grp * G * G + i];
+  for (int i = tid; i < G * G; i += NT) sWt[(i % G) * G + i / G] = p.Wmix[(size_t)grp * G * G + i];
   for (int i = tid; i < G * BR; i += NT) { sM[i] = -INFINITY; sL[i] = 0.f; }
   constexpr int ONT = D / 8;
   float accO[C::IPW][ONT][4];
@@ -181,35 +183,47 @@ __global__ void __launch_bounds__(NT, 1) hm_fwd_kernel(const TrainParams p) {
     load_set<D>(sKV, LD, BC, Vg, hs, G, j0, N, tid);     // V(kb) arrives under the mix and the softmax
     cp_async_commit();
 
-    // ---- mix + online softmax: a thread owns (head, row, 8 keys); the two halves of a row sit in adjacent lanes ----
-    for (int task = tid; task < G * BR * 2; task += NT) {
-      const int half = task & 1, row = (task >> 1) % BR, g = task / (2 * BR);
-      float c[8];
-      mix_strip<G>(c, sS, BR, row, half, sW + g * G, 1);
+    // ---- mix + online softmax: a thread owns (two output heads, row, 4 keys); the quads of a row sit in adjacent lanes ----
+    for (int task = tid; task < (G / 2) * BR * 4; task += NT) {
+      const int q = task & 3, row = (task >> 2) % BR, gp = task / (4 * BR);
+      float c[2][4];
+      mix_quad<G>(c, sS, BR, row, q, sWt + 2 * gp, G);
       const int qi = i0 + row;
-      float mx = -INFINITY;
+      float m_old[2], m_new[2], sum[2];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int kj = j0 + half * 8 + k;
-        if (kj >= N || (causal && kj > qi)) c[k] = -INFINITY;
-        mx = fmaxf(mx, c[k]);
+      for (int h = 0; h < 2; ++h) {
+        const int g = 2 * gp + h;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int kj = j0 + q * 4 + k;
+          if (kj >= N || (causal && kj > qi)) c[h][k] = -INFINITY;
+          mx = fmaxf(mx, c[h][k]);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        m_old[h] = sM[g * BR + row];
+        m_new[h] = fmaxf(m_old[h], mx);
+        const float m_use = (m_new[h] == -INFINITY) ? 0.f : m_new[h];
+        float pr[4], sm = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { pr[k] = exp2f((c[h][k] - m_use) * kLog2e); sm += pr[k]; }
+        sm += __shfl_xor_sync(0xffffffffu, sm, 1);
+        sm += __shfl_xor_sync(0xffffffffu, sm, 2);
+        sum[h] = sm;
+        *reinterpret_cast<uint2*>(sP + ((size_t)g * BR + row) * P_LD + q * 4) = make_uint2(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]));
       }
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      const float m_old = sM[g * BR + row];
-      const float m_new = fmaxf(m_old, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      float sum = 0.f, pr[8];
+      __syncwarp();                                      // every quad of the row has read the old maximum
+      if (q == 0) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) { pr[k] = exp2f((c[k] - m_use) * kLog2e); sum += pr[k]; }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      *reinterpret_cast<uint4*>(sP + ((size_t)g * BR + row) * P_LD + half * 8) =
-          make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
-      __syncwarp();                                      // both halves have read the old maximum
-      if (half == 0) {
-        const float alpha = (m_old == -INFINITY) ? 0.f : exp2f((m_old - m_use) * kLog2e);
-        sM[g * BR + row] = m_new;
-        sL[g * BR + row] = sL[g * BR + row] * alpha + sum;
-        sAlpha[g * BR + row] = alpha;
+        for (int h = 0; h < 2; ++h) {
+          const int g = 2 * gp + h;
+          const float m_use = (m_new[h] == -INFINITY) ? 0.f : m_new[h];
+          const float alpha = (m_old[h] == -INFINITY) ? 0.f : exp2f((m_old[h] - m_use) * kLog2e);
+          sM[g * BR + row] = m_new[h];
+          sL[g * BR + row] = sL[g * BR + row] * alpha + sum[h];
+          sAlpha[g * BR + row] = alpha;
+        }
       }
     }
     cp_async_wait<0>();
@@ -294,7 +308,7 @@ template <int D, int G, bool TR>
 struct BwdSmem {
   using C = Cfg<D, G>;
   // "big" sets have BR rows per head (Q, dO for dQ; K, V for dK/dV), "small" sets 16 (K, V; Q, dO)
-  static constexpr int kFixed = 2 * C::SSET + 2 * G * C::BR * 4 + G * G * 4 + (TR ? 0 : 4096);
+  static constexpr int kFixed = 2 * C::SSET + 2 * G * C::BR * 4 + 2 * G * G * 4 + (TR ? 0 : 4096);
   static constexpr int kBase = C::TSET + C::KSET + kFixed;                    // one big + one small buffer
   static constexpr int kPb = TR ? C::PSET : 0;                                // dK/dV: P^T needs a place of its own beside a resident V
   static constexpr bool BIG2 = kBase + C::TSET + kPb <= 227 * 1024;           // second big buffer (dO | V resident)
@@ -308,53 +322,56 @@ struct BwdSmem {
   static constexpr int oPb = (TR && BIG2) ? oDC + C::SSET : oBigB;            // without a resident V, P^T takes V's place
   static constexpr int oStat = oDC + C::SSET + ((TR && BIG2) ? C::PSET : 0);  // LSE, D
   static constexpr int oW = oStat + 2 * G * C::BR * 4;
-  static constexpr int oRed = oW + G * G * 4;                                 // dW reduction (dQ kernel)
+  static constexpr int oWt = oW + G * G * 4;                                  // W transposed: [input head][output head]
+  static constexpr int oRed = oWt + G * G * 4;                                // dW reduction (dQ kernel)
   static constexpr int kBytes = oRed + (TR ? 0 : 4096);
   static_assert(kBytes <= 227 * 1024, "backward: shared memory budget");
   static_assert(C::PSET <= C::TSET && C::PSET <= C::SSET, "aliased bf16 tiles");
 };
 
-// P (optional, bf16) and dC' = P (dP - D) in place of dP, for the strips of all heads.
+// P (optional, bf16) and dC' = P (dP - D) in place of dP, for all heads; a thread owns (two output heads, outer, 4 strip elements).
 template <int G, int BR, bool TR, bool WANT_P>
-FMTA_DEVINL void bwd_mix_phase(const float* sS, float* sDC, bf16* sPb, const float* sW, const float* sLSE, const float* sDv,
+FMTA_DEVINL void bwd_mix_phase(const float* sS, float* sDC, bf16* sPb, const float* sWt, const float* sLSE, const float* sDv,
                                int o0, int s0, int N, bool causal, int tid) {
   constexpr int LR = TR ? BC : BR;                       // rows of the per-row statistics per head
-  for (int task = tid; task < G * BR * 2; task += NT) {
-    const int half = task & 1, outer = (task >> 1) % BR, g = task / (2 * BR);
-    float c[8];
-    mix_strip<G>(c, sS, BR, outer, half, sW + g * G, 1);
-    float* dcr = sDC + ((size_t)g * BR + outer) * BC;
-    float* dca = dcr + sw_chunk(outer, 2 * half) * 4;
-    float* dcb = dcr + sw_chunk(outer, 2 * half + 1) * 4;
-    const float4 d0 = *reinterpret_cast<const float4*>(dca), d1 = *reinterpret_cast<const float4*>(dcb);
-    const float dp[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-    float pr[8], out[8];
+  for (int task = tid; task < (G / 2) * BR * 4; task += NT) {
+    const int q = task & 3, outer = (task >> 2) % BR, gp = task / (4 * BR);
+    float c[2][4];
+    mix_quad<G>(c, sS, BR, outer, q, sWt + 2 * gp, G);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const int st = half * 8 + k;
-      const int qi = TR ? s0 + st : o0 + outer, kj = TR ? o0 + outer : s0 + st;
-      const int ri = g * LR + (TR ? st : outer);
-      const bool ok = qi < N && kj < N && !(causal && kj > qi);
-      pr[k] = ok ? exp2f((c[k] - sLSE[ri]) * kLog2e) : 0.f;
-      out[k] = pr[k] * (dp[k] - sDv[ri]);
+    for (int h = 0; h < 2; ++h) {
+      const int g = 2 * gp + h;
+      float* dc = sDC + ((size_t)g * BR + outer) * BC + sw_chunk(outer, q) * 4;
+      const float4 d4 = *reinterpret_cast<const float4*>(dc);
+      const float dp[4] = {d4.x, d4.y, d4.z, d4.w};
+      float pr[4], out[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int st = q * 4 + k;
+        const int qi = TR ? s0 + st : o0 + outer, kj = TR ? o0 + outer : s0 + st;
+        const int ri = g * LR + (TR ? st : outer);
+        const bool ok = qi < N && kj < N && !(causal && kj > qi);
+        pr[k] = ok ? exp2f((c[h][k] - sLSE[ri]) * kLog2e) : 0.f;
+        out[k] = pr[k] * (dp[k] - sDv[ri]);
+      }
+      *reinterpret_cast<float4*>(dc) = make_float4(out[0], out[1], out[2], out[3]);
+      if (WANT_P)
+        *reinterpret_cast<uint2*>(sPb + ((size_t)g * BR + outer) * (BC + 8) + q * 4) = make_uint2(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]));
     }
-    *reinterpret_cast<float4*>(dca) = make_float4(out[0], out[1], out[2], out[3]);
-    *reinterpret_cast<float4*>(dcb) = make_float4(out[4], out[5], out[6], out[7]);
-    if (WANT_P)
-      *reinterpret_cast<uint4*>(sPb + ((size_t)g * BR + outer) * (BC + 8) + half * 8) =
-          make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
   }
 }
 
-// dS_g' = sum_g W[g,g'] dC'_g as bf16 strips [g'][outer][P_LD]
+// dS_g' = sum_g W[g,g'] dC'_g as bf16 strips [g'][outer][P_LD]; a thread owns (two input heads g', outer, 4 strip elements)
 template <int G, int BR>
 FMTA_DEVINL void bwd_unmix_phase(const float* sDC, bf16* sDS, const float* sW, int tid) {
-  for (int task = tid; task < G * BR * 2; task += NT) {
-    const int half = task & 1, outer = (task >> 1) % BR, g2 = task / (2 * BR);
-    float c[8];
-    mix_strip<G>(c, sDC, BR, outer, half, sW + g2, G);   // column g2 of W
-    *reinterpret_cast<uint4*>(sDS + ((size_t)g2 * BR + outer) * (BC + 8) + half * 8) =
-        make_uint4(pack_bf16(c[0], c[1]), pack_bf16(c[2], c[3]), pack_bf16(c[4], c[5]), pack_bf16(c[6], c[7]));
+  for (int task = tid; task < (G / 2) * BR * 4; task += NT) {
+    const int q = task & 3, outer = (task >> 2) % BR, gp = task / (4 * BR);
+    float c[2][4];
+    mix_quad<G>(c, sDC, BR, outer, q, sW + 2 * gp, G);   // columns 2gp, 2gp + 1 of W: the weights of head g sit at sW[g * G + ...]
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      *reinterpret_cast<uint2*>(sDS + ((size_t)(2 * gp + h) * BR + outer) * (BC + 8) + q * 4) =
+          make_uint2(pack_bf16(c[h][0], c[h][1]), pack_bf16(c[h][2], c[h][3]));
   }
 }
 
@@ -374,6 +391,7 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dq_kernel(const TrainParams p) {
   float* sLSE = reinterpret_cast<float*>(smem + SM::oStat);
   float* sDv = sLSE + G * BR;
   float* sW = reinterpret_cast<float*>(smem + SM::oW);
+  float* sWt = reinterpret_cast<float*>(smem + SM::oWt);
   float* sRed = reinterpret_cast<float*>(smem + SM::oRed);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -390,7 +408,11 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dq_kernel(const TrainParams p) {
   const bf16* Vg = p.V + bh0 * hs;
   const bf16* dOg = p.dO + bh0 * hs;
 
-  for (int i = tid; i < G * G; i += NT) sW[i] = p.Wmix[(size_t)grp * G * G + i];
+  for (int i = tid; i < G * G; i += NT) {
+    const float wv = p.Wmix[(size_t)grp * G * G + i];
+    sW[i] = wv;
+    sWt[(i % G) * G + i / G] = wv;
+  }
 
   // dW[g][g'] = sum over the tile of dC'_g * S_g': a thread owns a GB x GB block of (g, g') pairs and a share
   // of the tile's 4-float chunks (the shares of a block sit in adjacent lanes), so that 2 * GB loads feed
@@ -447,7 +469,7 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dq_kernel(const TrainParams p) {
         load_set<D>(sK, LD, BC, Kg, hs, G, j0, N, tid);
         cp_async_commit();
       }
-      bwd_mix_phase<G, BR, false, false>(sS, sDC, nullptr, sW, sLSE, sDv, i0, j0, N, causal, tid);
+      bwd_mix_phase<G, BR, false, false>(sS, sDC, nullptr, sWt, sLSE, sDv, i0, j0, N, causal, tid);
       __syncthreads();
       // ---- dW partial sums ----
       for (int ch = dw_part; ch < CH; ch += PARTS) {
@@ -564,6 +586,7 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dkdv_kernel(const TrainParams p)
   float* sLSE = reinterpret_cast<float*>(smem + SM::oStat);
   float* sDv = sLSE + G * BR;                                // (only G * 16 entries of each are used)
   float* sW = reinterpret_cast<float*>(smem + SM::oW);
+  float* sWt = reinterpret_cast<float*>(smem + SM::oWt);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = p.N, H = p.H;
@@ -580,7 +603,11 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dkdv_kernel(const TrainParams p)
   const bf16* Vg = p.V + bh0 * hs;
   const bf16* dOg = p.dO + bh0 * hs;
 
-  for (int i = tid; i < G * G; i += NT) sW[i] = p.Wmix[(size_t)grp * G * G + i];
+  for (int i = tid; i < G * G; i += NT) {
+    const float wv = p.Wmix[(size_t)grp * G * G + i];
+    sW[i] = wv;
+    sWt[(i % G) * G + i / G] = wv;
+  }
   constexpr int ONT = DH / 8;
   float accK[C::IPW][ONT][4], accV[C::IPW][ONT][4];
 #pragma unroll
@@ -622,7 +649,7 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dkdv_kernel(const TrainParams p)
     }
     head_products<D, G>(sDC, sV, BR, sdO, 1.f, warp, lane);              // dP^T
     __syncthreads();                                                     // V no longer read: P^T may take its place
-    bwd_mix_phase<G, BR, true, true>(sS, sDC, sPb, sW, sLSE, sDv, j0, i0, N, causal, tid);
+    bwd_mix_phase<G, BR, true, true>(sS, sDC, sPb, sWt, sLSE, sDv, j0, i0, N, causal, tid);
     __syncthreads();
     // ---- dV += P^T dO (columns c0 ...), and dS^T strips into the place of S^T ----
 #pragma unroll
