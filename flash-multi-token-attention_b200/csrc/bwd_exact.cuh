@@ -112,7 +112,11 @@ struct BwdSmem {
 // Leaves bf16 P (owned tile) in sPb and bf16 dS (owned tile) in sDS, visible CTA-wide.
 template <int D, int CQ, int CK, bool MIX, bool WANT_DTHETA>
 FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& p, int i0, int j0,
-                          int cq, int ck, int G, int grank, int tid) {
+                          int cq, int ck, int G, int grank, int tid, const float* xbase = nullptr, size_t xstride = 0,
+                          float* xme = nullptr) {
+  // head mix: xme != nullptr -> the heads' tiles are exchanged through global memory (slot A: own C, slot B:
+  // dC'; xbase = slot pair of head 0 of the group, xstride floats between heads), else through distributed
+  // shared memory
   using Cfg = BwdExactCfg<D, CQ, CK, MIX>;
   constexpr int BR = Cfg::BR, H1 = Cfg::H1, HC = Cfg::HC, ER = Cfg::ER, EC = Cfg::EC;
   constexpr int SR = Cfg::SR, SC = Cfg::SC, S_LD = Cfg::S_LD, E_LD = Cfg::E_LD, QK_LD = Cfg::QK_LD;
@@ -173,25 +177,25 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
     float4* o = reinterpret_cast<float4*>(cown + r * E_LD + s * 16);
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[i] = make_float4(acc[4*i], acc[4*i+1], acc[4*i+2], acc[4*i+3]);
+    if constexpr (MIX) {
+      if (xme != nullptr) {
+        float4* og = reinterpret_cast<float4*>(xme + r * E_LD + s * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) og[i] = make_float4(acc[4*i], acc[4*i+1], acc[4*i+2], acc[4*i+3]);
+      }
+    }
   }
   if constexpr (MIX) {
     cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();  // every head's conv output is in its sX
+    if (xme != nullptr) __threadfence();
+    cluster.sync();  // every head's conv output is in its sX (and in its global slot)
     for (int t = tid; t < ER * (EC / 16); t += Cfg::NT) {
       const int r = t % ER, s = t / ER;
       float acc[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      for (int g2 = 0; g2 < G; ++g2) {
-        const float w = sm.sW[grank * G + g2];
-        const float4* src = reinterpret_cast<const float4*>(cluster.map_shared_rank(sm.sX, g2) + r * E_LD + s * 16);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 v = src[i];
-          acc[4*i] = fmaf(w, v.x, acc[4*i]); acc[4*i+1] = fmaf(w, v.y, acc[4*i+1]);
-          acc[4*i+2] = fmaf(w, v.z, acc[4*i+2]); acc[4*i+3] = fmaf(w, v.w, acc[4*i+3]);
-        }
-      }
+      if (xme != nullptr) mix_global16(acc, xbase, xstride, r * E_LD + s * 16, sm.sW + grank * G, 1, G);
+      else mix_remote16(acc, cluster, sm.sX, r * E_LD + s * 16, sm.sW + grank * G, 1, G);
       const int qi = i0 + r;
       const float lse = sm.sLSE[r];
 #pragma unroll
@@ -242,17 +246,37 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
 #pragma unroll
         for (int i = 0; i < 4; ++i) { float4 v = src[i]; dcv[4*i] = v.x; dcv[4*i+1] = v.y; dcv[4*i+2] = v.z; dcv[4*i+3] = v.w; }
       }
-      for (int g2 = 0; g2 < G; ++g2) {
-        const float4* src = reinterpret_cast<const float4*>(cluster.map_shared_rank(sm.sX, g2) + r * E_LD + HC + s * 16);
-        float a = 0.f;
+      for (int g0 = 0; g0 < G; g0 += 4) {   // the loads of four heads are issued together (remote latency)
+        float4 v[4][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 v = src[i];
-          a = fmaf(dcv[4*i], v.x, a); a = fmaf(dcv[4*i+1], v.y, a); a = fmaf(dcv[4*i+2], v.z, a); a = fmaf(dcv[4*i+3], v.w, a);
+        for (int u = 0; u < 4; ++u) {
+          const float4* src = (xme != nullptr)
+              ? reinterpret_cast<const float4*>(xbase + (size_t)min(g0 + u, G - 1) * xstride + r * E_LD + HC + s * 16)
+              : reinterpret_cast<const float4*>(cluster.map_shared_rank(sm.sX, min(g0 + u, G - 1)) + r * E_LD + HC + s * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[u][i] = (xme != nullptr) ? __ldcg(src + i) : src[i];
         }
-        a = warp_sum(a);
-        if (lane == 0) sm.sDW[warp * 64 + g2] += a;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float a = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            a = fmaf(dcv[4*i], v[u][i].x, a); a = fmaf(dcv[4*i+1], v[u][i].y, a); a = fmaf(dcv[4*i+2], v[u][i].z, a); a = fmaf(dcv[4*i+3], v[u][i].w, a);
+          }
+          a = warp_sum(a);
+          if (lane == 0 && g0 + u < G) sm.sDW[warp * 64 + g0 + u] += a;
+        }
       }
+    }
+    if (xme != nullptr) {   // publish dC' (slot B)
+      for (int t = tid; t < ER * (EC / 16); t += Cfg::NT) {
+        const int r = t % ER, s = t / ER;
+        const float4* src = reinterpret_cast<const float4*>(sm.sE + r * E_LD + s * 16);
+        float4* og = reinterpret_cast<float4*>(xme + kMixXchFloats + r * E_LD + s * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) og[i] = src[i];
+      }
+      __threadfence();
     }
     cluster.sync();  // all dC' tiles complete, all remote reads of sX (own C) done
     for (int t = tid; t < ER * (EC / 16); t += Cfg::NT) {
@@ -260,16 +284,8 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
       float acc[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      for (int g2 = 0; g2 < G; ++g2) {
-        const float w = sm.sW[g2 * G + grank];  // transposed mix
-        const float4* src = reinterpret_cast<const float4*>(cluster.map_shared_rank(sm.sE, g2) + r * E_LD + s * 16);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 v = src[i];
-          acc[4*i] = fmaf(w, v.x, acc[4*i]); acc[4*i+1] = fmaf(w, v.y, acc[4*i+1]);
-          acc[4*i+2] = fmaf(w, v.z, acc[4*i+2]); acc[4*i+3] = fmaf(w, v.w, acc[4*i+3]);
-        }
-      }
+      if (xme != nullptr) mix_global16(acc, xbase + kMixXchFloats, xstride, r * E_LD + s * 16, sm.sW + grank, G, G);   // transposed mix
+      else mix_remote16(acc, cluster, sm.sE, r * E_LD + s * 16, sm.sW + grank, G, G);
       float4* o = reinterpret_cast<float4*>(sm.sX + r * E_LD + s * 16);
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[i] = make_float4(acc[4*i], acc[4*i+1], acc[4*i+2], acc[4*i+3]);
@@ -407,6 +423,10 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
   const bf16* Vg = p.V + bh * (size_t)N * D;
   const bf16* dOg = p.dO + bh * (size_t)N * D;
   const int G = MIX ? p.G : 1, grank = MIX ? (h % G) : 0;
+  // head mix through global memory when the caller gave the scratch: this CTA's slot pair and its group's
+  const size_t xstride = (size_t)gridDim.x * 2 * kMixXchFloats;
+  const float* xbase = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  float* xme = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
 
   bwd_load_theta_w<D, CQ, CK, MIX>(sm, p, h, cq, ck, tid);
   bwd_load_rowstats<D, CQ, CK, MIX>(sm, p, bh, i0, tid);
@@ -426,7 +446,7 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    bwd_tile<D, CQ, CK, MIX, true>(sm, p, i0, j0, cq, ck, G, grank, tid);
+    bwd_tile<D, CQ, CK, MIX, true>(sm, p, i0, j0, cq, ck, G, grank, tid, xbase, xstride, xme);
     // dQ += dS K   (K rows of the owned key block start at row 2*HC of sK)
     warp_gemm<ONT, false, true>(accQ, sm.sDS + mt * 16 * B_LD, B_LD, sm.sK + (2 * HC) * QK_LD + nh * (D / 2), QK_LD, BC, lane);
     __syncthreads();
@@ -497,6 +517,10 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
   const bf16* Vg = p.V + bh * (size_t)N * D;
   const bf16* dOg = p.dO + bh * (size_t)N * D;
   const int G = MIX ? p.G : 1, grank = MIX ? (h % G) : 0;
+  // head mix through global memory when the caller gave the scratch: this CTA's slot pair and its group's
+  const size_t xstride = (size_t)gridDim.x * 2 * kMixXchFloats;
+  const float* xbase = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  float* xme = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
 
   bwd_load_theta_w<D, CQ, CK, MIX>(sm, p, h, cq, ck, tid);
   load_rows_async<D, Cfg::NT>(sm.sK, QK_LD, Kg, j0 - 2 * HC, Cfg::SR, N, tid);
@@ -516,7 +540,7 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    bwd_tile<D, CQ, CK, MIX, false>(sm, p, i0, j0, cq, ck, G, grank, tid);
+    bwd_tile<D, CQ, CK, MIX, false>(sm, p, i0, j0, cq, ck, G, grank, tid, xbase, xstride, xme);
     // dV += P^T dO ; dK += dS^T Q   (A operands stored [query][key] -> transposed loads)
     warp_gemm<ONT, true, true>(accV, sm.sPb + mt * 16, B_LD, sm.sdO + nh * (D / 2), QK_LD, BR, lane);
     warp_gemm<ONT, true, true>(accK, sm.sDS + mt * 16, B_LD, sm.sQ + H1 * QK_LD + nh * (D / 2), QK_LD, BR, lane);

@@ -140,6 +140,11 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
     return part + (op == FMTA_OP_BWD_TC_STREAM && d == 64 ? bwd_tc_stream_workspace_bytes(B, H, N, d, cq)
                                                           : bwd_tc_workspace_bytes(B, H, N, d, cq));
   }
+  if (op == FMTA_OP_MIX_EXCHANGE) {
+    // optional scratch of the conv + mix cluster kernels: two fp32 tiles per CTA (one CTA per 64 rows / keys and head)
+    if (G <= 1) return 0;
+    return (size_t)B * H * ((N + 63) / 64) * 2 * kMixXchFloats * sizeof(float);
+  }
   if (op == FMTA_OP_FWD_TC) {
     // the stacked key operand (c_q bf16 copies of K) + un-normalised partial O (fp32), M, L
     return fwd_tc_workspace_bytes(B, H, N, d, cq);
@@ -181,6 +186,10 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
     if (int s = check_cuda(launch_fwd_tc(p, workspace, &p.Opart, &p.Mpart, &p.Lpart, (cudaStream_t)stream))) return s;
     return check_cuda(launch_fwd_band(p, (cudaStream_t)stream));
   }
+  // conv + mix: with enough workspace the heads' tiles are exchanged through global memory (faster)
+  if (p.Wmix && p.theta && workspace && aligned16(workspace) &&
+      workspace_bytes >= fmta_workspace_bytes(FMTA_OP_MIX_EXCHANGE, B, H, N, d, p.cq, p.ck, p.G))
+    p.xchg = reinterpret_cast<float*>(workspace);
   return check_cuda(launch_fwd_exact(p, (cudaStream_t)stream));
 }
 
@@ -190,6 +199,16 @@ int fmta_bwd_prep_D(const void* dO, const void* O, int o_dtype, float* D, size_t
   if (rows == 0 || d < 2 || (d % 2) != 0) return FMTA_ERR_SHAPE;
   if (o_dtype != FMTA_DTYPE_F32 && o_dtype != FMTA_DTYPE_BF16) return FMTA_ERR_UNSUPPORTED;
   return check_cuda(launch_rowdot(dO, O, o_dtype == FMTA_DTYPE_BF16, D, rows, d, (cudaStream_t)stream));
+}
+
+// conv + mix backward: the exchange scratch, when the workspace has room for it behind the partial sums
+// (`part_bytes`, rounded up to 256); nullptr = exchange through distributed shared memory
+static float* mix_exchange_scratch(const TrainParams& p, void* workspace, size_t workspace_bytes, size_t part_bytes) {
+  if (!p.Wmix || !p.theta || p.G <= 1 || !workspace) return nullptr;
+  const size_t off = (part_bytes + 255) / 256 * 256;
+  const size_t need = fmta_workspace_bytes(FMTA_OP_MIX_EXCHANGE, p.B, p.H, p.N, p.d, p.cq, p.ck, p.G);
+  if (workspace_bytes < off + need || !aligned16(workspace)) return nullptr;
+  return reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + off);
 }
 
 static int fill_bwd(TrainParams& p, const void* Q, const void* K, const void* V, const void* dO,
@@ -225,6 +244,7 @@ int fmta_bwd_dq_dw(const void* Q, const void* K, const void* V, const void* dO, 
   p.n_slots = slots;
   p.dTheta_part = theta ? reinterpret_cast<float*>(workspace) : nullptr;
   p.dW_part = wmix ? reinterpret_cast<float*>(workspace) + (theta ? (size_t)slots * n_theta : 0) : nullptr;
+  p.xchg = mix_exchange_scratch(p, workspace, workspace_bytes, need);
   cudaStream_t st = (cudaStream_t)stream;
   if (int s = check_cuda(launch_bwd_dq(p, st))) return s;
   if (theta)
@@ -275,6 +295,7 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
     p.n_slots = slots_ex;
     p.dTheta_part = theta ? reinterpret_cast<float*>(workspace) : nullptr;
     p.dW_part = wmix ? reinterpret_cast<float*>(workspace) + (theta ? (size_t)slots_ex * n_theta : 0) : nullptr;
+    p.xchg = mix_exchange_scratch(p, workspace, workspace_bytes, need);
     if (int s = check_cuda(launch_bwd_dq(p, st))) return s;
     if (int s = check_cuda(launch_bwd_dkdv(p, st))) return s;
     if (theta)

@@ -27,12 +27,16 @@ struct TrainParams {
   float* dV;
   float* dTheta_part;        // [n_slots, H, cq*ck] per-CTA-slot partial sums (reduced later)
   float* dW_part;            // [n_slots, H/G, G*G]
+  float* xchg;               // conv + mix cluster kernels: optional global scratch, 2 * kMixXchFloats floats per CTA (nullptr: exchange through distributed shared memory)
   int B, H, N, d, cq, ck, G;
   float scale;
   int causal;
   int o_bf16;
   int n_slots;
 };
+
+// One exchanged tile of the conv + mix cluster kernels: the backward's 80 x 84 fp32 region (the forward's 64 x 68 tile fits)
+constexpr int kMixXchFloats = 80 * 84;
 
 struct DecodeParams {
   const __nv_bfloat16* Q;    // [B,H,q_len,d]

@@ -91,6 +91,11 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
     if (tid < G * G) sW[tid] = p.Wmix[(size_t)(h / G) * G * G + tid];
   }
 
+  // head mix: the heads' tiles go through global memory (L2) when the caller gave the scratch, else through
+  // distributed shared memory; a CTA's slot and the slots of its group (same row block, same batch entry)
+  const size_t xstride = (size_t)gridDim.x * 2 * kMixXchFloats;
+  const float* xbase = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  float* xme = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
   const int kb_begin = 0, kb_end = causal ? min(nKB - 1, (i0 + BR - 1) / BC) : nKB - 1;
 
   // running softmax state and output accumulators
@@ -153,22 +158,21 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
     if constexpr (MIX) {
       // C'_g = sum_g' W[g,g'] C_g' : read the other heads' tiles through distributed shared memory
       cg::cluster_group cluster = cg::this_cluster();
+      const int r = tid & 63, s = tid >> 6;
+      if (xme != nullptr) {   // publish the own tile for the other heads of the group
+        const float4* src = reinterpret_cast<const float4*>(cbuf + r * C_LD + s * 16);
+        float4* dst = reinterpret_cast<float4*>(xme + r * C_LD + s * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = src[i];
+        __threadfence();
+      }
       cluster.sync();
       float* mixed = Cfg::kNoConv ? sC : sS;  // a buffer nobody reads remotely
-      const int r = tid & 63, s = tid >> 6;
       float acc[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      for (int g2 = 0; g2 < G; ++g2) {
-        const float w = sW[grank * G + g2];
-        const float4* src = reinterpret_cast<const float4*>(cluster.map_shared_rank(cbuf, g2) + r * C_LD + s * 16);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 t = src[i];
-          acc[4 * i] = fmaf(w, t.x, acc[4 * i]); acc[4 * i + 1] = fmaf(w, t.y, acc[4 * i + 1]);
-          acc[4 * i + 2] = fmaf(w, t.z, acc[4 * i + 2]); acc[4 * i + 3] = fmaf(w, t.w, acc[4 * i + 3]);
-        }
-      }
+      if (xme != nullptr) mix_global16(acc, xbase, xstride, r * C_LD + s * 16, sW + grank * G, 1, G);
+      else mix_remote16(acc, cluster, cbuf, r * C_LD + s * 16, sW + grank * G, 1, G);
       float4* o = reinterpret_cast<float4*>(mixed + r * C_LD + s * 16);
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);

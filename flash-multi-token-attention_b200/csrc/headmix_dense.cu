@@ -122,9 +122,12 @@ FMTA_DEVINL void mix_quad(float (&acc)[2][4], const float* sS, int rows, int row
 template <int D, int G>
 struct FwdSmem {
   using C = Cfg<D, G>;
+  static constexpr int kOne = C::TSET + C::KSET + C::SSET + C::PSET + 3 * G * C::BR * 4 + G * G * 4;
+  static constexpr bool TWO = kOne + C::KSET <= 227 * 1024;     // K and V in buffers of their own: both copies run a phase ahead
   static constexpr int oQ = 0;
   static constexpr int oKV = oQ + C::TSET;
-  static constexpr int oS = oKV + C::KSET;
+  static constexpr int oV2 = TWO ? oKV + C::KSET : oKV;
+  static constexpr int oS = oV2 + C::KSET;
   static constexpr int oP = oS + C::SSET;
   static constexpr int oStat = oP + C::PSET;                 // M, L, alpha: [G][BR] each
   static constexpr int oWt = oStat + 3 * G * C::BR * 4;        // W transposed: [input head][output head]
@@ -139,7 +142,8 @@ __global__ void __launch_bounds__(NT, 1) hm_fwd_kernel(const TrainParams p) {
   constexpr int BR = C::BR, LD = C::LD, P_LD = C::P_LD;
   extern __shared__ __align__(16) unsigned char smem[];
   bf16* sQ = reinterpret_cast<bf16*>(smem + SM::oQ);
-  bf16* sKV = reinterpret_cast<bf16*>(smem + SM::oKV);
+  bf16* sKV = reinterpret_cast<bf16*>(smem + SM::oKV);       // K, and V too without a second buffer
+  bf16* sV2 = reinterpret_cast<bf16*>(smem + SM::oV2);       // V (= sKV without a second buffer)
   float* sS = reinterpret_cast<float*>(smem + SM::oS);
   bf16* sP = reinterpret_cast<bf16*>(smem + SM::oP);
   float* sM = reinterpret_cast<float*>(smem + SM::oStat);
@@ -173,14 +177,24 @@ __global__ void __launch_bounds__(NT, 1) hm_fwd_kernel(const TrainParams p) {
   load_set<D>(sQ, LD, BR, Qg, hs, G, i0, N, tid);
   load_set<D>(sKV, LD, BC, Kg, hs, G, 0, N, tid);
   cp_async_commit();
+  if (SM::TWO) {
+    load_set<D>(sV2, LD, BC, Vg, hs, G, 0, N, tid);
+    cp_async_commit();
+  }
 
+  // Copy groups are committed in the order K(0) [V(0)] K(1) V(1) ...; with two buffers one later group may
+  // still be in flight at each wait (empty groups keep the count uniform at the end of the loop).
   for (int kb = 0; kb <= kb_end; ++kb) {
     const int j0 = kb * BC;
-    cp_async_wait<0>();
+    if (SM::TWO) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();                                     // K(kb) (and Q) have landed
     head_products<D, G>(sS, sQ, BR, sKV, p.scale, warp, lane);
     __syncthreads();                                     // score tiles complete, K no longer read
-    load_set<D>(sKV, LD, BC, Vg, hs, G, j0, N, tid);     // V(kb) arrives under the mix and the softmax
+    if (SM::TWO) {
+      if (kb < kb_end) load_set<D>(sKV, LD, BC, Kg, hs, G, j0 + BC, N, tid);   // K(kb+1) under the mix and PV
+    } else {
+      load_set<D>(sKV, LD, BC, Vg, hs, G, j0, N, tid);   // V(kb) arrives under the mix and the softmax
+    }
     cp_async_commit();
 
     // ---- mix + online softmax: a thread owns (two output heads, row, 4 keys); the quads of a row sit in adjacent lanes ----
@@ -226,7 +240,7 @@ __global__ void __launch_bounds__(NT, 1) hm_fwd_kernel(const TrainParams p) {
         }
       }
     }
-    cp_async_wait<0>();
+    if (SM::TWO) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();                                     // V(kb) has landed, P and alpha are complete
 
     // ---- O = alpha * O + P V ----
@@ -239,11 +253,14 @@ __global__ void __launch_bounds__(NT, 1) hm_fwd_kernel(const TrainParams p) {
         const float a0 = sAlpha[g * BR + mt * 16 + (lane >> 2)], a1 = sAlpha[g * BR + mt * 16 + (lane >> 2) + 8];
 #pragma unroll
         for (int j = 0; j < ONT; ++j) { accO[i][j][0] *= a0; accO[i][j][1] *= a0; accO[i][j][2] *= a1; accO[i][j][3] *= a1; }
-        warp_gemm<ONT, false, true>(accO[i], sP + ((size_t)g * BR + mt * 16) * P_LD, P_LD, sKV + (size_t)g * BC * LD, LD, BC, lane);
+        warp_gemm<ONT, false, true>(accO[i], sP + ((size_t)g * BR + mt * 16) * P_LD, P_LD, sV2 + (size_t)g * BC * LD, LD, BC, lane);
       }
     }
     __syncthreads();                                     // V and P no longer read
-    if (kb < kb_end) {
+    if (SM::TWO) {
+      if (kb < kb_end) load_set<D>(sV2, LD, BC, Vg, hs, G, j0 + BC, N, tid);   // V(kb+1) under the next scores and mix
+      cp_async_commit();
+    } else if (kb < kb_end) {
       load_set<D>(sKV, LD, BC, Kg, hs, G, j0 + BC, N, tid);
       cp_async_commit();
     }

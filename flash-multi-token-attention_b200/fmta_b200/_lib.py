@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libfmta_b200.so")
 FMTA_DTYPE_F32 = 0
 FMTA_DTYPE_BF16 = 1
 FMTA_OP_BWD_DQ = 1
+FMTA_OP_MIX_EXCHANGE = 5
 FMTA_OP_FWD_TC = 2
 FMTA_OP_BWD_TC = 3
 FMTA_OP_BWD_TC_STREAM = 4

@@ -10,6 +10,7 @@ through distributed shared memory.  A dense [H,H] matrix is the single-group cas
 mixing takes ``w`` as [H/G, G, G].
 """
 import math
+import os
 
 import torch
 import torch.nn as nn
@@ -43,6 +44,19 @@ def _group_of(w, H, d=0, has_conv=False):
     return G, wg
 
 
+# A mix that follows a key-query conv exchanges the heads' score tiles between the CTAs of a cluster; with this
+# optional scratch (two fp32 tiles per CTA) the exchange goes through global memory, which is faster.  Above the
+# limit the calls run without it.
+MIX_EXCHANGE_LIMIT_BYTES = int(float(os.environ.get("FMTA_MIX_EXCHANGE_LIMIT_GB", "4")) * (1 << 30))
+
+
+def _exchange_bytes(th, B, H, N, d, cq, ck, G):
+    if th is None or G <= 1:
+        return 0
+    n = int(lib.fmta_workspace_bytes(_lib.FMTA_OP_MIX_EXCHANGE, B, H, N, d, cq, ck, G))
+    return n if n <= MIX_EXCHANGE_LIMIT_BYTES else 0
+
+
 def _theta_args(conv_kernel):
     if conv_kernel is None:
         return None, 1, 1
@@ -66,9 +80,11 @@ def conv_headmix_forward(q, k, v, w, conv_kernel=None, scale=1.0, causal=False, 
     M = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     L = torch.empty_like(M)
     LSE = torch.empty_like(M)
+    xb = _exchange_bytes(th, B, H, N, d, cq, ck, G)
+    ws = torch.empty(xb, dtype=torch.uint8, device=q.device) if xb else None
     st = lib.fmta_fwd(ptr(qb), ptr(kb), ptr(vb), ptr(th), ptr(wg), ptr(O), ptr(M), ptr(L), ptr(LSE), B, H, N, d,
                       cq, ck, G, float(scale), int(bool(causal)),
-                      _lib.FMTA_DTYPE_BF16 if odt == torch.bfloat16 else _lib.FMTA_DTYPE_F32, 0, None, 0,
+                      _lib.FMTA_DTYPE_BF16 if odt == torch.bfloat16 else _lib.FMTA_DTYPE_F32, 0, ptr(ws), xb,
                       stream_ptr())
     check(st, "fmta_fwd(head mix)")
     if odt != q.dtype and out_dtype is None:
@@ -115,8 +131,11 @@ def conv_headmix_bwd_dq_dw(q, k, v, w, o, do, l, m, conv_kernel=None, causal=Fal
     dQ = torch.empty((B, H, N, d), dtype=torch.float32, device=q.device)
     dW = torch.empty((H // G, G, G), dtype=torch.float32, device=q.device)
     dTh = torch.empty((H, cq, ck), dtype=torch.float32, device=q.device) if th is not None else None
-    ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_BWD_DQ, B, H, N, d, cq, ck, G)
-    ws = torch.empty(max(int(ws_bytes), 16), dtype=torch.uint8, device=q.device)
+    ws_bytes = int(lib.fmta_workspace_bytes(_lib.FMTA_OP_BWD_DQ, B, H, N, d, cq, ck, G))
+    xb = _exchange_bytes(th, B, H, N, d, cq, ck, G)
+    if xb:
+        ws_bytes = (ws_bytes + 255) // 256 * 256 + xb
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
     st = lib.fmta_bwd_dq_dw(ptr(qb), ptr(kb), ptr(vb), ptr(dob), ptr(D), ptr(lse), ptr(th), ptr(wg), ptr(dQ),
                             ptr(dTh), ptr(dW), B, H, N, d, cq, ck, G, scale, int(bool(causal)), ptr(ws), ws_bytes,
                             stream_ptr())
@@ -146,8 +165,11 @@ def conv_headmix_backward(q, k, v, w, o, do, l, m, conv_kernel=None, causal=Fals
     dV = torch.empty_like(dQ)
     dW = torch.empty((H // G, G, G), dtype=torch.float32, device=q.device)
     dTh = torch.empty((H, cq, ck), dtype=torch.float32, device=q.device) if th is not None else None
-    ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_BWD_DQ, B, H, N, d, cq, ck, G)
-    ws = torch.empty(max(int(ws_bytes), 16), dtype=torch.uint8, device=q.device)
+    ws_bytes = int(lib.fmta_workspace_bytes(_lib.FMTA_OP_BWD_DQ, B, H, N, d, cq, ck, G))
+    xb = _exchange_bytes(th, B, H, N, d, cq, ck, G)
+    if xb:
+        ws_bytes = (ws_bytes + 255) // 256 * 256 + xb
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
     st = lib.fmta_bwd(ptr(qb), ptr(kb), ptr(vb), ptr(dob), ptr(D), ptr(lse), ptr(th), ptr(wg), ptr(dQ), ptr(dK), ptr(dV),
                       ptr(dTh), ptr(dW), B, H, N, d, cq, ck, G, scale, int(bool(causal)), 0, ptr(ws), ws_bytes,
                       stream_ptr())

@@ -55,6 +55,11 @@ extern "C" {
 #define FMTA_OP_FWD_TC 2
 #define FMTA_OP_BWD_TC 3
 #define FMTA_OP_BWD_TC_STREAM 4 /* FMTA_OP_BWD_TC plus room for P and dC (bf16, 4 * B*H*N*roundup(N,128) bytes) */
+/* OPTIONAL scratch of a head mix that follows a key-query conv (theta and wmix both given): with it the heads
+ * of a group exchange their score tiles through global memory (L2), about 1.5x faster than through distributed
+ * shared memory.  fmta_fwd: a workspace of this size; fmta_bwd_dq_dw and fmta_bwd (path 0): this size behind the
+ * FMTA_OP_BWD_DQ bytes rounded up to 256.  A smaller workspace is not an error. */
+#define FMTA_OP_MIX_EXCHANGE 5
 
 /* Library version (major*10000 + minor*100 + patch). */
 int fmta_version(void);
