@@ -18,7 +18,8 @@
 //   hm_fwd_kernel      : CTA = (row tile, group, batch); loops key steps; O, M, L (and LSE)
 //   hm_bwd_dq_kernel   : CTA = (row tile, group, batch); loops key steps; dQ and one dW partial per CTA
 //                        (summed in a fixed order by reduce_partials_kernel)
-//   hm_bwd_dkdv_kernel : CTA = (key tile, output-column pass, group, batch); loops 16-row steps; dK, dV
+//   hm_bwd_dkdv_kernel : CTA = (key tile, group, batch); loops 16-row steps; dK and dV (one launch each where the
+//                        accumulators of both do not fit the registers)
 #include <cuda_runtime.h>
 
 #include "fmta_common.cuh"
@@ -347,7 +348,7 @@ struct BwdSmem {
 };
 
 // P (optional, bf16) and dC' = P (dP - D) in place of dP, for all heads; a thread owns (two output heads, outer, 4 strip elements).
-template <int G, int BR, bool TR, bool WANT_P>
+template <int G, int BR, bool TR, bool WANT_P, bool WANT_DC = true>
 FMTA_DEVINL void bwd_mix_phase(const float* sS, float* sDC, bf16* sPb, const float* sWt, const float* sLSE, const float* sDv,
                                int o0, int s0, int N, bool causal, int tid) {
   constexpr int LR = TR ? BC : BR;                       // rows of the per-row statistics per head
@@ -359,7 +360,8 @@ FMTA_DEVINL void bwd_mix_phase(const float* sS, float* sDC, bf16* sPb, const flo
     for (int h = 0; h < 2; ++h) {
       const int g = 2 * gp + h;
       float* dc = sDC + ((size_t)g * BR + outer) * BC + sw_chunk(outer, q) * 4;
-      const float4 d4 = *reinterpret_cast<const float4*>(dc);
+      float4 d4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (WANT_DC) d4 = *reinterpret_cast<const float4*>(dc);
       const float dp[4] = {d4.x, d4.y, d4.z, d4.w};
       float pr[4], out[4];
 #pragma unroll
@@ -371,7 +373,7 @@ FMTA_DEVINL void bwd_mix_phase(const float* sS, float* sDC, bf16* sPb, const flo
         pr[k] = ok ? exp2f((c[h][k] - sLSE[ri]) * kLog2e) : 0.f;
         out[k] = pr[k] * (dp[k] - sDv[ri]);
       }
-      *reinterpret_cast<float4*>(dc) = make_float4(out[0], out[1], out[2], out[3]);
+      if (WANT_DC) *reinterpret_cast<float4*>(dc) = make_float4(out[0], out[1], out[2], out[3]);
       if (WANT_P)
         *reinterpret_cast<uint2*>(sPb + ((size_t)g * BR + outer) * (BC + 8) + q * 4) = make_uint2(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]));
     }
@@ -580,17 +582,18 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dq_kernel(const TrainParams p) {
 
 template <int D, int G>
 struct DkvPass {
-  static constexpr int IPW = Cfg<D, G>::IPW;
-  static constexpr int DH = (IPW == 1) ? (D > 64 ? 64 : D) : (D > 32 ? 32 : D);   // output columns per pass: two accumulators of IPW * DH / 8 tiles
-  static constexpr int PASSES = D / DH;
+  // dK and dV accumulators of a warp's items: IPW * D / 8 tiles of 4 registers each.  Where both together pass
+  // 64 registers (head dim 128, or 32 heads at head dim 64) dV and dK come from two launches (MODE 1: dV only,
+  // no dP, no dS; MODE 2: dK only), else from one (MODE 0).
+  static constexpr bool SPLIT = Cfg<D, G>::IPW * (D / 8) * 4 * 2 > 64;
 };
 
-template <int D, int G>
+template <int D, int G, int MODE>
 __global__ void __launch_bounds__(NT, 1) hm_bwd_dkdv_kernel(const TrainParams p) {
+  constexpr bool DO_V = MODE != 2, DO_K = MODE != 1;
   using C = Cfg<D, G>;
   using SM = BwdSmem<D, G, true>;
   constexpr int BR = C::BR, LD = C::LD, P_LD = C::P_LD;
-  constexpr int DH = DkvPass<D, G>::DH, PASSES = DkvPass<D, G>::PASSES;
   extern __shared__ __align__(16) unsigned char smem[];
   bf16* sK = reinterpret_cast<bf16*>(smem + SM::oBigA);
   bf16* sV = reinterpret_cast<bf16*>(smem + SM::oBigB);      // = sK without a second big buffer
@@ -608,10 +611,9 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dkdv_kernel(const TrainParams p)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = p.N, H = p.H;
   const int nRB = (N + BC - 1) / BC;                         // 16-row steps
-  const int kt = blockIdx.x / PASSES, pass = blockIdx.x % PASSES;   // early key tiles see the most rows: longest first
+  const int kt = blockIdx.x;                                 // early key tiles see the most rows: longest first
   const int grp = blockIdx.y, b = blockIdx.z;
   const int j0 = kt * BR;
-  const int c0 = pass * DH;                                  // output columns of this pass
   const bool causal = p.causal != 0;
   const size_t hs = (size_t)N * D;
   const size_t bh0 = (size_t)b * H + (size_t)grp * G;
@@ -625,18 +627,21 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dkdv_kernel(const TrainParams p)
     sW[i] = wv;
     sWt[(i % G) * G + i / G] = wv;
   }
-  constexpr int ONT = DH / 8;
-  float accK[C::IPW][ONT][4], accV[C::IPW][ONT][4];
+  constexpr int ONT = D / 8;
+  float accK[DO_K ? C::IPW : 1][ONT][4], accV[DO_V ? C::IPW : 1][ONT][4];
 #pragma unroll
   for (int i = 0; i < C::IPW; ++i)
 #pragma unroll
     for (int j = 0; j < ONT; ++j)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { accK[i][j][e] = 0.f; accV[i][j][e] = 0.f; }
+      for (int e = 0; e < 4; ++e) {
+        if (DO_K) accK[DO_K ? i : 0][j][e] = 0.f;
+        if (DO_V) accV[DO_V ? i : 0][j][e] = 0.f;
+      }
 
   if (SM::BIG2) {                                            // K and V stay for the whole row loop
     load_set<D>(sK, LD, BR, Kg, hs, G, j0, N, tid);
-    load_set<D>(sV, LD, BR, Vg, hs, G, j0, N, tid);
+    if (DO_K) load_set<D>(sV, LD, BR, Vg, hs, G, j0, N, tid);
     cp_async_commit();
   }
   const int rb_begin = causal ? j0 / BC : 0;
@@ -658,42 +663,46 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dkdv_kernel(const TrainParams p)
     head_products<D, G>(sS, sK, BR, sQ, p.scale, warp, lane);            // S^T
     if (!SM::BIG2 || !SM::SMALL2) {
       __syncthreads();
-      if (!SM::BIG2) load_set<D>(sV, LD, BR, Vg, hs, G, j0, N, tid);
+      if (!SM::BIG2 && DO_K) load_set<D>(sV, LD, BR, Vg, hs, G, j0, N, tid);
       if (!SM::SMALL2) load_set<D>(sdO, LD, BC, dOg, hs, G, i0, N, tid);
       cp_async_commit();
       cp_async_wait<0>();
       __syncthreads();
     }
-    head_products<D, G>(sDC, sV, BR, sdO, 1.f, warp, lane);              // dP^T
+    if (DO_K) head_products<D, G>(sDC, sV, BR, sdO, 1.f, warp, lane);    // dP^T
     __syncthreads();                                                     // V no longer read: P^T may take its place
-    bwd_mix_phase<G, BR, true, true>(sS, sDC, sPb, sWt, sLSE, sDv, j0, i0, N, causal, tid);
+    bwd_mix_phase<G, BR, true, DO_V, DO_K>(sS, sDC, sPb, sWt, sLSE, sDv, j0, i0, N, causal, tid);
     __syncthreads();
-    // ---- dV += P^T dO (columns c0 ...), and dS^T strips into the place of S^T ----
+    // ---- dV += P^T dO, and dS^T strips into the place of S^T ----
+    if (DO_V) {
 #pragma unroll
-    for (int i = 0; i < C::IPW; ++i) {
-      const int item = warp + i * NW;
-      if (item < C::ITEMS) {
-        int g, mt;
-        item_of<G, C::MT>(item, g, mt);
-        warp_gemm<ONT, false, true>(accV[i], sPb + ((size_t)g * BR + mt * 16) * P_LD, P_LD, sdO + (size_t)g * BC * LD + c0, LD, BC, lane);
+      for (int i = 0; i < C::IPW; ++i) {
+        const int item = warp + i * NW;
+        if (item < C::ITEMS) {
+          int g, mt;
+          item_of<G, C::MT>(item, g, mt);
+          warp_gemm<ONT, false, true>(accV[DO_V ? i : 0], sPb + ((size_t)g * BR + mt * 16) * P_LD, P_LD, sdO + (size_t)g * BC * LD, LD, BC, lane);
+        }
       }
     }
-    bwd_unmix_phase<G, BR>(sDC, sDS, sW, tid);
-    __syncthreads();
-    if (!SM::SMALL2) {                                                   // Q again, in the place of dO
-      load_set<D>(sQ, LD, BC, Qg, hs, G, i0, N, tid);
-      cp_async_commit();
-      cp_async_wait<0>();
+    if (DO_K) {
+      bwd_unmix_phase<G, BR>(sDC, sDS, sW, tid);
       __syncthreads();
-    }
-    // ---- dK += dS^T Q ----
+      if (!SM::SMALL2) {                                                 // Q again, in the place of dO
+        load_set<D>(sQ, LD, BC, Qg, hs, G, i0, N, tid);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+      }
+      // ---- dK += dS^T Q ----
 #pragma unroll
-    for (int i = 0; i < C::IPW; ++i) {
-      const int item = warp + i * NW;
-      if (item < C::ITEMS) {
-        int g, mt;
-        item_of<G, C::MT>(item, g, mt);
-        warp_gemm<ONT, false, true>(accK[i], sDS + ((size_t)g * BR + mt * 16) * P_LD, P_LD, sQ + (size_t)g * BC * LD + c0, LD, BC, lane);
+      for (int i = 0; i < C::IPW; ++i) {
+        const int item = warp + i * NW;
+        if (item < C::ITEMS) {
+          int g, mt;
+          item_of<G, C::MT>(item, g, mt);
+          warp_gemm<ONT, false, true>(accK[DO_K ? i : 0], sDS + ((size_t)g * BR + mt * 16) * P_LD, P_LD, sQ + (size_t)g * BC * LD, LD, BC, lane);
+        }
       }
     }
   }
@@ -709,14 +718,14 @@ __global__ void __launch_bounds__(NT, 1) hm_bwd_dkdv_kernel(const TrainParams p)
       float* bv = p.dV + (bh0 + g) * hs;
 #pragma unroll
       for (int j = 0; j < ONT; ++j) {
-        const int col = c0 + j * 8 + (lane & 3) * 2;
+        const int col = j * 8 + (lane & 3) * 2;
         if (j0 + r0 < N) {
-          *reinterpret_cast<float2*>(bk + (size_t)(j0 + r0) * D + col) = make_float2(accK[i][j][0] * p.scale, accK[i][j][1] * p.scale);
-          *reinterpret_cast<float2*>(bv + (size_t)(j0 + r0) * D + col) = make_float2(accV[i][j][0], accV[i][j][1]);
+          if (DO_K) *reinterpret_cast<float2*>(bk + (size_t)(j0 + r0) * D + col) = make_float2(accK[DO_K ? i : 0][j][0] * p.scale, accK[DO_K ? i : 0][j][1] * p.scale);
+          if (DO_V) *reinterpret_cast<float2*>(bv + (size_t)(j0 + r0) * D + col) = make_float2(accV[DO_V ? i : 0][j][0], accV[DO_V ? i : 0][j][1]);
         }
         if (j0 + r1 < N) {
-          *reinterpret_cast<float2*>(bk + (size_t)(j0 + r1) * D + col) = make_float2(accK[i][j][2] * p.scale, accK[i][j][3] * p.scale);
-          *reinterpret_cast<float2*>(bv + (size_t)(j0 + r1) * D + col) = make_float2(accV[i][j][2], accV[i][j][3]);
+          if (DO_K) *reinterpret_cast<float2*>(bk + (size_t)(j0 + r1) * D + col) = make_float2(accK[DO_K ? i : 0][j][2] * p.scale, accK[DO_K ? i : 0][j][3] * p.scale);
+          if (DO_V) *reinterpret_cast<float2*>(bv + (size_t)(j0 + r1) * D + col) = make_float2(accV[DO_V ? i : 0][j][2], accV[DO_V ? i : 0][j][3]);
         }
       }
     }
@@ -777,8 +786,15 @@ cudaError_t launch_hm_bwd_dq(const TrainParams& p, cudaStream_t stream) {
 cudaError_t launch_hm_bwd_dkdv(const TrainParams& p, cudaStream_t stream) {
   FMTA_HM_DISPATCH(p, {
     using C = hm::Cfg<D_, G_>;
-    dim3 grid(((p.N + C::BR - 1) / C::BR) * hm::DkvPass<D_, G_>::PASSES, p.H / p.G, p.B);
-    return launch_kernel<TrainParams>(hm::hm_bwd_dkdv_kernel<D_, G_>, grid, dim3(hm::NT), hm::BwdSmem<D_, G_, true>::kBytes, stream, 1, p);
+    dim3 grid((p.N + C::BR - 1) / C::BR, p.H / p.G, p.B);
+    constexpr int smem = hm::BwdSmem<D_, G_, true>::kBytes;
+    if constexpr (hm::DkvPass<D_, G_>::SPLIT) {
+      cudaError_t e = launch_kernel<TrainParams>(hm::hm_bwd_dkdv_kernel<D_, G_, 1>, grid, dim3(hm::NT), smem, stream, 1, p);
+      if (e != cudaSuccess) return e;
+      return launch_kernel<TrainParams>(hm::hm_bwd_dkdv_kernel<D_, G_, 2>, grid, dim3(hm::NT), smem, stream, 1, p);
+    } else {
+      return launch_kernel<TrainParams>(hm::hm_bwd_dkdv_kernel<D_, G_, 0>, grid, dim3(hm::NT), smem, stream, 1, p);
+    }
   });
   return cudaErrorInvalidValue;
 }
