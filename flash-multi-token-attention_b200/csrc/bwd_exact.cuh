@@ -194,7 +194,7 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
       float acc[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      if (xme != nullptr) mix_global16(acc, xbase, xstride, r * E_LD + s * 16, sm.sW + grank * G, 1, G);
+      if (xme != nullptr) mix_global16(acc, xbase, xstride, r * E_LD + s * 16, sm.sW + grank * G, 1, G, grank, sm.sX);
       else mix_remote16(acc, cluster, sm.sX, r * E_LD + s * 16, sm.sW + grank * G, 1, G);
       const int qi = i0 + r;
       const float lse = sm.sLSE[r];
@@ -250,11 +250,13 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
         float4 v[4][4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const float4* src = (xme != nullptr)
-              ? reinterpret_cast<const float4*>(xbase + (size_t)min(g0 + u, G - 1) * xstride + r * E_LD + HC + s * 16)
-              : reinterpret_cast<const float4*>(cluster.map_shared_rank(sm.sX, min(g0 + u, G - 1)) + r * E_LD + HC + s * 16);
+          const int g2 = min(g0 + u, G - 1);
+          const bool glob = (xme != nullptr) && g2 != grank;          // the own tile is read from shared memory
+          const float4* src = glob
+              ? reinterpret_cast<const float4*>(xbase + (size_t)g2 * xstride + r * E_LD + HC + s * 16)
+              : reinterpret_cast<const float4*>(cluster.map_shared_rank(sm.sX, g2) + r * E_LD + HC + s * 16);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) v[u][i] = (xme != nullptr) ? __ldcg(src + i) : src[i];
+          for (int i = 0; i < 4; ++i) v[u][i] = glob ? __ldcg(src + i) : src[i];
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -284,7 +286,7 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
       float acc[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      if (xme != nullptr) mix_global16(acc, xbase + kMixXchFloats, xstride, r * E_LD + s * 16, sm.sW + grank, G, G);   // transposed mix
+      if (xme != nullptr) mix_global16(acc, xbase + kMixXchFloats, xstride, r * E_LD + s * 16, sm.sW + grank, G, G, grank, sm.sE);   // transposed mix
       else mix_remote16(acc, cluster, sm.sE, r * E_LD + s * 16, sm.sW + grank, G, G);
       float4* o = reinterpret_cast<float4*>(sm.sX + r * E_LD + s * 16);
 #pragma unroll

@@ -112,14 +112,23 @@ FMTA_DEVINL void mix_remote16(float (&acc)[16], Cluster& cluster, float* buf, in
 // The same sum with the heads' tiles published in global memory (one slot of `xstride` floats per head of the
 // group, `xbase` = slot of head 0): measured on B200, tiles read back from L2 arrive about three times faster
 // than through distributed shared memory (4.3 bytes per cycle and SM there).
-FMTA_DEVINL void mix_global16(float (&acc)[16], const float* xbase, size_t xstride, int off, const float* w, int wstride, int G) {
+// The CTA's own tile (head `self`) is taken from its shared-memory copy `own`.
+FMTA_DEVINL void mix_global16(float (&acc)[16], const float* xbase, size_t xstride, int off, const float* w, int wstride, int G,
+                              int self, const float* own) {
   for (int g0 = 0; g0 < G; g0 += 4) {
     float4 v[4][4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const float4* src = reinterpret_cast<const float4*>(xbase + (size_t)min(g0 + u, G - 1) * xstride + off);
+      const int g2 = min(g0 + u, G - 1);
+      if (g2 == self) {
+        const float4* src = reinterpret_cast<const float4*>(own + off);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[u][i] = __ldcg(src + i);
+        for (int i = 0; i < 4; ++i) v[u][i] = src[i];
+      } else {
+        const float4* src = reinterpret_cast<const float4*>(xbase + (size_t)g2 * xstride + off);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[u][i] = __ldcg(src + i);
+      }
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {

@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
       float acc[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      if (xme != nullptr) mix_global16(acc, xbase, xstride, r * C_LD + s * 16, sW + grank * G, 1, G);
+      if (xme != nullptr) mix_global16(acc, xbase, xstride, r * C_LD + s * 16, sW + grank * G, 1, G, grank, cbuf);
       else mix_remote16(acc, cluster, cbuf, r * C_LD + s * 16, sW + grank * G, 1, G);
       float4* o = reinterpret_cast<float4*>(mixed + r * C_LD + s * 16);
 #pragma unroll
