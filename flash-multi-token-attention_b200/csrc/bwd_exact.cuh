@@ -125,6 +125,9 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
   const int N = p.N;
   const bool causal = p.causal != 0;
   const int pq = cq - 1, pk = (ck - 1) / 2;
+  // the adjoint conv of the owned rows reads dC rows up to pad_q below them: the rows of the E region beyond
+  // that (it is laid out for pad_q = 15) are neither computed nor exchanged
+  const int er_eff = Cfg::kNoConv ? ER : min(ER, BR + pq);
   // band mode: entries with query - key >= pad_q + pad_k belong to the stacked tensor-core kernels
 
   // ---- 1. S on the large region ----
@@ -154,8 +157,8 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
 
   // ---- 2. C = conv(S) on the E region -> (mix) -> P = exp(C - LSE), masked ----
   float* cown = MIX ? sm.sX : sm.sE;  // where this head's own conv output goes
-  for (int t = tid; t < ER * (EC / 16); t += Cfg::NT) {
-    const int r = t % ER, s = t / ER;
+  for (int t = tid; t < er_eff * (EC / 16); t += Cfg::NT) {
+    const int r = t % er_eff, s = t / er_eff;
     float acc[16];
     if constexpr (!Cfg::kNoConv) {
       conv_strip<CQ, CK, HC - (CK - 1) / 2, false>(acc, sm.sS, S_LD, r, s, H1 - pq, sm.sTheta, cq, ck, HC - pk);
@@ -189,8 +192,8 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
     cg::cluster_group cluster = cg::this_cluster();
     if (xme != nullptr) __threadfence();
     cluster.sync();  // every head's conv output is in its sX (and in its global slot)
-    for (int t = tid; t < ER * (EC / 16); t += Cfg::NT) {
-      const int r = t % ER, s = t / ER;
+    for (int t = tid; t < er_eff * (EC / 16); t += Cfg::NT) {
+      const int r = t % er_eff, s = t / er_eff;
       float acc[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
@@ -216,6 +219,7 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
     constexpr int NU = (ER / 16) * (EC / 16);
     for (int u = warp; u < NU; u += Cfg::NT / 32) {
       const int um = u / (EC / 16), un = u % (EC / 16);
+      if (um * 16 >= er_eff) continue;
       float acc[2][4] = {};
       warp_gemm<2, false, false>(acc, sm.sdO + um * 16 * QK_LD, QK_LD, sm.sV + un * 16 * QK_LD, QK_LD, D, lane);
 #pragma unroll
@@ -271,8 +275,8 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
       }
     }
     if (xme != nullptr) {   // publish dC' (slot B)
-      for (int t = tid; t < ER * (EC / 16); t += Cfg::NT) {
-        const int r = t % ER, s = t / ER;
+      for (int t = tid; t < er_eff * (EC / 16); t += Cfg::NT) {
+        const int r = t % er_eff, s = t / er_eff;
         const float4* src = reinterpret_cast<const float4*>(sm.sE + r * E_LD + s * 16);
         float4* og = reinterpret_cast<float4*>(xme + kMixXchFloats + r * E_LD + s * 16);
 #pragma unroll
@@ -281,8 +285,8 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
       __threadfence();
     }
     cluster.sync();  // all dC' tiles complete, all remote reads of sX (own C) done
-    for (int t = tid; t < ER * (EC / 16); t += Cfg::NT) {
-      const int r = t % ER, s = t / ER;
+    for (int t = tid; t < er_eff * (EC / 16); t += Cfg::NT) {
+      const int r = t % er_eff, s = t / er_eff;
       float acc[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
