@@ -241,39 +241,6 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
   if constexpr (MIX) {
     cg::cluster_group cluster = cg::this_cluster();
     __syncthreads();
-    if constexpr (WANT_DTHETA) {
-      // dW[g, g'] += sum over the owned tile of dC'_g * C_g'
-      const int r = tid & 63, s = tid >> 6;
-      float dcv[16];
-      {
-        const float4* src = reinterpret_cast<const float4*>(sm.sE + r * E_LD + HC + s * 16);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { float4 v = src[i]; dcv[4*i] = v.x; dcv[4*i+1] = v.y; dcv[4*i+2] = v.z; dcv[4*i+3] = v.w; }
-      }
-      for (int g0 = 0; g0 < G; g0 += 4) {   // the loads of four heads are issued together (remote latency)
-        float4 v[4][4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int g2 = min(g0 + u, G - 1);
-          const bool glob = (xme != nullptr) && g2 != grank;          // the own tile is read from shared memory
-          const float4* src = glob
-              ? reinterpret_cast<const float4*>(xbase + (size_t)g2 * xstride + r * E_LD + HC + s * 16)
-              : reinterpret_cast<const float4*>(cluster.map_shared_rank(sm.sX, g2) + r * E_LD + HC + s * 16);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) v[u][i] = glob ? __ldcg(src + i) : src[i];
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float a = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            a = fmaf(dcv[4*i], v[u][i].x, a); a = fmaf(dcv[4*i+1], v[u][i].y, a); a = fmaf(dcv[4*i+2], v[u][i].z, a); a = fmaf(dcv[4*i+3], v[u][i].w, a);
-          }
-          a = warp_sum(a);
-          if (lane == 0 && g0 + u < G) sm.sDW[warp * 64 + g0 + u] += a;
-        }
-      }
-    }
     if (xme != nullptr) {   // publish dC' (slot B)
       for (int t = tid; t < er_eff * (EC / 16); t += Cfg::NT) {
         const int r = t % er_eff, s = t / er_eff;
@@ -285,16 +252,64 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
       __threadfence();
     }
     cluster.sync();  // all dC' tiles complete, all remote reads of sX (own C) done
-    for (int t = tid; t < er_eff * (EC / 16); t += Cfg::NT) {
-      const int r = t % er_eff, s = t / er_eff;
-      float acc[16];
+    // Transposed mix dC_own = sum_g W[g, own] dC'_g, and (dQ kernel) column `own` of dW on the way:
+    // dW[g, own] += sum over the owned tile of dC'_g * C_own -- the dC' strips of all heads pass through this
+    // CTA's registers here anyway, and C_own is the strip of sX that the result is about to replace.
+    const int nstrips = er_eff * (EC / 16);
+    for (int t0 = 0; t0 < nstrips; t0 += Cfg::NT) {        // warp-uniform trip count (the dW sums use shuffles)
+      const int t = t0 + tid;
+      const bool live = t < nstrips;
+      const int r = live ? t % er_eff : 0, s = live ? t / er_eff : 0;
+      float acc[16], cown[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      if (xme != nullptr) mix_global16(acc, xbase + kMixXchFloats, xstride, r * E_LD + s * 16, sm.sW + grank, G, G, grank, sm.sE);   // transposed mix
-      else mix_remote16(acc, cluster, sm.sE, r * E_LD + s * 16, sm.sW + grank, G, G);
-      float4* o = reinterpret_cast<float4*>(sm.sX + r * E_LD + s * 16);
+      if constexpr (WANT_DTHETA) {
+        const float4* src = reinterpret_cast<const float4*>(sm.sX + r * E_LD + s * 16);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) o[i] = make_float4(acc[4*i], acc[4*i+1], acc[4*i+2], acc[4*i+3]);
+        for (int i = 0; i < 4; ++i) { const float4 v = src[i]; cown[4*i] = v.x; cown[4*i+1] = v.y; cown[4*i+2] = v.z; cown[4*i+3] = v.w; }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {                     // owned tile: rows < BR, region columns HC .. HC + BC
+          const int c = s * 16 + i;
+          if (!live || r >= BR || c < HC || c >= HC + Cfg::BC) cown[i] = 0.f;
+        }
+      }
+      for (int g0 = 0; g0 < G; g0 += 4) {                  // the loads of four heads are issued together
+        float4 v[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int g2 = min(g0 + u, G - 1);
+          const bool glob = (xme != nullptr) && g2 != grank;
+          const float4* src = glob
+              ? reinterpret_cast<const float4*>(xbase + kMixXchFloats + (size_t)g2 * xstride + r * E_LD + s * 16)
+              : reinterpret_cast<const float4*>(cluster.map_shared_rank(sm.sE, g2) + r * E_LD + s * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[u][i] = glob ? __ldcg(src + i) : src[i];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float wv = (g0 + u < G) ? sm.sW[(g0 + u) * G + grank] : 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[4*i] = fmaf(wv, v[u][i].x, acc[4*i]); acc[4*i+1] = fmaf(wv, v[u][i].y, acc[4*i+1]);
+            acc[4*i+2] = fmaf(wv, v[u][i].z, acc[4*i+2]); acc[4*i+3] = fmaf(wv, v[u][i].w, acc[4*i+3]);
+          }
+          if constexpr (WANT_DTHETA) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              a = fmaf(cown[4*i], v[u][i].x, a); a = fmaf(cown[4*i+1], v[u][i].y, a);
+              a = fmaf(cown[4*i+2], v[u][i].z, a); a = fmaf(cown[4*i+3], v[u][i].w, a);
+            }
+            a = warp_sum(a);
+            if (lane == 0 && g0 + u < G) sm.sDW[warp * 64 + g0 + u] += a;
+          }
+        }
+      }
+      if (live) {
+        float4* o = reinterpret_cast<float4*>(sm.sX + r * E_LD + s * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] = make_float4(acc[4*i], acc[4*i+1], acc[4*i+2], acc[4*i+3]);
+      }
     }
     cluster.sync();  // remote reads of sE done; sX now holds this head's dC
     dcfin = sm.sX;
@@ -496,8 +511,8 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
       float t = 0.f;
 #pragma unroll
       for (int w = 0; w < 8; ++w) t += sm.sDW[w * 64 + tid];
-      // row `grank` of this group's G x G matrix
-      p.dW_part[((size_t)slot * (H / G) + h / G) * (G * G) + grank * G + tid] = t;
+      // column `grank` of this group's G x G matrix: dW[tid, grank] = sum dC'_tid * C_grank
+      p.dW_part[((size_t)slot * (H / G) + h / G) * (G * G) + tid * G + grank] = t;
     }
   }
 }
