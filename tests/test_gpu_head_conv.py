@@ -107,6 +107,8 @@ def test_autograd_function_dropin():
     (1, 16, 8, 300, 128, False),
     (1, 32, 32, 16, 64, True),        # exactly one tile
     (1, 16, 16, 1, 64, True),         # single token
+    (1, 16, 16, 1024, 64, True),      # 64 row tiles x up to 64 key steps: long accumulations, dW over 1 k partials
+    (1, 32, 32, 512, 64, True),
 ])
 def test_mix_without_conv_all_heads_in_one_cta(B, H, G, N, d, causal):
     """Dense and grouped mixing for every supported (group size, head dim) family against the oracle."""
