@@ -450,10 +450,10 @@ def main():
     if kms:
         ach = 6.0 * d * E / (kms * 1e-3) / 1e12
         exe = 2.0 * d * (2 * cq + 2) * E / (kms * 1e-3) / 1e12
-        # DRAM bytes per launch from the committed ncu capture at B=2,H=16,N=4096 (152.1 MB read + 89.3 MB
+        # DRAM bytes per launch from the committed ncu capture at B=2,H=16,N=4096 (152.2 MB read + 88.4 MB
         # written; summary under profiles/), scaled by the (batch, head)
         # units; only quoted for that sequence length and head dimension
-        traffic = (152.12e6 + 89.30e6) * (B * H) / 32.0 if (N == 4096 and d == 64 and cq == 6) else None
+        traffic = (152.20e6 + 88.37e6) * (B * H) / 32.0 if (N == 4096 and d == 64 and cq == 6) else None
         roof = dict(bound="tensor", kernel=KERNELS[DOMINANT], achieved=ach, peak=peaks["tflops_sustained"],
                     unit="TFLOP/s", frac=ach / peaks["tflops_sustained"], peak_source=peaks["source"] + " (sustained)",
                     traffic=traffic, traffic_unit="bytes per launch (ncu capture of a smaller case, scaled)",
