@@ -311,7 +311,8 @@ FMTA_DEVINL void bwd_tile(const BwdSmem<D, CQ, CK, MIX>& sm, const TrainParams& 
         for (int i = 0; i < 4; ++i) o[i] = make_float4(acc[4*i], acc[4*i+1], acc[4*i+2], acc[4*i+3]);
       }
     }
-    cluster.sync();  // remote reads of sE done; sX now holds this head's dC
+    if (xme != nullptr) __syncthreads();   // sX now holds this head's dC (the slots alternate between tiles: no barrier needed after the reads)
+    else cluster.sync();                   // remote reads of sE done; sX now holds this head's dC
     dcfin = sm.sX;
   } else {
     __syncthreads();
@@ -445,9 +446,11 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
   const bf16* dOg = p.dO + bh * (size_t)N * D;
   const int G = MIX ? p.G : 1, grank = MIX ? (h % G) : 0;
   // head mix through global memory when the caller gave the scratch: this CTA's slot pair and its group's
+  // (two sets of slots, used by alternate tiles)
   const size_t xstride = (size_t)gridDim.x * 2 * kMixXchFloats;
-  const float* xbase = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
-  float* xme = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  const size_t xset = (size_t)gridDim.x * gridDim.y * gridDim.z * 2 * kMixXchFloats;
+  const float* xbase0 = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  float* xme0 = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
 
   bwd_load_theta_w<D, CQ, CK, MIX>(sm, p, h, cq, ck, tid);
   bwd_load_rowstats<D, CQ, CK, MIX>(sm, p, bh, i0, tid);
@@ -467,7 +470,8 @@ __global__ void __launch_bounds__(256, 1) bwd_dq_kernel(const TrainParams p) {
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    bwd_tile<D, CQ, CK, MIX, true>(sm, p, i0, j0, cq, ck, G, grank, tid, xbase, xstride, xme);
+    bwd_tile<D, CQ, CK, MIX, true>(sm, p, i0, j0, cq, ck, G, grank, tid, xbase0 ? xbase0 + (size_t)(kb & 1) * xset : nullptr, xstride,
+                                   xme0 ? xme0 + (size_t)(kb & 1) * xset : nullptr);
     // dQ += dS K   (K rows of the owned key block start at row 2*HC of sK)
     warp_gemm<ONT, false, true>(accQ, sm.sDS + mt * 16 * B_LD, B_LD, sm.sK + (2 * HC) * QK_LD + nh * (D / 2), QK_LD, BC, lane);
     __syncthreads();
@@ -539,9 +543,11 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
   const bf16* dOg = p.dO + bh * (size_t)N * D;
   const int G = MIX ? p.G : 1, grank = MIX ? (h % G) : 0;
   // head mix through global memory when the caller gave the scratch: this CTA's slot pair and its group's
+  // (two sets of slots, used by alternate tiles)
   const size_t xstride = (size_t)gridDim.x * 2 * kMixXchFloats;
-  const float* xbase = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
-  float* xme = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  const size_t xset = (size_t)gridDim.x * gridDim.y * gridDim.z * 2 * kMixXchFloats;
+  const float* xbase0 = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  float* xme0 = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
 
   bwd_load_theta_w<D, CQ, CK, MIX>(sm, p, h, cq, ck, tid);
   load_rows_async<D, Cfg::NT>(sm.sK, QK_LD, Kg, j0 - 2 * HC, Cfg::SR, N, tid);
@@ -561,7 +567,8 @@ __global__ void __launch_bounds__(256, 1) bwd_dkdv_kernel(const TrainParams p) {
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    bwd_tile<D, CQ, CK, MIX, false>(sm, p, i0, j0, cq, ck, G, grank, tid, xbase, xstride, xme);
+    bwd_tile<D, CQ, CK, MIX, false>(sm, p, i0, j0, cq, ck, G, grank, tid, xbase0 ? xbase0 + (size_t)(qb & 1) * xset : nullptr, xstride,
+                                    xme0 ? xme0 + (size_t)(qb & 1) * xset : nullptr);
     // dV += P^T dO ; dK += dS^T Q   (A operands stored [query][key] -> transposed loads)
     warp_gemm<ONT, true, true>(accV, sm.sPb + mt * 16, B_LD, sm.sdO + nh * (D / 2), QK_LD, BR, lane);
     warp_gemm<ONT, true, true>(accK, sm.sDS + mt * 16, B_LD, sm.sQ + H1 * QK_LD + nh * (D / 2), QK_LD, BR, lane);

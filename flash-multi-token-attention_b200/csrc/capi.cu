@@ -141,9 +141,10 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
                                                           : bwd_tc_workspace_bytes(B, H, N, d, cq));
   }
   if (op == FMTA_OP_MIX_EXCHANGE) {
-    // optional scratch of the conv + mix cluster kernels: two fp32 tiles per CTA (one CTA per 64 rows / keys and head)
+    // optional scratch of the conv + mix cluster kernels: two sets (alternate tiles) of two fp32 tiles per CTA
+    // (one CTA per 64 rows / keys and head)
     if (G <= 1) return 0;
-    return (size_t)B * H * ((N + 63) / 64) * 2 * kMixXchFloats * sizeof(float);
+    return (size_t)2 * B * H * ((N + 63) / 64) * 2 * kMixXchFloats * sizeof(float);
   }
   if (op == FMTA_OP_FWD_TC) {
     // the stacked key operand (c_q bf16 copies of K) + un-normalised partial O (fp32), M, L

@@ -27,7 +27,7 @@ struct TrainParams {
   float* dV;
   float* dTheta_part;        // [n_slots, H, cq*ck] per-CTA-slot partial sums (reduced later)
   float* dW_part;            // [n_slots, H/G, G*G]
-  float* xchg;               // conv + mix cluster kernels: optional global scratch, 2 * kMixXchFloats floats per CTA (nullptr: exchange through distributed shared memory)
+  float* xchg;               // conv + mix cluster kernels: optional global scratch, 2 sets x 2 * kMixXchFloats floats per CTA (nullptr: exchange through distributed shared memory)
   int B, H, N, d, cq, ck, G;
   float scale;
   int causal;

@@ -93,9 +93,12 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
 
   // head mix: the heads' tiles go through global memory (L2) when the caller gave the scratch, else through
   // distributed shared memory; a CTA's slot and the slots of its group (same row block, same batch entry)
+  // (two sets of slots used by alternate key blocks: a CTA may publish its next tile while a slower head of the
+  // group still reads the previous one, which saves the cluster barrier after the reads)
   const size_t xstride = (size_t)gridDim.x * 2 * kMixXchFloats;
-  const float* xbase = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
-  float* xme = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  const size_t xset = (size_t)gridDim.x * gridDim.y * gridDim.z * 2 * kMixXchFloats;
+  const float* xbase0 = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + (h / G) * G) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
+  float* xme0 = (MIX && p.xchg) ? p.xchg + (((size_t)b * H + h) * gridDim.x + blockIdx.x) * 2 * kMixXchFloats : nullptr;
   const int kb_begin = 0, kb_end = causal ? min(nKB - 1, (i0 + BR - 1) / BC) : nKB - 1;
 
   // running softmax state and output accumulators
@@ -159,6 +162,8 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
       // C'_g = sum_g' W[g,g'] C_g' : read the other heads' tiles through distributed shared memory
       cg::cluster_group cluster = cg::this_cluster();
       const int r = tid & 63, s = tid >> 6;
+      const float* xbase = xbase0 ? xbase0 + (size_t)(kb & 1) * xset : nullptr;
+      float* xme = xme0 ? xme0 + (size_t)(kb & 1) * xset : nullptr;
       if (xme != nullptr) {   // publish the own tile for the other heads of the group
         const float4* src = reinterpret_cast<const float4*>(cbuf + r * C_LD + s * 16);
         float4* dst = reinterpret_cast<float4*>(xme + r * C_LD + s * 16);
@@ -176,7 +181,8 @@ __global__ void __launch_bounds__(256, 1) fwd_exact_kernel(const TrainParams p) 
       float4* o = reinterpret_cast<float4*>(mixed + r * C_LD + s * 16);
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
-      cluster.sync();  // all remote reads of cbuf are done; `mixed` is visible CTA-wide
+      if (xme != nullptr) __syncthreads();   // `mixed` is visible CTA-wide (the other heads read this CTA's slot, not its shared memory)
+      else cluster.sync();                   // all remote reads of cbuf are done; `mixed` is visible CTA-wide
       cbuf = mixed;
     } else {
       __syncthreads();
