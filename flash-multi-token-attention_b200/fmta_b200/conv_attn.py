@@ -33,6 +33,22 @@ def _workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
 
 
+# Head dim 32 has no tensor-core kernels of its own (their operand tiles are 128-byte rows = 64 bf16).  With
+# the library's default path it runs on the head-dim-64 tensor-core kernels with the head dim zero-padded: the
+# scores, the softmax and the first 32 output / gradient columns are unchanged, at twice the tensor work of a
+# native kernel and still several times faster than the exact kernels.  FMTA_PAD_D32=0 turns it off.
+PAD_D32 = os.environ.get("FMTA_PAD_D32", "1") != "0"
+
+
+def _pads_to_64(d, cq, path):
+    """True when a head-dim-32 call with the default path goes to the padded head-dim-64 tensor-core kernels."""
+    return PAD_D32 and d == 32 and path == -1 and cq <= 7 and lib.fmta_set_path(99) != 0
+
+
+def _pad64(t):
+    return torch.nn.functional.pad(t, (0, 32)).contiguous()
+
+
 def forward(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, out_dtype=torch.float32, return_lse=False,
             path=-1):
     """(O, M, L) -- `forward` of conv_attn/bindings.cpp:46-48.  O is fp32 as in
@@ -42,6 +58,9 @@ def forward(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, out_dtype=torch.f
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
     if K.shape != Q.shape or V.shape != Q.shape:
         raise RuntimeError("Q, K, V must have the same shape [batch, heads, seq, d_head]")
+    if _pads_to_64(d, cq, path):
+        out = forward(_pad64(Q), _pad64(K), _pad64(V), conv_kernel, scale, pad_q, pad_k, causal, out_dtype, return_lse, path)
+        return (out[0][..., :32].contiguous(),) + tuple(out[1:])
     require_on(Q, K, "K"); require_on(Q, V, "V"); require_on(Q, conv_kernel, "conv_kernel")
     arm_status(Q.device)
     theta = as_f32(conv_kernel)
@@ -132,6 +151,10 @@ def backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, path=-
         require_cuda_bf16(t, n)
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
     _check_bwd_args(Q, K, V, dO, D, L, conv_kernel)
+    if _pads_to_64(d, cq, path):
+        dQ, dK, dV, dTheta = backward(_pad64(Q), _pad64(K), _pad64(V), _pad64(dO), D, L, conv_kernel, scale, pad_q, pad_k,
+                                      causal, path, stream_pdc)
+        return dQ[..., :32].contiguous(), dK[..., :32].contiguous(), dV[..., :32].contiguous(), dTheta
     theta, Dv, LSE = as_f32(conv_kernel), as_f32(D), as_f32(L)
     dQ = torch.empty((B, H, N, d), dtype=torch.float32, device=Q.device)
     dK = torch.empty_like(dQ)

@@ -186,6 +186,31 @@ def test_fused_backward_paths(path, B, H, N, d, cq, ck, causal):
                                                               " (recomputing dK/dV)" if stream_pdc is False else ""))
 
 
+@pytest.mark.parametrize("B,H,N,cq,ck,causal", [(1, 2, 520, 6, 11, True), (2, 1, 300, 3, 5, False), (1, 2, 83, 6, 11, True)])
+def test_head_dim_32_default_path(B, H, N, cq, ck, causal):
+    """Head dim 32 with the library's default path: the head-dim-64 tensor-core kernels on zero-padded
+    operands (the Python layer pads and slices); same bound as every other path."""
+    import fmta_b200 as F
+    d = 32
+    Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=5 + N, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
+    th = theta.cuda()
+    O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, causal, return_lse=True)
+    assert O.shape == q.shape
+    Dv = F.rowdot(do, O)
+    dQ, dK, dV, dTh = F.backward(q, k, v, do, Dv, LSE, th, scale, cq - 1, (ck - 1) // 2, causal)
+    torch.cuda.synchronize()
+    Or, Mr, Lr = orc.conv_attn_fwd(Q, K, V, theta, scale, causal)
+    rq, rk, rv, rt = orc.conv_attn_bwd_autograd(Q, K, V, theta, dO, scale, causal)
+    _check(dict(O=O, M=M, L=L, LSE=LSE, dQ=dQ, dK=dK, dV=dV, dTheta=dTh),
+           dict(O=Or, M=Mr, L=Lr, dQ=rq, dK=rk, dV=rv, dTheta=rt),
+           "B%d H%d N%d d32 (padded to 64) theta(%d,%d) causal=%d default path" % (B, H, N, cq, ck, causal))
+    # the exact kernels (path 0) take head dim 32 as it is and agree
+    O0, _, _ = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, causal, path=0)
+    assert float((O0 - O).abs().max()) <= 2e-2
+
+
 def test_fp32_configuration_N256_theta_3x5_both_paths():
     """The fp32 CPU-path configuration of the benchmark (B=1, H=4, N=256, d=64, theta (3,5), N(0,0.05)
     filter) run through the bf16 kernels on both paths, against the oracle on the same bf16-rounded inputs."""
