@@ -275,6 +275,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-headmix", action="store_true")
     ap.add_argument("--headmix-shape", default=None, help="B,H,N,d: time only this dense head-mix shape (profiling captures)")
+    ap.add_argument("--convmix-shape", default=None, help="B,H,N,d: time only conv (6,11) + mix in groups of 4 at this shape (profiling captures)")
     ap.add_argument("--sweep-max-n", type=int, default=65536)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="tiny shapes (profiling / debugging)")
@@ -498,7 +499,7 @@ def main():
     # ---- head mixing: the reference's head-conv operator (no conv) and the composed conv + mix configuration ----
     if not args.no_headmix and not args.small and not args.train_shape:
         try:
-            line["headmix"] = bench_headmix(F, dev, timed, args.headmix_shape)
+            line["headmix"] = bench_headmix(F, dev, timed, args.headmix_shape, args.convmix_shape)
         except torch.OutOfMemoryError as e:   # pragma: no cover
             line["headmix"] = dict(error="out of memory: %s" % str(e)[:80])
 
@@ -588,7 +589,7 @@ def bench_sweep(F, dev, world, rank, peaks, barrier, max_n):
                 peak=peaks["tflops_sustained"], peak_source=peaks["source"] + " (sustained)", points=points)
 
 
-def bench_headmix(F, dev, timed, shape=None):
+def bench_headmix(F, dev, timed, shape=None, convmix_shape=None):
     """Rank-local timings (ms, CUDA events) of the head-mixing operators, forward + dQ/dW + dK/dV, causal, bf16:
     the reference's head-conv attention (dense W over 16 and 32 heads, no conv) and, unless a shape is given, the
     head-mixing training configuration (theta (6,11) then groups of 4; B=2,H=32,N=8192,d=128).  TFLOP/s counts
@@ -596,6 +597,8 @@ def bench_headmix(F, dev, timed, shape=None):
     pts = []
     g = torch.Generator(device=dev).manual_seed(11)
     shapes = [tuple(int(x) for x in shape.split(","))] if shape else [(2, 16, 4096, 64), (2, 32, 4096, 64), (2, 16, 4096, 128)]
+    if convmix_shape and not shape:
+        shapes = []
     for (B, H, N, d) in shapes:
         q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).to(torch.bfloat16) for _ in range(4))
         w = torch.randn(H, H, device=dev, generator=g) / math.sqrt(H)
@@ -614,6 +617,8 @@ def bench_headmix(F, dev, timed, shape=None):
         del q, k, v, do, o, l, m
     if not shape:
         B, H, N, d, G, cq, ck = 2, 32, 8192, 128, 4, 6, 11
+        if convmix_shape:
+            B, H, N, d = (int(x) for x in convmix_shape.split(","))
         q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).to(torch.bfloat16) for _ in range(4))
         th = torch.randn(H, cq, ck, device=dev, generator=g) * 0.02
         th[:, cq - 1, ck // 2] += 1.0
