@@ -69,6 +69,16 @@ def test_host_validation_needs_no_gpu():
     assert lib.fmta_bwd_dq_dw(good, good, good, good, good, good, good, None, good, good, None, 1, 2, 64, 64, 3, 3,
                               1, 1.0, 1, None, 0, None) == -5     # workspace missing
     assert lib.fmta_workspace_bytes(1, 4, 16, 4096, 64, 6, 11, 1) == 4 * 64 * 16 * 66 * 4
+    # head mix: one dW partial per CTA of the finest kernel that may run (16-row tiles from 16 heads per group on)
+    assert lib.fmta_workspace_bytes(1, 2, 16, 1000, 64, 1, 1, 16) == (2 * 63) * (16 * 1 + 1 * 16 * 16) * 4
+    assert lib.fmta_workspace_bytes(1, 2, 8, 1000, 64, 1, 1, 4) == (2 * 16) * (8 * 1 + 2 * 4 * 4) * 4
+    # optional exchange scratch of conv + mix: two sets of two 80 x 84 fp32 tiles per CTA; none without a mix
+    assert lib.fmta_workspace_bytes(5, 2, 32, 8192, 128, 6, 11, 4) == 2 * 2 * 32 * 128 * 2 * 80 * 84 * 4
+    assert lib.fmta_workspace_bytes(5, 2, 32, 8192, 128, 6, 11, 1) == 0
+    # 32 mixed heads: accepted without a conv up to head dim 64 (the missing workspace is what is reported), refused otherwise
+    mix = lambda d, theta: lib.fmta_bwd_dq_dw(good, good, good, good, good, good, theta, good, good, good if theta else None, good,
+                                              1, 32, 64, d, 3, 3, 32, 1.0, 1, None, 0, None)
+    assert mix(64, None) == -5 and mix(128, None) == -3 and mix(64, good) == -3
 
 
 def test_ops_refuse_cpu_tensors():
