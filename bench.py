@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the conv-attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl ours|reference] [--no-decode] [--no-sweep] [--no-headmix]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl ours|reference] [--no-decode] [--no-sweep] [--no-headmix] [--no-keep-ktilde]
 
 One "step" = conv-attention forward + backward (D prep, dQ/dTheta, dK/dV, partial reduction,
 and for N > 1 the all-reduce of dTheta) on the bf16 training configuration
@@ -274,6 +274,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-headmix", action="store_true")
+    ap.add_argument("--no-keep-ktilde", action="store_true",
+                    help="let forward and backward each build the stacked key operand (the reference-shaped pair of calls)")
     ap.add_argument("--headmix-shape", default=None, help="B,H,N,d: time only this dense head-mix shape (profiling captures)")
     ap.add_argument("--convmix-shape", default=None, help="B,H,N,d: time only conv (6,11) + mix in groups of 4 at this shape (profiling captures)")
     ap.add_argument("--sweep-max-n", type=int, default=65536)
@@ -328,15 +330,18 @@ def main():
     DOMINANT = 4
     kern_ev = []   # (start, end) events around the dominant kernel, per step
 
+    kt = None if args.no_keep_ktilde else F.ktilde_buffer(q, th)   # bf16 [B,H,cq,N,d], allocated once
+
     def step(q, k, v, do, record=False):
         if record:
             e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
             e0.record(stream); e1.record(stream)       # creates the underlying CUDA events
             _lib.lib.fmta_profile_kernel(DOMINANT, ctypes.c_void_p(e0.cuda_event), ctypes.c_void_p(e1.cuda_event))
             kern_ev.append((e0, e1))
-        O, M, L, LSE = F.forward(q, k, v, th, scale, pq, pk, True, return_lse=True)
+        # the forward leaves its stacked key operand in `kt`; the backward reads it instead of rebuilding it
+        O, M, L, LSE = F.forward(q, k, v, th, scale, pq, pk, True, return_lse=True, ktilde=kt)
         D = F.rowdot(do, O)
-        dQ, dK, dV, dTh = F.backward(q, k, v, do, D, LSE, th, scale, pq, pk, True)
+        dQ, dK, dV, dTh = F.backward(q, k, v, do, D, LSE, th, scale, pq, pk, True, ktilde=kt)
         if record:
             _lib.lib.fmta_profile_kernel(0, None, None)
         if world > 1:
@@ -475,11 +480,12 @@ def main():
                 config=dict(workload="train fwd+bwd bf16 B=%d(per GPU),H=%d,N=%d,d=%d,theta(%d,%d),causal" % (B, H, N, d, cq, ck),
                             global_batch=B * world, parallelism="batch x head sharding, dTheta all-reduce" if world > 1 else "single GPU",
                             l2="inputs+outputs per step (%.0f MB) exceed the 126 MB L2" % ((4 * 2 + 4 * 4) * B * H * N * d / 1e6),
+                            stacked_keys="built once per step (forward), kept for the backward" if kt is not None else "built by forward and by backward",
                             flops_attn_gflop=fl / 1e9, flops_conv_gflop=8 * cq * ck * E / 1e9),
                 # kernels of this library per step: forward = stacked-key pre-pass, fwd_tc, status fold, fwd_band;
-                # rowdot; backward = pre-pass, dq_tc, dkdv_tc, Toeplitz tiles + dKt adjoint, status fold, bwd_band,
+                # rowdot; backward = pre-pass (not when the forward's operand is kept), dq_tc, dkdv_tc, Toeplitz tiles + dKt adjoint, status fold, bwd_band,
                 # partial reduction
-                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=13 * args.steps * len(loops))
+                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=(13 if kt is None else 12) * args.steps * len(loops))
 
     # ---- decode (HBM-bound), rank-local, reported beside the headline ----
     if not args.no_decode:
@@ -553,9 +559,10 @@ def bench_sweep(F, dev, world, rank, peaks, barrier, max_n):
         def step():
             dth = None
             for q, k, v, do in chunks:
-                O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True)
+                kt = F.ktilde_buffer(q, th)
+                O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True, ktilde=kt)
                 D = F.rowdot(do, O)
-                dQ, dK, dV, dTh = F.backward(q, k, v, do, D, LSE, th, scale, cq - 1, (ck - 1) // 2, True)
+                dQ, dK, dV, dTh = F.backward(q, k, v, do, D, LSE, th, scale, cq - 1, (ck - 1) // 2, True, ktilde=kt)
                 dth = dTh if dth is None else dth + dTh
             return sharding.allreduce_param_grad(dth, plan)      # [H, cq, ck] on every rank
 

@@ -1085,12 +1085,15 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pd
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
   __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * p.d * 2);
+  if (p.Kt_ext) Kt = p.Kt_ext;                        // the stacked key operand kept from the forward
   w += up(rows * p.cq * p.d * 2);
   int* status = reinterpret_cast<int*>(w);
   cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
   if (e != cudaSuccess) return e;
-  e = launch_ktilde(p, Kt, stream);
-  if (e != cudaSuccess) return e;
+  if (!(p.Kt_ext && p.kt_valid)) {
+    e = launch_ktilde(p, Kt, stream);
+    if (e != cudaSuccess) return e;
+  }
   if (p.d == 128) return launch_bwd_dq_tc128(p, Kt, status, stream);
   alignas(64) CUtensorMap tmQ, tmdO, tmKt, tmV;
   if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QR / 2, false)) return cudaErrorInvalidValue;
@@ -1156,6 +1159,7 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
   __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
+  if (p.Kt_ext) Kt = p.Kt_ext;
   __nv_bfloat16* dKt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
   int* status = reinterpret_cast<int*>(w);
   cudaError_t e;

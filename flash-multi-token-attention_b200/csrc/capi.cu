@@ -153,11 +153,12 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
   return 0;
 }
 
-int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, const float* wmix,
-             void* O, float* M, float* L, float* LSE, int B, int H, int N, int d, int cq, int ck,
-             int G, float scale, int causal, int o_dtype, int path, void* workspace,
-             size_t workspace_bytes, void* stream) {
+static int fwd_impl(const void* Q, const void* K, const void* V, const float* theta, const float* wmix,
+                    void* O, float* M, float* L, float* LSE, int B, int H, int N, int d, int cq, int ck,
+                    int G, float scale, int causal, int o_dtype, int path, void* workspace,
+                    size_t workspace_bytes, void* stream, void* ktilde) {
   if (!Q || !K || !V || !O) return FMTA_ERR_NULL;
+  if (ktilde && !aligned16(ktilde)) return FMTA_ERR_ALIGN;
   if (int s = check_train_dims(B, H, N, d, cq, ck, G, theta != nullptr, wmix != nullptr)) return s;
   if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return FMTA_ERR_ALIGN;
   if (o_dtype != FMTA_DTYPE_F32 && o_dtype != FMTA_DTYPE_BF16) return FMTA_ERR_UNSUPPORTED;
@@ -181,6 +182,8 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
       use_tc = false;   // library default without a workspace: exact kernel everywhere
     }
   }
+  if (ktilde && !use_tc) return FMTA_ERR_UNSUPPORTED;   // only the tensor-core path makes the stacked key operand
+  p.Kt_ext = reinterpret_cast<__nv_bfloat16*>(ktilde);
   if (use_tc) {
     // stacked tensor-core kernel off the causal band, then the band kernel, which continues the
     // online softmax from the un-normalised partial and writes the final O, M, L
@@ -192,6 +195,22 @@ int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, co
       workspace_bytes >= fmta_workspace_bytes(FMTA_OP_MIX_EXCHANGE, B, H, N, d, p.cq, p.ck, p.G))
     p.xchg = reinterpret_cast<float*>(workspace);
   return check_cuda(launch_fwd_exact(p, (cudaStream_t)stream));
+}
+
+int fmta_fwd(const void* Q, const void* K, const void* V, const float* theta, const float* wmix,
+             void* O, float* M, float* L, float* LSE, int B, int H, int N, int d, int cq, int ck,
+             int G, float scale, int causal, int o_dtype, int path, void* workspace,
+             size_t workspace_bytes, void* stream) {
+  return fwd_impl(Q, K, V, theta, wmix, O, M, L, LSE, B, H, N, d, cq, ck, G, scale, causal, o_dtype, path, workspace,
+                  workspace_bytes, stream, nullptr);
+}
+
+int fmta_fwd_keep_ktilde(const void* Q, const void* K, const void* V, const float* theta, void* O, float* M, float* L,
+                         float* LSE, int B, int H, int N, int d, int cq, int ck, float scale, int causal, int o_dtype,
+                         void* workspace, size_t workspace_bytes, void* ktilde, void* stream) {
+  if (!ktilde || !theta) return FMTA_ERR_NULL;
+  return fwd_impl(Q, K, V, theta, nullptr, O, M, L, LSE, B, H, N, d, cq, ck, 1, scale, causal, o_dtype, 1, workspace,
+                  workspace_bytes, stream, ktilde);
 }
 
 int fmta_bwd_prep_D(const void* dO, const void* O, int o_dtype, float* D, size_t rows, int d,
@@ -267,11 +286,12 @@ int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, c
   return check_cuda(launch_bwd_dkdv(p, (cudaStream_t)stream));
 }
 
-int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const float* D,
-             const float* LSE, const float* theta, const float* wmix, float* dQ, float* dK, float* dV,
-             float* dTheta, float* dW, int B, int H, int N, int d, int cq, int ck, int G, float scale,
-             int causal, int path, void* workspace, size_t workspace_bytes, void* stream) {
+static int bwd_impl(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+                    const float* LSE, const float* theta, const float* wmix, float* dQ, float* dK, float* dV,
+                    float* dTheta, float* dW, int B, int H, int N, int d, int cq, int ck, int G, float scale,
+                    int causal, int path, void* workspace, size_t workspace_bytes, void* stream, const void* ktilde) {
   TrainParams p = {};
+  if (ktilde && !aligned16(ktilde)) return FMTA_ERR_ALIGN;
   if (int s = fill_bwd(p, Q, K, V, dO, D, LSE, theta, wmix, B, H, N, d, cq, ck, G, scale, causal)) return s;
   if (!dQ || !dK || !dV) return FMTA_ERR_NULL;
   if (!aligned16(dQ) || !aligned16(dK) || !aligned16(dV)) return FMTA_ERR_ALIGN;
@@ -289,6 +309,7 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
   p.dQ = dQ; p.dK = dK; p.dV = dV;
   int slots_ex = (!use_tc && hm_dense_supported(p)) ? hm_dq_slots(B, N, p.G) : B * ((N + 63) / 64);
   const size_t n_theta = (size_t)H * p.cq * p.ck;
+  if (ktilde && !use_tc) return FMTA_ERR_UNSUPPORTED;   // only the tensor-core path uses the stacked key operand
   if (!use_tc) {
     const size_t need = fmta_workspace_bytes(FMTA_OP_BWD_DQ, B, H, N, d, p.cq, p.ck, p.G);
     const bool want_part = (theta != nullptr) || (wmix != nullptr);
@@ -306,6 +327,8 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
     return FMTA_OK;
   }
   // tensor-core kernels for the entries off the causal band, then the band kernel adds its part
+  p.Kt_ext = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(ktilde));   // the forward's stacked key operand, kept by the caller
+  p.kt_valid = ktilde != nullptr;
   slots_ex = bwd_band_theta_slots(B, N, p.cq, p.ck);            // one dTheta partial per band CTA
   const int slots_tc = bwd_tc_theta_slots(B, N, d);
   float* part = reinterpret_cast<float*>(workspace);
@@ -325,6 +348,23 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
     if (int s = check_cuda(cudaMemsetAsync(part, 0, (size_t)slots_ex * n_theta * sizeof(float), st))) return s;
   }
   return check_cuda(launch_reduce_partials(part, dTheta, slots_ex + slots_tc, (int)n_theta, st));
+}
+
+int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+             const float* LSE, const float* theta, const float* wmix, float* dQ, float* dK, float* dV,
+             float* dTheta, float* dW, int B, int H, int N, int d, int cq, int ck, int G, float scale,
+             int causal, int path, void* workspace, size_t workspace_bytes, void* stream) {
+  return bwd_impl(Q, K, V, dO, D, LSE, theta, wmix, dQ, dK, dV, dTheta, dW, B, H, N, d, cq, ck, G, scale, causal, path,
+                  workspace, workspace_bytes, stream, nullptr);
+}
+
+int fmta_bwd_with_ktilde(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+                         const float* LSE, const float* theta, float* dQ, float* dK, float* dV, float* dTheta,
+                         int B, int H, int N, int d, int cq, int ck, float scale, int causal, void* workspace,
+                         size_t workspace_bytes, const void* ktilde, void* stream) {
+  if (!ktilde || !theta) return FMTA_ERR_NULL;
+  return bwd_impl(Q, K, V, dO, D, LSE, theta, nullptr, dQ, dK, dV, dTheta, nullptr, B, H, N, d, cq, ck, 1, scale, causal, 1,
+                  workspace, workspace_bytes, stream, ktilde);
 }
 
 static int decode_impl(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,

@@ -27,6 +27,8 @@ struct TrainParams {
   float* dV;
   float* dTheta_part;        // [n_slots, H, cq*ck] per-CTA-slot partial sums (reduced later)
   float* dW_part;            // [n_slots, H/G, G*G]
+  __nv_bfloat16* Kt_ext;     // tensor-core path: caller-owned stacked key operand [B,H,cq,N,d] instead of the workspace's (nullptr: none)
+  int kt_valid;              //   ... which already holds the operand of these K / theta / scale: the pre-pass is skipped
   float* xchg;               // conv + mix cluster kernels: optional global scratch, 2 sets x 2 * kMixXchFloats floats per CTA (nullptr: exchange through distributed shared memory)
   int B, H, N, d, cq, ck, G;
   float scale;

@@ -568,7 +568,7 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
                         cudaStream_t stream) {
   using Cfg = TcCfg<D>;
   const size_t BH = (size_t)p.B * p.H;
-  {
+  if (!(p.Kt_ext && p.kt_valid)) {
     cudaError_t e = launch_ktilde(p, Kt, stream);
     if (e != cudaSuccess) return e;
   }
@@ -610,6 +610,7 @@ cudaError_t launch_fwd_tc(const TrainParams& p, void* workspace, const float** O
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   unsigned char* w = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 1023) & ~uintptr_t(1023));
   bf16* Kt = reinterpret_cast<bf16*>(w); w += up(rows * p.cq * p.d * 2);
+  if (p.Kt_ext) Kt = p.Kt_ext;                      // the caller keeps the stacked key operand (for the backward)
   float* Op = reinterpret_cast<float*>(w); w += up(rows * p.d * 4);
   float* Mp = reinterpret_cast<float*>(w); w += up(rows * 4);
   float* Lp = reinterpret_cast<float*>(w); w += up(rows * 4);

@@ -8,7 +8,7 @@ C ABI (libfmta_b200.so).  Importing fails if the library has not been built.
 """
 from ._lib import lib as _c_lib, LIB_PATH, check_device_status  # noqa: F401  (raises ImportError when missing)
 from .conv_attn import (ConvAttentionCUDA, FlashConvAttentionCUDAFunction, forward, dq_backward,  # noqa: F401
-                        dkdv_backward, backward, rowdot)
+                        dkdv_backward, backward, rowdot, ktilde_buffer)
 from .inference import (forward_inference, fwd_conv_attn_inference, forward_inference_paged,  # noqa: F401
                         kv_append_paged)
 from .head_conv import (HeadConvAttentionFunction, HeadConvAttention, head_conv_attention,  # noqa: F401

@@ -49,16 +49,46 @@ def _pad64(t):
     return torch.nn.functional.pad(t, (0, 32)).contiguous()
 
 
+# The tensor-core kernels read the keys through a stacked operand (c_q filtered copies of K, bf16) that a pre-pass
+# writes; forward and backward each run it.  A training step can keep the forward's copy for the backward
+# (c_q times the size of K for as long as the graph lives; about 2 % of a step at B=4, H=16, N=4096, d=64):
+# `ktilde_buffer` + the ``ktilde`` argument of `forward` / `backward`, or FMTA_KEEP_KTILDE=1 for the autograd Function.
+KEEP_KTILDE = os.environ.get("FMTA_KEEP_KTILDE", "0") != "0"
+
+
+def ktilde_buffer(Q, conv_kernel):
+    """An uninitialised bf16 [B, H, c_q, N, d] buffer for the ``ktilde`` argument of `forward` and `backward`, or
+    None where the stacked operand cannot be shared (shapes without tensor-core backward kernels, or the exact
+    kernels selected process-wide)."""
+    B, H, N, d = Q.shape
+    cq = conv_kernel.shape[1]
+    if not ((d == 64 and cq <= 7) or (d == 128 and cq <= 6)) or lib.fmta_set_path(99) == 0:
+        return None
+    return torch.empty((B, H, cq, N, d), dtype=torch.bfloat16, device=Q.device)
+
+
+def _check_ktilde(ktilde, Q, cq, path):
+    B, H, N, d = Q.shape
+    require_on(Q, ktilde, "ktilde", (B, H, cq, N, d))
+    if ktilde.dtype != torch.bfloat16 or not ktilde.is_contiguous():
+        raise RuntimeError("ktilde must be a contiguous bf16 tensor (see ktilde_buffer)")
+    if path == 0:
+        raise RuntimeError("ktilde belongs to the tensor-core path; path=0 selects the exact kernels")
+
+
 def forward(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, out_dtype=torch.float32, return_lse=False,
-            path=-1):
+            path=-1, ktilde=None):
     """(O, M, L) -- `forward` of conv_attn/bindings.cpp:46-48.  O is fp32 as in
-    fwd_wrapper.cu:44-46 unless ``out_dtype=torch.bfloat16``; ``return_lse`` appends M+log L."""
+    fwd_wrapper.cu:44-46 unless ``out_dtype=torch.bfloat16``; ``return_lse`` appends M+log L.
+    ``ktilde`` (from `ktilde_buffer`): the stacked key operand is left there for `backward`."""
     for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
         require_cuda_bf16(t, n)
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
     if K.shape != Q.shape or V.shape != Q.shape:
         raise RuntimeError("Q, K, V must have the same shape [batch, heads, seq, d_head]")
-    if _pads_to_64(d, cq, path):
+    if ktilde is not None:
+        _check_ktilde(ktilde, Q, cq, path)
+    elif _pads_to_64(d, cq, path):
         out = forward(_pad64(Q), _pad64(K), _pad64(V), conv_kernel, scale, pad_q, pad_k, causal, out_dtype, return_lse, path)
         return (out[0][..., :32].contiguous(),) + tuple(out[1:])
     require_on(Q, K, "K"); require_on(Q, V, "V"); require_on(Q, conv_kernel, "conv_kernel")
@@ -70,6 +100,13 @@ def forward(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, out_dtype=torch.f
     LSE = torch.empty_like(M) if return_lse else None
     ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_FWD_TC, B, H, N, d, cq, ck, 1) if path != 0 else 0
     ws = _workspace(ws_bytes, Q.device) if ws_bytes else None
+    odt = _lib.FMTA_DTYPE_BF16 if out_dtype == torch.bfloat16 else _lib.FMTA_DTYPE_F32
+    if ktilde is not None:
+        st = lib.fmta_fwd_keep_ktilde(ptr(Q), ptr(K), ptr(V), ptr(theta), ptr(O), ptr(M), ptr(L), ptr(LSE), B, H, N, d,
+                                      cq, ck, float(scale), int(bool(causal)), odt, ptr(ws), ws_bytes, ptr(ktilde),
+                                      stream_ptr())
+        check(st, "fmta_fwd_keep_ktilde")
+        return (O, M, L, LSE) if return_lse else (O, M, L)
     st = lib.fmta_fwd(ptr(Q), ptr(K), ptr(V), ptr(theta), None, ptr(O), ptr(M), ptr(L), ptr(LSE), B, H, N, d,
                       cq, ck, 1, float(scale), int(bool(causal)),
                       _lib.FMTA_DTYPE_BF16 if out_dtype == torch.bfloat16 else _lib.FMTA_DTYPE_F32,
@@ -142,16 +179,19 @@ def dkdv_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
 STREAM_LIMIT_BYTES = int(float(os.environ.get("FMTA_STREAM_LIMIT_GB", "1")) * (1 << 30))
 
 
-def backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, path=-1, stream_pdc=None):
+def backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, path=-1, stream_pdc=None, ktilde=None):
     """(dQ, dK, dV, dconv_kernel), all fp32, in one call (`fmta_bwd`): what the reference obtains
     from `dq_backward` + `dkdv_backward` (conv_attention_cuda.py:147-152).  ``path`` as in the C ABI:
     0 exact kernels, 1 tensor-core kernels + band kernel, -1 library default.  ``stream_pdc``: let the dQ
-    kernel keep P and dC for a streaming dK/dV kernel (None: whenever they fit STREAM_LIMIT_BYTES)."""
+    kernel keep P and dC for a streaming dK/dV kernel (None: whenever they fit STREAM_LIMIT_BYTES).
+    ``ktilde``: the buffer `forward` filled for the same K, conv_kernel and scale; its pre-pass is then skipped."""
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (dO, "dO")):
         require_cuda_bf16(t, n)
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
     _check_bwd_args(Q, K, V, dO, D, L, conv_kernel)
-    if _pads_to_64(d, cq, path):
+    if ktilde is not None:
+        _check_ktilde(ktilde, Q, cq, path)
+    elif _pads_to_64(d, cq, path):
         dQ, dK, dV, dTheta = backward(_pad64(Q), _pad64(K), _pad64(V), _pad64(dO), D, L, conv_kernel, scale, pad_q, pad_k,
                                       causal, path, stream_pdc)
         return dQ[..., :32].contiguous(), dK[..., :32].contiguous(), dV[..., :32].contiguous(), dTheta
@@ -168,6 +208,12 @@ def backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, path=-
             op = _lib.FMTA_OP_BWD_TC_STREAM
     ws_bytes = lib.fmta_workspace_bytes(op, B, H, N, d, cq, ck, 1)
     ws = _workspace(ws_bytes, Q.device)
+    if ktilde is not None:
+        st = lib.fmta_bwd_with_ktilde(ptr(Q), ptr(K), ptr(V), ptr(dO), ptr(Dv), ptr(LSE), ptr(theta), ptr(dQ), ptr(dK),
+                                      ptr(dV), ptr(dTheta), B, H, N, d, cq, ck, float(scale), int(bool(causal)), ptr(ws),
+                                      ws_bytes, ptr(ktilde), stream_ptr())
+        check(st, "fmta_bwd_with_ktilde")
+        return dQ, dK, dV, dTheta
     st = lib.fmta_bwd(ptr(Q), ptr(K), ptr(V), ptr(dO), ptr(Dv), ptr(LSE), ptr(theta), None, ptr(dQ), ptr(dK), ptr(dV),
                       ptr(dTheta), None, B, H, N, d, cq, ck, 1, float(scale), int(bool(causal)), int(path), ptr(ws),
                       ws_bytes, stream_ptr())
@@ -181,7 +227,9 @@ class FlashConvAttentionCUDAFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, conv_kernel, scale, pad_q, pad_k, causal):
         Qb, Kb, Vb = (t.to(torch.bfloat16).contiguous() for t in (Q, K, V))
-        O, M, L, LSE = forward(Qb, Kb, Vb, conv_kernel, scale, pad_q, pad_k, causal, return_lse=True)
+        needs_grad = any(t.requires_grad for t in (Q, K, V, conv_kernel))
+        ctx.ktilde = ktilde_buffer(Qb, conv_kernel) if (KEEP_KTILDE and needs_grad) else None
+        O, M, L, LSE = forward(Qb, Kb, Vb, conv_kernel, scale, pad_q, pad_k, causal, return_lse=True, ktilde=ctx.ktilde)
         ctx.save_for_backward(Qb, Kb, Vb, conv_kernel, LSE, O)
         ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal = scale, pad_q, pad_k, causal
         ctx.in_dtypes = (Q.dtype, K.dtype, V.dtype)
@@ -192,7 +240,9 @@ class FlashConvAttentionCUDAFunction(torch.autograd.Function):
         Q, K, V, conv_kernel, LSE, O = ctx.saved_tensors
         dOb = dO.to(torch.bfloat16).contiguous()
         D = rowdot(dOb, O)
-        dQ, dK, dV, dTheta = backward(Q, K, V, dOb, D, LSE, conv_kernel, ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal)
+        dQ, dK, dV, dTheta = backward(Q, K, V, dOb, D, LSE, conv_kernel, ctx.scale, ctx.pad_q, ctx.pad_k, ctx.causal,
+                                      ktilde=ctx.ktilde)
+        ctx.ktilde = None
         tq, tk, tv = ctx.in_dtypes
         return dQ.to(tq), dK.to(tk), dV.to(tv), dTheta.to(conv_kernel.dtype), None, None, None, None
 

@@ -176,6 +176,26 @@ int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const 
              int causal, int path, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Forward / backward pair that shares the stacked key operand (no counterpart in the reference, whose
+ * backward recomputes everything from Q, K, V).  The tensor-core kernels read keys through
+ * Ktilde[b,h,t,j,:] = scale * log2(e) * sum_u theta[h,t,u] * K[b,h,j-u,:] (bf16 [B,H,cq,N,d], written by a
+ * pre-pass).  fmta_fwd and fmta_bwd each run that pre-pass into their own workspace; a training step that calls
+ * fmta_fwd_keep_ktilde instead leaves the operand in the caller's buffer `ktilde` (B*H*cq*N*d*2 bytes, 16-byte
+ * aligned), and fmta_bwd_with_ktilde reads it back and skips the second pre-pass.  The caller guarantees that K,
+ * theta and scale are unchanged in between; the results are bit-identical to fmta_fwd / fmta_bwd with path 1.
+ * Tensor-core path only: the shapes fmta_fwd / fmta_bwd accept with path = 1 (theta given, no head mixing) and
+ * the same workspace sizes (FMTA_OP_FWD_TC / FMTA_OP_BWD_TC or FMTA_OP_BWD_TC_STREAM); anything else returns
+ * FMTA_ERR_UNSUPPORTED or FMTA_ERR_WORKSPACE.
+ */
+int fmta_fwd_keep_ktilde(const void* Q, const void* K, const void* V, const float* theta, void* O, float* M, float* L,
+                         float* LSE, int B, int H, int N, int d, int cq, int ck, float scale, int causal, int o_dtype,
+                         void* workspace, size_t workspace_bytes, void* ktilde, void* stream);
+int fmta_bwd_with_ktilde(const void* Q, const void* K, const void* V, const void* dO, const float* D,
+                         const float* LSE, const float* theta, float* dQ, float* dK, float* dV, float* dTheta,
+                         int B, int H, int N, int d, int cq, int ck, float scale, int causal, void* workspace,
+                         size_t workspace_bytes, const void* ktilde, void* stream);
+
+/*
  * Decode: last query row over a KV cache with split-K.  Replaces
  * `forward_inference(Q,K,V,conv_kernel,k_splits,scale,pad_q,pad_k,causal,num_k_blocks) ->
  * (O_splits,M_splits,L_splits)` (conv_attn/fwd_inference_bindings.cpp:20-23,

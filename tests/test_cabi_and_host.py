@@ -52,6 +52,14 @@ def test_host_validation_needs_no_gpu():
     assert fwd(Q=P(0x1004)) == -4
     assert fwd(G=3, w=good, H=6) == -3
     assert fwd(G=4, w=good, H=6) == -2
+    # the pair that shares the stacked key operand: the buffer is required and must be aligned; shapes without
+    # tensor-core kernels are refused rather than served by the exact kernels
+    keep = lambda kt=good, d=64, th=good: lib.fmta_fwd_keep_ktilde(good, good, good, th, good, None, None, None, 1, 2, 16, d,
+                                                                   3, 3, 1.0, 1, 0, None, 0, kt, None)
+    assert keep(kt=None) == -1 and keep(th=None) == -1 and keep(kt=P(0x1008)) == -4 and keep(d=32) == -3
+    use = lambda kt=good, d=64: lib.fmta_bwd_with_ktilde(good, good, good, good, good, good, good, good, good, good, good,
+                                                         1, 2, 16, d, 3, 3, 1.0, 1, None, 0, kt, None)
+    assert use(kt=None) == -1 and use(kt=P(0x1008)) == -4 and use(d=32) == -3
     dec = lambda q_len=6, ks=1, Nk=64: lib.fmta_decode(good, good, good, good, good, good, good, 1, 1, q_len, Nk,
                                                         64, 3, 3, ks, 1.0, None)
     assert dec(q_len=17) == -2 and dec(ks=0) == -2 and dec(ks=65) == -2

@@ -211,6 +211,63 @@ def test_head_dim_32_default_path(B, H, N, cq, ck, causal):
     assert float((O0 - O).abs().max()) <= 2e-2
 
 
+@pytest.mark.parametrize("B,H,N,d,cq,ck,causal,stream_pdc", [
+    (2, 2, 640, 64, 6, 11, True, False), (2, 2, 640, 64, 6, 11, True, True), (1, 2, 333, 64, 7, 5, True, False),
+    (1, 3, 512, 64, 3, 5, False, None), (1, 2, 512, 128, 6, 11, True, None), (1, 1, 200, 128, 2, 3, True, None)])
+def test_forward_hands_stacked_keys_to_backward(B, H, N, d, cq, ck, causal, stream_pdc):
+    """`forward(..., ktilde=buf)` leaves the stacked key operand in the caller's buffer and `backward(..., ktilde=buf)`
+    skips its own pre-pass: every output is bit-identical to the pair of calls that each build the operand."""
+    import fmta_b200 as F
+    Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=77 + N, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
+    th = theta.cuda()
+    pq, pk = cq - 1, (ck - 1) // 2
+    O0, M0, L0, LSE0 = F.forward(q, k, v, th, scale, pq, pk, causal, return_lse=True, path=1)
+    Dv = F.rowdot(do, O0)
+    ref = F.backward(q, k, v, do, Dv, LSE0, th, scale, pq, pk, causal, path=1, stream_pdc=stream_pdc)
+    kt = F.ktilde_buffer(q, th)
+    assert kt is not None and kt.shape == (B, H, cq, N, d)
+    kt.fill_(float("nan"))
+    O1, M1, L1, LSE1 = F.forward(q, k, v, th, scale, pq, pk, causal, return_lse=True, ktilde=kt)
+    assert bool(torch.isfinite(kt.float()).all())
+    got = F.backward(q, k, v, do, Dv, LSE1, th, scale, pq, pk, causal, stream_pdc=stream_pdc, ktilde=kt)
+    torch.cuda.synchronize()
+    for a, b, n in ((O0, O1, "O"), (M0, M1, "M"), (L0, L1, "L"), (LSE0, LSE1, "LSE")):
+        assert torch.equal(a, b), n
+    for a, b, n in zip(ref, got, ("dQ", "dK", "dV", "dTheta")):
+        assert torch.equal(a, b), n
+    # a stale buffer is the caller's responsibility, and it shows: with the operand zeroed the backward changes
+    if N >= 512:
+        kt.zero_()
+        stale = F.backward(q, k, v, do, Dv, LSE1, th, scale, pq, pk, causal, stream_pdc=stream_pdc, ktilde=kt)
+        assert not torch.equal(stale[0], ref[0])
+    # rejected: the exact path, a buffer of the wrong shape
+    with pytest.raises(RuntimeError):
+        F.forward(q, k, v, th, scale, pq, pk, causal, path=0, ktilde=kt)
+    with pytest.raises(RuntimeError):
+        F.backward(q, k, v, do, Dv, LSE1, th, scale, pq, pk, causal, ktilde=kt[:, :, :1].contiguous())
+
+
+def test_autograd_function_keeps_stacked_keys_when_asked(monkeypatch):
+    """FMTA_KEEP_KTILDE (here: the module switch it sets) makes the autograd Function carry the operand from its
+    forward to its backward; gradients are bit-identical to the default."""
+    import fmta_b200 as F
+    from fmta_b200 import conv_attn
+    B, H, N, d, cq, ck = 1, 2, 384, 64, 6, 11
+    Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=9, dtype=torch.bfloat16)
+    grads = []
+    for keep in (False, True):
+        monkeypatch.setattr(conv_attn, "KEEP_KTILDE", keep)
+        q, k, v = (t.cuda().to(torch.bfloat16).requires_grad_() for t in (Q, K, V))
+        th = theta.cuda().requires_grad_()
+        O = F.FlashConvAttentionCUDAFunction.apply(q, k, v, th, 1.0 / math.sqrt(d), cq - 1, (ck - 1) // 2, True)
+        O.backward(dO.cuda().to(O.dtype))
+        grads.append([t.grad.clone() for t in (q, k, v, th)] + [O.detach()])
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
+
+
 def test_fp32_configuration_N256_theta_3x5_both_paths():
     """The fp32 CPU-path configuration of the benchmark (B=1, H=4, N=256, d=64, theta (3,5), N(0,0.05)
     filter) run through the bf16 kernels on both paths, against the oracle on the same bf16-rounded inputs."""
