@@ -91,11 +91,12 @@ __global__ void __launch_bounds__(bandcfg::NT, bandcfg::Layout<D>::kCtasPerSm) b
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = p.N, H = p.H, cq = (CQ > 0) ? CQ : p.cq, ck = (CQ > 0) ? CK : p.ck;
   const int pq = cq - 1, pk = (ck - 1) / 2, band = pq + pk, W = band + pk;
-  const int R = min(RC, RC - (W - 1 + pq));
+  const int Rt = min(RC, RC - (W - 1 + pq));           // positions per CTA
   const bool mma_out = (W <= 17);
   const int h = blockIdx.y, b = blockIdx.z;
   const size_t bh = (size_t)b * H + h;
-  const int t0 = blockIdx.x * R;
+  const int t0 = win_lo(p) + blockIdx.x * Rt;
+  const int R = p.row_hi > 0 ? min(Rt, p.row_hi - t0) : Rt;   // a call with a window owns no position past its end
   const bf16* Qg = p.Q + bh * (size_t)N * D;
   const bf16* Kg = p.K + bh * (size_t)N * D;
   const bf16* Vg = p.V + bh * (size_t)N * D;
@@ -493,7 +494,7 @@ static cudaError_t launch_bwd_band_d(const TrainParams& p, dim3 grid, cudaStream
 
 cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream) {
   const int R = bwd_band_positions(p.cq, p.ck);
-  dim3 grid((p.N + R - 1) / R, p.H, p.B);
+  dim3 grid((win_hi(p) - win_lo(p) + R - 1) / R, p.H, p.B);
   ScopedKernelTimer timer_(kKernBwdBand, stream);
   if (p.d == 128) return launch_bwd_band_d<128>(p, grid, stream);
   return launch_bwd_band_d<64>(p, grid, stream);

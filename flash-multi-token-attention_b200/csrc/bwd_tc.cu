@@ -100,7 +100,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
   const int band = pq + pk;
   const int rows_per_cta = OWN * NT;
-  const int nQB = (N + rows_per_cta - 1) / rows_per_cta;
+  const int nQB = (p.row_end - p.row_base + rows_per_cta - 1) / rows_per_cta;
   // CTAs are dispatched in linear block order; walk it length-major (all (batch, head) pairs of the
   // longest row block first) so that the greedy hardware scheduler ends with the short CTAs
   const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
@@ -108,13 +108,13 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int qb = nQB - 1 - lin / nBH;
   const int h = (lin % nBH) % (int)gridDim.y, b = (lin % nBH) / (int)gridDim.y;
   const int bh = b * p.H + h;
-  const int R0 = qb * rows_per_cta;
+  const int R0 = p.row_base + qb * rows_per_cta;
   const int nKB = (N + BC - 1) / BC;
   int nkb_t[2] = {0, 0};
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
     const int r0 = R0 + t * OWN;
-    if (r0 >= N) nkb_t[t] = 0;
+    if (r0 >= p.row_end) nkb_t[t] = 0;
     else if (p.causal) {
       const int last = min(N - 1, r0 + BM - 1) - band;
       nkb_t[t] = last >= 0 ? min(nKB, last / BC + 1) : 0;
@@ -384,7 +384,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (my_nkb - 1) & 1, s_abort));
     tc::tc_fence_after();
     const bool have = (my_nkb > 0) && ok;
-    const bool store = row_ok && (m < OWN);
+    const bool store = row_ok && (m < OWN) && (gi < p.row_end);
     float* orow = p.dQ + ((size_t)bh * N + (row_ok ? gi : 0)) * D;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
@@ -498,6 +498,7 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   // block order: see dkdv_block_order
   int h, b, j0;
   dkdv_block_order(BK, h, b, j0);
+  j0 += p.key_base;
   const int bh = b * p.H + h;
   const int nQB = (N + BR - 1) / BR;
   const int qb_begin = p.causal ? min(nQB, (j0 + band) / BR) : 0;
@@ -882,7 +883,7 @@ __global__ void dk_post_toeplitz_kernel(const float* __restrict__ theta, bf16* _
 __global__ void __launch_bounds__(DkPostCfg::NT, 2)
 dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmX,
                    const bf16* __restrict__ Tg, float* __restrict__ dK, float* __restrict__ dTheta_part, int* status,
-                   int H, int N, int cq, int ck, float scale, int n_jblocks, int dfull) {
+                   int H, int N, int cq, int ck, float scale, int n_jblocks, int dfull, int j_base) {
   using Cfg = DkPostCfg;
   constexpr int D = Cfg::D, NT = Cfg::NT, KEYS = Cfg::KEYS, HALO = Cfg::HALO;
   constexpr int T_LD = Cfg::T_LD, T_ELEMS = Cfg::T_ELEMS, RED_LD = Cfg::RED_LD;
@@ -899,7 +900,7 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const int bh = gridDim.y - 1 - blockIdx.y, h = bh % H, b = bh / H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pk = (ck - 1) / 2;
-  const int J0 = blockIdx.x * KEYS;
+  const int J0 = j_base + blockIdx.x * KEYS;                 // j_base: the first key of the call's window
   const int col0 = blockIdx.z * D;                           // a CTA handles 64 of the head's `dfull` columns
   const int half = (cq + 1) / 2;                             // the taps arrive in two batches
   // 16-byte chunk c of row r of tile t
@@ -1104,8 +1105,9 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pd
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dQ = p.dQ; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
+  bp.row_base = win_lo(p); bp.row_end = win_hi(p);
   const int rows_per_cta = Cfg::OWN * Cfg::NT;
-  dim3 grid((p.N + rows_per_cta - 1) / rows_per_cta, p.H, p.B);
+  dim3 grid((bp.row_end - bp.row_base + rows_per_cta - 1) / rows_per_cta, p.H, p.B);
   if (keep_pdc) {
     stream_buffers(p, workspace, &bp.Pout, &bp.dCout, &bp.ldp);
     if (p.N % 64 != 0) zero_tail_rows_kernel<<<dim3(bp.ldp / 64, (unsigned)BH), 128, 0, stream>>>(bp.Pout, bp.dCout, p.N, bp.ldp / 64);
@@ -1129,7 +1131,7 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pd
 // One launch of the dK/dV kernel for the taps [tap0, tap0 + ntap) (and dV).
 template <int CQMAX, bool PAIR>
 static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* Kt, __nv_bfloat16* dKt, int* status, int tap0,
-                                    int ntap, int with_dv, cudaStream_t stream) {
+                                    int ntap, int with_dv, int key_lo, int key_hi, cudaStream_t stream) {
   constexpr int D = 64;
   using Cfg = DkvCfg<D, CQMAX, PAIR>;
   const size_t BH = (size_t)p.B * p.H;
@@ -1144,11 +1146,12 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dV = p.dV; bp.dKt = dKt; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.tap0 = tap0; bp.ntap = ntap; bp.with_dv = with_dv;
+  bp.key_base = key_lo;
   bp.selftest_expire = take_selftest_expire(kKernBwdDkdvTc);
   auto kern = bwd_dkdv_tc_kernel<D, CQMAX, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.N + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
+  dim3 grid((key_hi - key_lo + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, tmdKt, tmdV, bp);
   return cudaGetLastError();
 }
@@ -1164,22 +1167,35 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   int* status = reinterpret_cast<int*>(w);
   cudaError_t e;
   { ScopedKernelTimer timer_(kKernBwdDkdvTc, stream);
-    if (D == 128) {
-      e = launch_bwd_dkdv_tc128(p, Kt, dKt, status, stream);
-    } else if (keep_pdc) {
+    // A call with a window computes dV and dK of its keys [lo, hi).  dK needs dKt of pad_k keys on either side
+    // (the adjoint of the pre-pass), so one key tile before and one after the window are computed too, without dV.
+    const int BK = (D == 128) ? 64 : 128;
+    const int lo = win_lo(p), hi = win_hi(p);
+    const int seg_lo[3] = {lo, max(0, lo - BK), hi}, seg_hi[3] = {hi, lo, min(p.N, hi + BK)}, seg_dv[3] = {1, 0, 0};
+    e = cudaSuccess;
+    if (keep_pdc) {
       __nv_bfloat16 *Pb, *dCb; int ldp;
       stream_buffers(p, workspace, &Pb, &dCb, &ldp);
       e = launch_bwd_dkdv_stream(p, Pb, dCb, ldp, dKt, status, stream);
-    } else if (p.cq <= 6) {
-      e = launch_dkdv_pass<6, true>(p, Kt, dKt, status, 0, p.cq, 1, stream);
     } else {
-      // seven taps: dV + 7 accumulators + the scratch columns exceed the tensor memory, so the taps are
-      // split over two launches (each recomputes S^T and dP^T)
-      e = launch_dkdv_pass<7, false>(p, Kt, dKt, status, 0, 4, 1, stream);
-      if (e == cudaSuccess) e = launch_dkdv_pass<7, false>(p, Kt, dKt, status, 4, p.cq - 4, 0, stream);
+      for (int sg = 0; sg < 3 && e == cudaSuccess; ++sg) {
+        const int klo = seg_lo[sg], khi = seg_hi[sg], dv = seg_dv[sg];
+        if (khi <= klo) continue;
+        if (D == 128) {
+          e = launch_bwd_dkdv_tc128(p, Kt, dKt, status, dv, klo, khi, stream);
+        } else if (p.cq <= 6) {
+          e = launch_dkdv_pass<6, true>(p, Kt, dKt, status, 0, p.cq, dv, klo, khi, stream);
+        } else {
+          // seven taps: dV + 7 accumulators + the scratch columns exceed the tensor memory, so the taps are
+          // split over two launches (each recomputes S^T and dP^T)
+          e = launch_dkdv_pass<7, false>(p, Kt, dKt, status, 0, 4, dv, klo, khi, stream);
+          if (e == cudaSuccess) e = launch_dkdv_pass<7, false>(p, Kt, dKt, status, 4, p.cq - 4, 0, klo, khi, stream);
+        }
+      }
     } }
   if (e != cudaSuccess) return e;
-  const int njb = (p.N + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS;
+  const int j_base = win_lo(p);
+  const int njb = (win_hi(p) - j_base + DkPostCfg::KEYS - 1) / DkPostCfg::KEYS;
   dim3 g2(njb, (unsigned)BH, D / DkPostCfg::D);      // one CTA per 64 keys and 64 columns of the head dim
   const int smem = DkPostCfg::smem_bytes(p.cq);
   auto kern = dk_post_mma_kernel;
@@ -1192,7 +1208,7 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   // (the maps span the full head dim; each CTA fetches its 64-column slab)
   ScopedKernelTimer timer2_(kKernDkPost, stream);
   dk_post_toeplitz_kernel<<<p.H, 256, 0, stream>>>(p.theta, Tg, p.cq, p.ck, p.scale);
-  kern<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb, D);
+  kern<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb, D, j_base);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   return launch_fold_status(status, stream);

@@ -23,6 +23,9 @@ struct BwdTcParams {
   // dK/dV kernel: the filter taps whose dKt this launch accumulates ([tap0, tap0 + ntap)) and whether it
   // accumulates dV as well; seven taps do not fit the tensor memory at once and take two launches
   int tap0, ntap, with_dv;
+  // window of the call: the dQ kernel tiles the rows [row_base, row_end) and writes no other row; the dK/dV
+  // kernel's key tile 0 starts at key_base (whole sequence: 0, N, 0)
+  int row_base, row_end, key_base;
   int selftest_expire;   // failure-detection self-test: the element-wise warps' first wait is on a barrier nothing arrives at
   // dQ kernel (optional outputs): the off-band P and dC = P (dP - D) of every entry, bf16, tile-major
   // [B*H][row block of 64][key block of 64][64 rows][64 keys] with ldp / 64 key blocks (ldp = N rounded up to
@@ -44,7 +47,8 @@ cudaError_t launch_bwd_dkdv_stream(const TrainParams& p, const __nv_bfloat16* Pb
 
 // head dim 128 (bwd_tc128.cu)
 cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, int* status, cudaStream_t stream);
-cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt, __nv_bfloat16* dKt, int* status, cudaStream_t stream);
+cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt, __nv_bfloat16* dKt, int* status, int with_dv,
+                                  int key_lo, int key_hi, cudaStream_t stream);
 
 // Work assignment of the dK/dV kernels (grid: key tiles x heads x batch).  (batch, head)-major: the key tiles
 // of one (batch, head) run side by side and share its Q / dO stream in L2 (a fully length-major order was 7 %
@@ -60,7 +64,7 @@ __device__ __forceinline__ void dkdv_block_order(int BK, int& h, int& b, int& j0
   int bhl, kt;
   if (lin < head_ctas) { bhl = lin / nKT; kt = lin - bhl * nKT; }
   else { const int r = lin - head_ctas; kt = r / X; bhl = nBH - X + (r - kt * X); }
-  j0 = kt * BK;
+  j0 = kt * BK;                                               // + the window's first key, added by the caller
   h = bhl % (int)gridDim.y; b = bhl / (int)gridDim.y;
 }
 #endif

@@ -89,14 +89,14 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
   const int band = pq + pk;
-  const int nQB = (N + OWN - 1) / OWN;
+  const int nQB = (p.row_end - p.row_base + OWN - 1) / OWN;
   // length-major walk of the linear block order (longest row blocks first), as in the d = 64 kernel
   const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   const int nBH = gridDim.y * gridDim.z;
   const int qb = nQB - 1 - lin / nBH;
   const int h = (lin % nBH) % (int)gridDim.y, b = (lin % nBH) / (int)gridDim.y;
   const int bh = b * p.H + h;
-  const int R0 = qb * OWN;
+  const int R0 = p.row_base + qb * OWN;                  // the call's window starts at row_base
   const int nKB = (N + BC - 1) / BC;
   int nkb = 0;
   if (p.causal) {
@@ -307,7 +307,7 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(dq_done, (nkb - 1) & 1, s_abort));
     tc::tc_fence_after();
     const bool have = (nkb > 0) && ok;
-    const bool store = row_ok && (m < OWN);
+    const bool store = row_ok && (m < OWN) && (gi < p.row_end);
     float* orow = p.dQ + ((size_t)bh * N + (row_ok ? gi : 0)) * D + 64 * cg;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
@@ -417,6 +417,7 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int band = pq + pk;
   int h, b, j0;
   dkdv_block_order(BK, h, b, j0);          // (batch, head)-major, key-tile-major tail
+  j0 += p.key_base;
   const int bh = b * p.H + h;
   const int nQB = (N + BR - 1) / BR;
   const int qb_begin = p.causal ? min(nQB, (j0 + band) / BR) : 0;
@@ -751,17 +752,18 @@ cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, i
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dQ = p.dQ; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
+  bp.row_base = win_lo(p); bp.row_end = win_hi(p);
   auto kern = bwd_dq_tc128_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.N + Cfg::OWN - 1) / Cfg::OWN, p.H, p.B);
+  dim3 grid((bp.row_end - bp.row_base + Cfg::OWN - 1) / Cfg::OWN, p.H, p.B);
   { ScopedKernelTimer timer_(kKernBwdDqTc, stream);
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, p.dO, bp); }
   return cudaGetLastError();
 }
 
-cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt, __nv_bfloat16* dKt, int* status,
-                                  cudaStream_t stream) {
+cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt, __nv_bfloat16* dKt, int* status, int with_dv,
+                                  int key_lo, int key_hi, cudaStream_t stream) {
   using Cfg = Dkv128Cfg;
   constexpr int D = Cfg::D;
   const size_t BH = (size_t)p.B * p.H;
@@ -773,12 +775,13 @@ cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt,
   BwdTcParams bp = {};
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dV = p.dV; bp.dKt = dKt; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
-  bp.tap0 = 0; bp.ntap = p.cq; bp.with_dv = 1;
+  bp.tap0 = 0; bp.ntap = p.cq; bp.with_dv = with_dv;
+  bp.key_base = key_lo;
   bp.selftest_expire = take_selftest_expire(kKernBwdDkdvTc);
   auto kern = bwd_dkdv_tc128_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.N + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
+  dim3 grid((key_hi - key_lo + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
   return cudaGetLastError();
 }

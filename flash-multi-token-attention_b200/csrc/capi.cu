@@ -153,10 +153,18 @@ size_t fmta_workspace_bytes(int op, int B, int H, int N, int d, int cq, int ck, 
   return 0;
 }
 
+// A window [lo, hi) of sequence positions: starts on a multiple of 256 (the rows of one CTA of the forward
+// kernel, and a multiple of every other kernel's tile start) and ends on one or at N.
+static int check_window(int lo, int hi, int N) {
+  if (lo < 0 || hi <= lo || hi > N) return FMTA_ERR_SHAPE;
+  if (lo % 256 != 0 || (hi % 256 != 0 && hi != N)) return FMTA_ERR_SHAPE;
+  return FMTA_OK;
+}
+
 static int fwd_impl(const void* Q, const void* K, const void* V, const float* theta, const float* wmix,
                     void* O, float* M, float* L, float* LSE, int B, int H, int N, int d, int cq, int ck,
                     int G, float scale, int causal, int o_dtype, int path, void* workspace,
-                    size_t workspace_bytes, void* stream, void* ktilde) {
+                    size_t workspace_bytes, void* stream, void* ktilde, int row_lo = 0, int row_hi = 0) {
   if (!Q || !K || !V || !O) return FMTA_ERR_NULL;
   if (ktilde && !aligned16(ktilde)) return FMTA_ERR_ALIGN;
   if (int s = check_train_dims(B, H, N, d, cq, ck, G, theta != nullptr, wmix != nullptr)) return s;
@@ -184,6 +192,11 @@ static int fwd_impl(const void* Q, const void* K, const void* V, const float* th
   }
   if (ktilde && !use_tc) return FMTA_ERR_UNSUPPORTED;   // only the tensor-core path makes the stacked key operand
   p.Kt_ext = reinterpret_cast<__nv_bfloat16*>(ktilde);
+  if (row_hi > 0) {                                      // a window of rows: tensor-core path only
+    if (int s = check_window(row_lo, row_hi, N)) return s;
+    if (!use_tc) return FMTA_ERR_UNSUPPORTED;
+    p.row_lo = row_lo; p.row_hi = row_hi;
+  }
   if (use_tc) {
     // stacked tensor-core kernel off the causal band, then the band kernel, which continues the
     // online softmax from the un-normalised partial and writes the final O, M, L
@@ -289,7 +302,8 @@ int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, c
 static int bwd_impl(const void* Q, const void* K, const void* V, const void* dO, const float* D,
                     const float* LSE, const float* theta, const float* wmix, float* dQ, float* dK, float* dV,
                     float* dTheta, float* dW, int B, int H, int N, int d, int cq, int ck, int G, float scale,
-                    int causal, int path, void* workspace, size_t workspace_bytes, void* stream, const void* ktilde) {
+                    int causal, int path, void* workspace, size_t workspace_bytes, void* stream, const void* ktilde,
+                    int row_lo = 0, int row_hi = 0) {
   TrainParams p = {};
   if (ktilde && !aligned16(ktilde)) return FMTA_ERR_ALIGN;
   if (int s = fill_bwd(p, Q, K, V, dO, D, LSE, theta, wmix, B, H, N, d, cq, ck, G, scale, causal)) return s;
@@ -329,14 +343,19 @@ static int bwd_impl(const void* Q, const void* K, const void* V, const void* dO,
   // tensor-core kernels for the entries off the causal band, then the band kernel adds its part
   p.Kt_ext = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(ktilde));   // the forward's stacked key operand, kept by the caller
   p.kt_valid = ktilde != nullptr;
-  slots_ex = bwd_band_theta_slots(B, N, p.cq, p.ck);            // one dTheta partial per band CTA
-  const int slots_tc = bwd_tc_theta_slots(B, N, d);
+  int Nw = N;                                                   // positions this call owns
+  if (row_hi > 0) {
+    if (int s = check_window(row_lo, row_hi, N)) return s;
+    p.row_lo = row_lo; p.row_hi = row_hi; Nw = row_hi - row_lo;
+  }
+  slots_ex = bwd_band_theta_slots(B, Nw, p.cq, p.ck);           // one dTheta partial per band CTA
+  const int slots_tc = bwd_tc_theta_slots(B, Nw, d);
   float* part = reinterpret_cast<float*>(workspace);
   const size_t part_bytes = ((size_t)(slots_ex + slots_tc) * n_theta * sizeof(float) + 1023) / 1024 * 1024;
   void* tcw = reinterpret_cast<unsigned char*>(workspace) + part_bytes;
   // with the larger workspace of FMTA_OP_BWD_TC_STREAM (head dim 64) the dQ kernel leaves P and dC in global
   // memory and the dK/dV kernel streams them instead of recomputing them
-  const bool keep_pdc = (d == 64) &&
+  const bool keep_pdc = (d == 64) && row_hi == 0 &&
       workspace_bytes >= fmta_workspace_bytes(FMTA_OP_BWD_TC_STREAM, B, H, N, d, p.cq, p.ck, p.G);
   if (int s = check_cuda(launch_bwd_dq_tc(p, tcw, keep_pdc, st))) return s;
   if (int s = check_cuda(launch_bwd_dkdv_tc(p, tcw, part + (size_t)slots_ex * n_theta, keep_pdc, st))) return s;
@@ -365,6 +384,25 @@ int fmta_bwd_with_ktilde(const void* Q, const void* K, const void* V, const void
   if (!ktilde || !theta) return FMTA_ERR_NULL;
   return bwd_impl(Q, K, V, dO, D, LSE, theta, nullptr, dQ, dK, dV, dTheta, nullptr, B, H, N, d, cq, ck, 1, scale, causal, 1,
                   workspace, workspace_bytes, stream, ktilde);
+}
+
+int fmta_fwd_window(const void* Q, const void* K, const void* V, const float* theta, void* O, float* M, float* L,
+                    float* LSE, int B, int H, int N, int d, int cq, int ck, float scale, int causal, int o_dtype,
+                    int row_lo, int row_hi, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!theta) return FMTA_ERR_NULL;
+  if (row_hi <= 0) return FMTA_ERR_SHAPE;
+  return fwd_impl(Q, K, V, theta, nullptr, O, M, L, LSE, B, H, N, d, cq, ck, 1, scale, causal, o_dtype, 1, workspace,
+                  workspace_bytes, stream, nullptr, row_lo, row_hi);
+}
+
+int fmta_bwd_window(const void* Q, const void* K, const void* V, const void* dO, const float* D, const float* LSE,
+                    const float* theta, float* dQ, float* dK, float* dV, float* dTheta, int B, int H, int N, int d,
+                    int cq, int ck, float scale, int causal, int row_lo, int row_hi, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  if (!theta) return FMTA_ERR_NULL;
+  if (row_hi <= 0) return FMTA_ERR_SHAPE;
+  return bwd_impl(Q, K, V, dO, D, LSE, theta, nullptr, dQ, dK, dV, dTheta, nullptr, B, H, N, d, cq, ck, 1, scale, causal, 1,
+                  workspace, workspace_bytes, stream, nullptr, row_lo, row_hi);
 }
 
 static int decode_impl(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,

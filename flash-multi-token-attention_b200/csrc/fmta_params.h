@@ -29,6 +29,8 @@ struct TrainParams {
   float* dW_part;            // [n_slots, H/G, G*G]
   __nv_bfloat16* Kt_ext;     // tensor-core path: caller-owned stacked key operand [B,H,cq,N,d] instead of the workspace's (nullptr: none)
   int kt_valid;              //   ... which already holds the operand of these K / theta / scale: the pre-pass is skipped
+  int row_lo, row_hi;        // tensor-core path: the window of sequence positions this call computes (output rows of the
+                             //   forward; dQ rows, dK / dV keys and the dTheta terms of the backward); 0, 0 = the whole sequence
   float* xchg;               // conv + mix cluster kernels: optional global scratch, 2 sets x 2 * kMixXchFloats floats per CTA (nullptr: exchange through distributed shared memory)
   int B, H, N, d, cq, ck, G;
   float scale;
@@ -36,6 +38,10 @@ struct TrainParams {
   int o_bf16;
   int n_slots;
 };
+
+// The window of a call: [win_lo(p), win_hi(p))
+__host__ __device__ inline int win_lo(const TrainParams& p) { return p.row_hi > 0 ? p.row_lo : 0; }
+__host__ __device__ inline int win_hi(const TrainParams& p) { return p.row_hi > 0 ? p.row_hi : p.N; }
 
 // One exchanged tile of the conv + mix cluster kernels: the backward's 80 x 84 fp32 region (the forward's 64 x 68 tile fits)
 constexpr int kMixXchFloats = 80 * 84;

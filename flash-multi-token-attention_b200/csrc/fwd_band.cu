@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(FwdBandCfg<D>::NT, 2) fwd_band_kernel(const Tr
   const int W = band > 0 ? band + pk : 0;
   const int h = blockIdx.y, b = blockIdx.z;
   const size_t bh = (size_t)b * H + h;
-  const int t0 = blockIdx.x * R;
+  const int t0 = win_lo(p) + blockIdx.x * R;          // a window starts on a multiple of R
   const int koff = (band > 16) ? 32 : 16;             // the P tile of 16 rows starts koff keys before them
 
   if (band > 0) {
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(FwdBandCfg<D>::NT, 2) fwd_band_kernel(const Tr
 template <int D>
 static cudaError_t launch_fwd_band_t(const TrainParams& p, cudaStream_t stream) {
   using Cfg = FwdBandCfg<D>;
-  dim3 grid((p.N + Cfg::R - 1) / Cfg::R, p.H, p.B);
+  dim3 grid((win_hi(p) - win_lo(p) + Cfg::R - 1) / Cfg::R, p.H, p.B);
   if (p.cq == 6 && p.ck == 11)
     return launch_kernel<TrainParams>(fwd_band_kernel<D, 6, 11>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
   if (p.cq == 7 && p.ck == 7)

@@ -129,6 +129,7 @@ struct TcParams {
   float* Lpart;
   int* status;    // device word: set non-zero when a bounded wait expired
   int H, N, cq, ck, causal;
+  int qb_hi;      // the grid covers the row blocks [qb_hi - gridDim.x, qb_hi) (all of them unless the call has a window)
   int selftest_expire;   // failure-detection self-test: the softmax warps' first wait is on a barrier nothing arrives at
 };
 
@@ -204,7 +205,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   // longest row block first) so that the greedy hardware scheduler ends with the short CTAs
   const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   const int nBH = gridDim.y * gridDim.z;
-  const int qb = nQB - 1 - lin / nBH;
+  const int qb = p.qb_hi - 1 - lin / nBH;
   const int h = (lin % nBH) % (int)gridDim.y, b = (lin % nBH) / (int)gridDim.y;
   const int bh = b * p.H + h;
   const int i0 = qb * NT * BM;
@@ -583,7 +584,9 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
   auto kern = fwd_tc_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.N + Cfg::NT * Cfg::BM - 1) / (Cfg::NT * Cfg::BM), p.H, p.B);
+  constexpr int RB = Cfg::NT * Cfg::BM;                           // rows per CTA; a window starts on a multiple of it
+  tp.qb_hi = (win_hi(p) + RB - 1) / RB;
+  dim3 grid(tp.qb_hi - win_lo(p) / RB, p.H, p.B);
   { ScopedKernelTimer timer_(kKernFwdTc, stream);
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, tp); }
   return cudaGetLastError();

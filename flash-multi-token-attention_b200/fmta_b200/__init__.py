@@ -16,5 +16,8 @@ from .head_conv import (HeadConvAttentionFunction, HeadConvAttention, head_conv_
                         head_conv_attention_bwd_dkdv, conv_headmix_attention, conv_headmix_forward,
                         conv_headmix_bwd_dq_dw, conv_headmix_bwd_dkdv, conv_headmix_backward)
 from . import sharding  # noqa: F401
+from . import context_parallel  # noqa: F401
+from .context_parallel import (ContextParallelConvAttentionFunction, context_parallel_conv_attention,  # noqa: F401
+                               forward_window, backward_window, windows_for_rank)
 
 __version__ = "0.1.0"

@@ -196,6 +196,28 @@ int fmta_bwd_with_ktilde(const void* Q, const void* K, const void* V, const void
                          size_t workspace_bytes, const void* ktilde, void* stream);
 
 /*
+ * One window of sequence positions of a forward / backward (no counterpart in the reference, which has no
+ * sequence parallelism): the building block of context-parallel training and prefill, where every GPU holds the
+ * whole Q, K, V (dO, D, LSE) of its (batch, head) pairs -- gathered over NVLink -- and computes one or two
+ * windows of the sequence.  [row_lo, row_hi) starts on a multiple of 256 and ends on one or at N.
+ *   fmta_fwd_window: writes O, M, L, LSE of the query rows in the window and touches no other row.  Reads Q from
+ *     row_lo - pad_q on and, with a causal mask, K and V up to row_hi + pad_k.
+ *   fmta_bwd_window: writes dQ of the query rows in the window, dK and dV of the KEYS in the window (each from all
+ *     the query rows that see them, so D and LSE must be complete), and in dTheta the window's share: the shares of
+ *     disjoint windows that cover [0, N) add up to the dTheta of fmta_bwd.  No other row of dQ, dK, dV is touched.
+ * Tensor-core path only (theta given, the shapes of fmta_fwd / fmta_bwd with path = 1), with the workspace of the
+ * whole problem (FMTA_OP_FWD_TC / FMTA_OP_BWD_TC).  The windows of one sequence computed one after the other into the
+ * same buffers give the results of fmta_fwd / fmta_bwd (dQ to rounding: its row tiles start at the window).
+ */
+int fmta_fwd_window(const void* Q, const void* K, const void* V, const float* theta, void* O, float* M, float* L,
+                    float* LSE, int B, int H, int N, int d, int cq, int ck, float scale, int causal, int o_dtype,
+                    int row_lo, int row_hi, void* workspace, size_t workspace_bytes, void* stream);
+int fmta_bwd_window(const void* Q, const void* K, const void* V, const void* dO, const float* D, const float* LSE,
+                    const float* theta, float* dQ, float* dK, float* dV, float* dTheta, int B, int H, int N, int d,
+                    int cq, int ck, float scale, int causal, int row_lo, int row_hi, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/*
  * Decode: last query row over a KV cache with split-K.  Replaces
  * `forward_inference(Q,K,V,conv_kernel,k_splits,scale,pad_q,pad_k,causal,num_k_blocks) ->
  * (O_splits,M_splits,L_splits)` (conv_attn/fwd_inference_bindings.cpp:20-23,

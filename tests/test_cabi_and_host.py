@@ -168,3 +168,108 @@ def test_sharded_backward_matches_unsharded_gloo_world2(tmp_path):
     outs = [p.communicate(timeout=240)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
     assert all("OK" in o for o in outs)
+
+
+def test_context_parallel_windows_partition_the_sequence():
+    from fmta_b200 import context_parallel as cp
+    for N, W, layout in ((4096, 1, "zigzag"), (4096, 2, "zigzag"), (65536, 8, "zigzag"), (8192, 4, "contiguous")):
+        plan = [cp.windows_for_rank(N, W, r, layout) for r in range(W)]
+        seen = torch.zeros(N, dtype=torch.int32)
+        for wins in plan:
+            assert sum(hi - lo for lo, hi in wins) == N // W
+            for lo, hi in wins:
+                assert lo % cp.ALIGN == 0 and hi % cp.ALIGN == 0
+                seen[lo:hi] += 1
+        assert bool((seen == 1).all())
+        if layout == "zigzag" and W > 1:
+            # a causal forward costs about (rows x mean key count); the zigzag shares are equal to one chunk's worth
+            cost = [sum((hi - lo) * (lo + hi) / 2 for lo, hi in wins) for wins in plan]
+            assert max(cost) - min(cost) <= 1e-9 * max(cost)
+        # gather_sequence / take_local are inverse to each other (one rank: no process group needed)
+        full = torch.arange(N, dtype=torch.float32).view(1, 1, N, 1).expand(1, 2, N, 3).contiguous()
+        for r in range(W):
+            loc = cp.take_local(full, plan[r])
+            at = 0
+            for lo, hi in plan[r]:
+                assert torch.equal(loc[:, :, at:at + hi - lo], full[:, :, lo:hi])
+                at += hi - lo
+    for bad in ((1000, 2, "zigzag"), (4096, 3, "contiguous"), (4096, 2, "ring")):
+        with pytest.raises(ValueError):
+            cp.windows_for_rank(*bad[:2], 0, bad[2])
+
+
+def test_window_entry_points_validate_on_the_host():
+    from fmta_b200._lib import lib
+    P = ctypes.c_void_p
+    good = P(0x1000)
+    fw = lambda lo, hi, N=1024, d=64: lib.fmta_fwd_window(good, good, good, good, good, None, None, None, 1, 1, N, d, 3, 3,
+                                                          1.0, 1, 0, lo, hi, None, 0, None)
+    bw = lambda lo, hi, N=1024, d=64: lib.fmta_bwd_window(good, good, good, good, good, good, good, good, good, good, good,
+                                                          1, 1, N, d, 3, 3, 1.0, 1, lo, hi, None, 0, None)
+    for f in (fw, bw):
+        assert f(0, 0) == -2                       # a window is required
+        assert f(0, 512, d=32) == -3               # tensor-core shapes only
+    assert lib.fmta_fwd_window(good, good, good, None, good, None, None, None, 1, 1, 1024, 64, 3, 3, 1.0, 1, 0, 0, 512,
+                               None, 0, None) == -1
+
+
+_CP_WORKER = r'''
+import math, os, sys, datetime, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[2])
+from fmta_b200 import context_parallel as cp
+from oracle import conv_attn_oracle as orc
+rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=ws, timeout=datetime.timedelta(seconds=120))
+
+# the oracle stands in for the CUDA window calls, so that the gathers, the window bookkeeping and the all-reduce
+# of the filter gradient run on CPU ranks
+def fwd_window(Q, K, V, th, scale, pq, pk, causal, lo, hi, out=None):
+    O, M, L = orc.conv_attn_fwd(Q.float(), K.float(), V.float(), th, scale, causal)
+    if out is None:
+        out = (torch.full_like(O, float("nan")),) + tuple(torch.full_like(M, float("nan")) for _ in range(3))
+    for dst, src in zip(out, (O, M, L, M + torch.log(L))):
+        dst[:, :, lo:hi] = src[:, :, lo:hi]
+    return out
+def bwd_window(Q, K, V, dO, D, L, th, scale, pq, pk, causal, lo, hi, out=None):
+    with torch.enable_grad():                      # called from inside an autograd backward
+        g = orc.conv_attn_bwd_autograd(Q.float(), K.float(), V.float(), th.detach(), dO.float(), scale, causal)
+    if out is None:
+        out = tuple(torch.full_like(g[0], float("nan")) for _ in range(3))
+    for dst, src in zip(out, g[:3]):
+        dst[:, :, lo:hi] = src[:, :, lo:hi]
+    return out + (g[3] * ((hi - lo) / Q.shape[2]),)       # shares that add up to the whole gradient
+cp.forward_window, cp.backward_window = fwd_window, bwd_window
+cp._rowdot = lambda dO, O: (dO.float() * O.float()).sum(-1)
+
+B, H, N, d, cq, ck = 1, 2, 1024, 16, 3, 5
+Q, K, V, dO, th = orc.make_inputs(B, H, N, d, cq, ck, seed=4, dtype=torch.bfloat16)
+scale = 1.0 / math.sqrt(d)
+Or, _, _ = orc.conv_attn_fwd(Q, K, V, th, scale, True)
+gr = orc.conv_attn_bwd_autograd(Q, K, V, th, dO, scale, True)
+for layout in ("zigzag", "contiguous"):
+    wins = cp.windows_for_rank(N, ws, rank, layout)
+    ql, kl, vl = (cp.take_local(t, wins).requires_grad_() for t in (Q, K, V))
+    t1 = th.clone().requires_grad_()
+    Ol = cp.context_parallel_conv_attention(ql, kl, vl, t1, scale, cq - 1, (ck - 1) // 2, True, None, layout)
+    Ol.backward(cp.take_local(dO, wins))
+    assert float((Ol.detach() - cp.take_local(Or, wins)).abs().max()) <= 1e-5
+    for a, b in ((ql.grad, gr[0]), (kl.grad, gr[1]), (vl.grad, gr[2])):
+        assert float((a - cp.take_local(b, wins)).abs().max()) <= 1e-4
+    assert float((t1.grad - gr[3]).abs().max()) <= 1e-3 * float(gr[3].abs().max())
+dist.destroy_process_group()
+print("OK", rank)
+'''
+
+
+def test_context_parallel_plumbing_gloo_world2(tmp_path):
+    """Two CPU ranks hold zigzag / contiguous shares of one sequence; the gathers, the window bookkeeping and the
+    all-reduce of the filter gradient run for real, the window computation is the oracle."""
+    script = tmp_path / "cp_worker.py"
+    script.write_text(_CP_WORKER)
+    pkg = os.path.join(ROOT, "flash-multi-token-attention_b200")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29537", WORLD_SIZE="2", OMP_NUM_THREADS="2")
+    procs = [subprocess.Popen([sys.executable, str(script), pkg, ROOT], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+    assert all("OK" in o for o in outs)
