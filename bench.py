@@ -273,6 +273,7 @@ def main():
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated (median reported)")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--cp-shape", default=None, help="B,H,N,d of the sequence-sharded problem (default 1,4,65536,128)")
     ap.add_argument("--no-headmix", action="store_true")
     ap.add_argument("--no-keep-ktilde", action="store_true",
                     help="let forward and backward each build the stacked key operand (the reference-shaped pair of calls)")
@@ -502,6 +503,14 @@ def main():
             line["sweep"] = dict(error="out of memory: %s" % str(e)[:80])
         F.check_device_status(dev)
 
+    # ---- one long sequence with fewer (batch, head) pairs than GPUs: sharded along the sequence ----
+    if not args.no_sweep and not args.small and not args.train_shape:
+        try:
+            line["context_parallel"] = bench_context_parallel(F, dev, world, rank, peaks, timed, args.cp_shape)
+        except torch.OutOfMemoryError as e:   # pragma: no cover
+            line["context_parallel"] = dict(error="out of memory: %s" % str(e)[:80])
+        F.check_device_status(dev)
+
     # ---- head mixing: the reference's head-conv operator (no conv) and the composed conv + mix configuration ----
     if not args.no_headmix and not args.small and not args.train_shape:
         try:
@@ -594,6 +603,50 @@ def bench_sweep(F, dev, world, rank, peaks, barrier, max_n):
                                      "sharded by (batch, head)" % (B, H, d, cq, ck), shard_mode=plan["mode"],
                             collective="all-reduce of dTheta [H,%d,%d] fp32 (NCCL)" % (cq, ck) if world > 1 else "none"),
                 peak=peaks["tflops_sustained"], peak_source=peaks["source"] + " (sustained)", points=points)
+
+
+def bench_context_parallel(F, dev, world, rank, peaks, timed, shape=None):
+    """One fixed problem with few (batch, head) pairs and a long sequence (default B=1,H=4,N=65536,d=128,
+    theta (6,11), causal), sharded along the SEQUENCE: every rank holds the zigzag share of the positions and calls
+    `context_parallel_conv_attention` (gathers of Q, K, V, dO, D, LSE over the process group, the rank's windows on
+    its GPU, one all-reduce of dTheta).  A step is forward + backward through the autograd Function, gathers
+    included; strong scaling.  TFLOP/s by the headline's convention."""
+    from fmta_b200 import context_parallel as cp
+    B, H, N, d = tuple(int(x) for x in shape.split(",")) if shape else (1, 4, 65536, 128)
+    cq, ck = 6, 11
+    scale = 1.0 / math.sqrt(d)
+    layout = "zigzag" if N % (2 * world * cp.ALIGN) == 0 else "contiguous"
+    wins = cp.windows_for_rank(N, world, rank, layout)
+    n_loc = sum(hi - lo for lo, hi in wins)
+    g = torch.Generator(device=dev).manual_seed(77)       # the same sequence at every world size
+    ql, kl, vl, dol = (cp.take_local(torch.randn(B, H, N, d, device=dev, generator=g).to(torch.bfloat16), wins) for _ in range(4))
+    gt = torch.Generator(device=dev).manual_seed(5)
+    th = torch.randn(H, cq, ck, device=dev, generator=gt) * 0.02
+    th[:, cq - 1, ck // 2] += 1.0
+    dol32 = dol.float()
+    out = {}
+
+    def step():
+        q, k, v = (t.detach().requires_grad_() for t in (ql, kl, vl))
+        t = th.detach().requires_grad_()
+        O = cp.context_parallel_conv_attention(q, k, v, t, scale, cq - 1, (ck - 1) // 2, True, None, layout)
+        O.backward(dol32)
+        out["dth"] = t.grad
+
+    fl, E = flops_attn(B, H, N, d)
+    step()
+    steps = max(2, min(10, int(1.0 / max(fl / (150e12 * world), 1e-4))))
+    ms = timed(step, steps) / steps
+    tf = fl / (ms * 1e-3) / 1e12
+    gathered = 4 * B * H * N * d * 2 + 2 * B * H * N * 4
+    return dict(metric="conv-attn fwd+bwd TFLOP/s, one sequence sharded along its length", scaling="strong",
+                config=dict(workload="train fwd+bwd bf16 B=%d,H=%d,N=%d,d=%d,theta(%d,%d),causal; %d (batch, head) pairs"
+                                     % (B, H, N, d, cq, ck, B * H), layout=layout, windows_rank0=[list(w) for w in cp.windows_for_rank(N, world, 0, layout)],
+                            collective=("all-gather of Q, K, V, dO (bf16), D, LSE: %.0f MB per rank and step; all-reduce of dTheta (NCCL)"
+                                        % (gathered / 1e6)) if world > 1 else "none"),
+                ms_per_step=ms, steps=steps, value=tf, unit="TFLOP/s", per_gpu_tflops=tf / world,
+                frac_of_peak=tf / world / peaks["tflops_sustained"], flops_attn_tflop=fl / 1e12,
+                dtheta_checksum=float(out["dth"].double().abs().sum().item()))
 
 
 def bench_headmix(F, dev, timed, shape=None, convmix_shape=None):

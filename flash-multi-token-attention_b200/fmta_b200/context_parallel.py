@@ -142,6 +142,39 @@ def backward_window(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal,
     return dQ, dK, dV, dTheta
 
 
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device, i):
+    key = (device.index if device.index is not None else torch.cuda.current_device(), i)
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device)
+    return _SIDE_STREAMS[key]
+
+
+def _on_streams(windows, fn, device):
+    """``fn(i, lo, hi)`` for every window; on a GPU the second window runs on a side stream, so that its CTAs fill
+    the SMs the first window's last wave leaves idle (the windows write disjoint rows and have their own workspaces).
+    Returns the results in window order."""
+    if len(windows) < 2 or device.type != "cuda":
+        return [fn(i, lo, hi) for i, (lo, hi) in enumerate(windows)]
+    main = torch.cuda.current_stream(device)
+    res = [None] * len(windows)
+    sides = []
+    for i, (lo, hi) in enumerate(windows):
+        if i == 0:
+            continue
+        side = _side_stream(device, i)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            res[i] = fn(i, lo, hi)
+        sides.append(side)
+    res[0] = fn(0, *windows[0])
+    for side in sides:
+        main.wait_stream(side)
+    return res
+
+
 def _rowdot(dO, O):
     from .conv_attn import rowdot
     return rowdot(dO, O)
@@ -162,9 +195,11 @@ class ContextParallelConvAttentionFunction(torch.autograd.Function):
         N = q.shape[2] * world
         plan = [windows_for_rank(N, world, r, layout) for r in range(world)]
         Qf, Kf, Vf = (gather_sequence(t.to(torch.bfloat16), plan, group) for t in (q, k, v))
-        out = None
-        for lo, hi in plan[rank]:
-            out = forward_window(Qf, Kf, Vf, conv_kernel, scale, pad_q, pad_k, causal, lo, hi, out=out)
+        B, H, _, d = Qf.shape
+        out = (torch.empty((B, H, N, d), dtype=torch.float32, device=Qf.device),) + tuple(
+            torch.empty((B, H, N), dtype=torch.float32, device=Qf.device) for _ in range(3))
+        _on_streams(plan[rank], lambda i, lo, hi: forward_window(Qf, Kf, Vf, conv_kernel, scale, pad_q, pad_k, causal,
+                                                                 lo, hi, out=out), Qf.device)
         o_loc, lse_loc = take_local(out[0], plan[rank]), take_local(out[3], plan[rank])
         ctx.save_for_backward(Qf, Kf, Vf, conv_kernel, o_loc, lse_loc)
         ctx.args = (scale, pad_q, pad_k, causal, group, plan, rank)
@@ -179,11 +214,12 @@ class ContextParallelConvAttentionFunction(torch.autograd.Function):
         d_loc = _rowdot(do_b, o_loc)                                  # D of the local rows
         dOf = gather_sequence(do_b, plan, group)
         Df, LSEf = gather_sequence(d_loc, plan, group), gather_sequence(lse_loc, plan, group)
-        out, dth = None, None
-        for lo, hi in plan[rank]:
-            res = backward_window(Qf, Kf, Vf, dOf, Df, LSEf, conv_kernel, scale, pad_q, pad_k, causal, lo, hi, out=out)
-            out = res[:3]
-            dth = res[3] if dth is None else dth + res[3]
+        out = tuple(torch.empty(Qf.shape, dtype=torch.float32, device=Qf.device) for _ in range(3))
+        res = _on_streams(plan[rank], lambda i, lo, hi: backward_window(Qf, Kf, Vf, dOf, Df, LSEf, conv_kernel, scale, pad_q,
+                                                                        pad_k, causal, lo, hi, out=out), Qf.device)
+        dth = res[0][3]
+        for r in res[1:]:
+            dth = dth + r[3]
         if len(plan) > 1:
             dist.all_reduce(dth, group=group)
         tq, tk, tv = ctx.in_dtypes
