@@ -100,7 +100,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int N = p.N, cq = p.cq, pq = cq - 1, pk = (p.ck - 1) / 2;
   const int band = pq + pk;
   const int rows_per_cta = OWN * NT;
-  const int nQB = (p.row_end - p.row_base + rows_per_cta - 1) / rows_per_cta;
+  const int nQB = (p.row_anchor - p.row_base + rows_per_cta - 1) / rows_per_cta;
   // CTAs are dispatched in linear block order; walk it length-major (all (batch, head) pairs of the
   // longest row block first) so that the greedy hardware scheduler ends with the short CTAs
   const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
@@ -108,13 +108,18 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int qb = nQB - 1 - lin / nBH;
   const int h = (lin % nBH) % (int)gridDim.y, b = (lin % nBH) / (int)gridDim.y;
   const int bh = b * p.H + h;
-  const int R0 = p.row_base + qb * rows_per_cta;
+  // The row blocks are laid out from the END of the rows: when their number is not a multiple of the block, the
+  // partly filled block is the first one, which sees the fewest keys, not the last one, which sees them all
+  // (N = 4096: the 18th block of 240 rows held 16 rows and walked every key block).  Its rows before row_base are
+  // computed (negative rows as zero rows) and not stored.  The variant that leaves P and dC for the streaming dK/dV
+  // kernel needs blocks that start at multiples of 8 rows: its anchor is row_end rounded up to one.
+  const int R0 = p.row_anchor - (nQB - qb) * rows_per_cta;
   const int nKB = (N + BC - 1) / BC;
   int nkb_t[2] = {0, 0};
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
     const int r0 = R0 + t * OWN;
-    if (r0 >= p.row_end) nkb_t[t] = 0;
+    if (r0 >= p.row_end || r0 + OWN <= p.row_base) nkb_t[t] = 0;
     else if (p.causal) {
       const int last = min(N - 1, r0 + BM - 1) - band;
       nkb_t[t] = last >= 0 ? min(nKB, last / BC + 1) : 0;
@@ -249,7 +254,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const int r0 = R0 + t * OWN, r1 = min(N, r0 + OWN);
                 const int nkb64 = p.ldp >> 6;
                 const uint64_t pol_ef = tc::l2_policy_evict_first();
-                for (int g = r0; g < r1;) {
+                for (int g = max(r0, 0); g < r1;) {
                   const int gend = min(r1, (g | 63) + 1);
                   const size_t tile = (((size_t)bh * ((N + 63) >> 6) + (g >> 6)) * nkb64 + kb) * 4096 + (size_t)(g & 63) * 64;
                   tc::bulk_store_hint(p.Pout + tile, smem + Cfg::oP + t * Cfg::P_BYTES + (g - r0) * 128, (uint32_t)(gend - g) * 128, pol_ef);
@@ -300,7 +305,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + t * 256 + lane_base, tP = tS + 128, tQ = tS + 192;
     const int my_nkb = nkb_t[t];
-    const bool row_ok = gi < N;
+    const bool row_ok = gi >= 0 && gi < N;
     const float lse2 = row_ok ? p.LSE[(size_t)bh * N + gi] * kLog2e : 0.f;
     const float dvec = row_ok ? p.Dvec[(size_t)bh * N + gi] : 0.f;
     unsigned char* ctile = sdC + t * Cfg::DC_BYTES;     // this tile's dC buffer; chunk c of row r at r*128 + ((c ^ (r & 7)) << 4)
@@ -384,7 +389,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (my_nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&dq_done[t], (my_nkb - 1) & 1, s_abort));
     tc::tc_fence_after();
     const bool have = (my_nkb > 0) && ok;
-    const bool store = row_ok && (m < OWN) && (gi < p.row_end);
+    const bool store = row_ok && (m < OWN) && (gi >= p.row_base) && (gi < p.row_end);
     float* orow = p.dQ + ((size_t)bh * N + (row_ok ? gi : 0)) * D;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
@@ -1106,8 +1111,9 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pd
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
   bp.row_base = win_lo(p); bp.row_end = win_hi(p);
+  bp.row_anchor = keep_pdc ? (bp.row_end + 7) / 8 * 8 : bp.row_end;
   const int rows_per_cta = Cfg::OWN * Cfg::NT;
-  dim3 grid((bp.row_end - bp.row_base + rows_per_cta - 1) / rows_per_cta, p.H, p.B);
+  dim3 grid((bp.row_anchor - bp.row_base + rows_per_cta - 1) / rows_per_cta, p.H, p.B);
   if (keep_pdc) {
     stream_buffers(p, workspace, &bp.Pout, &bp.dCout, &bp.ldp);
     if (p.N % 64 != 0) zero_tail_rows_kernel<<<dim3(bp.ldp / 64, (unsigned)BH), 128, 0, stream>>>(bp.Pout, bp.dCout, p.N, bp.ldp / 64);

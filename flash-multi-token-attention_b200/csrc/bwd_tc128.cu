@@ -96,7 +96,9 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int qb = nQB - 1 - lin / nBH;
   const int h = (lin % nBH) % (int)gridDim.y, b = (lin % nBH) / (int)gridDim.y;
   const int bh = b * p.H + h;
-  const int R0 = p.row_base + qb * OWN;                  // the call's window starts at row_base
+  // tiles are laid out from the END of the window's rows, so that a partly filled tile is the first one (fewest
+  // keys), not the last one (all keys); its rows before row_base are computed (negative rows as zero rows), not stored
+  const int R0 = p.row_end - (nQB - qb) * OWN;
   const int nKB = (N + BC - 1) / BC;
   int nkb = 0;
   if (p.causal) {
@@ -242,7 +244,7 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int gi = R0 + m;                              // query index of this dC row
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     const uint32_t tS = tmem + lane_base, tP = tS + Cfg::colP, tQ = tS + Cfg::colQ, tO = tS + Cfg::colO;
-    const bool row_ok = gi < N;
+    const bool row_ok = gi >= 0 && gi < N;
     const float lse2 = row_ok ? p.LSE[(size_t)bh * N + gi] * kLog2e : 0.f;
     const float dvec = row_ok ? p.Dvec[(size_t)bh * N + gi] : 0.f;
     unsigned char* cbuf = sdC + m * 16 + cg * (CW / 8) * (DR * 16);
@@ -307,7 +309,7 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (nkb > 0 && ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(dq_done, (nkb - 1) & 1, s_abort));
     tc::tc_fence_after();
     const bool have = (nkb > 0) && ok;
-    const bool store = row_ok && (m < OWN) && (gi < p.row_end);
+    const bool store = row_ok && (m < OWN) && (gi >= p.row_base) && (gi < p.row_end);
     float* orow = p.dQ + ((size_t)bh * N + (row_ok ? gi : 0)) * D + 64 * cg;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
@@ -752,7 +754,7 @@ cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, i
   bp.LSE = p.LSE; bp.Dvec = p.Dvec; bp.dQ = p.dQ; bp.status = status;
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
-  bp.row_base = win_lo(p); bp.row_end = win_hi(p);
+  bp.row_base = win_lo(p); bp.row_end = win_hi(p); bp.row_anchor = bp.row_end;
   auto kern = bwd_dq_tc128_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;

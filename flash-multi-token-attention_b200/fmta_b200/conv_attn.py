@@ -173,10 +173,11 @@ def dkdv_backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal):
 
 
 # The streaming dK/dV kernel (head dim 64) needs 4 * B*H*N*roundup(N,128) bytes for P and dC; it is used when
-# that is at most this many bytes (the recomputing kernel otherwise).  Measured on B200 at N = 4096: 0.54 GB
-# (16 (batch, head) pairs) -- backward 10 % faster; 2.1 GB (64 pairs) -- 1 % (the dQ kernel pays about 0.2 ms per
-# GB it writes, the dK/dV kernel gains about 0.25 ms per GB it no longer recomputes).
-STREAM_LIMIT_BYTES = int(float(os.environ.get("FMTA_STREAM_LIMIT_GB", "1")) * (1 << 30))
+# that is at most this many bytes (the recomputing kernel otherwise).  Off by default (0): since the recomputing pair
+# got its current block order and row-block layout it is the faster one at every size measured on B200 (backward at
+# N = 4096: 8 (batch, head) pairs 0.406 against 0.461 ms streaming, 16 pairs 0.588 against 0.601; N = 1024 and 2048
+# likewise by 4-8 %); ``stream_pdc=True`` or FMTA_STREAM_LIMIT_GB select the streaming pair.
+STREAM_LIMIT_BYTES = int(float(os.environ.get("FMTA_STREAM_LIMIT_GB", "0")) * (1 << 30))
 
 
 def backward(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, path=-1, stream_pdc=None, ktilde=None):
