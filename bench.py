@@ -273,6 +273,7 @@ def main():
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed loop of --steps steps is repeated (median reported)")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-context-parallel", action="store_true")
     ap.add_argument("--cp-shape", default=None, help="B,H,N,d of the sequence-sharded problem (default 1,4,65536,128)")
     ap.add_argument("--no-headmix", action="store_true")
     ap.add_argument("--no-keep-ktilde", action="store_true",
@@ -504,7 +505,7 @@ def main():
         F.check_device_status(dev)
 
     # ---- one long sequence with fewer (batch, head) pairs than GPUs: sharded along the sequence ----
-    if not args.no_sweep and not args.small and not args.train_shape:
+    if not args.no_sweep and not args.no_context_parallel and not args.small and not args.train_shape:
         try:
             line["context_parallel"] = bench_context_parallel(F, dev, world, rank, peaks, timed, args.cp_shape)
         except torch.OutOfMemoryError as e:   # pragma: no cover
