@@ -41,13 +41,14 @@ template <int D, bool STREAM = false>   // STREAM: the kernel also leaves P and 
 struct DqCfg {
   static_assert(D == 64, "the dQ tensor-core kernel is instantiated for d = 64");
   static constexpr int BM = 128;               // dC rows per tile (= TMEM lanes)
-  static constexpr int OWN = 120;              // dQ rows a tile owns (dQ row i needs dC rows i .. i + pad_q, pad_q <= 6)
+  static constexpr int OWN = 120;              // dQ rows a tile owns at most when its rows must start on a multiple of 8 (STREAM); else 128 - pad_q (dQ row i needs dC rows i .. i + pad_q)
+  static constexpr int OWN_MAX = 128;
   static constexpr int BC = 64;                // keys per block
   static constexpr int NT = 2;                 // row tiles per CTA
   static constexpr int HALO = 16;
   // rows of Q staged: 264 are read; the buffer is 272 so that both TMA boxes of QR / 2 rows x 16 bytes land
   // on 128-byte boundaries of shared memory (a tiled TMA copy needs that of its destination)
-  static constexpr int QR = ((HALO + OWN * (NT - 1) + BM + 15) / 16) * 16;
+  static constexpr int QR = ((HALO + OWN_MAX * (NT - 1) + BM + 15) / 16) * 16;
   static_assert((QR / 2 * 16) % 128 == 0, "TMA destination alignment");
   static constexpr int DR = BM + 16;           // rows of a dC buffer (16 zero rows below)
   static constexpr int TILE_BYTES = BC * 128;  // Kt / V ring tile: 64 keys x 64 elements
@@ -74,7 +75,8 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmKt, const __grid_constant__ CUtensorMap tmV,
                  const BwdTcParams p) {
   using Cfg = DqCfg<D, STREAM>;
-  constexpr int BM = Cfg::BM, OWN = Cfg::OWN, BC = Cfg::BC, NT = Cfg::NT, HALO = Cfg::HALO, QR = Cfg::QR;
+  constexpr int BM = Cfg::BM, BC = Cfg::BC, NT = Cfg::NT, HALO = Cfg::HALO, QR = Cfg::QR;
+  const int OWN = STREAM ? Cfg::OWN : p.own;
   constexpr int DR = Cfg::DR, NSLOT = Cfg::NSLOT;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1112,7 +1114,8 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pd
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
   bp.row_base = win_lo(p); bp.row_end = win_hi(p);
   bp.row_anchor = keep_pdc ? (bp.row_end + 7) / 8 * 8 : bp.row_end;
-  const int rows_per_cta = Cfg::OWN * Cfg::NT;
+  bp.own = keep_pdc ? Cfg::OWN : Cfg::BM - (p.cq - 1);
+  const int rows_per_cta = bp.own * Cfg::NT;
   dim3 grid((bp.row_anchor - bp.row_base + rows_per_cta - 1) / rows_per_cta, p.H, p.B);
   if (keep_pdc) {
     stream_buffers(p, workspace, &bp.Pout, &bp.dCout, &bp.ldp);

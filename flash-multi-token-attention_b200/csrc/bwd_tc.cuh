@@ -26,6 +26,7 @@ struct BwdTcParams {
   // window of the call: the dQ kernel tiles the rows [row_base, row_end) and writes no other row; the dK/dV
   // kernel's key tile 0 starts at key_base (whole sequence: 0, N, 0)
   int row_base, row_end, key_base;
+  int own;          // dQ kernels: dQ rows a tile of 128 dC rows owns (128 - pad_q; 120 where tiles must start on multiples of 8 rows)
   int row_anchor;   // dQ kernels: the row blocks are laid out backwards from this row (row_end, rounded up to a multiple of 8 by the variant that leaves P and dC)
   int selftest_expire;   // failure-detection self-test: the element-wise warps' first wait is on a barrier nothing arrives at
   // dQ kernel (optional outputs): the off-band P and dC = P (dP - D) of every entry, bf16, tile-major

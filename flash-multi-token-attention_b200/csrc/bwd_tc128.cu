@@ -62,7 +62,8 @@ __global__ void __launch_bounds__(Dq128Cfg::kThreads, 1)
 bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKt,
                     const __grid_constant__ CUtensorMap tmV, const bf16* __restrict__ dO, const BwdTcParams p) {
   using Cfg = Dq128Cfg;
-  constexpr int D = Cfg::D, BM = Cfg::BM, OWN = Cfg::OWN, BC = Cfg::BC, HALO = Cfg::HALO, QR = Cfg::QR;
+  constexpr int D = Cfg::D, BM = Cfg::BM, BC = Cfg::BC, HALO = Cfg::HALO, QR = Cfg::QR;
+  const int OWN = p.own;                                 // 128 - pad_q dQ rows per tile of 128 dC rows
   constexpr int DR = Cfg::DR, NSLOT = Cfg::NSLOT;
   constexpr int NEW = Cfg::kEwWarps * 32;      // element-wise threads
   constexpr int W_TMA = Cfg::kEwWarps, W_S = Cfg::kEwWarps + 1, W_DQ = Cfg::kEwWarps + 2;   // warp roles
@@ -755,10 +756,11 @@ cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, i
   bp.H = p.H; bp.N = p.N; bp.cq = p.cq; bp.ck = p.ck; bp.causal = p.causal;
   bp.selftest_expire = take_selftest_expire(kKernBwdDqTc);
   bp.row_base = win_lo(p); bp.row_end = win_hi(p); bp.row_anchor = bp.row_end;
+  bp.own = Cfg::BM - (p.cq - 1);
   auto kern = bwd_dq_tc128_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((bp.row_end - bp.row_base + Cfg::OWN - 1) / Cfg::OWN, p.H, p.B);
+  dim3 grid((bp.row_end - bp.row_base + bp.own - 1) / bp.own, p.H, p.B);
   { ScopedKernelTimer timer_(kKernBwdDqTc, stream);
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, p.dO, bp); }
   return cudaGetLastError();
