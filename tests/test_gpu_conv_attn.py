@@ -123,7 +123,7 @@ def test_rejects_bad_inputs():
 
 @pytest.mark.parametrize("path", [0, 1, 2])
 @pytest.mark.parametrize("B,H,N,d,cq,ck,causal", [
-    (1, 2, 520, 64, 6, 11, True),     # several 240-row dQ tiles and 128-key dK tiles, ragged N
+    (1, 2, 520, 64, 6, 11, True),     # several 246-row dQ blocks (laid out from the last row) and 128-key dK tiles, ragged N
     (2, 1, 300, 64, 3, 5, False),     # no causal band: everything on the tensor-core kernels
     (1, 1, 100, 64, 6, 11, True),     # shorter than one tile
     (1, 2, 400, 64, 6, 17, True),     # wide key filter (W = 21): three key tiles per row tile, FMA output phase
@@ -145,12 +145,14 @@ def test_rejects_bad_inputs():
     (1, 2, 65, 64, 6, 11, True),      # one key into the second tile: its halo rows are mostly past the end
     (1, 2, 129, 64, 7, 17, True),     # the same with the widest filter (halo of 8 rows fully used)
     (1, 1, 130, 64, 1, 3, False),     # one tap, no band
-    # head dim 128: dQ tile of 120 owned rows, 64-key dK/dV CTAs with 128-row query blocks
+    # head dim 128: dQ tile of 128 - pad_q owned rows, 64-key dK/dV CTAs with 128-row query blocks
     (1, 2, 520, 128, 6, 11, True),
     (2, 1, 300, 128, 3, 5, False),    # no causal band: everything on the tensor-core kernels
     (1, 1, 100, 128, 6, 11, True),    # shorter than one tile
-    (1, 1, 120, 128, 6, 11, True),    # exactly the rows one dQ tile owns
-    (1, 1, 121, 128, 6, 11, True),    # one row into the second dQ tile
+    (1, 1, 123, 128, 6, 11, True),    # exactly the rows one dQ tile owns
+    (1, 1, 124, 128, 6, 11, True),    # one row into the second dQ tile
+    (1, 1, 246, 64, 6, 11, True),     # exactly one dQ block of two tiles
+    (1, 1, 247, 64, 6, 11, True),     # one row more: the first block holds that row only
     (1, 2, 257, 128, 1, 3, True),     # single query tap
     (1, 1, 450, 128, 4, 7, True),
     (1, 1, 611, 128, 6, 13, True),    # W = 17
