@@ -484,10 +484,10 @@ def main():
                             l2="inputs+outputs per step (%.0f MB) exceed the 126 MB L2" % ((4 * 2 + 4 * 4) * B * H * N * d / 1e6),
                             stacked_keys="built once per step (forward), kept for the backward" if kt is not None else "built by forward and by backward",
                             flops_attn_gflop=fl / 1e9, flops_conv_gflop=8 * cq * ck * E / 1e9),
-                # kernels of this library per step: forward = stacked-key pre-pass, fwd_tc, status fold, fwd_band;
-                # rowdot; backward = pre-pass (not when the forward's operand is kept), dq_tc, dkdv_tc, Toeplitz tiles + dKt adjoint, status fold, bwd_band,
+                # kernels of this library per step: forward = stacked-key pre-pass, fwd_tc, fwd_band;
+                # rowdot; backward = pre-pass (not when the forward's operand is kept), dq_tc, dkdv_tc, Toeplitz tiles + dKt adjoint, bwd_band,
                 # partial reduction
-                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=(13 if kt is None else 12) * args.steps * len(loops))
+                e2e=e2e, roofline=roof, clocks=clocks, gpu_launches=(11 if kt is None else 10) * args.steps * len(loops))
 
     # ---- decode (HBM-bound), rank-local, reported beside the headline ----
     if not args.no_decode:

@@ -1095,8 +1095,8 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pd
   __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * p.d * 2);
   if (p.Kt_ext) Kt = p.Kt_ext;                        // the stacked key operand kept from the forward
   w += up(rows * p.cq * p.d * 2);
-  int* status = reinterpret_cast<int*>(w);
-  cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  int* status = nullptr;
+  cudaError_t e = status_word_of(reinterpret_cast<int*>(w), stream, &status);
   if (e != cudaSuccess) return e;
   if (!(p.Kt_ext && p.kt_valid)) {
     e = launch_ktilde(p, Kt, stream);
@@ -1173,7 +1173,8 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   __nv_bfloat16* Kt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
   if (p.Kt_ext) Kt = p.Kt_ext;
   __nv_bfloat16* dKt = reinterpret_cast<__nv_bfloat16*>(w); w += up(rows * p.cq * D * 2);
-  int* status = reinterpret_cast<int*>(w);
+  int* status = registered_status_word();               // else the workspace word the dQ launch cleared
+  if (status == nullptr) status = reinterpret_cast<int*>(w);
   cudaError_t e;
   { ScopedKernelTimer timer_(kKernBwdDkdvTc, stream);
     // A call with a window computes dV and dK of its keys [lo, hi).  dK needs dKt of pad_k keys on either side
@@ -1218,9 +1219,7 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   ScopedKernelTimer timer2_(kKernDkPost, stream);
   dk_post_toeplitz_kernel<<<p.H, 256, 0, stream>>>(p.theta, Tg, p.cq, p.ck, p.scale);
   kern<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb, D, j_base);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  return launch_fold_status(status, stream);
+  return cudaGetLastError();
 }
 
 // slots of dTheta partials written by the dKt adjoint kernel: one per CTA

@@ -46,21 +46,21 @@ constexpr int kMaxDevices = 64;
 int* g_status_word[kMaxDevices] = {};   // caller-owned device word per device (fmta_set_status_word)
 int g_selftest_kernel = 0;              // kernel id whose next launch runs the expiry self-test
 
-__global__ void fold_status_kernel(const int* __restrict__ status, int* __restrict__ sink) {
-  if (*status != 0) atomicOr(sink, *status);
-}
 }  // namespace
 
 namespace fmta {
 ProfileHook g_profile_hook = {0, nullptr, nullptr};
 
-cudaError_t launch_fold_status(const int* status, cudaStream_t stream) {
+int* registered_status_word() {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaSuccess;
-  int* sink = g_status_word[dev];
-  if (sink == nullptr) return cudaSuccess;
-  fold_status_kernel<<<1, 1, 0, stream>>>(status, sink);
-  return cudaGetLastError();
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  return g_status_word[dev];
+}
+
+cudaError_t status_word_of(int* ws_word, cudaStream_t stream, int** word) {
+  if (int* reg = registered_status_word()) { *word = reg; return cudaSuccess; }
+  *word = ws_word;
+  return cudaMemsetAsync(ws_word, 0, sizeof(int), stream);
 }
 
 int take_selftest_expire(int kernel_id) {

@@ -617,14 +617,13 @@ cudaError_t launch_fwd_tc(const TrainParams& p, void* workspace, const float** O
   float* Op = reinterpret_cast<float*>(w); w += up(rows * p.d * 4);
   float* Mp = reinterpret_cast<float*>(w); w += up(rows * 4);
   float* Lp = reinterpret_cast<float*>(w); w += up(rows * 4);
-  int* status = reinterpret_cast<int*>(w);
-  cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  int* status = nullptr;
+  cudaError_t e = status_word_of(reinterpret_cast<int*>(w), stream, &status);
   if (e != cudaSuccess) return e;
   if (p.d == 64) e = launch_tc_t<64>(p, Kt, Op, Mp, Lp, status, stream);
   else e = launch_tc_t<128>(p, Kt, Op, Mp, Lp, status, stream);
   *Opart = Op; *Mpart = Mp; *Lpart = Lp;
-  if (e != cudaSuccess) return e;
-  return launch_fold_status(status, stream);
+  return e;
 }
 
 

@@ -65,12 +65,14 @@ struct ScopedKernelTimer {
   ~ScopedKernelTimer() { if (on) cudaEventRecord(g_profile_hook.stop, st); }
 };
 
-// Failure detection.  A tensor-core kernel whose bounded wait ran out sets the status word of its
-// workspace; launch_fold_status ORs that word into the word the caller registered for the current
-// device (fmta_set_status_word), if any.  take_selftest_expire returns 1 once after
+// Failure detection.  A tensor-core kernel whose bounded wait ran out sets a status word: the word the caller
+// registered for the current device (fmta_set_status_word) -- the kernels write it directly, no extra launch --
+// or, when none is registered, a word of the call's workspace.  status_word_of returns the registered word, or
+// clears (on `stream`) and returns `ws_word`.  take_selftest_expire returns 1 once after
 // fmta_selftest_expire_next(id) named this kernel: that launch runs with its first consumer wait pointed at a
 // barrier nothing arrives at, so the wait runs out and the kernel leaves through its abort path.
-cudaError_t launch_fold_status(const int* status, cudaStream_t stream);
+cudaError_t status_word_of(int* ws_word, cudaStream_t stream, int** word);
+int* registered_status_word();
 int take_selftest_expire(int kernel_id);
 
 cudaError_t launch_fwd_exact(const TrainParams& p, cudaStream_t stream);

@@ -81,8 +81,8 @@ int fmta_set_path(int path);
  * outputs of that call are invalid.  The reference has no counterpart (its forward only prints a
  * launch error, conv_attn/kernels/fwd.cu:306-309; its backward throws on one, dq_bwd.cu:585-586).
  * fmta_set_status_word registers, for the CURRENT device, a caller-owned int32 in device memory
- * (zeroed by the caller); from then on every tensor-core entry point ends by OR-ing its kernels'
- * status into that word on its stream.  The caller reads the word after a synchronisation it does
+ * (zeroed by the caller); from then on the tensor-core kernels of every entry point set that word
+ * themselves when a wait of theirs runs out.  The caller reads the word after a synchronisation it does
  * anyway: non-zero = FMTA_ERR_DEVICE_WAIT.  NULL unregisters.  Process-wide per device, not thread-safe.
  */
 int fmta_set_status_word(int* device_word);
