@@ -164,7 +164,8 @@ static int check_window(int lo, int hi, int N) {
 static int fwd_impl(const void* Q, const void* K, const void* V, const float* theta, const float* wmix,
                     void* O, float* M, float* L, float* LSE, int B, int H, int N, int d, int cq, int ck,
                     int G, float scale, int causal, int o_dtype, int path, void* workspace,
-                    size_t workspace_bytes, void* stream, void* ktilde, int row_lo = 0, int row_hi = 0) {
+                    size_t workspace_bytes, void* stream, void* ktilde, int row_lo = 0, int row_hi = 0,
+                    int ktilde_valid = 0) {
   if (!Q || !K || !V || !O) return FMTA_ERR_NULL;
   if (ktilde && !aligned16(ktilde)) return FMTA_ERR_ALIGN;
   if (int s = check_train_dims(B, H, N, d, cq, ck, G, theta != nullptr, wmix != nullptr)) return s;
@@ -192,6 +193,7 @@ static int fwd_impl(const void* Q, const void* K, const void* V, const float* th
   }
   if (ktilde && !use_tc) return FMTA_ERR_UNSUPPORTED;   // only the tensor-core path makes the stacked key operand
   p.Kt_ext = reinterpret_cast<__nv_bfloat16*>(ktilde);
+  p.kt_valid = ktilde != nullptr && ktilde_valid;        // the caller's buffer already holds the operand: no pre-pass
   if (row_hi > 0) {                                      // a window of rows: tensor-core path only
     if (int s = check_window(row_lo, row_hi, N)) return s;
     if (!use_tc) return FMTA_ERR_UNSUPPORTED;
@@ -386,23 +388,35 @@ int fmta_bwd_with_ktilde(const void* Q, const void* K, const void* V, const void
                   workspace, workspace_bytes, stream, ktilde);
 }
 
+int fmta_stacked_keys(const void* K, const float* theta, void* ktilde, int B, int H, int N, int d, int cq, int ck,
+                      float scale, void* stream) {
+  if (!K || !theta || !ktilde) return FMTA_ERR_NULL;
+  if (int s = check_train_dims(B, H, N, d, cq, ck, 1, true, false)) return s;
+  if (d != 64 && d != 128) return FMTA_ERR_UNSUPPORTED;      // the tensor-core kernels' head dims
+  if (!aligned16(K) || !aligned16(ktilde)) return FMTA_ERR_ALIGN;
+  TrainParams p = {};
+  p.K = (const __nv_bfloat16*)K; p.theta = theta;
+  p.B = B; p.H = H; p.N = N; p.d = d; p.cq = cq; p.ck = ck; p.G = 1; p.scale = scale;
+  return check_cuda(launch_ktilde(p, reinterpret_cast<__nv_bfloat16*>(ktilde), (cudaStream_t)stream));
+}
+
 int fmta_fwd_window(const void* Q, const void* K, const void* V, const float* theta, void* O, float* M, float* L,
                     float* LSE, int B, int H, int N, int d, int cq, int ck, float scale, int causal, int o_dtype,
-                    int row_lo, int row_hi, void* workspace, size_t workspace_bytes, void* stream) {
+                    int row_lo, int row_hi, const void* ktilde, void* workspace, size_t workspace_bytes, void* stream) {
   if (!theta) return FMTA_ERR_NULL;
   if (row_hi <= 0) return FMTA_ERR_SHAPE;
   return fwd_impl(Q, K, V, theta, nullptr, O, M, L, LSE, B, H, N, d, cq, ck, 1, scale, causal, o_dtype, 1, workspace,
-                  workspace_bytes, stream, nullptr, row_lo, row_hi);
+                  workspace_bytes, stream, const_cast<void*>(ktilde), row_lo, row_hi, 1);
 }
 
 int fmta_bwd_window(const void* Q, const void* K, const void* V, const void* dO, const float* D, const float* LSE,
                     const float* theta, float* dQ, float* dK, float* dV, float* dTheta, int B, int H, int N, int d,
-                    int cq, int ck, float scale, int causal, int row_lo, int row_hi, void* workspace,
+                    int cq, int ck, float scale, int causal, int row_lo, int row_hi, const void* ktilde, void* workspace,
                     size_t workspace_bytes, void* stream) {
   if (!theta) return FMTA_ERR_NULL;
   if (row_hi <= 0) return FMTA_ERR_SHAPE;
   return bwd_impl(Q, K, V, dO, D, LSE, theta, nullptr, dQ, dK, dV, dTheta, nullptr, B, H, N, d, cq, ck, 1, scale, causal, 1,
-                  workspace, workspace_bytes, stream, nullptr, row_lo, row_hi);
+                  workspace, workspace_bytes, stream, ktilde, row_lo, row_hi);
 }
 
 static int decode_impl(const void* Q, const void* K, const void* V, const float* theta, float* O_splits,

@@ -85,6 +85,8 @@ cudaError_t launch_kv_append_paged(void* Kpool, void* Vpool, const int* block_ta
                                    const void* Knew, const void* Vnew, int B, int H, int n_new, int d, int page_size,
                                    int page_shift, int max_pages, cudaStream_t stream);
 bool fwd_tc_supported(const TrainParams& p);
+// pre-pass of the tensor-core kernels: Kt[b,h,t,j,:] = scale * log2(e) * sum_u theta[h,t,u] * K[b,h,j + pad_k - u,:]
+cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t stream);
 size_t fwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);
 bool bwd_tc_supported(const TrainParams& p);
 size_t bwd_tc_workspace_bytes(int B, int H, int N, int d, int cq);

@@ -55,11 +55,13 @@ lib.fmta_bwd_with_ktilde.restype = _i
 lib.fmta_bwd_with_ktilde.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _f, _i,
                                      _vp, _sz, _vp, _vp]
 lib.fmta_fwd_window.restype = _i
-lib.fmta_fwd_window.argtypes = [_vp, _vp, _vp, _fp, _vp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _sz,
-                                _vp]
+lib.fmta_fwd_window.argtypes = [_vp, _vp, _vp, _fp, _vp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp,
+                                _sz, _vp]
+lib.fmta_stacked_keys.restype = _i
+lib.fmta_stacked_keys.argtypes = [_vp, _fp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]
 lib.fmta_bwd_window.restype = _i
 lib.fmta_bwd_window.argtypes = [_vp, _vp, _vp, _vp, _fp, _fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i,
-                                _vp, _sz, _vp]
+                                _vp, _vp, _sz, _vp]
 lib.fmta_profile_kernel.restype = _i
 lib.fmta_profile_kernel.argtypes = [_i, _vp, _vp]
 lib.fmta_set_path.restype = _i
@@ -82,7 +84,7 @@ lib.fmta_selftest_expire_next.restype = _i
 lib.fmta_selftest_expire_next.argtypes = [_i]
 
 EXPORTS = ["fmta_set_status_word", "fmta_selftest_expire_next", "fmta_version", "fmta_strerror", "fmta_last_cuda_error", "fmta_workspace_bytes", "fmta_fwd",
-           "fmta_bwd_prep_D", "fmta_bwd", "fmta_fwd_keep_ktilde", "fmta_bwd_with_ktilde", "fmta_fwd_window", "fmta_bwd_window", "fmta_set_path", "fmta_profile_kernel", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode", "fmta_decode_offset_causal", "fmta_decode_paged", "fmta_kv_append_paged"]
+           "fmta_bwd_prep_D", "fmta_bwd", "fmta_fwd_keep_ktilde", "fmta_bwd_with_ktilde", "fmta_fwd_window", "fmta_bwd_window", "fmta_stacked_keys", "fmta_set_path", "fmta_profile_kernel", "fmta_bwd_dq_dw", "fmta_bwd_dq_dw_static", "fmta_bwd_dkdv", "fmta_decode", "fmta_decode_offset_causal", "fmta_decode_paged", "fmta_kv_append_paged"]
 
 
 def check(status, what):

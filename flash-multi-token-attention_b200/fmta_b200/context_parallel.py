@@ -85,10 +85,33 @@ def _dims(Q, conv_kernel, pad_q, pad_k):
     return B, H, N, d, cq, ck
 
 
-def forward_window(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, row_lo, row_hi, out=None):
+def stacked_keys(K, conv_kernel, scale):
+    """`fmta_stacked_keys`: the stacked key operand (bf16 [B, H, c_q, N, d]) that the tensor-core kernels read the
+    keys through, made once for all the window calls of a step (``ktilde`` of `forward_window` / `backward_window`)."""
+    require_cuda_bf16(K, "K")
+    require_on(K, conv_kernel, "conv_kernel")
+    B, H, N, d = K.shape
+    cq, ck = int(conv_kernel.shape[1]), int(conv_kernel.shape[2])
+    kt = torch.empty((B, H, cq, N, d), dtype=torch.bfloat16, device=K.device)
+    st = lib.fmta_stacked_keys(ptr(K), ptr(as_f32(conv_kernel)), ptr(kt), B, H, N, d, cq, ck, float(scale), stream_ptr())
+    check(st, "fmta_stacked_keys")
+    return kt
+
+
+def _check_kt(ktilde, Q, cq):
+    if ktilde is None:
+        return
+    B, H, N, d = Q.shape
+    require_on(Q, ktilde, "ktilde", (B, H, cq, N, d))
+    if ktilde.dtype != torch.bfloat16 or not ktilde.is_contiguous():
+        raise RuntimeError("ktilde must be a contiguous bf16 tensor (see stacked_keys)")
+
+
+def forward_window(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, row_lo, row_hi, out=None, ktilde=None):
     """`fmta_fwd_window`: O (fp32), M, L, LSE of the query rows [row_lo, row_hi) of the WHOLE tensors Q, K, V
     ([B, H, N, d] bf16).  ``out`` = (O, M, L, LSE) whole-size buffers to write the window into (allocated
-    uninitialised when None); rows outside the window are left as they are.  Returns ``out``."""
+    uninitialised when None); rows outside the window are left as they are.  ``ktilde``: `stacked_keys` of the
+    same K, conv_kernel and scale (None: the call makes its own).  Returns ``out``."""
     for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
         require_cuda_bf16(t, n)
     B, H, N, d, cq, ck = _dims(Q, conv_kernel, pad_q, pad_k)
@@ -102,16 +125,17 @@ def forward_window(Q, K, V, conv_kernel, scale, pad_q, pad_k, causal, row_lo, ro
     require_on(Q, O, "O", Q.shape)
     for t, n in ((M, "M"), (L, "L"), (LSE, "LSE")):
         require_on(Q, t, n, Q.shape[:-1])
+    _check_kt(ktilde, Q, cq)
     ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_FWD_TC, B, H, N, d, cq, ck, 1)
     ws = torch.empty(max(int(ws_bytes), 16), dtype=torch.uint8, device=Q.device)
     st = lib.fmta_fwd_window(ptr(Q), ptr(K), ptr(V), ptr(theta), ptr(O), ptr(M), ptr(L), ptr(LSE), B, H, N, d, cq, ck,
                              float(scale), int(bool(causal)), _lib.FMTA_DTYPE_BF16 if O.dtype == torch.bfloat16 else _lib.FMTA_DTYPE_F32,
-                             int(row_lo), int(row_hi), ptr(ws), ws_bytes, stream_ptr())
+                             int(row_lo), int(row_hi), ptr(ktilde), ptr(ws), ws_bytes, stream_ptr())
     check(st, "fmta_fwd_window")
     return out
 
 
-def backward_window(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, row_lo, row_hi, out=None):
+def backward_window(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal, row_lo, row_hi, out=None, ktilde=None):
     """`fmta_bwd_window` on the WHOLE tensors (Q, K, V, dO bf16 [B, H, N, d]; D and the log-sum-exp ``L`` fp32
     [B, H, N], complete): dQ of the query rows and dK, dV of the keys in [row_lo, row_hi) are written into
     ``out`` = (dQ, dK, dV) (fp32, whole size; allocated uninitialised when None), other rows are left alone.
@@ -133,11 +157,12 @@ def backward_window(Q, K, V, dO, D, L, conv_kernel, scale, pad_q, pad_k, causal,
         if t.dtype != torch.float32 or not t.is_contiguous():
             raise RuntimeError("%s must be a contiguous fp32 tensor" % n)
     dTheta = torch.empty((H, cq, ck), dtype=torch.float32, device=Q.device)
+    _check_kt(ktilde, Q, cq)
     ws_bytes = lib.fmta_workspace_bytes(_lib.FMTA_OP_BWD_TC, B, H, N, d, cq, ck, 1)
     ws = torch.empty(max(int(ws_bytes), 16), dtype=torch.uint8, device=Q.device)
     st = lib.fmta_bwd_window(ptr(Q), ptr(K), ptr(V), ptr(dO), ptr(Dv), ptr(LSE), ptr(theta), ptr(dQ), ptr(dK), ptr(dV),
                              ptr(dTheta), B, H, N, d, cq, ck, float(scale), int(bool(causal)), int(row_lo), int(row_hi),
-                             ptr(ws), ws_bytes, stream_ptr())
+                             ptr(ktilde), ptr(ws), ws_bytes, stream_ptr())
     check(st, "fmta_bwd_window")
     return dQ, dK, dV, dTheta
 
@@ -198,10 +223,12 @@ class ContextParallelConvAttentionFunction(torch.autograd.Function):
         B, H, _, d = Qf.shape
         out = (torch.empty((B, H, N, d), dtype=torch.float32, device=Qf.device),) + tuple(
             torch.empty((B, H, N), dtype=torch.float32, device=Qf.device) for _ in range(3))
+        kt = stacked_keys(Kf, conv_kernel, scale)      # once per step: both windows, forward and backward, read it
         _on_streams(plan[rank], lambda i, lo, hi: forward_window(Qf, Kf, Vf, conv_kernel, scale, pad_q, pad_k, causal,
-                                                                 lo, hi, out=out), Qf.device)
+                                                                 lo, hi, out=out, ktilde=kt), Qf.device)
         o_loc, lse_loc = take_local(out[0], plan[rank]), take_local(out[3], plan[rank])
         ctx.save_for_backward(Qf, Kf, Vf, conv_kernel, o_loc, lse_loc)
+        ctx.kt = kt
         ctx.args = (scale, pad_q, pad_k, causal, group, plan, rank)
         ctx.in_dtypes = (q.dtype, k.dtype, v.dtype)
         return o_loc
@@ -215,8 +242,9 @@ class ContextParallelConvAttentionFunction(torch.autograd.Function):
         dOf = gather_sequence(do_b, plan, group)
         Df, LSEf = gather_sequence(d_loc, plan, group), gather_sequence(lse_loc, plan, group)
         out = tuple(torch.empty(Qf.shape, dtype=torch.float32, device=Qf.device) for _ in range(3))
+        kt, ctx.kt = ctx.kt, None
         res = _on_streams(plan[rank], lambda i, lo, hi: backward_window(Qf, Kf, Vf, dOf, Df, LSEf, conv_kernel, scale, pad_q,
-                                                                        pad_k, causal, lo, hi, out=out), Qf.device)
+                                                                        pad_k, causal, lo, hi, out=out, ktilde=kt), Qf.device)
         dth = res[0][3]
         for r in res[1:]:
             dth = dth + r[3]

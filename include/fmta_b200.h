@@ -206,15 +206,19 @@ int fmta_bwd_with_ktilde(const void* Q, const void* K, const void* V, const void
  *     the query rows that see them, so D and LSE must be complete), and in dTheta the window's share: the shares of
  *     disjoint windows that cover [0, N) add up to the dTheta of fmta_bwd.  No other row of dQ, dK, dV is touched.
  * Tensor-core path only (theta given, the shapes of fmta_fwd / fmta_bwd with path = 1), with the workspace of the
- * whole problem (FMTA_OP_FWD_TC / FMTA_OP_BWD_TC).  The windows of one sequence computed one after the other into the
+ * whole problem (FMTA_OP_FWD_TC / FMTA_OP_BWD_TC).  ktilde: NULL, or the stacked key operand of the whole sequence
+ * (bf16 [B,H,cq,N,d]) made once by fmta_stacked_keys for these K, theta and scale -- every window call otherwise
+ * repeats that O(N) pre-pass.  The windows of one sequence computed one after the other into the
  * same buffers give the results of fmta_fwd / fmta_bwd (dQ to rounding: its row tiles start at the window).
  */
+int fmta_stacked_keys(const void* K, const float* theta, void* ktilde, int B, int H, int N, int d, int cq, int ck,
+                      float scale, void* stream);
 int fmta_fwd_window(const void* Q, const void* K, const void* V, const float* theta, void* O, float* M, float* L,
                     float* LSE, int B, int H, int N, int d, int cq, int ck, float scale, int causal, int o_dtype,
-                    int row_lo, int row_hi, void* workspace, size_t workspace_bytes, void* stream);
+                    int row_lo, int row_hi, const void* ktilde, void* workspace, size_t workspace_bytes, void* stream);
 int fmta_bwd_window(const void* Q, const void* K, const void* V, const void* dO, const float* D, const float* LSE,
                     const float* theta, float* dQ, float* dK, float* dV, float* dTheta, int B, int H, int N, int d,
-                    int cq, int ck, float scale, int causal, int row_lo, int row_hi, void* workspace,
+                    int cq, int ck, float scale, int causal, int row_lo, int row_hi, const void* ktilde, void* workspace,
                     size_t workspace_bytes, void* stream);
 
 /*

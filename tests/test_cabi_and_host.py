@@ -203,14 +203,16 @@ def test_window_entry_points_validate_on_the_host():
     P = ctypes.c_void_p
     good = P(0x1000)
     fw = lambda lo, hi, N=1024, d=64: lib.fmta_fwd_window(good, good, good, good, good, None, None, None, 1, 1, N, d, 3, 3,
-                                                          1.0, 1, 0, lo, hi, None, 0, None)
+                                                          1.0, 1, 0, lo, hi, None, None, 0, None)
     bw = lambda lo, hi, N=1024, d=64: lib.fmta_bwd_window(good, good, good, good, good, good, good, good, good, good, good,
-                                                          1, 1, N, d, 3, 3, 1.0, 1, lo, hi, None, 0, None)
+                                                          1, 1, N, d, 3, 3, 1.0, 1, lo, hi, None, None, 0, None)
     for f in (fw, bw):
         assert f(0, 0) == -2                       # a window is required
         assert f(0, 512, d=32) == -3               # tensor-core shapes only
     assert lib.fmta_fwd_window(good, good, good, None, good, None, None, None, 1, 1, 1024, 64, 3, 3, 1.0, 1, 0, 0, 512,
-                               None, 0, None) == -1
+                               None, None, 0, None) == -1
+    sk = lambda K=good, kt=good, d=64: lib.fmta_stacked_keys(K, good, kt, 1, 1, 1024, d, 3, 3, 1.0, None)
+    assert sk(K=None) == -1 and sk(kt=None) == -1 and sk(d=32) == -3 and sk(kt=P(0x1004)) == -4
 
 
 _CP_WORKER = r'''
@@ -223,14 +225,14 @@ dist.init_process_group("gloo", rank=rank, world_size=ws, timeout=datetime.timed
 
 # the oracle stands in for the CUDA window calls, so that the gathers, the window bookkeeping and the all-reduce
 # of the filter gradient run on CPU ranks
-def fwd_window(Q, K, V, th, scale, pq, pk, causal, lo, hi, out=None):
+def fwd_window(Q, K, V, th, scale, pq, pk, causal, lo, hi, out=None, ktilde=None):
     O, M, L = orc.conv_attn_fwd(Q.float(), K.float(), V.float(), th, scale, causal)
     if out is None:
         out = (torch.full_like(O, float("nan")),) + tuple(torch.full_like(M, float("nan")) for _ in range(3))
     for dst, src in zip(out, (O, M, L, M + torch.log(L))):
         dst[:, :, lo:hi] = src[:, :, lo:hi]
     return out
-def bwd_window(Q, K, V, dO, D, L, th, scale, pq, pk, causal, lo, hi, out=None):
+def bwd_window(Q, K, V, dO, D, L, th, scale, pq, pk, causal, lo, hi, out=None, ktilde=None):
     with torch.enable_grad():                      # called from inside an autograd backward
         g = orc.conv_attn_bwd_autograd(Q.float(), K.float(), V.float(), th.detach(), dO.float(), scale, causal)
     if out is None:
@@ -239,6 +241,7 @@ def bwd_window(Q, K, V, dO, D, L, th, scale, pq, pk, causal, lo, hi, out=None):
         dst[:, :, lo:hi] = src[:, :, lo:hi]
     return out + (g[3] * ((hi - lo) / Q.shape[2]),)       # shares that add up to the whole gradient
 cp.forward_window, cp.backward_window = fwd_window, bwd_window
+cp.stacked_keys = lambda K, th, scale: None
 cp._rowdot = lambda dO, O: (dO.float() * O.float()).sum(-1)
 
 B, H, N, d, cq, ck = 1, 2, 1024, 16, 3, 5
