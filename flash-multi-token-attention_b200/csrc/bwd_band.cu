@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(bandcfg::NT, bandcfg::Layout<D>::kCtasPerSm) b
   const size_t bh = (size_t)b * H + h;
   const int t0 = win_lo(p) + blockIdx.x * Rt;
   const int R = p.row_hi > 0 ? min(Rt, p.row_hi - t0) : Rt;   // a call with a window owns no position past its end
+  pdl_trigger();
+  pdl_wait();                                          // launched with programmatic stream serialization
   const bf16* Qg = p.Q + bh * (size_t)N * D;
   const bf16* Kg = p.K + bh * (size_t)N * D;
   const bf16* Vg = p.V + bh * (size_t)N * D;
@@ -484,12 +486,12 @@ template <int D>
 static cudaError_t launch_bwd_band_d(const TrainParams& p, dim3 grid, cudaStream_t stream) {
   constexpr int smem = bandcfg::Layout<D>::kSmemBytes;
   if (p.cq == 6 && p.ck == 11)
-    return launch_kernel<TrainParams>(bwd_band_kernel<D, 6, 11>, grid, dim3(bandcfg::NT), smem, stream, 1, p);
+    return launch_kernel<TrainParams>(bwd_band_kernel<D, 6, 11>, grid, dim3(bandcfg::NT), smem, stream, -1, p);
   if (p.cq == 7 && p.ck == 7 && D == 64)
-    return launch_kernel<TrainParams>(bwd_band_kernel<D, 7, 7>, grid, dim3(bandcfg::NT), smem, stream, 1, p);
+    return launch_kernel<TrainParams>(bwd_band_kernel<D, 7, 7>, grid, dim3(bandcfg::NT), smem, stream, -1, p);
   if (p.cq == 3 && p.ck == 5)
-    return launch_kernel<TrainParams>(bwd_band_kernel<D, 3, 5>, grid, dim3(bandcfg::NT), smem, stream, 1, p);
-  return launch_kernel<TrainParams>(bwd_band_kernel<D, 0, 0>, grid, dim3(bandcfg::NT), smem, stream, 1, p);
+    return launch_kernel<TrainParams>(bwd_band_kernel<D, 3, 5>, grid, dim3(bandcfg::NT), smem, stream, -1, p);
+  return launch_kernel<TrainParams>(bwd_band_kernel<D, 0, 0>, grid, dim3(bandcfg::NT), smem, stream, -1, p);
 }
 
 cudaError_t launch_bwd_band(const TrainParams& p, cudaStream_t stream) {

@@ -14,6 +14,7 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __res
   const int col = threadIdx.x & 31, k = threadIdx.x >> 5;
   const int i = blockIdx.x * 32 + col;
   float t = 0.f;
+  pdl_wait();                                          // launched with programmatic stream serialization
   if (i < n)
     for (int s = k; s < n_slots; s += 8) t += part[(size_t)s * n + i];
   sSub[k][col] = t;
@@ -59,6 +60,8 @@ __global__ void __launch_bounds__(256) rowdot_vec_kernel(const bf16* __restrict_
   const size_t row = (size_t)blockIdx.x * (256 / TPR) + threadIdx.x / TPR;
   const int c = (threadIdx.x % TPR) * 8;
   float t = 0.f;
+  pdl_trigger();
+  pdl_wait();                                          // launched with programmatic stream serialization
   if (row < rows) {
     const uint4 g = *reinterpret_cast<const uint4*>(dO + row * D + c);
     const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
@@ -114,17 +117,15 @@ cudaError_t launch_bwd_dq(const TrainParams& p, cudaStream_t stream) {
 }
 
 cudaError_t launch_reduce_partials(const float* part, float* out, int n_slots, int n, cudaStream_t stream) {
-  reduce_partials_kernel<<<(n + 31) / 32, 256, 0, stream>>>(part, out, n_slots, n);
-  return cudaGetLastError();
+  return launch_pdl(reduce_partials_kernel, dim3((n + 31) / 32), dim3(256), 0, stream, part, out, n_slots, n);
 }
 
 cudaError_t launch_rowdot(const void* dO, const void* O, int o_bf16, float* Dv, size_t rows, int d, cudaStream_t stream) {
   const bf16* g = reinterpret_cast<const bf16*>(dO);
 #define FMTA_ROWDOT(TPR)                                                                                   \
   { const unsigned nb = (unsigned)((rows + 256 / TPR - 1) / (256 / TPR));                                  \
-    if (o_bf16) rowdot_vec_kernel<true, TPR><<<nb, 256, 0, stream>>>(g, O, Dv, rows);                      \
-    else rowdot_vec_kernel<false, TPR><<<nb, 256, 0, stream>>>(g, O, Dv, rows);                            \
-    return cudaGetLastError(); }
+    if (o_bf16) return launch_pdl(rowdot_vec_kernel<true, TPR>, dim3(nb), dim3(256), 0, stream, g, O, Dv, rows);      \
+    return launch_pdl(rowdot_vec_kernel<false, TPR>, dim3(nb), dim3(256), 0, stream, g, O, Dv, rows); }
   const bool al = (reinterpret_cast<uintptr_t>(dO) % 16 == 0) && (reinterpret_cast<uintptr_t>(O) % 16 == 0);
   if (al && d == 64) FMTA_ROWDOT(8)
   if (al && d == 128) FMTA_ROWDOT(16)

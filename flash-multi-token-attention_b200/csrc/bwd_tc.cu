@@ -149,7 +149,9 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   for (int i = tid; i < NT * Cfg::DC_BYTES / 4; i += Cfg::kThreads) reinterpret_cast<uint32_t*>(sdC)[i] = 0u;
   tc::fence_proxy_async_smem();
   tc::tc_fence_before();
+  pdl_trigger();   // the next kernel's CTAs may be scheduled once every CTA here has got this far
   __syncthreads();
+  pdl_wait();      // nothing before this line touches global memory
   tc::tc_fence_after();
   const uint32_t tmem = *s_tmem;
 
@@ -527,7 +529,9 @@ bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc::tmem_relinquish();
   }
   tc::tc_fence_before();
+  pdl_trigger();
   __syncthreads();
+  pdl_wait();      // nothing before this line touches global memory
   tc::tc_fence_after();
   const uint32_t tmem = *s_tmem;
   const uint32_t tX = tmem + Cfg::colX;
@@ -876,6 +880,7 @@ struct DkPostCfg {
 __global__ void dk_post_toeplitz_kernel(const float* __restrict__ theta, bf16* __restrict__ Tg, int cq, int ck, float scale) {
   constexpr int T_LD = DkPostCfg::T_LD, T_ELEMS = DkPostCfg::T_ELEMS, HALO = DkPostCfg::HALO;
   const int h = blockIdx.x, pk = (ck - 1) / 2;
+  pdl_trigger();
   for (int i = threadIdx.x; i < cq * 16 * T_LD; i += blockDim.x) {
     const int a = i / (16 * T_LD), x = (i / T_LD) % 16, r = i % T_LD;
     const int bb = x + pk + HALO - r;
@@ -885,6 +890,9 @@ __global__ void dk_post_toeplitz_kernel(const float* __restrict__ theta, bf16* _
     dst[0] = hi;
     dst[T_ELEMS] = __float2bfloat16_rn(w - __bfloat162float(hi));
   }
+  // the tiles depend on the filter only, so they are built while the kernel before this one still runs; waiting
+  // here keeps "this kernel has completed" implying that one has, which the adjoint kernel behind it relies on
+  pdl_wait();
 }
 
 __global__ void __launch_bounds__(DkPostCfg::NT, 2)
@@ -921,7 +929,9 @@ dk_post_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     *s_abort = 0;
     tc::mbar_fence_init();
   }
+  pdl_trigger();
   __syncthreads();
+  pdl_wait();      // nothing before this line touches global memory
   if (tid == 0) {
     tc::mbar_expect_tx(&bars[0], (1 + half) * Cfg::TILE_BYTES + Cfg::t_bytes(cq));
     tc::tma_load_3d(smem, &tmK, &bars[0], col0, J0 - HALO, bh);
@@ -1132,8 +1142,8 @@ cudaError_t launch_bwd_dq_tc(const TrainParams& p, void* workspace, bool keep_pd
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   { ScopedKernelTimer timer_(kKernBwdDqTc, stream);
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp); }
-  return cudaGetLastError();
+    e = launch_pdl(kern, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tmQ, tmdO, tmKt, tmV, bp); }
+  return e;
 }
 
 
@@ -1161,8 +1171,7 @@ static cudaError_t launch_dkdv_pass(const TrainParams& p, const __nv_bfloat16* K
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((key_hi - key_lo + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, tmdKt, tmdV, bp);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tmQ, tmdO, tmKt, tmV, tmdKt, tmdV, bp);
 }
 
 cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTheta_part_tc, bool keep_pdc, cudaStream_t stream) {
@@ -1217,9 +1226,10 @@ cudaError_t launch_bwd_dkdv_tc(const TrainParams& p, void* workspace, float* dTh
   if (!make_tensor_map_bf16(&tmX, dKt, D, p.N, BH * p.cq, 64, DkPostCfg::ROWS, true)) return cudaErrorInvalidValue;
   // (the maps span the full head dim; each CTA fetches its 64-column slab)
   ScopedKernelTimer timer2_(kKernDkPost, stream);
-  dk_post_toeplitz_kernel<<<p.H, 256, 0, stream>>>(p.theta, Tg, p.cq, p.ck, p.scale);
-  kern<<<g2, DkPostCfg::NT, smem, stream>>>(tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq, p.ck, p.scale, njb, D, j_base);
-  return cudaGetLastError();
+  e = launch_pdl(dk_post_toeplitz_kernel, dim3(p.H), dim3(256), 0, stream, p.theta, Tg, p.cq, p.ck, p.scale);
+  if (e != cudaSuccess) return e;
+  return launch_pdl(kern, g2, dim3(DkPostCfg::NT), (size_t)smem, stream, tmK, tmX, Tg, p.dK, dTheta_part_tc, status, p.H, p.N, p.cq,
+                    p.ck, p.scale, njb, D, j_base);
 }
 
 // slots of dTheta partials written by the dKt adjoint kernel: one per CTA

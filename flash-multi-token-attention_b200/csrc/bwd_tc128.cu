@@ -124,7 +124,9 @@ bwd_dq_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   for (int i = tid; i < (BC / 8) * DR * 4; i += Cfg::kThreads) reinterpret_cast<uint32_t*>(sdC)[i] = 0u;
   tc::fence_proxy_async_smem();
   tc::tc_fence_before();
+  pdl_trigger();
   __syncthreads();
+  pdl_wait();      // nothing before this line touches global memory that a kernel of this library writes or reads back
   tc::tc_fence_after();
   const uint32_t tmem = *s_tmem;
   const int per_kb = cq + 1;   // ring tiles per key block
@@ -443,7 +445,9 @@ bwd_dkdv_tc128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     tc::tmem_relinquish();
   }
   tc::tc_fence_before();
+  pdl_trigger();
   __syncthreads();
+  pdl_wait();      // nothing before this line touches global memory that a kernel of this library writes or reads back
   tc::tc_fence_after();
   const uint32_t tmem = *s_tmem;
   const uint32_t tX = tmem + Cfg::colX;
@@ -762,8 +766,8 @@ cudaError_t launch_bwd_dq_tc128(const TrainParams& p, const __nv_bfloat16* Kt, i
   if (e != cudaSuccess) return e;
   dim3 grid((bp.row_end - bp.row_base + bp.own - 1) / bp.own, p.H, p.B);
   { ScopedKernelTimer timer_(kKernBwdDqTc, stream);
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, p.dO, bp); }
-  return cudaGetLastError();
+    e = launch_pdl(kern, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tmQ, tmKt, tmV, p.dO, bp); }
+  return e;
 }
 
 cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt, __nv_bfloat16* dKt, int* status, int with_dv,
@@ -786,8 +790,7 @@ cudaError_t launch_bwd_dkdv_tc128(const TrainParams& p, const __nv_bfloat16* Kt,
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((key_hi - key_lo + Cfg::BK - 1) / Cfg::BK, p.H, p.B);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmdO, tmKt, tmV, bp);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tmQ, tmdO, tmKt, tmV, bp);
 }
 
 }  // namespace fmta

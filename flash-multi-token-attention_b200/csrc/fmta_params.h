@@ -39,6 +39,16 @@ struct TrainParams {
   int n_slots;
 };
 
+#ifdef __CUDACC__
+// Programmatic dependent launch.  A kernel launched with launch_pdl may start while the kernel before it in the
+// stream is still running; it must call pdl_wait() before it reads anything an earlier kernel wrote or writes
+// anything one reads (pdl_wait returns once the preceding kernel has completed and its writes are visible; every CTA
+// calls it before it exits, so that "this kernel has completed" keeps implying "every earlier one has").
+// pdl_trigger() lets the NEXT kernel's CTAs be scheduled as soon as every CTA of this one has called it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 // The window of a call: [win_lo(p), win_hi(p))
 __host__ __device__ inline int win_lo(const TrainParams& p) { return p.row_hi > 0 ? p.row_lo : 0; }
 __host__ __device__ inline int win_hi(const TrainParams& p) { return p.row_hi > 0 ? p.row_hi : p.N; }

@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(FwdBandCfg<D>::NT, 2) fwd_band_kernel(const Tr
   const size_t bh = (size_t)b * H + h;
   const int t0 = win_lo(p) + blockIdx.x * R;          // a window starts on a multiple of R
   const int koff = (band > 16) ? 32 : 16;             // the P tile of 16 rows starts koff keys before them
+  pdl_trigger();
+  pdl_wait();                                         // launched with programmatic stream serialization
 
   if (band > 0) {
     load_rows_async<D, NT>(sQ, LD, p.Q + bh * (size_t)N * D, t0 - 16, RS, N, tid);
@@ -231,12 +233,12 @@ static cudaError_t launch_fwd_band_t(const TrainParams& p, cudaStream_t stream) 
   using Cfg = FwdBandCfg<D>;
   dim3 grid((win_hi(p) - win_lo(p) + Cfg::R - 1) / Cfg::R, p.H, p.B);
   if (p.cq == 6 && p.ck == 11)
-    return launch_kernel<TrainParams>(fwd_band_kernel<D, 6, 11>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
+    return launch_kernel<TrainParams>(fwd_band_kernel<D, 6, 11>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, -1, p);
   if (p.cq == 7 && p.ck == 7)
-    return launch_kernel<TrainParams>(fwd_band_kernel<D, 7, 7>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
+    return launch_kernel<TrainParams>(fwd_band_kernel<D, 7, 7>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, -1, p);
   if (p.cq == 3 && p.ck == 5)
-    return launch_kernel<TrainParams>(fwd_band_kernel<D, 3, 5>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
-  return launch_kernel<TrainParams>(fwd_band_kernel<D, 0, 0>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, 1, p);
+    return launch_kernel<TrainParams>(fwd_band_kernel<D, 3, 5>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, -1, p);
+  return launch_kernel<TrainParams>(fwd_band_kernel<D, 0, 0>, grid, dim3(Cfg::NT), Cfg::kSmemBytes, stream, -1, p);
 }
 
 // Finishes the forward started by the stacked tensor-core kernel: band entries + normalisation.

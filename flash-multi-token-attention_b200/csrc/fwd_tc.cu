@@ -45,7 +45,9 @@ __global__ void __launch_bounds__(256) ktilde_kernel(const bf16* __restrict__ K,
   __shared__ float sTh[20];
   const int bh = blockIdx.y, h = bh % H, a = blockIdx.z;
   if (threadIdx.x < ck) sTh[threadIdx.x] = theta[((size_t)h * cq + a) * ck + threadIdx.x] * scale;   // scale carries log2(e)
+  pdl_trigger();
   __syncthreads();
+  pdl_wait();      // nothing before this line touches global memory that a kernel of this library writes or reads back
   const int j = blockIdx.x * RPB + threadIdx.x / CPR, c = threadIdx.x % CPR;
   if (j >= N) return;
   const int pk = (ck - 1) / 2;
@@ -82,7 +84,9 @@ __global__ void __launch_bounds__(256) ktilde_window_kernel(const bf16* __restri
   __shared__ float sTh[16 * CK];
   const int bh = blockIdx.y, h = bh % H;
   for (int i = threadIdx.x; i < cq * CK; i += 256) sTh[i] = theta[(size_t)h * cq * CK + i] * scale;
+  pdl_trigger();
   __syncthreads();
+  pdl_wait();      // nothing before this line touches global memory that a kernel of this library writes or reads back
   const int j0 = (blockIdx.x * RUNS + threadIdx.x / CPR) * RR, c = threadIdx.x % CPR;
   if (j0 >= N) return;
   const bf16* Kb = K + (size_t)bh * N * D + c * 8;
@@ -236,7 +240,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     tc::tmem_relinquish();
   }
   tc::tc_fence_before();
+  pdl_trigger();
   __syncthreads();
+  pdl_wait();      // nothing before this line touches global memory that a kernel of this library writes or reads back
   tc::tc_fence_after();
   const uint32_t tmem = *s_tmem;
 
@@ -541,7 +547,7 @@ cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t 
 #define FMTA_KT_WIN(DD, CKK)                                                                                      \
     { constexpr int RUNS = 256 / (DD / 8);                                                                        \
       dim3 grid((p.N + RUNS * RR - 1) / (RUNS * RR), (unsigned)BH);                                               \
-      ktilde_window_kernel<DD, CKK, RR><<<grid, 256, 0, stream>>>(p.K, p.theta, Kt, p.H, p.N, p.cq, sc); }
+      (void)launch_pdl(ktilde_window_kernel<DD, CKK, RR>, grid, dim3(256), 0, stream, p.K, p.theta, Kt, p.H, p.N, p.cq, sc); }
     if (p.d == 64) {
       if (p.ck == 11) FMTA_KT_WIN(64, 11) else if (p.ck == 7) FMTA_KT_WIN(64, 7) else if (p.ck == 5) FMTA_KT_WIN(64, 5) else FMTA_KT_WIN(64, 3)
     } else {
@@ -588,8 +594,8 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
   tp.qb_hi = (win_hi(p) + RB - 1) / RB;
   dim3 grid(tp.qb_hi - win_lo(p) / RB, p.H, p.B);
   { ScopedKernelTimer timer_(kKernFwdTc, stream);
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tmQ, tmKt, tmV, tp); }
-  return cudaGetLastError();
+    e = launch_pdl(kern, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tmQ, tmKt, tmV, tp); }
+  return e;
 }
 
 }  // namespace

@@ -2,9 +2,17 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "fmta_params.h"
 
 namespace fmta {
+
+// FMTA_NO_PDL=1 in the environment launches every kernel with plain stream order (read once per process).
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("FMTA_NO_PDL"); return !(e && e[0] == '1'); }();
+  return on;
+}
 
 // Launch `kern` with dynamic shared memory and, when cluster_y > 1, a thread-block cluster of
 // (1, cluster_y, 1) CTAs (the heads of one mixing group).  No TMA multicast is involved; the
@@ -31,8 +39,26 @@ inline cudaError_t launch_kernel(void (*kern)(const P), dim3 grid, dim3 block, s
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+  } else if (cluster_y == -1 && pdl_enabled()) {   // no cluster; programmatic stream serialization (the kernel calls pdl_wait())
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
   }
   return cudaLaunchKernelEx(&cfg, kern, params);
+}
+
+// Launch with programmatic stream serialization: the kernel may be scheduled before the previous kernel of the
+// stream has completed (it calls pdl_wait() before touching global memory).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (pdl_enabled()) { cfg.attrs = attr; cfg.numAttrs = 1; }
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 // Compile-time specialisations of the filter shape: (6,11) and (3,5) are unrolled, a NULL filter skips
