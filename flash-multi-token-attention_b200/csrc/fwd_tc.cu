@@ -148,11 +148,12 @@ struct TcParams {
 //            fourteen 16 KB tiles per block for 128 rows -- 62 bytes per cycle, more than eleven ring
 //            slots cover at the latency of a TMA copy (tensor pipe 42 % busy); sharing every tile between
 //            256 rows halves that.
-template <int D>
+template <int D, int NT_ = 2>
 struct TcCfg {
   static constexpr int BM = 128;               // rows per tile (= TMEM lanes)
   static constexpr int BC = (D == 64) ? 128 : 64;   // keys per block
-  static constexpr int NT = 2;                 // row tiles per CTA (TMEM: NT * (BC + BC / 2 + D) <= 512)
+  static constexpr int NT = NT_;               // row tiles per CTA (TMEM: NT * (BC + BC / 2 + D) <= 512); 2, or 1 for
+                                               // grids that would leave SMs without a CTA (one long sequence, few heads)
   static constexpr int HALO = 16;              // rows staged above the block (pad_q <= 15)
   static constexpr int QR = NT * BM + HALO;    // rows of Q in shared memory
   static constexpr int QBOX = QR / 2;          // Q is fetched as two boxes per 16-byte column slab
@@ -175,11 +176,11 @@ struct TcCfg {
 
 constexpr float kRescaleTau = 8.f;   // log2 units: P may reach 2^8 before O is rescaled
 
-template <int D>
-__global__ void __launch_bounds__(TcCfg<D>::kThreads, 1)
+template <int D, int NT_>
+__global__ void __launch_bounds__(TcCfg<D, NT_>::kThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKt,
               const __grid_constant__ CUtensorMap tmV, const TcParams p) {
-  using Cfg = TcCfg<D>;
+  using Cfg = TcCfg<D, NT_>;
   constexpr int BM = Cfg::BM, BC = Cfg::BC, HALO = Cfg::HALO, QR = Cfg::QR, NSLOT = Cfg::NSLOT, NT = Cfg::NT;
   constexpr int SLABS = Cfg::SLABS;
   extern __shared__ unsigned char smem_raw[];
@@ -570,15 +571,11 @@ cudaError_t launch_ktilde(const TrainParams& p, __nv_bfloat16* Kt, cudaStream_t 
 
 namespace {
 
-template <int D>
+template <int D, int NT_>
 cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpart, float* Lpart, int* status,
                         cudaStream_t stream) {
-  using Cfg = TcCfg<D>;
+  using Cfg = TcCfg<D, NT_>;
   const size_t BH = (size_t)p.B * p.H;
-  if (!(p.Kt_ext && p.kt_valid)) {
-    cudaError_t e = launch_ktilde(p, Kt, stream);
-    if (e != cudaSuccess) return e;
-  }
   alignas(64) CUtensorMap tmQ, tmKt, tmV;
   if (!make_tensor_map_bf16(&tmQ, p.Q, D, p.N, BH, 8, Cfg::QBOX, false)) return cudaErrorInvalidValue;
   if (!make_tensor_map_bf16(&tmKt, Kt, D, p.N, BH * p.cq, 64, Cfg::BC, true)) return cudaErrorInvalidValue;
@@ -587,7 +584,7 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
   tp.Opart = Opart; tp.Mpart = Mpart; tp.Lpart = Lpart; tp.status = status;
   tp.H = p.H; tp.N = p.N; tp.cq = p.cq; tp.ck = p.ck; tp.causal = p.causal;
   tp.selftest_expire = take_selftest_expire(kKernFwdTc);
-  auto kern = fwd_tc_kernel<D>;
+  auto kern = fwd_tc_kernel<D, NT_>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
   constexpr int RB = Cfg::NT * Cfg::BM;                           // rows per CTA; a window starts on a multiple of it
@@ -596,6 +593,14 @@ cudaError_t launch_tc_t(const TrainParams& p, bf16* Kt, float* Opart, float* Mpa
   { ScopedKernelTimer timer_(kKernFwdTc, stream);
     e = launch_pdl(kern, grid, dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, tmQ, tmKt, tmV, tp); }
   return e;
+}
+
+int sm_count() {
+  static int n[16] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return 148;
+  if (n[dev] == 0 && cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n[dev] = 148;
+  return n[dev];
 }
 
 }  // namespace
@@ -626,8 +631,16 @@ cudaError_t launch_fwd_tc(const TrainParams& p, void* workspace, const float** O
   int* status = nullptr;
   cudaError_t e = status_word_of(reinterpret_cast<int*>(w), stream, &status);
   if (e != cudaSuccess) return e;
-  if (p.d == 64) e = launch_tc_t<64>(p, Kt, Op, Mp, Lp, status, stream);
-  else e = launch_tc_t<128>(p, Kt, Op, Mp, Lp, status, stream);
+  if (!(p.Kt_ext && p.kt_valid)) {
+    e = launch_ktilde(p, Kt, stream);
+    if (e != cudaSuccess) return e;
+  }
+  // Two row tiles per CTA share every key tile they stage; when that leaves SMs without a CTA (fewer CTAs than SMs:
+  // a window of one long sequence with few heads) one tile per CTA doubles the CTAs instead.
+  const long ctas2 = (long)((win_hi(p) - win_lo(p) + 255) / 256) * p.B * p.H;
+  const bool one_tile = ctas2 < sm_count();
+  if (p.d == 64) e = one_tile ? launch_tc_t<64, 1>(p, Kt, Op, Mp, Lp, status, stream) : launch_tc_t<64, 2>(p, Kt, Op, Mp, Lp, status, stream);
+  else e = one_tile ? launch_tc_t<128, 1>(p, Kt, Op, Mp, Lp, status, stream) : launch_tc_t<128, 2>(p, Kt, Op, Mp, Lp, status, stream);
   *Opart = Op; *Mpart = Mp; *Lpart = Lp;
   return e;
 }
