@@ -150,3 +150,42 @@ def test_two_ranks_share_one_sequence_nccl(tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
     assert all("OK" in o for o in outs)
+
+
+def test_windows_of_one_rank_at_N65536_d128():
+    """The share of rank 0 of 8 (zigzag: the first and the last 4096 positions) of one (batch, head) pair at
+    N = 65536, d = 128: 16 forward CTAs of one row tile each, up to 1020 key blocks long.  The window calls
+    reproduce the whole-sequence forward bit for bit and the whole-sequence backward to rounding on their rows,
+    and the forward meets the oracle bound on row blocks."""
+    import fmta_b200 as F
+    from fmta_b200 import context_parallel as cp
+    B, H, N, d, cq, ck = 1, 1, 65536, 128, 6, 11
+    Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=65536, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
+    th = theta.cuda()
+    pq, pk = cq - 1, (ck - 1) // 2
+    O, M, L, LSE = F.forward(q, k, v, th, scale, pq, pk, True, return_lse=True)
+    Dv = F.rowdot(do, O)
+    ref = F.backward(q, k, v, do, Dv, LSE, th, scale, pq, pk, True)
+    wins = cp.windows_for_rank(N, 8, 0, "zigzag")
+    assert wins == [(0, 4096), (61440, 65536)]
+    kt = cp.stacked_keys(k, th, scale)
+    nan = float("nan")
+    out = (torch.full_like(O, nan),) + tuple(torch.full_like(M, nan) for _ in range(3))
+    g = tuple(torch.full_like(ref[0], nan) for _ in range(3))
+    for lo, hi in wins:
+        F.forward_window(q, k, v, th, scale, pq, pk, True, lo, hi, out=out, ktilde=kt)
+        F.backward_window(q, k, v, do, Dv, LSE, th, scale, pq, pk, True, lo, hi, out=g, ktilde=kt)
+    torch.cuda.synchronize()
+    F.check_device_status()
+    for lo, hi in wins:
+        assert torch.equal(out[0][:, :, lo:hi], O[:, :, lo:hi]) and torch.equal(out[3][:, :, lo:hi], LSE[:, :, lo:hi])
+        for a, b, n in zip(ref[:3], g, ("dQ", "dK", "dV")):
+            e = float((a[:, :, lo:hi] - b[:, :, lo:hi]).abs().max())
+            assert e <= 1e-6 * max(1.0, float(a.abs().max())), (n, lo, e)
+    assert bool(torch.isnan(out[0][:, :, 4096:61440]).all()) and bool(torch.isnan(g[1][:, :, 4096:61440]).all())
+    for i0, i1 in ((4080, 4096), (61440, 61456), (65520, 65536)):
+        Or, Mr, Lr = orc.conv_attn_fwd_rowblock(Q, K, V, theta, i0, i1, scale, True)
+        check_outputs(dict(O=out[0][:, :, i0:i1], M=out[1][:, :, i0:i1], LSE=out[3][:, :, i0:i1]),
+                      dict(O=Or, M=Mr, LSE=Mr + torch.log(Lr)), "window rows %d-%d of N=65536, d=128" % (i0, i1))
