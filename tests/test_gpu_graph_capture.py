@@ -87,3 +87,49 @@ def test_decode_replays_from_a_cuda_graph():
         torch.cuda.synchronize()
         for g_, r_ in zip(outs, ref):
             assert torch.equal(g_, r_)
+
+
+_PLAIN_ORDER_WORKER = r'''
+import math, sys, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[2])
+import fmta_b200 as F
+from oracle import conv_attn_oracle as orc
+out = {}
+for d in (64, 128):
+    B, H, N, cq, ck = 2, 2, 700, 6, 11
+    Q, K, V, dO, theta = orc.make_inputs(B, H, N, d, cq, ck, seed=21 + d, dtype=torch.bfloat16)
+    q, k, v, do = (t.cuda().to(torch.bfloat16).contiguous() for t in (Q, K, V, dO))
+    th = theta.cuda()
+    scale = 1.0 / math.sqrt(d)
+    for rep in range(3):          # back to back: the launches of one step follow those of the step before
+        O, M, L, LSE = F.forward(q, k, v, th, scale, cq - 1, (ck - 1) // 2, True, return_lse=True, path=1)
+        g = F.backward(q, k, v, do, F.rowdot(do, O), LSE, th, scale, cq - 1, (ck - 1) // 2, True, path=1)
+    torch.cuda.synchronize()
+    F.check_device_status()
+    out[d] = [t.cpu() for t in (O, LSE) + tuple(g)]
+torch.save(out, sys.argv[3])
+print("OK")
+'''
+
+
+def test_plain_stream_order_gives_the_same_bits(tmp_path):
+    """FMTA_NO_PDL=1 (every kernel launched in plain stream order) against the default, programmatic dependent
+    launch: the same step in two processes, bit-identical outputs -- the early-started kernels read nothing before
+    their predecessors have completed."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pkg = os.path.join(root, "flash-multi-token-attention_b200")
+    script = tmp_path / "worker.py"
+    script.write_text(_PLAIN_ORDER_WORKER)
+    res = []
+    for flag in ("0", "1"):
+        dst = tmp_path / ("out%s.pt" % flag)
+        r = subprocess.run([sys.executable, str(script), pkg, root, str(dst)], env=dict(os.environ, FMTA_NO_PDL=flag),
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+        assert r.returncode == 0 and "OK" in r.stdout, r.stdout
+        res.append(torch.load(dst))
+    for d in (64, 128):
+        for a, b, n in zip(res[0][d], res[1][d], ("O", "LSE", "dQ", "dK", "dV", "dTheta")):
+            assert torch.equal(a, b), (d, n)
