@@ -167,8 +167,9 @@ int fmta_bwd_dkdv(const void* Q, const void* K, const void* V, const void* dO, c
  * Head dim 64 with a workspace of fmta_workspace_bytes(FMTA_OP_BWD_TC_STREAM, ...) or more: the dQ kernel
  * leaves the probabilities P and dC = P (dP - D) of every entry off the causal band in the workspace (bf16),
  * and the dK/dV kernel streams them through two accumulating GEMMs instead of recomputing scores and
- * exponentials -- faster whenever the 4*B*H*N^2 bytes fit (1 GiB per 16 (batch, head) pairs at N = 4096);
- * same numbers as the recomputing kernel (it rounds P and dC to bf16 too).
+ * exponentials (4*B*H*N^2 bytes: 1 GiB per 16 (batch, head) pairs at N = 4096) -- an option: on B200 the
+ * recomputing pair is as fast or faster at every size measured, so pass the plain FMTA_OP_BWD_TC size unless
+ * measurement says otherwise; same numbers as the recomputing kernel (it rounds P and dC to bf16 too).
  */
 int fmta_bwd(const void* Q, const void* K, const void* V, const void* dO, const float* D,
              const float* LSE, const float* theta, const float* wmix, float* dQ, float* dK, float* dV,

@@ -32,7 +32,7 @@ def test_status_is_zero_after_normal_calls():
     F.check_device_status()       # synchronises; raises on a non-zero word
 
 
-@pytest.mark.parametrize("d,stream_pdc", [(64, None), (64, False), (128, None)])
+@pytest.mark.parametrize("d,stream_pdc", [(64, True), (64, False), (128, None)])
 @pytest.mark.parametrize("kernel", [KERN_FWD, KERN_DQ, KERN_DKDV])
 def test_expired_wait_is_reported_and_the_next_call_is_clean(kernel, d, stream_pdc):
     """Every tensor-core kernel family: head dim 64 (recomputing and streaming dK/dV) and head dim 128."""
