@@ -35,19 +35,19 @@ def windows_for_rank(N: int, world_size: int, rank: int, layout: str = "zigzag")
     2 * W * ALIGN); ``"contiguous"``: one block of N / W positions (N a multiple of W * ALIGN)."""
     if not 0 <= rank < world_size:
         raise ValueError("rank %d outside a world of %d" % (rank, world_size))
+    if layout not in ("zigzag", "contiguous"):
+        raise ValueError("layout must be 'zigzag' or 'contiguous'")
+    if world_size == 1:
+        return [(0, N)]                      # one rank: the whole sequence, any length
     if layout == "zigzag":
         if N % (2 * world_size * ALIGN) != 0:
             raise ValueError("zigzag layout: the sequence length must be a multiple of %d" % (2 * world_size * ALIGN))
         c = N // (2 * world_size)
-        if world_size == 1:
-            return [(0, N)]
         return [(rank * c, (rank + 1) * c), ((2 * world_size - 1 - rank) * c, (2 * world_size - rank) * c)]
-    if layout == "contiguous":
-        if N % (world_size * ALIGN) != 0:
-            raise ValueError("contiguous layout: the sequence length must be a multiple of %d" % (world_size * ALIGN))
-        c = N // world_size
-        return [(rank * c, (rank + 1) * c)]
-    raise ValueError("layout must be 'zigzag' or 'contiguous'")
+    if N % (world_size * ALIGN) != 0:
+        raise ValueError("contiguous layout: the sequence length must be a multiple of %d" % (world_size * ALIGN))
+    c = N // world_size
+    return [(rank * c, (rank + 1) * c)]
 
 
 def take_local(full: torch.Tensor, windows: Sequence[Window]) -> torch.Tensor:
